@@ -1,0 +1,111 @@
+/*
+ * rlt_canonical.h — arithmetic that must give the same bits on the host and on
+ * the GPU.  Included by the CUDA acceptance kernels and by the CPU oracle.
+ *
+ * The acceptance sampler compares u*q[c] against p[c] in fp32
+ * (vllm-rlt: vllm_rlt/worker/speculative.py:56-58) and draws from fp32
+ * distributions (vllm_rlt/worker/sampler.py:57-60); accepted-token sequences
+ * must be identical for identical logits and uniforms.  To make that hold on
+ * any machine and for any parallel decomposition:
+ *   - exp is evaluated by rlt_expf below, built only from IEEE-754 fused
+ *     multiply-adds, multiplies and adds in a fixed order (no library exp,
+ *     no hardware approximation);
+ *   - every sum over the vocabulary is an integer sum of 2^-40 fixed-point
+ *     terms, so it does not depend on summation order;
+ *   - divisions are IEEE round-to-nearest.
+ * Build host code that includes this file with -ffp-contract=off.
+ */
+#ifndef RLT_CANONICAL_H_
+#define RLT_CANONICAL_H_
+
+#include <stdint.h>
+
+#if defined(__CUDA_ARCH__)
+#define RLT_HD __host__ __device__ __forceinline__
+#define RLT_FMA(a, b, c) __fmaf_rn((a), (b), (c))
+#define RLT_MUL(a, b) __fmul_rn((a), (b))
+#define RLT_ADD(a, b) __fadd_rn((a), (b))
+#define RLT_SUB(a, b) __fsub_rn((a), (b))
+#define RLT_DIV(a, b) __fdiv_rn((a), (b))
+#define RLT_F2ULL(x) __float2ull_rz((x))
+#define RLT_ULL2F(x) __ull2float_rn((x))
+#define RLT_DMUL(a, b) __dmul_rn((a), (b))
+#define RLT_D2ULL(x) __double2ull_rz((x))
+#else
+#include <math.h>
+#if defined(__CUDACC__)
+#define RLT_HD __host__ __device__ inline
+#else
+#define RLT_HD static inline
+#endif
+#define RLT_FMA(a, b, c) fmaf((a), (b), (c))
+#define RLT_MUL(a, b) ((float)(a) * (float)(b))
+#define RLT_ADD(a, b) ((float)(a) + (float)(b))
+#define RLT_SUB(a, b) ((float)(a) - (float)(b))
+#define RLT_DIV(a, b) ((float)(a) / (float)(b))
+#define RLT_F2ULL(x) ((unsigned long long)(x))
+#define RLT_ULL2F(x) ((float)(long long)(x))
+#define RLT_DMUL(a, b) ((double)(a) * (double)(b))
+#define RLT_D2ULL(x) ((unsigned long long)(x))
+#endif
+
+/* 2^40: one unit of probability mass in fixed point. */
+#define RLT_FIX_ONE 1099511627776.0f
+#define RLT_FIX_INV 9.094947017729282e-13f /* 2^-40, exact */
+
+RLT_HD float rlt_bits_to_float(uint32_t b) {
+  union { uint32_t u; float f; } c;
+  c.u = b;
+  return c.f;
+}
+RLT_HD uint32_t rlt_float_to_bits(float f) {
+  union { uint32_t u; float f; } c;
+  c.f = f;
+  return c.u;
+}
+
+/*
+ * exp(d) for the softmax numerator.  d <= 0 in every use (d = t - max t); the
+ * function is defined for any float:
+ *   NaN -> NaN;  d < -86 -> 0;  d > 88 -> +inf;
+ *   otherwise k = round(d*log2 e), r = d - k*ln2 (two-constant Cody-Waite),
+ *   exp(r) = 1 + r + r^2 * P(r) with the degree-5 polynomial of Cephes expf,
+ *   result = exp(r) * 2^k by exponent-field addition.  Max error about 1 ulp.
+ */
+RLT_HD float rlt_expf(float d) {
+  if (d != d) return d;
+  if (d < -86.0f) return 0.0f;
+  if (d > 88.0f) return rlt_bits_to_float(0x7f800000u);
+  const float magic = 12582912.0f; /* 1.5 * 2^23: adding and subtracting rounds to nearest integer */
+  float k = RLT_SUB(RLT_FMA(d, 1.44269504088896341f, magic), magic);
+  float r = RLT_FMA(k, -0.693359375f, d);
+  r = RLT_FMA(k, 2.12194440e-4f, r);
+  float p = 1.9875691500e-4f;
+  p = RLT_FMA(p, r, 1.3981999507e-3f);
+  p = RLT_FMA(p, r, 8.3334519073e-3f);
+  p = RLT_FMA(p, r, 4.1665795894e-2f);
+  p = RLT_FMA(p, r, 1.6666665459e-1f);
+  p = RLT_FMA(p, r, 5.0000001201e-1f);
+  float r2 = RLT_MUL(r, r);
+  float y = RLT_ADD(RLT_FMA(p, r2, r), 1.0f);
+  int32_t ki = (int32_t)k;
+  return rlt_bits_to_float(rlt_float_to_bits(y) + ((uint32_t)ki << 23));
+}
+
+/* Fixed-point weight of a probability-like value in [0, 1]; NaN and negatives give 0. */
+RLT_HD unsigned long long rlt_fix_weight(float mass) {
+  if (!(mass > 0.0f)) return 0ull;
+  return RLT_F2ULL(RLT_MUL(mass, RLT_FIX_ONE));
+}
+
+/* Normaliser as a float from the fixed-point sum of exp terms (sum < 2^57). */
+RLT_HD float rlt_fix_to_float(unsigned long long zfix) {
+  return RLT_MUL(RLT_ULL2F(zfix), RLT_FIX_INV);
+}
+
+/* Draw threshold: floor(u * total), u in [0, 1), total < 2^53. */
+RLT_HD unsigned long long rlt_draw_threshold(float u, unsigned long long total) {
+  return RLT_D2ULL(RLT_DMUL((double)u, (double)total));
+}
+
+#endif /* RLT_CANONICAL_H_ */

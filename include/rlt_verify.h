@@ -1,0 +1,238 @@
+/*
+ * rlt_verify.h — C ABI of the B200 (sm_100a) self-speculative verify step for
+ * looped (Ouro-style) language models.
+ *
+ * Every entry point takes plain pointers and sizes, launches on the CUDA stream
+ * it is given (no host synchronisation, no host read of device data, static
+ * launch geometry, so calls can be captured in a CUDA graph), borrows its
+ * pointer arguments for the lifetime of the work on that stream, and returns
+ * an int status: RLT_OK or a negative RLT_ERR_* code.  No exception crosses
+ * this boundary.  The library keeps no mutable global state besides a
+ * per-device cache of immutable properties (SM count, driver entry points).
+ *
+ * Each declaration cites the reference interface (vllm-rlt v0.2.0, paths
+ * relative to that project) it stands in for.
+ *
+ * Element type codes (`dtype` arguments): see rlt_dtype.
+ */
+#ifndef RLT_VERIFY_H_
+#define RLT_VERIFY_H_
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque CUDA stream handle (cudaStream_t / CUstream); NULL = legacy default stream. */
+typedef void* rlt_stream_t;
+
+typedef enum rlt_dtype {
+  RLT_F32 = 0,
+  RLT_F16 = 1,
+  RLT_BF16 = 2
+} rlt_dtype;
+
+enum {
+  RLT_OK = 0,
+  RLT_ERR_INVALID = -1,     /* bad argument (shape, alignment, null pointer, range) */
+  RLT_ERR_UNSUPPORTED = -2, /* valid request that this build has no kernel for        */
+  RLT_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed (see rlt_last_error) */
+  RLT_ERR_WORKSPACE = -4    /* workspace missing or too small                          */
+};
+
+/* Per-request status words written by the acceptance kernels. */
+enum {
+  RLT_ROW_OK = 0,
+  RLT_ROW_ZERO_PROPOSAL = 1,    /* q[candidate] == 0: ValueError in worker/speculative.py:53-55      */
+  RLT_ROW_INVALID_RESIDUAL = 2, /* residual mass zero / non-finite: RuntimeError, speculative.py:61-62 */
+  RLT_ROW_BAD_LOGITS = 3,       /* NaN / +inf in a logits row that had to be normalised               */
+  RLT_ROW_SHARED_PAGE = 4,      /* rollback would truncate a page with refcount > 1,
+                                   core/kv_cache_manager.py:349-351                                    */
+  RLT_ROW_BAD_POSITION = 5      /* position outside the request's block table                         */
+};
+
+/* Library / build identification: "rlt_verify <version> sm_100a". */
+const char* rlt_version(void);
+/* Text of the most recent CUDA error seen by this thread in this library ("" if none). */
+const char* rlt_last_error(void);
+
+/* ------------------------------------------------------------------------
+ * SiLU-and-Mul.  out[i] = T(silu_f32(f32(gate[i]))) * up[i], the activation
+ * rounded to T before the multiply, the multiply rounded once to T.
+ * Replaces: torch.ops.vllm_rlt.silu_and_mul -> vllm_rlt::silu_and_mul_cuda
+ *   (csrc/torch_bindings.cpp:7-13, csrc/activation/silu_and_mul.cu:220-247;
+ *    arithmetic contract csrc/activation/silu_and_mul.cu:20-22,74-79;
+ *    Python reference vllm_rlt/kernels/activation.py:20-28).
+ * gate/up/out: `n` contiguous elements of `dtype`, any element alignment;
+ * out must not alias the inputs.  n == 0 launches nothing.
+ * ---------------------------------------------------------------------- */
+int rlt_silu_and_mul(const void* gate, const void* up, void* out, int64_t n,
+                     int dtype, rlt_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * KV write.  For each active row r: cache[write_blocks[r], write_offsets[r], :, :] = k[r]
+ * (and v).  A row is active iff r < *active_rows (when active_rows != NULL) and
+ * write_mask[r] != 0 (when write_mask != NULL); inactive rows load no address
+ * and write nothing.
+ * Replaces: KVCacheManager._write_prepared (vllm_rlt/core/kv_cache_manager.py:675-701),
+ *   masked_kv_store (vllm_rlt/kernels/routing.py:180-225),
+ *   write_graph_kv (vllm_rlt/kernels/graph_kv.py:6-65).
+ * key_cache/value_cache: one layer's view [num_blocks, block_size, kv_heads, head_dim];
+ *   block_stride and token_stride are in ELEMENTS; the [kv_heads, head_dim] tail is contiguous.
+ * k, v: [rows, kv_heads, head_dim] contiguous.  write_blocks/write_offsets: int64 [rows].
+ * write_mask: uint8/bool [rows] or NULL.  active_rows: device int32 scalar or NULL.
+ * ---------------------------------------------------------------------- */
+int rlt_kv_write(void* key_cache, void* value_cache, int64_t block_stride, int64_t token_stride,
+                 int64_t num_blocks, int block_size, int kv_heads, int head_dim, int dtype,
+                 const void* k, const void* v, const int64_t* write_blocks,
+                 const int64_t* write_offsets, const uint8_t* write_mask,
+                 const int32_t* active_rows, int rows, rlt_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Depth-aware paged-KV verify attention.
+ *   out[r,h,:] = sum_t softmax_t(q[r,h,:].K[t,h/g,:] / sqrt(D)) V[t,h/g,:],  t in [0, len_r)
+ *   K[t] = key_cache[table_r[t / block_size], t % block_size]
+ * Rows whose block-table rows are identical (the k+1 rows of one request at
+ * one depth plane, or k x depths rows in a shared-plane layout) are detected
+ * on the device and scored together, so each K/V page is read from HBM once
+ * per group instead of once per row.  A row's result is a function of its
+ * own query, length and K/V only (bit-identical alone, in any batch and in
+ * any group).  len_r == 0 gives a zero row and never dereferences its table.
+ * Table entries at or beyond ceil(len_r / block_size) are never read as page ids
+ * for that row.
+ * Replaces: TritonPagedAttention.__call__ / paged_attention
+ *   (vllm_rlt/kernels/paged_attention.py:119-120, vllm_rlt/kernels/triton_attention.py:150-202,
+ *    kernels :20-147); oracle torch_paged_attention (vllm_rlt/kernels/paged_attention.py:12-36);
+ *   dispatch KVCacheManager._attend_prepared (vllm_rlt/core/kv_cache_manager.py:728-770).
+ *
+ * q, out: [rows, q_heads, head_dim] contiguous.  key_cache/value_cache as in rlt_kv_write.
+ * block_tables: int32 [table_rows, table_width] contiguous.
+ * context_lengths: int32 [rows] (unpacked) or [table_rows] (packed).
+ * cu_seqlens_q: NULL for one table row per query row (table_rows == rows).
+ *   Otherwise int32 [table_rows + 1]: query rows cu[s]..cu[s+1]-1 belong to table
+ *   row s, are consecutive positions ending at context_lengths[s]-1, and row i of
+ *   the n_s rows sees context_lengths[s] - n_s + i + 1 keys (bottom-right causal) —
+ *   the packed form of AttentionBackend.prefill (vllm_rlt/attention/backend.py:41-42,
+ *   vllm_rlt/kernels/triton_attention.py:314-366).
+ * workspace: device scratch of at least rlt_verify_attention_workspace_bytes(...)
+ *   bytes, 256-byte aligned, owned by the caller, private to this call until its
+ *   work on `stream` completes.  Contents on entry are irrelevant.
+ * ---------------------------------------------------------------------- */
+size_t rlt_verify_attention_workspace_bytes(int rows, int q_heads, int kv_heads, int head_dim,
+                                            int block_size, int table_width);
+
+int rlt_verify_attention(const void* q, void* out, const void* key_cache, const void* value_cache,
+                         int64_t block_stride, int64_t token_stride, int64_t num_blocks,
+                         int block_size, int q_heads, int kv_heads, int head_dim, int dtype,
+                         const int32_t* block_tables, int table_rows, int table_width,
+                         const int32_t* context_lengths, const int32_t* cu_seqlens_q, int rows,
+                         void* workspace, size_t workspace_bytes, rlt_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Row argmax: targets[r] = argmax_v logits[r, v], lowest index on ties, a NaN
+ * counts as the maximum (first NaN wins), as torch.argmax does.
+ * Replaces: logits.argmax(-1) in SpeculativeRunner._collect_round
+ *   (vllm_rlt/worker/speculative.py:469) and AsyncSpeculativeRunner._verify
+ *   (vllm_rlt/worker/async_speculative.py:415).
+ * logits: [rows, vocab] of `dtype`, row stride in elements.
+ * ---------------------------------------------------------------------- */
+int rlt_argmax_rows(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
+                    int64_t* targets, rlt_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Greedy acceptance + device state update for n requests whose verification
+ * rows are request-major: request i owns rows cu_rows[i] .. cu_rows[i+1]-1
+ * (c_i = that count >= 1; column 0 of `tokens` is the committed input token,
+ * columns 1..c_i-1 the drafts).
+ *   targets[row]       = argmax(logits[row])                       (as rlt_argmax_rows)
+ *   accepted[i]        = #leading j < c_i-1 with tokens[i, j+1] == targets[cu_rows[i]+j]
+ *   next_token[i]      = targets[cu_rows[i] + accepted[i]]
+ *   next_position[i]   = starts[i] + accepted[i] + 1
+ *   result             = [targets (rows) | accepted (n) | next_position (n)]   int64
+ *   slot_values[slots[i]] = (next_token[i], next_position[i])      (when slots != NULL)
+ * Replaces: greedy_accept (vllm_rlt/worker/speculative.py:32-44) and
+ *   AsyncSpeculativeRunner._accept_and_update_state
+ *   (vllm_rlt/worker/async_speculative.py:417-447; wire layout :62-77).
+ * tokens: int64 [n, tokens_width].  slot_values: int64 [*, 2].
+ * ---------------------------------------------------------------------- */
+int rlt_accept_greedy(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
+                      const int32_t* cu_rows, int n, const int64_t* tokens, int tokens_width,
+                      const int64_t* starts, const int64_t* slots, int64_t* slot_values,
+                      int64_t* result, rlt_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Token draw from softmax(logits / temperature) with a supplied uniform:
+ *   tokens[r] = first index whose inclusive fixed-point prefix mass exceeds
+ *   floor(u[r] * total)   (see rlt_accept_rejection for the arithmetic).
+ * temperature[r] == 0 gives argmax.  Used for draft proposals and bonus draws.
+ * Replaces: Sampler.sample / Sampler.draw (vllm_rlt/worker/sampler.py:57-81) with the
+ *   generator replaced by an explicit uniform.
+ * ---------------------------------------------------------------------- */
+int rlt_sample_rows(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
+                    const float* temperature, const float* uniforms, int64_t* tokens,
+                    int32_t* status, rlt_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Rejection-sampling acceptance (sequential per request, parallel over requests).
+ * For request i with rows cu_rows[i]..cu_rows[i+1]-1 (c_i rows, c_i-1 drafts) and
+ * temperature T_i > 0:
+ *   p_j = softmax(target_logits[row_j] / T_i),  q_j = softmax(draft_logits[row_j] / T_i)
+ *   for j = 0 .. c_i-2, d = tokens[i, j+1]:
+ *       accept iff  u_accept[row_j] * q_j[d] < p_j[d]          (fp32, strict)
+ *       on the first rejection emit a draw from max(p_j - q_j, 0) / sum with u_final[i]; stop
+ *   if every draft was accepted emit a draw from p_{c_i-1} with u_final[i].
+ * T_i == 0 selects greedy acceptance for that request (as rlt_accept_greedy).
+ * Outputs as rlt_accept_greedy, except result[row] holds the EMITTED tokens of each
+ * request at cu_rows[i] .. cu_rows[i]+accepted[i] (later rows of the request: -1),
+ * and status[i] is an RLT_ROW_* code (on error accepted/next_* describe the prefix
+ * emitted before the failing draft).
+ *
+ * Arithmetic (identical in the CPU oracle, so results are bit-exact):
+ *   t = x / T (IEEE);  m = max t;  e = rlt_expf(t - m);  Zfix = sum (u64)(e * 2^40);
+ *   Z = (float)Zfix * 2^-40;  p[v] = e / Z (IEEE).  Draw weights w[v] = (u64)(mass[v] * 2^40),
+ *   threshold = (u64)((double)u * (double)sum w), token = first v with prefix(v) > threshold.
+ *   Integer sums make every result independent of summation order.
+ * Replaces: rejection_sample (vllm_rlt/worker/speculative.py:47-63), the loop in
+ *   SpeculativeRunner._collect_round (:483-510), Sampler.probabilities for top_k = -1,
+ *   top_p = 1 (vllm_rlt/worker/sampler.py:27-55).
+ * target_logits, draft_logits: [rows, vocab]; draft row j of a request holds the logits
+ *   draft j+1 was sampled from (its last row is unused).
+ * ---------------------------------------------------------------------- */
+int rlt_accept_rejection(const void* target_logits, const void* draft_logits, int64_t row_stride,
+                         int rows, int vocab, int dtype, const int32_t* cu_rows, int n,
+                         const int64_t* tokens, int tokens_width, const int64_t* starts,
+                         const float* temperature, const float* u_accept, const float* u_final,
+                         const int64_t* slots, int64_t* slot_values, int64_t* result,
+                         int32_t* status, rlt_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Device rollback of rejected positions.  For request i with round start
+ * starts[i] and emitted[i] committed tokens (accepted + 1):
+ *   frontier[i]             = starts[i] + emitted[i]
+ *   written_prefix[i,p,l]   = min(written_prefix[i,p,l], frontier[i])      (all planes, layers)
+ *   context_lengths[i]      = frontier[i] + 1
+ *   write_offsets[i]        = frontier[i] % block_size
+ *   write_blocks[i,p]       = tables[i, p, frontier[i] / block_size]
+ * Block tables and physical pages are not modified (the reservation is kept).
+ * If refcounts != NULL and any page of request i at or after frontier[i] / block_size
+ * (within pages_used[i]) has refcounts[page] > 1 the request is left untouched and
+ * status[i] = RLT_ROW_SHARED_PAGE.
+ * Replaces: KVCacheManager.truncate_suffix (vllm_rlt/core/kv_cache_manager.py:338-356)
+ *   called from Scheduler.update_from_output (vllm_rlt/core/scheduler.py:1386-1394), and the
+ *   device slot mapping of AsyncSpeculativeRunner._execute_recurrent_step
+ *   (vllm_rlt/worker/async_speculative.py:267-281).
+ * tables: int32 [n, planes, table_width].  written_prefix: int64 [n, planes, layers] or NULL.
+ * pages_used: int32 [n] (table entries that are real pages) or NULL (= all table_width).
+ * ---------------------------------------------------------------------- */
+int rlt_rollback(const int64_t* starts, const int64_t* emitted, int n, const int32_t* tables,
+                 int planes, int table_width, int block_size, const int32_t* pages_used,
+                 const int32_t* refcounts, int64_t num_blocks, int64_t* written_prefix, int layers,
+                 int64_t* frontier, int32_t* context_lengths, int64_t* write_blocks,
+                 int64_t* write_offsets, int32_t* status, rlt_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RLT_VERIFY_H_ */

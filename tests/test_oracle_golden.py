@@ -1,0 +1,248 @@
+"""Pins the CPU oracle (oracle/rlt_oracle.c) against vectors produced by the vllm-rlt
+reference itself (tests/golden/make_golden.py) and against the known-answer values of the
+reference's own tests.  Runs without a GPU."""
+
+import pytest
+import torch
+
+from oracle import oracle
+
+
+def _bits(t):
+    return t.view(torch.int32 if t.dtype == torch.float32 else torch.int16)
+
+
+def test_silu_known_values_and_reference_outputs(golden):
+    cases = golden("silu.pt")
+    known = cases[0]
+    torch.testing.assert_close(oracle.silu_and_mul(known["gate"], known["up"]), known["known"])
+    for case in cases:
+        got = oracle.silu_and_mul(case["gate"], case["up"])
+        want = case["out"]
+        assert got.shape == want.shape and got.dtype == want.dtype
+        if want.dtype == torch.float32:
+            # libm expf vs torch's vectorised exp differ by an ulp or two in fp32.
+            torch.testing.assert_close(got, want, rtol=1e-6, atol=1e-30, equal_nan=True)
+        else:
+            # 16-bit outputs: identical except where that last fp32 ulp crosses a rounding
+            # boundary of the activation (then one unit in the last place of the product).
+            nan = torch.isnan(want)
+            assert torch.equal(torch.isnan(got), nan)
+            diff = (_bits(got)[~nan].int() - _bits(want)[~nan].int()).abs()
+            assert int(diff.max()) <= 1
+            assert float((diff != 0).float().mean()) < 2e-3
+
+
+def test_silu_staged_fp64_contract():
+    # The contract the reference states in tests/test_activation.py:56-75: round the
+    # activation to the storage type, then round the product once.
+    g = torch.Generator().manual_seed(42)
+    for dtype in (torch.float32, torch.float16, torch.bfloat16):
+        gate = torch.randn(2, 3, 9, generator=g).to(dtype)
+        up = torch.randn(2, 3, 9, generator=g).to(dtype)
+        activated = (gate.double() * torch.sigmoid(gate.double())).to(dtype)
+        expected = (activated.double() * up.double()).to(dtype)
+        torch.testing.assert_close(oracle.silu_and_mul(gate, up), expected)
+
+
+def test_attention_matches_reference_outputs(golden):
+    for case in golden("attention.pt"):
+        if case["kind"] == "direct":
+            k, v = case["k"], case["v"]
+        else:
+            k, v = case["key_cache"][:, case["layer"]], case["value_cache"][:, case["layer"]]
+        got = oracle.paged_attention(case["q"], k, v, case["tables"], case["lengths"])
+        tol = {torch.float32: 1e-5, torch.float16: 2e-3, torch.bfloat16: 2e-2}[case["q"].dtype]
+        torch.testing.assert_close(got, case["out"], rtol=tol, atol=tol)
+        zero_rows = (case["lengths"] == 0).nonzero().flatten().tolist()
+        for row in zero_rows:
+            assert torch.count_nonzero(got[row]) == 0
+
+
+def test_attention_packed_rows_equal_per_row_expansion():
+    g = torch.Generator().manual_seed(3)
+    block, heads, dim = 4, 2, 16
+    k = torch.randn(12, block, heads, dim, generator=g)
+    v = torch.randn(12, block, heads, dim, generator=g)
+    tables = torch.tensor([[3, 7, 1, 0], [5, 2, 9, 11]], dtype=torch.int32)
+    lengths = torch.tensor([9, 14], dtype=torch.int32)
+    cu = torch.tensor([0, 3, 8], dtype=torch.int32)
+    q = torch.randn(8, heads, dim, generator=g)
+    packed = oracle.paged_attention(q, k, v, tables, lengths, cu)
+    row_tables = torch.stack([tables[0]] * 3 + [tables[1]] * 5)
+    row_lengths = torch.tensor([7, 8, 9, 10, 11, 12, 13, 14], dtype=torch.int32)
+    rows = oracle.paged_attention(q, k, v, row_tables, row_lengths)
+    assert torch.equal(packed, rows)
+
+
+def test_greedy_accept_table_and_argmax(golden):
+    data = golden("greedy.pt")
+    for row in data["table"]:
+        candidates, targets = row["candidates"], row["targets"]
+        vocab = 300
+        logits = torch.full((len(targets), vocab), -100.0)
+        for j, t in enumerate(targets):
+            logits[j, t] = 100.0
+        tokens = torch.tensor([[5] + candidates], dtype=torch.int64)
+        cu = torch.tensor([0, len(targets)], dtype=torch.int32)
+        starts = torch.tensor([40], dtype=torch.int64)
+        result = oracle.accept_greedy(logits, cu, tokens, starts)
+        rows = len(targets)
+        accepted = int(result[rows])
+        assert accepted == row["accepted"]
+        assert result[:rows].tolist() == targets
+        assert result[: accepted + 1].tolist() == row["tokens"]
+        assert int(result[rows + 1]) == 40 + accepted + 1
+    arg = data["argmax"]
+    assert torch.equal(oracle.argmax_rows(arg["logits"]), arg["targets"])
+    assert torch.equal(oracle.argmax_rows(arg["bf16_logits"]), arg["bf16_targets"])
+    assert int(oracle.argmax_rows(arg["logits"])[3]) == 100  # tie -> lowest index
+
+
+def test_argmax_nan_counts_as_maximum():
+    logits = torch.tensor([[1.0, float("nan"), 5.0, float("nan")], [float("-inf")] * 4])
+    assert oracle.argmax_rows(logits).tolist() == logits.argmax(-1).tolist() == [1, 0]
+
+
+def test_async_accept_program(golden):
+    data = golden("async_accept.pt")
+    counts = data["counts"]
+    n, rows = counts.numel(), int(counts.sum())
+    cu = torch.zeros(n + 1, dtype=torch.int32)
+    cu[1:] = counts.cumsum(0)
+    vocab = 64
+    logits = torch.full((rows, vocab), -50.0)
+    logits[torch.arange(rows), data["target"]] = 50.0
+    slot_values = torch.full_like(data["slot_values"], -7)
+    result = oracle.accept_greedy(logits, cu, data["tokens"], data["starts"], data["slots"],
+                                  slot_values)
+    assert torch.equal(result, data["result"])
+    assert torch.equal(slot_values, data["slot_values"])
+
+
+def test_probabilities_match_reference_sampler(golden):
+    data = golden("sampler.pt")
+    for case in data["probabilities"]:
+        probs, status = oracle.probabilities(case["logits"], case["temperature"])
+        assert status == 0
+        torch.testing.assert_close(probs, case["probs"], rtol=2e-6, atol=1e-12)
+        assert abs(float(probs.double().sum()) - 1.0) < 1e-5
+
+
+def test_rejection_decisions_match_reference(golden):
+    data = golden("sampler.pt")
+    accepted_count = 0
+    for case in data["rejection"]:
+        vocab = case["target_logits"].numel()
+        target = torch.stack([case["target_logits"], torch.zeros(vocab)])
+        draft = torch.stack([case["draft_logits"], torch.zeros(vocab)])
+        tokens = torch.tensor([[0, case["candidate"]]], dtype=torch.int64)
+        cu = torch.tensor([0, 2], dtype=torch.int32)
+        starts = torch.tensor([10], dtype=torch.int64)
+        temperature = torch.tensor([case["temperature"]])
+        u_accept = torch.tensor([case["uniform"], 0.0])
+        # The decision must agree with the reference unless u*q is within rounding of p.
+        margin = abs(case["uniform"] * case["q_c"] - case["p_c"]) / max(case["p_c"], 1e-30)
+        for u_final in (0.0, 0.37, 0.999):
+            result, status = oracle.accept_rejection(target, draft, cu, tokens, starts, temperature,
+                                                     u_accept, torch.tensor([u_final]))
+            assert int(status[0]) == 0
+            accepted = int(result[2])
+            if margin > 1e-4:
+                assert accepted == int(case["accepted"])
+            if accepted:
+                assert int(result[0]) == case["candidate"]
+            else:
+                # A residual draw can only return a token with residual mass.
+                assert float(case["residual"][int(result[0])]) > 0
+            assert int(result[3]) == 10 + accepted + 1
+        accepted_count += int(case["accepted"])
+    assert 0 < accepted_count < len(data["rejection"])
+
+
+def test_residual_draw_follows_the_reference_residual_distribution(golden):
+    # Inverse CDF over a fine grid of uniforms reproduces max(p - q, 0) / sum.
+    case = next(c for c in golden("sampler.pt")["rejection"] if not c["accepted"])
+    vocab = case["target_logits"].numel()
+    target = torch.stack([case["target_logits"], torch.zeros(vocab)])
+    draft = torch.stack([case["draft_logits"], torch.zeros(vocab)])
+    tokens = torch.tensor([[0, case["candidate"]]], dtype=torch.int64)
+    cu = torch.tensor([0, 2], dtype=torch.int32)
+    counts = torch.zeros(vocab)
+    draws = 4000
+    for i in range(draws):
+        result, _ = oracle.accept_rejection(target, draft, cu, tokens, torch.tensor([0]),
+                                            torch.tensor([case["temperature"]]),
+                                            torch.tensor([case["uniform"], 0.0]),
+                                            torch.tensor([(i + 0.5) / draws]))
+        counts[int(result[0])] += 1
+    torch.testing.assert_close(counts / draws, case["residual"], atol=2.0 / draws, rtol=0)
+
+
+@pytest.mark.parametrize("index", [0, 1, 2])
+def test_rejection_sampling_recovers_target_distribution(golden, index):
+    # The statistical contract of tests/test_speculative.py:396-420 of the reference, with the
+    # generator replaced by seeded uniforms fed through the oracle's explicit-uniform interface.
+    case = golden("sampler.pt")["distribution"][index]
+    p, q = case["p"], case["q"]
+    logits_p = torch.where(p > 0, p.log(), torch.tensor(-80.0))
+    logits_q = torch.where(q > 0, q.log(), torch.tensor(-80.0))
+    g = torch.Generator().manual_seed(431)
+    n = 12000
+    uniforms = torch.rand(n, 3, generator=g)
+    temperature = torch.ones(n)
+    candidates, status = oracle.sample_rows(logits_q.expand(n, 3).contiguous(), temperature,
+                                            uniforms[:, 0].contiguous())
+    assert int(status.abs().sum()) == 0
+    target = torch.stack([logits_p, logits_p]).repeat(n, 1)
+    draft = torch.stack([logits_q, logits_q]).repeat(n, 1)
+    tokens = torch.stack([torch.zeros(n, dtype=torch.int64), candidates], 1)
+    cu = (torch.arange(n + 1) * 2).int()
+    u_accept = torch.stack([uniforms[:, 1], torch.zeros(n)], 1).flatten().contiguous()
+    result, status = oracle.accept_rejection(target, draft, cu, tokens,
+                                             torch.zeros(n, dtype=torch.int64), temperature,
+                                             u_accept, uniforms[:, 2].contiguous())
+    assert int(status.abs().sum()) == 0
+    first = result[: 2 * n].view(n, 2)[:, 0]
+    counts = torch.bincount(first, minlength=3).float()
+    torch.testing.assert_close(counts / counts.sum(), p, atol=0.016, rtol=0)
+
+
+def test_zero_proposal_and_bad_logits_are_reported():
+    vocab = 8
+    target = torch.zeros(2, vocab)
+    draft = torch.zeros(2, vocab)
+    draft[0, 3] = -2000.0  # q[3] underflows to exactly zero
+    tokens = torch.tensor([[0, 3]], dtype=torch.int64)
+    cu = torch.tensor([0, 2], dtype=torch.int32)
+    args = (cu, tokens, torch.tensor([5]), torch.tensor([1.0]), torch.tensor([0.5, 0.0]),
+            torch.tensor([0.5]))
+    _, status = oracle.accept_rejection(target, draft, *args)
+    assert int(status[0]) == 1
+    target[0, 0] = float("nan")
+    draft[0, 3] = 0.0
+    _, status = oracle.accept_rejection(target, draft, *args)
+    assert int(status[0]) == 3
+
+
+def test_rollback_frontiers_and_slot_mapping(golden):
+    for case in golden("rollback.pt"):
+        if case.get("shared"):
+            tables = case["tables"][None]
+            for frontier, want in ((case["refused_frontier"], 4), (case["allowed_frontier"], 0)):
+                out = oracle.rollback(torch.tensor([0]), torch.tensor([frontier]), tables,
+                                      case["block"], refcounts=case["refcounts"])
+                assert int(out[4][0]) == want
+            assert case["refused"]
+            continue
+        tables = case["tables"][None].contiguous()
+        prefix = case["before"][None].clone().long()
+        frontier, lengths, blocks, offsets, status = oracle.rollback(
+            torch.tensor([case["start"]]), torch.tensor([case["emitted"]]), tables, case["block"],
+            written_prefix=prefix)
+        assert int(status[0]) == 0
+        assert int(frontier[0]) == case["frontier"]
+        assert torch.equal(prefix[0], case["after"].long())
+        assert int(lengths[0]) == case["context_length"]
+        assert int(offsets[0]) == case["write_offset"]
+        assert torch.equal(blocks[0], case["write_blocks"])
