@@ -1,0 +1,433 @@
+"""Benchmark of the self-speculative verify step on B200 (and its CPU baseline).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One *step* is one pass of the verify hot path over one batch of synthetic input at the
+kernel-microbench shape of BASELINE.json (configs[1]) extended over the 24 layers of the
+Ouro-1.4B shape:
+
+    for each of 24 layers:  KV write of the new tokens -> grouped paged verify attention
+                            (64 requests, 16 heads x 128, 16-token pages, contexts U[512, 4096],
+                             16 rows per request = 4 tokens x 4 loop depths, shared depth plane)
+                         -> SiLU-and-Mul on [1024, 5632]
+    then                    greedy acceptance and rejection-sampling acceptance (T = 0.8) on
+                            64 x 4 rows of 49152 fp32 logits, and the device rollback.
+
+The model GEMMs / norms / RoPE between these calls are not part of the path and are not run.
+`value` is accepted tokens per second (device-resident inputs); committed tokens (accepted + 1
+per request) are reported beside it.  `e2e` is the same step driven from pinned host buffers
+through the public Python API (H2D of every input and D2H of the result inside the timed
+region).  One process per GPU; every rank runs an independent replica on its own requests
+(no collective on the path), the timed region is bracketed by a barrier, and the step time is
+the maximum over ranks.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+LAYERS, HEADS, HEAD_DIM, BLOCK, FFN, VOCAB = 24, 16, 128, 16, 5632, 49152
+REQUESTS, TOKENS, DEPTHS = 64, 4, 4
+TEMPERATURE = 0.8
+METRIC = "accepted tokens/s/GPU, Ouro-1.4B self-spec decode; verify-attn % HBM peak"
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class Workload:
+    """Seeded synthetic inputs of one replica (one GPU or the CPU sample)."""
+
+    def __init__(self, seed: int, requests: int = REQUESTS, layers: int = LAYERS, device="cpu"):
+        g = torch.Generator().manual_seed(seed)
+        self.requests, self.layers = requests, layers
+        self.contexts = torch.randint(512, 4097, (requests,), generator=g)
+        pages = (self.contexts + BLOCK - 1) // BLOCK
+        self.total_pages = int(pages.sum())
+        order = torch.randperm(self.total_pages, generator=g).int()
+        width = int(pages.max())
+        tables = torch.zeros(requests, width, dtype=torch.int32)
+        offset = 0
+        for i, n in enumerate(pages.tolist()):
+            tables[i, :n] = order[offset:offset + n]
+            offset += n
+        self.request_tables = tables
+        rows_per_request = TOKENS * DEPTHS
+        # row (depth, t) of a request sees ctx - 3 + t keys; all 16 rows share one table row
+        visible = torch.stack([self.contexts - (TOKENS - 1) + t for t in range(TOKENS)], 1)  # [req, tok]
+        self.lengths = visible.repeat(1, DEPTHS).reshape(-1).int()
+        self.tables = tables.repeat_interleave(rows_per_request, 0).contiguous()
+        self.rows = requests * rows_per_request
+        positions = (visible - 1).reshape(-1)  # new tokens: one K/V row per (request, token)
+        req_of = torch.arange(requests).repeat_interleave(TOKENS)
+        self.write_blocks = tables[req_of, (positions // BLOCK)].long()
+        self.write_offsets = (positions % BLOCK).long()
+        self.kv_rows = requests * TOKENS
+        self.seed = seed
+        self.device = torch.device(device)
+        self.generator = g
+        # acceptance inputs: 4 rows per request (3 drafts + bonus row)
+        self.accept_rows = requests * TOKENS
+        self.cu_rows = (torch.arange(requests + 1) * TOKENS).int()
+        self.starts = (self.contexts - TOKENS).long()
+        self.slots = torch.randperm(2 * requests, generator=g)[:requests]
+        self.temperature = torch.full((requests,), TEMPERATURE)
+
+    def algorithmic_attention_bytes(self) -> int:
+        """Each group's K/V once + Q + O + block tables, per layer call."""
+        kv = int(self.contexts.sum()) * HEADS * HEAD_DIM * 2 * 2
+        qo = self.rows * HEADS * HEAD_DIM * 2 * 2
+        tables = int(((self.contexts + BLOCK - 1) // BLOCK).sum()) * 4
+        return kv + qo + tables
+
+    def host_inputs(self, pin: bool):
+        """Per-step inputs as host tensors (bf16 activations, fp32 logits)."""
+        g = self.generator
+        def mk(*shape, scale=1.0, dtype=torch.bfloat16):
+            t = (torch.randn(*shape, generator=g) * scale).to(dtype)
+            return t.pin_memory() if pin else t
+        inputs = dict(
+            q=mk(self.layers, self.rows, HEADS, HEAD_DIM, scale=0.5),
+            k=mk(self.layers, self.kv_rows, HEADS, HEAD_DIM, scale=0.5),
+            v=mk(self.layers, self.kv_rows, HEADS, HEAD_DIM, scale=0.5),
+            gate=mk(self.layers, self.rows, FFN, scale=3.0),
+            up=mk(self.layers, self.rows, FFN),
+            target=mk(self.accept_rows, VOCAB, scale=3.0, dtype=torch.float32),
+        )
+        noise = mk(self.accept_rows, VOCAB, scale=0.5, dtype=torch.float32)
+        draft = inputs["target"] + noise
+        inputs["draft"] = draft.pin_memory() if pin else draft
+        small = dict(tables=self.tables, lengths=self.lengths, write_blocks=self.write_blocks,
+                     write_offsets=self.write_offsets, cu_rows=self.cu_rows, starts=self.starts,
+                     slots=self.slots, temperature=self.temperature,
+                     u_draft=torch.rand(self.accept_rows, generator=g),
+                     u_accept=torch.rand(self.accept_rows, generator=g),
+                     u_final=torch.rand(self.requests, generator=g),
+                     request_tables=self.request_tables[:, None, :].repeat(1, DEPTHS, 1).contiguous())
+        for name, t in small.items():
+            inputs[name] = t.pin_memory() if pin else t
+        return inputs
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        try:  # address the GPU by UUID: nvidia-smi indices ignore CUDA_VISIBLE_DEVICES
+            index = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+        except Exception:
+            pass
+        self.index, self.samples, self.stop = index, [], threading.Event()
+        self.thread = threading.Thread(target=self.run, daemon=True)
+
+    def run(self):
+        while not self.stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
+                                     timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            self.stop.wait(0.1)
+
+    def __enter__(self):
+        self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self.stop.set()
+        self.thread.join(timeout=6)
+
+    def summary(self):
+        sm = [float(s[1]) for s in self.samples if len(s) > 2 and s[1].replace(".", "").isdigit()]
+        mx = [float(s[2]) for s in self.samples if len(s) > 2 and s[2].replace(".", "").isdigit()]
+        reasons = set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for s in self.samples:
+            for name, flag in zip(names, s[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(self.samples)}
+
+
+def run_gpu(args):
+    import torch.distributed as dist
+
+    import vllm_rlt_b200 as rlt
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    work = Workload(seed=1234 + rank)
+    host = work.host_inputs(pin=True)
+    dev = {name: t.to(device) for name, t in host.items()}
+    g = torch.Generator(device=device).manual_seed(99 + rank)
+    pool_shape = (work.total_pages, LAYERS, BLOCK, HEADS, HEAD_DIM)
+    key_pool = torch.empty(pool_shape, dtype=torch.bfloat16, device=device)
+    value_pool = torch.empty(pool_shape, dtype=torch.bfloat16, device=device)
+    for pool in (key_pool, value_pool):  # N(0,1) * 0.5, generated in slabs to bound temporaries
+        flat = pool.view(-1)
+        step = 1 << 28
+        for start in range(0, flat.numel(), step):
+            n = min(step, flat.numel() - start)
+            flat[start:start + n] = (torch.randn(n, device=device, generator=g) * 0.5).to(torch.bfloat16)
+    backend = rlt.create_backend(device, torch.bfloat16, HEAD_DIM, BLOCK)
+    slot_values = torch.zeros(2 * work.requests, 2, dtype=torch.int64, device=device)
+    per_row_t = dev["temperature"].repeat_interleave(TOKENS)
+    launches = 0
+    attn_events = []
+
+    def hot_path(x, timed_attention):
+        """One verify pass on device tensors `x`; returns (result buffer, rollback state)."""
+        nonlocal launches
+        for layer in range(LAYERS):
+            kc, vc = key_pool[:, layer], value_pool[:, layer]
+            rlt.kv_write(kc, vc, x["k"][layer], x["v"][layer], x["write_blocks"], x["write_offsets"])
+            if timed_attention:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+            backend(x["q"][layer], kc, vc, x["tables"], x["lengths"])
+            if timed_attention:
+                b.record()
+                attn_events.append((a, b))
+            rlt.silu_and_mul(x["gate"][layer], x["up"][layer])
+            launches += 4  # kv_write, attention plan + main, silu_and_mul
+        # drafts proposed from q with the explicit-uniform rule, then both acceptance modes
+        drafts, _ = rlt.sample_rows(x["draft"], per_row_t, x["u_draft"])
+        tokens = torch.zeros(work.requests, TOKENS, dtype=torch.int64, device=device)
+        tokens[:, 1:] = drafts.view(work.requests, TOKENS)[:, :-1]
+        rlt.accept_greedy(x["target"], x["cu_rows"], tokens, x["starts"], x["slots"], slot_values)
+        result, _ = rlt.accept_rejection(x["target"], x["draft"], x["cu_rows"], tokens, x["starts"],
+                                         x["temperature"], x["u_accept"], x["u_final"], x["slots"], slot_values)
+        accepted = result[work.accept_rows:work.accept_rows + work.requests]
+        rolled = rlt.rollback(x["starts"], accepted + 1, x["request_tables"], BLOCK)
+        launches += 5  # sample_rows, argmax + greedy finish, rejection, rollback
+        return result, rolled
+
+    # ---- device-resident timing ----
+    for _ in range(args.warmup):
+        hot_path(dev, False)
+    barrier()
+    launches = 0
+    with ClockSampler(local) as clocks:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(args.steps):
+            result, _ = hot_path(dev, True)
+        stop.record()
+        barrier()
+    elapsed_ms = start.elapsed_time(stop)
+    launches_per_step = launches // args.steps
+    attention_ms = statistics.mean(a.elapsed_time(b) for a, b in attn_events)
+    accepted_per_step = int(result[work.accept_rows:work.accept_rows + work.requests].sum())
+    committed_per_step = accepted_per_step + work.requests
+
+    # ---- end to end from pinned host buffers through the public API ----
+    staged = {name: torch.empty_like(t, device=device) for name, t in host.items()}
+    result_host = torch.empty(work.accept_rows + 2 * work.requests, dtype=torch.int64).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = result_host.numel() * 8
+
+    def e2e_step():
+        for name, t in host.items():
+            staged[name].copy_(t, non_blocking=True)
+        result, _ = hot_path(staged, False)
+        result_host.copy_(result, non_blocking=True)
+
+    for _ in range(min(args.warmup, 3)):
+        e2e_step()
+    barrier()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e_stop.record()
+    barrier()
+    e2e_ms = e_start.elapsed_time(e_stop)
+    status = backend.kernel.last_status(device)
+
+    times = torch.tensor([elapsed_ms, e2e_ms, float(accepted_per_step), float(committed_per_step)],
+                         dtype=torch.float64, device=device)
+    if world > 1:
+        gathered = [torch.zeros_like(times) for _ in range(world)]
+        dist.all_gather(gathered, times)
+        gathered = torch.stack(gathered).cpu()
+    else:
+        gathered = times.cpu()[None]
+    if rank == 0:
+        max_ms, max_e2e_ms = float(gathered[:, 0].max()), float(gathered[:, 1].max())
+        accepted_total, committed_total = float(gathered[:, 2].sum()), float(gathered[:, 3].sum())
+        ms_per_step = max_ms / args.steps
+        value = accepted_total / (ms_per_step / 1e3)
+        peak, peak_kind = measured_peaks()
+        algorithmic = work.algorithmic_attention_bytes()
+        achieved = algorithmic / (attention_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "accepted tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {
+                "workload": "configs[1] verify-step microbench x 24 layers: 64 requests/GPU, 16x128 MHA, "
+                            "block 16, ctx U[512,4096], 4 tokens x 4 depths shared plane, bf16; sampler 256 rows x "
+                            "49152 fp32 (greedy + rejection T=0.8, draft = target + N(0,0.5)); rollback",
+                "requests_per_gpu": work.requests, "layers": LAYERS, "attention_rows": work.rows,
+                "kv_pool_gb": round(2 * key_pool.numel() * 2 / 1e9, 2),
+                "l2_policy": "inputs larger than L2 (KV pool streamed once per step)",
+                "parallelism": f"{world} independent replicas, no collective",
+            },
+            "committed_tokens_per_s": committed_total / (ms_per_step / 1e3),
+            "acceptance_rate": accepted_total / (world * work.requests * (TOKENS - 1)),
+            "e2e": {"value": accepted_total / (max_e2e_ms / args.steps / 1e3), "unit": "accepted tokens/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": max_e2e_ms / args.steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "verify_attention (plan + main, per layer call)",
+                         "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "algorithmic_bytes": algorithmic,
+                         "avg_launch_ms": attention_ms},
+            "clocks": clocks.summary(),
+            "attention_status": status,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_baseline(threads=os.cpu_count() or 1, budget_s=12.0)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_step_seconds(threads: int, budget_s: float):
+    """Times the CPU oracle on a bounded sample of the same workload and extrapolates linearly
+    to one full step.  Returns (estimated seconds per step, accepted tokens per step, sample text)."""
+    from oracle import oracle
+
+    torch.set_num_threads(threads)
+    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+    sample_requests = 32
+    work = Workload(seed=1234, requests=sample_requests, layers=1)
+    x = work.host_inputs(pin=False)
+    g = torch.Generator().manual_seed(5)
+    pool_shape = (work.total_pages, 1, BLOCK, HEADS, HEAD_DIM)
+    key_pool = (torch.randn(pool_shape, generator=g) * 0.5).bfloat16()
+    value_pool = (torch.randn(pool_shape, generator=g) * 0.5).bfloat16()
+    kc, vc = key_pool[:, 0], value_pool[:, 0]
+
+    def one_layer():
+        t = time.perf_counter()
+        oracle.kv_write(kc, vc, x["k"][0], x["v"][0], x["write_blocks"], x["write_offsets"])
+        oracle.paged_attention(x["q"][0], kc, vc, x["tables"], x["lengths"])
+        oracle.silu_and_mul(x["gate"][0], x["up"][0])
+        return time.perf_counter() - t
+
+    # The layers differ only in their data: time as many passes of one layer as fit the budget.
+    times = [one_layer()]
+    sample_layers = max(1, min(LAYERS, int(budget_s / max(times[0], 1e-3))))
+    times += [one_layer() for _ in range(sample_layers - 1)]
+    layer_s = statistics.mean(times)
+    t1 = time.perf_counter()
+    per_row_t = x["temperature"].repeat_interleave(TOKENS)
+    drafts, _ = oracle.sample_rows(x["draft"], per_row_t, x["u_draft"])
+    tokens = torch.zeros(sample_requests, TOKENS, dtype=torch.int64)
+    tokens[:, 1:] = drafts.view(sample_requests, TOKENS)[:, :-1]
+    oracle.accept_greedy(x["target"], x["cu_rows"], tokens, x["starts"])
+    result, _ = oracle.accept_rejection(x["target"], x["draft"], x["cu_rows"], tokens, x["starts"],
+                                        x["temperature"], x["u_accept"], x["u_final"])
+    accepted = result[work.accept_rows:work.accept_rows + sample_requests]
+    oracle.rollback(x["starts"], accepted + 1, x["request_tables"], BLOCK)
+    accept_s = time.perf_counter() - t1
+    scale = REQUESTS / sample_requests
+    step_s = scale * (LAYERS * layer_s + accept_s)
+    acceptance = float(accepted.sum()) / (sample_requests * (TOKENS - 1))
+    sample = (f"{sample_requests} of {REQUESTS} requests, {sample_layers} of {LAYERS} layers "
+              f"(kv_write + attention + silu) + acceptance on {work.accept_rows} rows; "
+              f"{sum(times) + accept_s:.1f} s measured, scaled x{scale:.0f} requests, layers x{LAYERS}")
+    return step_s, acceptance * REQUESTS * (TOKENS - 1), sample, oracle.num_threads()
+
+
+def cpu_baseline(threads: int, budget_s: float):
+    step_s, accepted, sample, used = cpu_step_seconds(threads, budget_s)
+    return {"value": accepted / step_s, "unit": "accepted tokens/s", "cores": used, "kind": "port",
+            "sample": sample, "estimated_s_per_step": step_s}
+
+
+def run_reference(args):
+    """The reference arm: the CPU restatement of the reference's Torch path for this step (the
+    reference package itself is Python over PyTorch and is not present on the GPU box), timed on
+    all host cores; each step is the same bounded sample, scaled to a full step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    for _ in range(min(args.warmup, 1)):
+        cpu_step_seconds(threads, 8.0)
+    steps = max(1, min(args.steps, 3))
+    results = [cpu_step_seconds(threads, 8.0) for _ in range(steps)]
+    step_s = statistics.mean(r[0] for r in results)
+    accepted, sample, used = results[0][1], results[0][2], results[0][3]
+    value = accepted / step_s
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "accepted tokens/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps, "warmup": min(args.warmup, 1),
+        "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "configs[1] verify-step microbench x 24 layers (CPU, bounded sample scaled to a full step)"},
+        "cpu_baseline": {"value": value, "unit": "accepted tokens/s", "cores": used, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "accepted tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the verify-step kernels have no CPU fallback")
+    run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -21,6 +21,12 @@
 #include <stdint.h>
 #include <stddef.h>
 
+#if defined(__GNUC__)
+#define RLT_API __attribute__((visibility("default")))
+#else
+#define RLT_API
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -54,9 +60,9 @@ enum {
 };
 
 /* Library / build identification: "rlt_verify <version> sm_100a". */
-const char* rlt_version(void);
+RLT_API const char* rlt_version(void);
 /* Text of the most recent CUDA error seen by this thread in this library ("" if none). */
-const char* rlt_last_error(void);
+RLT_API const char* rlt_last_error(void);
 
 /* ------------------------------------------------------------------------
  * SiLU-and-Mul.  out[i] = T(silu_f32(f32(gate[i]))) * up[i], the activation
@@ -68,7 +74,7 @@ const char* rlt_last_error(void);
  * gate/up/out: `n` contiguous elements of `dtype`, any element alignment;
  * out must not alias the inputs.  n == 0 launches nothing.
  * ---------------------------------------------------------------------- */
-int rlt_silu_and_mul(const void* gate, const void* up, void* out, int64_t n,
+RLT_API int rlt_silu_and_mul(const void* gate, const void* up, void* out, int64_t n,
                      int dtype, rlt_stream_t stream);
 
 /* ------------------------------------------------------------------------
@@ -84,7 +90,7 @@ int rlt_silu_and_mul(const void* gate, const void* up, void* out, int64_t n,
  * k, v: [rows, kv_heads, head_dim] contiguous.  write_blocks/write_offsets: int64 [rows].
  * write_mask: uint8/bool [rows] or NULL.  active_rows: device int32 scalar or NULL.
  * ---------------------------------------------------------------------- */
-int rlt_kv_write(void* key_cache, void* value_cache, int64_t block_stride, int64_t token_stride,
+RLT_API int rlt_kv_write(void* key_cache, void* value_cache, int64_t block_stride, int64_t token_stride,
                  int64_t num_blocks, int block_size, int kv_heads, int head_dim, int dtype,
                  const void* k, const void* v, const int64_t* write_blocks,
                  const int64_t* write_offsets, const uint8_t* write_mask,
@@ -120,15 +126,23 @@ int rlt_kv_write(void* key_cache, void* value_cache, int64_t block_stride, int64
  *   bytes, 256-byte aligned, owned by the caller, private to this call until its
  *   work on `stream` completes.  Contents on entry are irrelevant.
  * ---------------------------------------------------------------------- */
-size_t rlt_verify_attention_workspace_bytes(int rows, int q_heads, int kv_heads, int head_dim,
+RLT_API size_t rlt_verify_attention_workspace_bytes(int rows, int q_heads, int kv_heads, int head_dim,
                                             int block_size, int table_width);
 
-int rlt_verify_attention(const void* q, void* out, const void* key_cache, const void* value_cache,
+RLT_API int rlt_verify_attention(const void* q, void* out, const void* key_cache, const void* value_cache,
                          int64_t block_stride, int64_t token_stride, int64_t num_blocks,
                          int block_size, int q_heads, int kv_heads, int head_dim, int dtype,
                          const int32_t* block_tables, int table_rows, int table_width,
                          const int32_t* context_lengths, const int32_t* cu_seqlens_q, int rows,
                          void* workspace, size_t workspace_bytes, rlt_stream_t stream);
+
+/* Diagnostics for the tiled kernel (head_dim 128, 16-token pages, fp16/bf16): waits for
+ * `stream` and copies four words of the workspace header to the host —
+ * status4[0] = work items planned by the last call (groups x context chunks x kv heads; shows
+ * whether rows were grouped), status4[1] = work items claimed, status4[2] = error bits
+ * (nonzero: a bounded device-side wait gave up and the output is invalid), status4[3] = 0.
+ * Synchronises; not for the hot path.  No counterpart in the reference. */
+RLT_API int rlt_verify_attention_status(const void* workspace, rlt_stream_t stream, uint32_t* status4);
 
 /* ------------------------------------------------------------------------
  * Row argmax: targets[r] = argmax_v logits[r, v], lowest index on ties, a NaN
@@ -138,7 +152,7 @@ int rlt_verify_attention(const void* q, void* out, const void* key_cache, const 
  *   (vllm_rlt/worker/async_speculative.py:415).
  * logits: [rows, vocab] of `dtype`, row stride in elements.
  * ---------------------------------------------------------------------- */
-int rlt_argmax_rows(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
+RLT_API int rlt_argmax_rows(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
                     int64_t* targets, rlt_stream_t stream);
 
 /* ------------------------------------------------------------------------
@@ -157,7 +171,7 @@ int rlt_argmax_rows(const void* logits, int64_t row_stride, int rows, int vocab,
  *   (vllm_rlt/worker/async_speculative.py:417-447; wire layout :62-77).
  * tokens: int64 [n, tokens_width].  slot_values: int64 [*, 2].
  * ---------------------------------------------------------------------- */
-int rlt_accept_greedy(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
+RLT_API int rlt_accept_greedy(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
                       const int32_t* cu_rows, int n, const int64_t* tokens, int tokens_width,
                       const int64_t* starts, const int64_t* slots, int64_t* slot_values,
                       int64_t* result, rlt_stream_t stream);
@@ -170,7 +184,7 @@ int rlt_accept_greedy(const void* logits, int64_t row_stride, int rows, int voca
  * Replaces: Sampler.sample / Sampler.draw (vllm_rlt/worker/sampler.py:57-81) with the
  *   generator replaced by an explicit uniform.
  * ---------------------------------------------------------------------- */
-int rlt_sample_rows(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
+RLT_API int rlt_sample_rows(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
                     const float* temperature, const float* uniforms, int64_t* tokens,
                     int32_t* status, rlt_stream_t stream);
 
@@ -200,7 +214,7 @@ int rlt_sample_rows(const void* logits, int64_t row_stride, int rows, int vocab,
  * target_logits, draft_logits: [rows, vocab]; draft row j of a request holds the logits
  *   draft j+1 was sampled from (its last row is unused).
  * ---------------------------------------------------------------------- */
-int rlt_accept_rejection(const void* target_logits, const void* draft_logits, int64_t row_stride,
+RLT_API int rlt_accept_rejection(const void* target_logits, const void* draft_logits, int64_t row_stride,
                          int rows, int vocab, int dtype, const int32_t* cu_rows, int n,
                          const int64_t* tokens, int tokens_width, const int64_t* starts,
                          const float* temperature, const float* u_accept, const float* u_final,
@@ -226,7 +240,7 @@ int rlt_accept_rejection(const void* target_logits, const void* draft_logits, in
  * tables: int32 [n, planes, table_width].  written_prefix: int64 [n, planes, layers] or NULL.
  * pages_used: int32 [n] (table entries that are real pages) or NULL (= all table_width).
  * ---------------------------------------------------------------------- */
-int rlt_rollback(const int64_t* starts, const int64_t* emitted, int n, const int32_t* tables,
+RLT_API int rlt_rollback(const int64_t* starts, const int64_t* emitted, int n, const int32_t* tables,
                  int planes, int table_width, int block_size, const int32_t* pages_used,
                  const int32_t* refcounts, int64_t num_blocks, int64_t* written_prefix, int layers,
                  int64_t* frontier, int32_t* context_lengths, int64_t* write_blocks,

@@ -1,0 +1,181 @@
+"""Acceptance kernels vs the CPU oracle (bit-exact) and the reference's golden vectors."""
+
+import pytest
+import torch
+
+import vllm_rlt_b200 as rlt
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def make_round(n, k_max, vocab, dtype, seed, agree=True):
+    g = torch.Generator().manual_seed(seed)
+    counts = torch.randint(1, k_max + 2, (n,), generator=g)
+    cu = torch.zeros(n + 1, dtype=torch.int32)
+    cu[1:] = counts.cumsum(0)
+    rows = int(cu[-1])
+    logits = (torch.randn(rows, vocab, generator=g) * 3).to(dtype)
+    tokens = torch.randint(0, vocab, (n, k_max + 1), generator=g)
+    if agree:
+        targets = logits.argmax(-1)
+        for i in range(n):
+            a = int(torch.randint(0, int(counts[i]), (1,), generator=g))
+            tokens[i, 1:1 + a] = targets[int(cu[i]):int(cu[i]) + a]
+    starts = torch.randint(1, 3000, (n,), generator=g)
+    slots = torch.randperm(2 * n, generator=g)[:n]
+    return dict(cu=cu, rows=rows, logits=logits, tokens=tokens, starts=starts, slots=slots, counts=counts, g=g)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("vocab", [49152, 1024, 1027, 7])
+def test_argmax_matches_torch_and_oracle(dtype, vocab):
+    g = torch.Generator().manual_seed(3)
+    logits = (torch.randn(33, vocab, generator=g) * 3).to(dtype)
+    logits[1, vocab // 2] = logits[1, vocab - 1] = 60.0
+    logits[2] = 0.0
+    logits[3, 0] = -0.0
+    logits[4, vocab - 1] = float("nan")
+    logits[5, 3 % vocab] = float("nan")
+    logits[5, 5 % vocab] = float("inf")
+    got = rlt.argmax_rows(logits.cuda()).cpu()
+    assert torch.equal(got, oracle.argmax_rows(logits))
+    assert torch.equal(got, logits.argmax(-1))
+    # a strided row view (row stride > vocab) is honoured
+    wide = torch.zeros(33, vocab + 5, dtype=dtype)
+    wide[:, :vocab] = logits
+    assert torch.equal(rlt.argmax_rows(wide.cuda()[:, :vocab]).cpu(), got)
+
+
+def test_greedy_accept_table_of_the_reference(golden):
+    for row in golden("greedy.pt")["table"]:
+        candidates, targets = row["candidates"], row["targets"]
+        logits = torch.full((len(targets), 300), -100.0)
+        for j, t in enumerate(targets):
+            logits[j, t] = 100.0
+        tokens = torch.tensor([[5] + candidates], dtype=torch.int64)
+        cu = torch.tensor([0, len(targets)], dtype=torch.int32)
+        result = rlt.accept_greedy(logits.cuda(), cu.cuda(), tokens.cuda(), torch.tensor([40]).cuda()).cpu()
+        results, frontiers = rlt.decode_result(result.tolist(), cu.tolist())
+        assert results[0].accepted_count == row["accepted"]
+        assert results[0].token_ids == row["tokens"]
+        assert frontiers == [40 + row["accepted"] + 1]
+
+
+def test_async_accept_program_of_the_reference(golden):
+    data = golden("async_accept.pt")
+    counts = data["counts"]
+    n, rows = counts.numel(), int(counts.sum())
+    cu = torch.zeros(n + 1, dtype=torch.int32)
+    cu[1:] = counts.cumsum(0)
+    logits = torch.full((rows, 64), -50.0)
+    logits[torch.arange(rows), data["target"]] = 50.0
+    slot_values = torch.full_like(data["slot_values"], -7).cuda()
+    result = rlt.accept_greedy(logits.cuda(), cu.cuda(), data["tokens"].cuda(), data["starts"].cuda(),
+                               data["slots"].cuda(), slot_values)
+    assert torch.equal(result.cpu(), data["result"])
+    assert torch.equal(slot_values.cpu(), data["slot_values"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_greedy_round_matches_oracle_at_vocab_49152(dtype):
+    r = make_round(64, 4, 49152, dtype, seed=21)
+    want_slots = torch.full((128, 2), -1, dtype=torch.int64)
+    want = oracle.accept_greedy(r["logits"], r["cu"], r["tokens"], r["starts"], r["slots"], want_slots)
+    got_slots = torch.full((128, 2), -1, dtype=torch.int64).cuda()
+    got = rlt.accept_greedy(r["logits"].cuda(), r["cu"].cuda(), r["tokens"].cuda(), r["starts"].cuda(),
+                            r["slots"].cuda(), got_slots)
+    assert torch.equal(got.cpu(), want) and torch.equal(got_slots.cpu(), want_slots)
+    accepted = want[r["rows"]:r["rows"] + 64]
+    assert int(accepted.max()) > 0 and int(accepted.min()) == 0
+
+
+@pytest.mark.parametrize("vocab,dtype", [(49152, torch.float32), (4099, torch.float32), (49152, torch.bfloat16)])
+def test_sample_rows_matches_oracle_bit_for_bit(vocab, dtype):
+    g = torch.Generator().manual_seed(8)
+    rows = 24
+    logits = (torch.randn(rows, vocab, generator=g) * 3).to(dtype)
+    temperature = torch.tensor([0.8, 1.0, 0.0, 1.7] * 6)
+    uniforms = torch.rand(rows, generator=g)
+    uniforms[0], uniforms[1] = 0.0, 0.99999994
+    want_tokens, want_status = oracle.sample_rows(logits, temperature, uniforms)
+    got_tokens, got_status = rlt.sample_rows(logits.cuda(), temperature.cuda(), uniforms.cuda())
+    assert torch.equal(got_tokens.cpu(), want_tokens) and torch.equal(got_status.cpu(), want_status)
+    assert int(want_status.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("noise,dtype", [(0.0, torch.float32), (0.5, torch.float32), (3.0, torch.float32),
+                                         (0.5, torch.bfloat16)])
+def test_rejection_round_matches_oracle_bit_for_bit(noise, dtype):
+    # draft logits: identical (all accept), target + N(0, 0.5) (mixed), independent (mostly reject)
+    n, k, vocab = 32, 4, 49152
+    r = make_round(n, k, vocab, torch.float32, seed=33, agree=False)
+    g = r["g"]
+    target = r["logits"]
+    draft = target + torch.randn(r["rows"], vocab, generator=g) * noise if noise < 3 else \
+        torch.randn(r["rows"], vocab, generator=g) * 3
+    target, draft = target.to(dtype), draft.to(dtype)
+    temperature = torch.full((n,), 0.8)
+    temperature[::7] = 0.0   # greedy requests mixed into the batch
+    # candidates are drawn from q with the same explicit-uniform rule
+    per_row_t = torch.repeat_interleave(temperature, r["counts"])
+    drafts, _ = oracle.sample_rows(draft, per_row_t, torch.rand(r["rows"], generator=g))
+    tokens = r["tokens"]
+    for i in range(n):
+        a, c = int(r["cu"][i]), int(r["counts"][i])
+        tokens[i, 1:c] = drafts[a:a + c - 1]
+    u_accept, u_final = torch.rand(r["rows"], generator=g), torch.rand(n, generator=g)
+    want_slots = torch.full((2 * n, 2), -1, dtype=torch.int64)
+    want, want_status = oracle.accept_rejection(target, draft, r["cu"], tokens, r["starts"], temperature,
+                                                u_accept, u_final, r["slots"], want_slots)
+    got_slots = torch.full((2 * n, 2), -1, dtype=torch.int64).cuda()
+    got, got_status = rlt.accept_rejection(target.cuda(), draft.cuda(), r["cu"].cuda(), tokens.cuda(),
+                                           r["starts"].cuda(), temperature.cuda(), u_accept.cuda(),
+                                           u_final.cuda(), r["slots"].cuda(), got_slots)
+    assert torch.equal(got_status.cpu(), want_status) and int(want_status.abs().sum()) == 0
+    assert torch.equal(got.cpu(), want)
+    assert torch.equal(got_slots.cpu(), want_slots)
+    accepted = want[r["rows"]:r["rows"] + n]
+    drafts_per_request = r["counts"] - 1
+    if noise == 0.0:
+        sampled = temperature != 0
+        assert torch.equal(accepted[sampled], drafts_per_request[sampled])
+    if noise == 3.0:
+        assert int(accepted.sum()) < int(drafts_per_request.sum()) // 2
+
+
+def test_rejection_decisions_of_the_reference(golden):
+    for case in golden("sampler.pt")["rejection"]:
+        vocab = case["target_logits"].numel()
+        target = torch.stack([case["target_logits"], torch.zeros(vocab)]).cuda()
+        draft = torch.stack([case["draft_logits"], torch.zeros(vocab)]).cuda()
+        tokens = torch.tensor([[0, case["candidate"]]], dtype=torch.int64).cuda()
+        cu = torch.tensor([0, 2], dtype=torch.int32).cuda()
+        result, status = rlt.accept_rejection(target, draft, cu, tokens, torch.tensor([10]).cuda(),
+                                              torch.tensor([case["temperature"]]).cuda(),
+                                              torch.tensor([case["uniform"], 0.0]).cuda(),
+                                              torch.tensor([0.37]).cuda())
+        result = result.cpu()
+        margin = abs(case["uniform"] * case["q_c"] - case["p_c"]) / max(case["p_c"], 1e-30)
+        assert int(status[0]) == 0
+        if margin > 1e-4:
+            assert int(result[2]) == int(case["accepted"])
+        if not int(result[2]):
+            assert float(case["residual"][int(result[0])]) > 0
+
+
+def test_error_statuses_are_reported_not_raised_on_device():
+    vocab = 8
+    target = torch.zeros(2, vocab)
+    draft = torch.zeros(2, vocab)
+    draft[0, 3] = -2000.0
+    args = [torch.tensor([0, 2], dtype=torch.int32), torch.tensor([[0, 3]]), torch.tensor([5]),
+            torch.tensor([1.0]), torch.tensor([0.5, 0.0]), torch.tensor([0.5])]
+    _, status = rlt.accept_rejection(target.cuda(), draft.cuda(), *[a.cuda() for a in args])
+    assert status.tolist() == [1]
+    with pytest.raises(ValueError, match="zero proposal"):
+        rlt.raise_for_status(status.tolist())
+    target[0, 0] = float("nan")
+    draft[0, 3] = 0.0
+    _, status = rlt.accept_rejection(target.cuda(), draft.cuda(), *[a.cuda() for a in args])
+    assert status.tolist() == [3]

@@ -1,0 +1,222 @@
+"""Verify attention on the GPU vs the CPU oracle, the golden vectors of the reference, and
+its own invariance contract (a row's bits do not depend on its batch or its group).
+
+Tolerances: bf16 2e-2 and fp16 2e-3 (the reference's own GPU tolerances,
+tests/test_attention.py:54 there), fp32 1e-5 relative.
+"""
+
+import pytest
+import torch
+
+import vllm_rlt_b200 as rlt
+from helpers import attention_tolerance, make_pool
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def kernel():
+    return rlt.B200PagedAttention()
+
+
+def run_gpu(kernel, q, key_pool, value_pool, layer, tables, lengths, cu=None):
+    k = key_pool.cuda()[:, layer]
+    v = value_pool.cuda()[:, layer]
+    if cu is None:
+        out = kernel(q.cuda(), k, v, tables.cuda(), lengths.cuda())
+    else:
+        out = kernel.prefill(q.cuda(), k, v, tables.cuda(), lengths.cuda(), cu.cuda(), 0)
+    torch.cuda.synchronize()
+    return out.cpu()
+
+
+def check(got, want, dtype):
+    tol = attention_tolerance(dtype)
+    if dtype == torch.float32:
+        torch.testing.assert_close(got, want, rtol=tol, atol=tol)
+    else:
+        torch.testing.assert_close(got.float(), want.float(), rtol=tol, atol=tol)
+
+
+def test_golden_vectors_of_the_reference(kernel, golden):
+    for case in golden("attention.pt"):
+        if case["kind"] == "direct":
+            k, v = case["k"], case["v"]
+        else:
+            k, v = case["key_cache"][:, case["layer"]], case["value_cache"][:, case["layer"]]
+        got = kernel(case["q"].cuda(), k.cuda(), v.cuda(), case["tables"].cuda(), case["lengths"].cuda()).cpu()
+        check(got, case["out"], case["q"].dtype)
+        for row in (case["lengths"] == 0).nonzero().flatten().tolist():
+            assert torch.count_nonzero(got[row]) == 0
+
+
+@pytest.mark.parametrize("dtype,heads,kv_heads,dim,block", [
+    (torch.float32, 4, 4, 64, 16),     # the tiny fp32 model of config 1
+    (torch.float32, 6, 2, 7, 2),
+    (torch.float16, 8, 8, 96, 16),
+    (torch.bfloat16, 6, 2, 32, 4),
+])
+def test_generic_shapes_match_oracle(kernel, dtype, heads, kv_heads, dim, block):
+    pool = make_pool([71, 5, 33, 64, 1], kv_heads=kv_heads, head_dim=dim, block=block, dtype=dtype, seed=11,
+                     layers=2, layer=1, row_lengths=[[1, 32, 71], [5], [33, 17], [64], [1]], scale=1.0)
+    g = torch.Generator().manual_seed(12)
+    q = torch.randn(pool["tables"].shape[0], heads, dim, generator=g).to(dtype)
+    got = run_gpu(kernel, q, pool["key_pool"], pool["value_pool"], 1, pool["tables"], pool["lengths"])
+    want = oracle.paged_attention(q, pool["key"], pool["value"], pool["tables"].clamp_min(0), pool["lengths"])
+    check(got, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("layout", ["shared", "last_exited", "verify"])
+def test_tiled_kernel_matches_oracle_on_verify_shapes(kernel, dtype, layout):
+    # Scaled-down config 2: requests with 16 heads x 128, 16-token pages, permuted pool, layer-strided view.
+    g = torch.Generator().manual_seed(77)
+    contexts = torch.randint(40, 1500, (6,), generator=g).tolist() + [512, 513]
+    if layout == "shared":       # 4 tokens x 4 depths share one table; row (t, depth) sees ctx - 3 + t
+        groups = contexts
+        row_lengths = [[c - 3 + t for _ in range(4) for t in range(4)] for c in contexts]
+    elif layout == "last_exited":  # one table per (request, depth plane), 4 rows each
+        groups = [c for c in contexts for _ in range(4)]
+        row_lengths = [[c - 3 + t for t in range(4)] for c in contexts for _ in range(4)]
+    else:                        # the real verify shape: k + 1 = 5..7 rows per request
+        groups = contexts
+        row_lengths = [[c - n + 1 + t for t in range(n)] for c, n in zip(contexts, [5, 6, 7, 5, 6, 7, 5, 5])]
+    pool = make_pool(groups, kv_heads=16, head_dim=128, block=16, dtype=dtype, seed=5, layers=3, layer=2,
+                     row_lengths=row_lengths)
+    q = (torch.randn(pool["tables"].shape[0], 16, 128, generator=g) * 0.5).to(dtype)
+    got = run_gpu(kernel, q, pool["key_pool"], pool["value_pool"], 2, pool["tables"], pool["lengths"])
+    want = oracle.paged_attention(q, pool["key"], pool["value"], pool["tables"].clamp_min(0), pool["lengths"])
+    check(got, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_split_kv_boundaries_and_batch_invariance(kernel, dtype):
+    # Empty row, page, chunk and octave boundaries, GQA 2 (tests/test_attention.py:154-184 of the reference).
+    lengths = [0, 1, 15, 16, 17, 511, 512, 513, 1024, 4096, 4097, 5121, 10000]
+    pool = make_pool(lengths, kv_heads=4, head_dim=128, block=16, dtype=dtype, seed=1, scale=1.0, pad=0)
+    g = torch.Generator().manual_seed(2)
+    q = torch.randn(len(lengths), 8, 128, generator=g).to(dtype)
+    got = run_gpu(kernel, q, pool["key_pool"], pool["value_pool"], 0, pool["tables"], pool["lengths"])
+    want = oracle.paged_attention(q, pool["key"], pool["value"], pool["tables"], pool["lengths"])
+    check(got, want, dtype)
+    assert torch.count_nonzero(got[0]) == 0
+    for row in (1, 5, 8, 10, 12):
+        one = slice(row, row + 1)
+        alone = run_gpu(kernel, q[one], pool["key_pool"], pool["value_pool"], 0, pool["tables"][one],
+                        pool["lengths"][one])
+        assert torch.equal(alone[0], got[row]), row
+
+
+def test_row_bits_do_not_depend_on_group_membership(kernel):
+    # The k+1 rows of a request scored as one group, one by one, and through the packed
+    # interface must agree bit for bit; lengths straddle a chunk boundary on purpose.
+    dtype = torch.bfloat16
+    contexts = [515, 1030, 64, 4100]
+    rows_per = [7, 5, 6, 4]
+    row_lengths = [[c - n + 1 + t for t in range(n)] for c, n in zip(contexts, rows_per)]
+    pool = make_pool(contexts, kv_heads=16, head_dim=128, block=16, dtype=dtype, seed=3, row_lengths=row_lengths)
+    g = torch.Generator().manual_seed(4)
+    rows = sum(rows_per)
+    q = (torch.randn(rows, 16, 128, generator=g) * 0.5).to(dtype)
+    grouped = run_gpu(kernel, q, pool["key_pool"], pool["value_pool"], 0, pool["tables"], pool["lengths"])
+    for row in range(rows):
+        one = slice(row, row + 1)
+        alone = run_gpu(kernel, q[one], pool["key_pool"], pool["value_pool"], 0, pool["tables"][one],
+                        pool["lengths"][one])
+        assert torch.equal(alone[0], grouped[row]), row
+    # packed: one table row per request, cu_seqlens_q, length of the last row
+    first_rows = [sum(rows_per[:i]) for i in range(len(rows_per))]
+    seq_tables = pool["tables"][first_rows]
+    seq_lengths = torch.tensor(contexts, dtype=torch.int32)
+    cu = torch.tensor(first_rows + [rows], dtype=torch.int32)
+    packed = run_gpu(kernel, q, pool["key_pool"], pool["value_pool"], 0, seq_tables, seq_lengths, cu)
+    assert torch.equal(packed, grouped)
+    # a shuffled batch of the same rows (groups broken up) still gives the same bits
+    perm = torch.randperm(rows, generator=g)
+    shuffled = run_gpu(kernel, q[perm], pool["key_pool"], pool["value_pool"], 0, pool["tables"][perm],
+                       pool["lengths"][perm])
+    assert torch.equal(shuffled, grouped[perm])
+
+
+def test_padding_entries_are_never_dereferenced(kernel):
+    dtype = torch.bfloat16
+    pool = make_pool([40, 300, 17], kv_heads=2, head_dim=128, block=16, dtype=dtype, seed=6,
+                     row_lengths=[[38, 39, 40], [300], [0, 17]])
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(pool["tables"].shape[0], 4, 128, generator=g).to(dtype)
+    clean = run_gpu(kernel, q, pool["key_pool"], pool["value_pool"], 0, pool["tables"].clamp_min(0), pool["lengths"])
+    for filler in (-1, 2**31 - 1):
+        tables = pool["tables"].clone()
+        tables[tables < 0] = filler
+        tables[4] = filler  # the zero-length row's whole table is garbage
+        got = run_gpu(kernel, q, pool["key_pool"], pool["value_pool"], 0, tables, pool["lengths"])
+        assert torch.equal(got, clean)
+    assert torch.count_nonzero(clean[4]) == 0
+
+
+def test_empty_batch_and_argument_errors(kernel):
+    k = torch.zeros(4, 16, 2, 128, device="cuda", dtype=torch.bfloat16)
+    empty = kernel(torch.empty(0, 4, 128, device="cuda", dtype=torch.bfloat16), k, k,
+                   torch.zeros(0, 3, dtype=torch.int32, device="cuda"), torch.zeros(0, dtype=torch.int32, device="cuda"))
+    assert empty.shape == (0, 4, 128)
+    q = torch.ones(1, 3, 128, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="positive multiple"):
+        kernel(q, k, k, torch.zeros(1, 1, dtype=torch.int32, device="cuda"), torch.ones(1, dtype=torch.int32, device="cuda"))
+    with pytest.raises(ValueError, match="int32"):
+        kernel(q[:, :2], k, k, torch.zeros(1, 1, dtype=torch.int64, device="cuda"),
+               torch.ones(1, dtype=torch.int32, device="cuda"))
+
+
+def test_backend_adapter_and_capabilities():
+    backend = rlt.create_backend("cuda", torch.bfloat16, 128, 16)
+    assert backend.info["selected_backend"] == "b200" and backend.info["tiled_kernel"]
+    caps = backend.capabilities
+    assert caps.cuda_graphs and caps.async_scheduling and caps.device_context_lengths
+    assert caps.packed_prefill and caps.packed_matches_decode and not caps.sliding_window
+    with pytest.raises(NotImplementedError, match="sliding-window"):
+        backend.windowed()
+    with pytest.raises(ValueError, match="CUDA"):
+        rlt.create_backend("cpu", torch.bfloat16, 128, 16)
+
+
+def test_int32_block_ids_use_64bit_physical_offsets(kernel):
+    # tests/test_attention_64bit.py of the reference: offset 2**31 elements.
+    if torch.cuda.mem_get_info()[0] < 9 * 2**30:
+        pytest.skip("needs 9 GiB of free device memory")
+    shape, strides = (2049, 1, 1, 16), (2**20, 16, 16, 1)
+    key = torch.empty_strided(shape, strides, device="cuda", dtype=torch.float16)
+    value = torch.empty_strided(shape, strides, device="cuda", dtype=torch.float16)
+    key[0].zero_()
+    value[0].fill_(-3)
+    key[2048].fill_(1)
+    expected = torch.arange(16, device="cuda", dtype=torch.float16).view(1, 1, 16)
+    value[2048].copy_(expected)
+    query = torch.ones((1, 1, 16), device="cuda", dtype=torch.float16)
+    table = torch.tensor([[2048]], device="cuda", dtype=torch.int32)
+    lengths = torch.tensor([1], device="cuda", dtype=torch.int32)
+    torch.testing.assert_close(kernel(query, key, value, table, lengths), expected, rtol=0, atol=0)
+
+
+def test_graph_capture_and_replay_with_device_lengths(kernel):
+    dtype = torch.bfloat16
+    pool = make_pool([600, 90], kv_heads=16, head_dim=128, block=16, dtype=dtype, seed=9,
+                     row_lengths=[[596, 597, 598, 599, 600], [86, 87, 88, 89, 90]])
+    g = torch.Generator().manual_seed(10)
+    q = (torch.randn(10, 16, 128, generator=g) * 0.5).to(dtype).cuda()
+    k, v = pool["key_pool"].cuda()[:, 0], pool["value_pool"].cuda()[:, 0]
+    tables, lengths = pool["tables"].cuda(), pool["lengths"].cuda()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            kernel(q, k, v, tables, lengths)
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        out = kernel(q, k, v, tables, lengths)
+    # new device-side lengths are picked up by a replay without any host involvement
+    lengths.sub_(20)
+    graph.replay()
+    torch.cuda.synchronize()
+    want = oracle.paged_attention(q.cpu(), pool["key"], pool["value"], pool["tables"].clamp_min(0), lengths.cpu())
+    check(out.cpu(), want, dtype)

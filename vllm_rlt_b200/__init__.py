@@ -1,0 +1,23 @@
+"""B200-native (sm_100a) self-speculative verify step for looped language models.
+
+Hand-written CUDA kernels behind a C ABI (``include/rlt_verify.h``,
+``vllm_rlt_b200/librlt_verify.so``) plus the thin PyTorch host layer that mirrors the
+attention-backend, sampler, speculative and ``torch.ops.vllm_rlt`` interfaces of vllm-rlt
+for this one path.  There is no CPU or library fallback: importing is cheap, the first call
+raises if the CUDA library has not been built.
+"""
+
+from ._capi import NativeLibraryMissing, load as load_library
+from .activation import register_torch_op, silu_and_mul
+from .attention import (B200_CAPABILITIES, AttentionBackend, B200PagedAttention, BackendCapabilities,
+                        create_backend)
+from .kv_cache import RollbackResult, kv_write, rollback
+from .speculative import (SpeculativeResult, accept_greedy, accept_rejection, argmax_rows, decode_result,
+                          raise_for_status, sample_rows)
+
+__all__ = [
+    "AttentionBackend", "B200PagedAttention", "B200_CAPABILITIES", "BackendCapabilities",
+    "NativeLibraryMissing", "RollbackResult", "SpeculativeResult", "accept_greedy", "accept_rejection",
+    "argmax_rows", "create_backend", "decode_result", "kv_write", "load_library", "raise_for_status",
+    "register_torch_op", "rollback", "sample_rows", "silu_and_mul",
+]

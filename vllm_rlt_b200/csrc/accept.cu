@@ -1,0 +1,411 @@
+// Acceptance sampler of the verify step: row argmax, greedy prefix acceptance with the
+// device state update, token draws with explicit uniforms and rejection sampling with
+// residual resampling.
+//
+// All of these are streaming reductions over [rows, vocab] logits (HBM-bound: rows * vocab *
+// sizeof(T) bytes, a few flops per byte).  Argmax is exact and order independent (a packed
+// (value, lowest index) key reduced with max).  The probabilistic kernels use the canonical
+// arithmetic of include/rlt_canonical.h — an exp built from IEEE fused multiply-adds and
+// 2^-40 fixed-point integer sums — so their results are identical to the CPU oracle's for
+// any thread count or reduction shape.
+#include "common.cuh"
+
+#include "../../include/rlt_canonical.h"
+
+namespace rlt {
+namespace {
+
+constexpr int kArgmaxThreads = 512;
+constexpr int kSampleThreads = 1024;
+
+// ---- packed argmax key ------------------------------------------------------------------
+// Larger key = better candidate: NaN above every number, then by value (-0 == +0), then the
+// LOWER index.  max() over keys therefore reproduces torch.argmax.
+__device__ __forceinline__ unsigned long long argmax_key(float x, int index) {
+  uint32_t bits;
+  if (x != x) {
+    bits = 0xffffffffu;
+  } else {
+    if (x == 0.0f) x = 0.0f;  // -0 -> +0
+    bits = __float_as_uint(x);
+    bits = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+  }
+  return (static_cast<unsigned long long>(bits) << 32) | (0xffffffffu - static_cast<uint32_t>(index));
+}
+__device__ __forceinline__ int key_index(unsigned long long key) {
+  return static_cast<int>(0xffffffffu - static_cast<uint32_t>(key & 0xffffffffu));
+}
+
+__device__ __forceinline__ unsigned long long warp_max(unsigned long long v) {
+#pragma unroll
+  for (int x = 16; x > 0; x >>= 1) {
+    const unsigned long long o = __shfl_xor_sync(0xffffffffu, v, x);
+    v = o > v ? o : v;
+  }
+  return v;
+}
+__device__ __forceinline__ unsigned long long warp_sum(unsigned long long v) {
+#pragma unroll
+  for (int x = 16; x > 0; x >>= 1) v += __shfl_xor_sync(0xffffffffu, v, x);
+  return v;
+}
+
+// Block-wide reductions for kThreads threads; every thread receives the result.
+template <int kThreads>
+__device__ __forceinline__ unsigned long long block_max(unsigned long long v, unsigned long long* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  v = lane < kThreads / 32 ? scratch[lane] : 0ull;
+  return warp_max(v);
+}
+template <int kThreads>
+__device__ __forceinline__ unsigned long long block_sum(unsigned long long v, unsigned long long* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  v = lane < kThreads / 32 ? scratch[lane] : 0ull;
+  return warp_sum(v);
+}
+
+// Argmax of one row by the whole CTA; 16-byte loads when the row allows them.
+template <typename T, int kThreads>
+__device__ __forceinline__ int block_argmax(const T* __restrict__ row, int vocab, unsigned long long* scratch) {
+  constexpr int kVec = 16 / sizeof(T);
+  unsigned long long best = 0ull;
+  if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0 && vocab % kVec == 0) {
+    const uint4* rv = reinterpret_cast<const uint4*>(row);
+    const int nvec = vocab / kVec;
+    for (int i = threadIdx.x; i < nvec; i += kThreads) {
+      const uint4 raw = __ldcs(rv + i);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) {
+        const unsigned long long key = argmax_key(Elem<T>::to_float(e[j]), i * kVec + j);
+        best = key > best ? key : best;
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += kThreads) {
+      const unsigned long long key = argmax_key(Elem<T>::to_float(row[i]), i);
+      best = key > best ? key : best;
+    }
+  }
+  return key_index(block_max<kThreads>(best, scratch));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kArgmaxThreads)
+argmax_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab, int64_t* __restrict__ targets) {
+  __shared__ unsigned long long scratch[32];
+  const int index = block_argmax<T, kArgmaxThreads>(logits + static_cast<int64_t>(blockIdx.x) * row_stride, vocab, scratch);
+  if (threadIdx.x == 0) targets[blockIdx.x] = index;
+}
+
+// One thread per request: matching prefix, next token / position, slot update, wire buffer.
+__global__ void greedy_finish_kernel(const int32_t* __restrict__ cu_rows, int n, int rows,
+                                     const int64_t* __restrict__ tokens, int tokens_width,
+                                     const int64_t* __restrict__ starts, const int64_t* __restrict__ slots,
+                                     int64_t* __restrict__ slot_values, int64_t* __restrict__ result) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int a = cu_rows[i], c = cu_rows[i + 1] - a;
+  const int64_t* tok = tokens + static_cast<int64_t>(i) * tokens_width;
+  int accepted = 0;
+  while (accepted < c - 1 && tok[accepted + 1] == result[a + accepted]) ++accepted;
+  const int64_t next_token = result[a + accepted];
+  const int64_t next_pos = starts[i] + accepted + 1;
+  result[rows + i] = accepted;
+  result[rows + n + i] = next_pos;
+  if (slots != nullptr && slot_values != nullptr) {
+    slot_values[2 * slots[i]] = next_token;
+    slot_values[2 * slots[i] + 1] = next_pos;
+  }
+}
+
+// ---- canonical distributions ----------------------------------------------------------
+struct RowNorm {
+  float m;   // max of logits / T
+  float z;   // normaliser (from the fixed-point sum)
+  int ok;    // 0: NaN / +inf / all -inf
+};
+
+template <typename T>
+__device__ __forceinline__ float scaled_logit(const T* row, int v, float temperature) {
+  return RLT_DIV(Elem<T>::to_float(row[v]), temperature);
+}
+
+template <typename T, int kThreads>
+__device__ __forceinline__ RowNorm block_normalise(const T* __restrict__ row, int vocab, float temperature,
+                                                   unsigned long long* scratch) {
+  unsigned long long best = 0ull;
+  unsigned bad = 0;
+  for (int v = threadIdx.x; v < vocab; v += kThreads) {
+    const float t = scaled_logit(row, v, temperature);
+    bad |= (t != t) || (t == INFINITY);
+    const unsigned long long key = argmax_key(t, 0);
+    best = key > best ? key : best;
+  }
+  bad = __syncthreads_or(bad);
+  best = block_max<kThreads>(best, scratch);
+  RowNorm n;
+  uint32_t bits = static_cast<uint32_t>(best >> 32);
+  bits = (bits & 0x80000000u) ? (bits & 0x7fffffffu) : ~bits;
+  n.m = __uint_as_float(bits);
+  n.ok = !bad && best != 0ull && n.m != -INFINITY;
+  n.z = 0.0f;
+  if (!n.ok) return n;
+  unsigned long long zfix = 0ull;
+  for (int v = threadIdx.x; v < vocab; v += kThreads)
+    zfix += rlt_fix_weight(rlt_expf(RLT_SUB(scaled_logit(row, v, temperature), n.m)));
+  n.z = rlt_fix_to_float(block_sum<kThreads>(zfix, scratch));
+  return n;
+}
+
+template <typename T>
+__device__ __forceinline__ float prob_at(const T* row, int v, float temperature, const RowNorm& n) {
+  return RLT_DIV(rlt_expf(RLT_SUB(scaled_logit(row, v, temperature), n.m)), n.z);
+}
+
+template <typename T>
+__device__ __forceinline__ unsigned long long draw_weight(const T* prow, const RowNorm& pn, const T* qrow,
+                                                          const RowNorm& qn, bool residual, int v,
+                                                          float temperature) {
+  float mass = prob_at(prow, v, temperature, pn);
+  if (residual) mass = RLT_SUB(mass, prob_at(qrow, v, temperature, qn));
+  return rlt_fix_weight(mass);
+}
+
+// Inverse-CDF draw over fixed-point weights in ascending token index; -1 if the mass is zero.
+// Thread t owns the contiguous tokens [t*span, (t+1)*span).
+template <typename T, int kThreads>
+__device__ __forceinline__ int block_draw(const T* __restrict__ prow, const RowNorm& pn,
+                                          const T* __restrict__ qrow, const RowNorm& qn, bool residual,
+                                          int vocab, float temperature, float u, unsigned long long* scratch,
+                                          int* token_slot) {
+  const int span = (vocab + kThreads - 1) / kThreads;
+  const int begin = min(static_cast<int>(threadIdx.x) * span, vocab), end = min(begin + span, vocab);
+  unsigned long long local = 0ull;
+  for (int v = begin; v < end; ++v) local += draw_weight(prow, pn, qrow, qn, residual, v, temperature);
+  // exclusive scan over threads: inclusive warp scan, then warp totals
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned long long inc = local;
+#pragma unroll
+  for (int x = 1; x < 32; x <<= 1) {
+    const unsigned long long o = __shfl_up_sync(0xffffffffu, inc, x);
+    if (lane >= x) inc += o;
+  }
+  __syncthreads();
+  if (lane == 31) scratch[warp] = inc;
+  if (threadIdx.x == 0) *token_slot = -1;
+  __syncthreads();
+  unsigned long long before = 0ull, total = 0ull;
+  for (int w = 0; w < kThreads / 32; ++w) {
+    const unsigned long long s = scratch[w];
+    if (w < warp) before += s;
+    total += s;
+  }
+  if (total != 0ull) {
+    const unsigned long long threshold = rlt_draw_threshold(u, total);
+    unsigned long long prefix = before + inc - local;
+    if (prefix <= threshold && threshold < prefix + local) {
+      for (int v = begin; v < end; ++v) {
+        prefix += draw_weight(prow, pn, qrow, qn, residual, v, temperature);
+        if (prefix > threshold) { *token_slot = v; break; }
+      }
+    }
+  }
+  __syncthreads();
+  return *token_slot;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kSampleThreads)
+sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
+                   const float* __restrict__ temperature, const float* __restrict__ uniforms,
+                   int64_t* __restrict__ tokens, int32_t* __restrict__ status) {
+  __shared__ unsigned long long scratch[32];
+  __shared__ int token_slot;
+  const int r = blockIdx.x;
+  const T* row = logits + static_cast<int64_t>(r) * row_stride;
+  const float temp = temperature[r];
+  int st = RLT_ROW_OK;
+  int token = -1;
+  if (temp == 0.0f) {
+    token = block_argmax<T, kSampleThreads>(row, vocab, scratch);
+  } else {
+    const RowNorm n = block_normalise<T, kSampleThreads>(row, vocab, temp, scratch);
+    if (!n.ok) {
+      st = RLT_ROW_BAD_LOGITS;
+    } else {
+      token = block_draw<T, kSampleThreads>(row, n, row, n, false, vocab, temp, uniforms[r], scratch, &token_slot);
+      if (token < 0) st = RLT_ROW_INVALID_RESIDUAL;
+    }
+  }
+  if (threadIdx.x == 0) { tokens[r] = token; status[r] = st; }
+}
+
+// One CTA per request; rows of the request are examined in order and the walk stops at the
+// first rejection, so only the rows that decide the outcome are read.
+template <typename T>
+__global__ void __launch_bounds__(kSampleThreads)
+accept_rejection_kernel(const T* __restrict__ target_logits, const T* __restrict__ draft_logits,
+                        int64_t row_stride, int rows, int vocab, const int32_t* __restrict__ cu_rows, int n,
+                        const int64_t* __restrict__ tokens, int tokens_width,
+                        const int64_t* __restrict__ starts, const float* __restrict__ temperature,
+                        const float* __restrict__ u_accept, const float* __restrict__ u_final,
+                        const int64_t* __restrict__ slots, int64_t* __restrict__ slot_values,
+                        int64_t* __restrict__ result, int32_t* __restrict__ status) {
+  __shared__ unsigned long long scratch[32];
+  __shared__ int token_slot;
+  const int i = blockIdx.x;
+  const int a = cu_rows[i], c = cu_rows[i + 1] - a;
+  const int64_t* tok = tokens + static_cast<int64_t>(i) * tokens_width;
+  const float temp = temperature[i];
+  for (int j = threadIdx.x; j < c; j += kSampleThreads) result[a + j] = -1;
+  __syncthreads();
+
+  int accepted = 0, st = RLT_ROW_OK;
+  int64_t final_token = -1;
+  if (temp == 0.0f) {
+    for (int j = 0; j < c; ++j) {
+      const int target = block_argmax<T, kSampleThreads>(target_logits + static_cast<int64_t>(a + j) * row_stride,
+                                                         vocab, scratch);
+      if (threadIdx.x == 0) result[a + j] = target;
+      final_token = target;
+      if (j < c - 1 && tok[j + 1] == target) { ++accepted; continue; }
+      break;
+    }
+  } else {
+    int j = 0;
+    for (; j < c - 1; ++j) {
+      const T* prow = target_logits + static_cast<int64_t>(a + j) * row_stride;
+      const T* qrow = draft_logits + static_cast<int64_t>(a + j) * row_stride;
+      const int64_t d = tok[j + 1];
+      const RowNorm pn = block_normalise<T, kSampleThreads>(prow, vocab, temp, scratch);
+      const RowNorm qn = block_normalise<T, kSampleThreads>(qrow, vocab, temp, scratch);
+      if (!pn.ok || !qn.ok || d < 0 || d >= vocab) { st = RLT_ROW_BAD_LOGITS; break; }
+      const float qd = prob_at(qrow, static_cast<int>(d), temp, qn);
+      const float pd = prob_at(prow, static_cast<int>(d), temp, pn);
+      if (!(qd > 0.0f)) { st = RLT_ROW_ZERO_PROPOSAL; break; }
+      if (RLT_MUL(u_accept[a + j], qd) < pd) {
+        if (threadIdx.x == 0) result[a + j] = d;
+        ++accepted;
+        continue;
+      }
+      final_token = block_draw<T, kSampleThreads>(prow, pn, qrow, qn, true, vocab, temp, u_final[i], scratch,
+                                                  &token_slot);
+      if (final_token < 0) st = RLT_ROW_INVALID_RESIDUAL;
+      break;
+    }
+    if (st == RLT_ROW_OK && j == c - 1) {
+      const T* prow = target_logits + static_cast<int64_t>(a + c - 1) * row_stride;
+      const RowNorm pn = block_normalise<T, kSampleThreads>(prow, vocab, temp, scratch);
+      if (!pn.ok) {
+        st = RLT_ROW_BAD_LOGITS;
+      } else {
+        final_token = block_draw<T, kSampleThreads>(prow, pn, prow, pn, false, vocab, temp, u_final[i], scratch,
+                                                    &token_slot);
+        if (final_token < 0) st = RLT_ROW_INVALID_RESIDUAL;
+      }
+    }
+  }
+  if (threadIdx.x == 0) {
+    if (temp != 0.0f && st == RLT_ROW_OK) result[a + accepted] = final_token;
+    const int64_t next_pos = starts[i] + accepted + 1;
+    result[rows + i] = accepted;
+    result[rows + n + i] = next_pos;
+    status[i] = st;
+    if (slots != nullptr && slot_values != nullptr) {
+      slot_values[2 * slots[i]] = final_token;
+      slot_values[2 * slots[i] + 1] = next_pos;
+    }
+  }
+}
+
+int check_logits(const void* logits, int64_t row_stride, int rows, int vocab, int dtype) {
+  RLT_REQUIRE(dtype_valid(dtype), "acceptance: logits must be float32, float16 or bfloat16");
+  RLT_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "acceptance: invalid logits shape");
+  RLT_REQUIRE(rows == 0 || logits != nullptr, "acceptance: null logits");
+  return RLT_OK;
+}
+
+}  // namespace
+}  // namespace rlt
+
+extern "C" RLT_API int rlt_argmax_rows(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
+                               int64_t* targets, rlt_stream_t stream) {
+  using namespace rlt;
+  int status = check_logits(logits, row_stride, rows, vocab, dtype);
+  if (status != RLT_OK || rows == 0) return status;
+  RLT_REQUIRE(targets != nullptr, "argmax_rows: null output");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RLT_DISPATCH_DTYPE(dtype, T, (argmax_rows_kernel<T><<<rows, kArgmaxThreads, 0, s>>>(
+                                   static_cast<const T*>(logits), row_stride, vocab, targets)));
+  return launch_status("argmax_rows_kernel");
+}
+
+extern "C" RLT_API int rlt_accept_greedy(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
+                                 const int32_t* cu_rows, int n, const int64_t* tokens, int tokens_width,
+                                 const int64_t* starts, const int64_t* slots, int64_t* slot_values,
+                                 int64_t* result, rlt_stream_t stream) {
+  using namespace rlt;
+  int status = check_logits(logits, row_stride, rows, vocab, dtype);
+  if (status != RLT_OK) return status;
+  RLT_REQUIRE(n >= 0 && tokens_width >= 1, "accept_greedy: invalid request count or token width");
+  if (n == 0 && rows == 0) return RLT_OK;
+  RLT_REQUIRE(cu_rows && tokens && starts && result, "accept_greedy: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (rows > 0) {
+    RLT_DISPATCH_DTYPE(dtype, T, (argmax_rows_kernel<T><<<rows, kArgmaxThreads, 0, s>>>(
+                                     static_cast<const T*>(logits), row_stride, vocab, result)));
+    status = launch_status("argmax_rows_kernel");
+    if (status != RLT_OK) return status;
+  }
+  if (n > 0) {
+    greedy_finish_kernel<<<(n + 127) / 128, 128, 0, s>>>(cu_rows, n, rows, tokens, tokens_width, starts, slots,
+                                                         slot_values, result);
+    status = launch_status("greedy_finish_kernel");
+  }
+  return status;
+}
+
+extern "C" RLT_API int rlt_sample_rows(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
+                               const float* temperature, const float* uniforms, int64_t* tokens,
+                               int32_t* status_out, rlt_stream_t stream) {
+  using namespace rlt;
+  int status = check_logits(logits, row_stride, rows, vocab, dtype);
+  if (status != RLT_OK || rows == 0) return status;
+  RLT_REQUIRE(temperature && uniforms && tokens && status_out, "sample_rows: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RLT_DISPATCH_DTYPE(dtype, T, (sample_rows_kernel<T><<<rows, kSampleThreads, 0, s>>>(
+                                   static_cast<const T*>(logits), row_stride, vocab, temperature, uniforms,
+                                   tokens, status_out)));
+  return launch_status("sample_rows_kernel");
+}
+
+extern "C" RLT_API int rlt_accept_rejection(const void* target_logits, const void* draft_logits, int64_t row_stride,
+                                    int rows, int vocab, int dtype, const int32_t* cu_rows, int n,
+                                    const int64_t* tokens, int tokens_width, const int64_t* starts,
+                                    const float* temperature, const float* u_accept, const float* u_final,
+                                    const int64_t* slots, int64_t* slot_values, int64_t* result,
+                                    int32_t* status_out, rlt_stream_t stream) {
+  using namespace rlt;
+  int status = check_logits(target_logits, row_stride, rows, vocab, dtype);
+  if (status != RLT_OK) return status;
+  RLT_REQUIRE(n >= 0 && tokens_width >= 1, "accept_rejection: invalid request count or token width");
+  if (n == 0) return RLT_OK;
+  RLT_REQUIRE(draft_logits && cu_rows && tokens && starts && temperature && u_accept && u_final && result &&
+                  status_out,
+              "accept_rejection: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RLT_DISPATCH_DTYPE(dtype, T, (accept_rejection_kernel<T><<<n, kSampleThreads, 0, s>>>(
+                                   static_cast<const T*>(target_logits), static_cast<const T*>(draft_logits),
+                                   row_stride, rows, vocab, cu_rows, n, tokens, tokens_width, starts, temperature,
+                                   u_accept, u_final, slots, slot_values, result, status_out)));
+  return launch_status("accept_rejection_kernel");
+}

@@ -1,0 +1,63 @@
+// Argument block and row addressing shared by the attention kernels.
+#pragma once
+
+#include "common.cuh"
+
+namespace rlt {
+
+struct AttentionArgs {
+  const void* q;
+  void* out;
+  const void* key_cache;
+  const void* value_cache;
+  int64_t block_stride;   // elements between consecutive physical blocks of this layer view
+  int64_t token_stride;   // elements between consecutive tokens inside a block
+  int64_t num_blocks;
+  int block_size;
+  int q_heads;
+  int kv_heads;
+  int head_dim;
+  int dtype;
+  const int32_t* block_tables;  // [table_rows, table_width]
+  int table_rows;
+  int table_width;
+  const int32_t* context_lengths;
+  const int32_t* cu_seqlens_q;  // nullptr: one table row per query row
+  int rows;
+};
+
+// Table row and number of visible keys of query row `row`.
+// Unpacked: its own table row and context length.  Packed: the sequence s that contains
+// the row, and context_lengths[s] - n_s + i + 1 for its i-th of n_s rows.
+__device__ __forceinline__ void resolve_row(const AttentionArgs& a, int row, int* table_row, int* len) {
+  if (a.cu_seqlens_q == nullptr) {
+    *table_row = row;
+    *len = a.context_lengths[row];
+    return;
+  }
+  int lo = 0, hi = a.table_rows - 1;  // last s with cu[s] <= row
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (a.cu_seqlens_q[mid] <= row) lo = mid; else hi = mid - 1;
+  }
+  const int first = a.cu_seqlens_q[lo], count = a.cu_seqlens_q[lo + 1] - first;
+  *table_row = lo;
+  const int n = a.context_lengths[lo] - count + (row - first) + 1;
+  *len = n > 0 ? n : 0;
+}
+
+// attention_generic.cu: any shape, one CTA per (row, head).
+int launch_attention_generic(const AttentionArgs& a, cudaStream_t stream);
+
+// attention_sm100.cu: head_dim 128, 16-token pages, fp16/bf16 — TMA page streaming,
+// request-grouped rows on tensor cores, split-KV with a deterministic merge.
+bool attention_sm100_supported(const AttentionArgs& a);
+size_t attention_sm100_workspace_bytes(int rows, int q_heads, int kv_heads, int head_dim,
+                                       int block_size, int table_width);
+int launch_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes,
+                           cudaStream_t stream);
+// Synchronous read-back of the workspace header of the last tiled call:
+// {work items planned, work items claimed, error bits, 0}.
+int attention_sm100_read_status(const void* workspace, cudaStream_t stream, unsigned* out4);
+
+}  // namespace rlt

@@ -1,0 +1,143 @@
+// SiLU-and-Mul for the Ouro MLP: out = T(silu_f32(gate)) * up.
+//
+// Pure streaming op (3 * n * sizeof(T) bytes of traffic, ~12 flops per element), so the
+// kernel is built around memory-level parallelism: every thread keeps four independent
+// 16-byte loads of each input in flight, inputs are read with the streaming (evict-first)
+// policy because they are dead after this op, and the output is stored with the default
+// policy so the down-projection GEMM that follows finds it in L2.  One launch covers the
+// vector body and the scalar edges (unaligned head, tail).
+//
+// Arithmetic contract (bit-exact with F.silu(gate) * up on the same GPU):
+//   silu(x) = x / (1 + expf(-x)) in fp32, rounded to T, then one multiply in T.
+#include "common.cuh"
+
+namespace rlt {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+
+template <typename T> struct Pack;  // 16 bytes of T
+
+template <> struct Pack<float> {
+  __device__ __forceinline__ static uint4 apply(uint4 g, uint4 u) {
+    float4 gf = *reinterpret_cast<float4*>(&g), uf = *reinterpret_cast<float4*>(&u), o;
+    o.x = __fmul_rn(silu_f32(gf.x), uf.x);
+    o.y = __fmul_rn(silu_f32(gf.y), uf.y);
+    o.z = __fmul_rn(silu_f32(gf.z), uf.z);
+    o.w = __fmul_rn(silu_f32(gf.w), uf.w);
+    return *reinterpret_cast<uint4*>(&o);
+  }
+  __device__ __forceinline__ static float scalar(float g, float u) { return __fmul_rn(silu_f32(g), u); }
+};
+
+template <> struct Pack<__half> {
+  __device__ __forceinline__ static uint32_t pair(uint32_t g, uint32_t u) {
+    float2 gf = __half22float2(*reinterpret_cast<__half2*>(&g));
+    __half2 act = __floats2half2_rn(silu_f32(gf.x), silu_f32(gf.y));
+    __half2 r = __hmul2(act, *reinterpret_cast<__half2*>(&u));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  __device__ __forceinline__ static uint4 apply(uint4 g, uint4 u) {
+    return make_uint4(pair(g.x, u.x), pair(g.y, u.y), pair(g.z, u.z), pair(g.w, u.w));
+  }
+  __device__ __forceinline__ static __half scalar(__half g, __half u) {
+    return __hmul(__float2half_rn(silu_f32(__half2float(g))), u);
+  }
+};
+
+template <> struct Pack<__nv_bfloat16> {
+  __device__ __forceinline__ static uint32_t pair(uint32_t g, uint32_t u) {
+    float2 gf = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&g));
+    __nv_bfloat162 act = __floats2bfloat162_rn(silu_f32(gf.x), silu_f32(gf.y));
+    __nv_bfloat162 r = __hmul2(act, *reinterpret_cast<__nv_bfloat162*>(&u));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  __device__ __forceinline__ static uint4 apply(uint4 g, uint4 u) {
+    return make_uint4(pair(g.x, u.x), pair(g.y, u.y), pair(g.z, u.z), pair(g.w, u.w));
+  }
+  __device__ __forceinline__ static __nv_bfloat16 scalar(__nv_bfloat16 g, __nv_bfloat16 u) {
+    return __hmul(__float2bfloat16_rn(silu_f32(__bfloat162float(g))), u);
+  }
+};
+
+// head: leading elements handled one by one so that the vector body starts 16-byte aligned
+// in all three arrays (head == n sends everything through the scalar loop).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+silu_and_mul_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out,
+                    int64_t n, int64_t head) {
+  constexpr int kElems = 16 / sizeof(T);
+  const int64_t nvec = (n - head) / kElems;
+  const int64_t tail_start = head + nvec * kElems;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * kThreads;
+
+  const uint4* gv = reinterpret_cast<const uint4*>(gate + head);
+  const uint4* uv = reinterpret_cast<const uint4*>(up + head);
+  uint4* ov = reinterpret_cast<uint4*>(out + head);
+  for (int64_t base = tid; base < nvec; base += nthreads * kUnroll) {
+    uint4 g[kUnroll], u[kUnroll];
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      int64_t i = base + j * nthreads;
+      if (i < nvec) { g[j] = __ldcs(gv + i); u[j] = __ldcs(uv + i); }
+    }
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      int64_t i = base + j * nthreads;
+      if (i < nvec) ov[i] = Pack<T>::apply(g[j], u[j]);
+    }
+  }
+  const int64_t edges = head + (n - tail_start);
+  for (int64_t e = tid; e < edges; e += nthreads) {
+    int64_t i = e < head ? e : tail_start + (e - head);
+    out[i] = Pack<T>::scalar(gate[i], up[i]);
+  }
+}
+
+template <typename T>
+int launch(const void* gate, const void* up, void* out, int64_t n, cudaStream_t stream) {
+  constexpr int kElems = 16 / sizeof(T);
+  DeviceInfo info;
+  int status = current_device_info(&info);
+  if (status != RLT_OK) return status;
+  const uintptr_t ga = reinterpret_cast<uintptr_t>(gate) & 15u;
+  const uintptr_t ua = reinterpret_cast<uintptr_t>(up) & 15u;
+  const uintptr_t oa = reinterpret_cast<uintptr_t>(out) & 15u;
+  int64_t head = n;  // all scalar unless the three arrays share one misalignment
+  if (ga == ua && ga == oa && ga % sizeof(T) == 0) {
+    head = ga == 0 ? 0 : static_cast<int64_t>((16 - ga) / sizeof(T));
+    if (head > n) head = n;
+  }
+  const int64_t nvec = (n - head) / kElems;
+  const int64_t scalar_work = n - nvec * kElems;
+  int64_t work = (nvec + kUnroll - 1) / kUnroll;
+  if (scalar_work > work) work = scalar_work;
+  int64_t blocks = (work + kThreads - 1) / kThreads;
+  const int64_t cap = static_cast<int64_t>(info.sm_count) * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  silu_and_mul_kernel<T><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(
+      static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<T*>(out), n, head);
+  return launch_status("silu_and_mul_kernel");
+}
+
+}  // namespace
+}  // namespace rlt
+
+extern "C" RLT_API int rlt_silu_and_mul(const void* gate, const void* up, void* out, int64_t n, int dtype,
+                                rlt_stream_t stream) {
+  using namespace rlt;
+  RLT_REQUIRE(dtype_valid(dtype), "silu_and_mul supports float32, float16 and bfloat16");
+  RLT_REQUIRE(n >= 0, "silu_and_mul: negative element count");
+  if (n == 0) return RLT_OK;
+  RLT_REQUIRE(gate && up && out, "silu_and_mul: null pointer");
+  RLT_REQUIRE(out != gate && out != up, "silu_and_mul: output must not alias an input");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int status = RLT_OK;
+  RLT_DISPATCH_DTYPE(dtype, T, status = launch<T>(gate, up, out, n, s));
+  return status;
+}

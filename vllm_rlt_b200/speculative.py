@@ -1,0 +1,189 @@
+"""Acceptance side of the verify step: argmax, greedy acceptance, draws, rejection sampling.
+
+Host-side mirror of ``greedy_accept`` / ``rejection_sample`` (``vllm_rlt/worker/speculative.py:32-63``),
+of the device acceptance ``AsyncSpeculativeRunner._accept_and_update_state``
+(``vllm_rlt/worker/async_speculative.py:417-447``) and of ``Sampler.sample``
+(``vllm_rlt/worker/sampler.py:62-81``), batched over requests and with explicit uniforms
+in place of a ``torch.Generator``.
+
+Verification rows are request-major: request ``i`` owns rows ``cu_rows[i] .. cu_rows[i+1]-1``.
+``tokens[i, 0]`` is the committed input token, ``tokens[i, 1:c_i]`` its drafts.  The result
+buffer has the reference's wire layout (async_speculative.py:62-77):
+``[per-row tokens (rows) | accepted (n) | next_position (n)]``, int64.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _capi
+
+
+@dataclass
+class SpeculativeResult:
+    """Same fields as ``vllm_rlt/worker/output.py:20-25``."""
+
+    token_ids: list
+    accepted_count: int
+    kv_frontier: int | None = None
+
+
+def _check_logits(logits):
+    if logits.dim() != 2 or logits.stride(1) != 1 or logits.dtype not in _capi.DTYPE_CODES:
+        raise ValueError("logits must be [rows, vocab] float32/float16/bfloat16 with unit inner stride")
+
+
+def _check_round(rows, cu_rows, tokens, starts, slots, slot_values):
+    n = cu_rows.numel() - 1
+    if cu_rows.dtype != torch.int32 or cu_rows.dim() != 1 or n < 0:
+        raise ValueError("cu_rows must be int32 [requests + 1]")
+    if tokens.dtype != torch.int64 or tokens.dim() != 2 or tokens.shape[0] != n or not tokens.is_contiguous():
+        raise ValueError("tokens must be contiguous int64 [requests, width]")
+    if starts.dtype != torch.int64 or starts.shape != (n,):
+        raise ValueError("starts must be int64 [requests]")
+    if (slots is None) != (slot_values is None):
+        raise ValueError("slots and slot_values go together")
+    if slots is not None:
+        if slots.dtype != torch.int64 or slots.shape != (n,):
+            raise ValueError("slots must be int64 [requests]")
+        if slot_values.dtype != torch.int64 or slot_values.dim() != 2 or slot_values.shape[1] != 2 \
+                or not slot_values.is_contiguous():
+            raise ValueError("slot_values must be contiguous int64 [slots, 2]")
+    return n
+
+
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    """``logits.argmax(-1)`` (lowest index on ties) as int64 on the device."""
+    _capi.require_cuda(logits)
+    _check_logits(logits)
+    targets = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+    if logits.shape[0] == 0:
+        return targets
+    with torch.cuda.device(logits.device):
+        status = _capi.load().rlt_argmax_rows(_capi.ptr(logits), logits.stride(0), logits.shape[0],
+                                              logits.shape[1], _capi.DTYPE_CODES[logits.dtype],
+                                              _capi.ptr(targets), _capi.stream_of(logits))
+    _capi.check(status, "argmax_rows")
+    return targets
+
+
+def accept_greedy(logits, cu_rows, tokens, starts, slots=None, slot_values=None, result=None):
+    """Greedy acceptance of a whole round on the device; returns the int64 wire buffer.
+
+    ``result[:rows]`` are the target ids of every verification row, ``result[rows:rows+n]``
+    the accepted counts, ``result[rows+n:]`` the next positions; ``slot_values[slots[i]]``
+    receives ``(next_token, next_position)``.  No generator is touched.
+    """
+    _capi.require_cuda(logits, cu_rows, tokens, starts, slots, slot_values, result)
+    _check_logits(logits)
+    rows = logits.shape[0]
+    n = _check_round(rows, cu_rows, tokens, starts, slots, slot_values)
+    if result is None:
+        result = torch.empty(rows + 2 * n, dtype=torch.int64, device=logits.device)
+    elif result.dtype != torch.int64 or result.numel() < rows + 2 * n or not result.is_contiguous():
+        raise ValueError("result must be contiguous int64 with at least rows + 2 * requests elements")
+    if n == 0:
+        return result
+    with torch.cuda.device(logits.device):
+        status = _capi.load().rlt_accept_greedy(
+            _capi.ptr(logits), logits.stride(0), rows, logits.shape[1], _capi.DTYPE_CODES[logits.dtype],
+            _capi.ptr(cu_rows.contiguous()), n, _capi.ptr(tokens), tokens.shape[1], _capi.ptr(starts.contiguous()),
+            _capi.ptr(slots), _capi.ptr(slot_values), _capi.ptr(result), _capi.stream_of(logits))
+    _capi.check(status, "accept_greedy")
+    return result
+
+
+def sample_rows(logits, temperature, uniforms):
+    """One draw per row from ``softmax(logits / temperature)``; temperature 0 is argmax.
+
+    Returns ``(tokens int64 [rows], status int32 [rows])``.
+    """
+    _capi.require_cuda(logits, temperature, uniforms)
+    _check_logits(logits)
+    rows = logits.shape[0]
+    for name, t in (("temperature", temperature), ("uniforms", uniforms)):
+        if t.dtype != torch.float32 or t.shape != (rows,):
+            raise ValueError(f"{name} must be float32 [rows]")
+    tokens = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    status = torch.zeros(rows, dtype=torch.int32, device=logits.device)
+    if rows == 0:
+        return tokens, status
+    with torch.cuda.device(logits.device):
+        code = _capi.load().rlt_sample_rows(
+            _capi.ptr(logits), logits.stride(0), rows, logits.shape[1], _capi.DTYPE_CODES[logits.dtype],
+            _capi.ptr(temperature.contiguous()), _capi.ptr(uniforms.contiguous()), _capi.ptr(tokens),
+            _capi.ptr(status), _capi.stream_of(logits))
+    _capi.check(code, "sample_rows")
+    return tokens, status
+
+
+def accept_rejection(target_logits, draft_logits, cu_rows, tokens, starts, temperature, u_accept, u_final,
+                     slots=None, slot_values=None, result=None):
+    """Rejection-sampling acceptance of a whole round; returns ``(result, status)``.
+
+    ``result[cu_rows[i] : cu_rows[i] + accepted_i + 1]`` are request i's emitted tokens (its
+    other rows hold -1); ``status[i]`` is 0, or 1 (zero proposal probability: ``ValueError`` in
+    the reference), 2 (invalid residual mass: ``RuntimeError``), 3 (NaN / +inf logits).
+    Use ``raise_for_status`` to turn them into those exceptions after the one host read of a
+    round.  ``temperature[i] == 0`` takes the greedy branch for that request.
+    """
+    _capi.require_cuda(target_logits, draft_logits, cu_rows, tokens, starts, temperature, u_accept, u_final,
+                       slots, slot_values, result)
+    _check_logits(target_logits)
+    _check_logits(draft_logits)
+    if target_logits.shape != draft_logits.shape or target_logits.stride() != draft_logits.stride() \
+            or target_logits.dtype != draft_logits.dtype:
+        raise ValueError("target and draft logits must share shape, strides and dtype")
+    rows = target_logits.shape[0]
+    n = _check_round(rows, cu_rows, tokens, starts, slots, slot_values)
+    for name, t, count in (("temperature", temperature, n), ("u_accept", u_accept, rows), ("u_final", u_final, n)):
+        if t.dtype != torch.float32 or t.shape != (count,):
+            raise ValueError(f"{name} must be float32 [{count}]")
+    if result is None:
+        result = torch.empty(rows + 2 * n, dtype=torch.int64, device=target_logits.device)
+    status = torch.zeros(n, dtype=torch.int32, device=target_logits.device)
+    if n == 0:
+        return result, status
+    with torch.cuda.device(target_logits.device):
+        code = _capi.load().rlt_accept_rejection(
+            _capi.ptr(target_logits), _capi.ptr(draft_logits), target_logits.stride(0), rows,
+            target_logits.shape[1], _capi.DTYPE_CODES[target_logits.dtype], _capi.ptr(cu_rows.contiguous()), n,
+            _capi.ptr(tokens), tokens.shape[1], _capi.ptr(starts.contiguous()),
+            _capi.ptr(temperature.contiguous()), _capi.ptr(u_accept.contiguous()),
+            _capi.ptr(u_final.contiguous()), _capi.ptr(slots), _capi.ptr(slot_values), _capi.ptr(result),
+            _capi.ptr(status), _capi.stream_of(target_logits))
+    _capi.check(code, "accept_rejection")
+    return result, status
+
+
+def raise_for_status(status_values) -> None:
+    """Raise what the reference raises for a per-request status list already on the host."""
+    for i, code in enumerate(status_values):
+        if code == _capi.ROW_ZERO_PROPOSAL:
+            raise ValueError(f"request {i}: candidate has zero proposal probability")
+        if code == _capi.ROW_INVALID_RESIDUAL:
+            raise RuntimeError(f"request {i}: invalid speculative residual probability mass")
+        if code == _capi.ROW_BAD_LOGITS:
+            raise RuntimeError(f"request {i}: non-finite logits in speculative acceptance")
+        if code == _capi.ROW_SHARED_PAGE:
+            raise ValueError(f"request {i}: cannot truncate shared prefix pages")
+        if code == _capi.ROW_BAD_POSITION:
+            raise ValueError(f"request {i}: invalid KV truncation frontier")
+
+
+def decode_result(result_host, cu_rows_host) -> tuple[list[SpeculativeResult], list[int]]:
+    """Split a round's wire buffer (already copied to the host) into per-request results.
+
+    The decoding ``SpeculativeRoundTicket.collect`` performs (async_speculative.py:122-136):
+    returns ``(results, frontiers)``.
+    """
+    n = len(cu_rows_host) - 1
+    rows = cu_rows_host[-1]
+    results = []
+    for i in range(n):
+        accepted = result_host[rows + i]
+        start = cu_rows_host[i]
+        results.append(SpeculativeResult(list(result_host[start : start + accepted + 1]), accepted))
+    return results, list(result_host[rows + n : rows + 2 * n])
