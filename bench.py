@@ -331,6 +331,40 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_attention_only(args):
+    """Profiling aid: only the verify-attention calls of `--layers` layers for `--requests` requests
+    (same shapes and seeds as the full step), timed per call with CUDA events.  Prints one JSON line."""
+    import vllm_rlt_b200 as rlt
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    work = Workload(seed=1234, requests=args.requests, layers=args.layers)
+    g = torch.Generator(device=device).manual_seed(99)
+    pool_shape = (work.total_pages, args.layers, BLOCK, HEADS, HEAD_DIM)
+    key_pool = (torch.randn(pool_shape, device=device, generator=g) * 0.5).to(torch.bfloat16)
+    value_pool = (torch.randn(pool_shape, device=device, generator=g) * 0.5).to(torch.bfloat16)
+    q = (torch.randn(args.layers, work.rows, HEADS, HEAD_DIM, device=device, generator=g) * 0.5).to(torch.bfloat16)
+    tables, lengths = work.tables.to(device), work.lengths.to(device)
+    backend = rlt.create_backend(device, torch.bfloat16, HEAD_DIM, BLOCK)
+    events = []
+    for step in range(args.warmup + args.steps):
+        for layer in range(args.layers):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            backend(q[layer], key_pool[:, layer], value_pool[:, layer], tables, lengths)
+            b.record()
+            if step >= args.warmup:
+                events.append((a, b))
+    torch.cuda.synchronize()
+    ms = statistics.mean(a.elapsed_time(b) for a, b in events)
+    peak, kind = measured_peaks()
+    algorithmic = work.algorithmic_attention_bytes()
+    print(json.dumps({"only": "attention", "requests": args.requests, "layers": args.layers, "rows": work.rows,
+                      "avg_call_ms": ms, "algorithmic_bytes": algorithmic,
+                      "achieved_gbs": algorithmic / ms / 1e6, "frac": algorithmic / ms / 1e6 / peak,
+                      "peak_kind": kind, "status": backend.kernel.last_status(device)}))
+
+
 def cpu_step_seconds(threads: int, budget_s: float):
     """Times the CPU oracle on a bounded sample of the same workload and extrapolates linearly
     to one full step.  Returns (estimated seconds per step, accepted tokens per step, sample text)."""
@@ -420,12 +454,19 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--only", default=None, choices=["attention"],
+                        help="profiling aid: run only this kernel family (not a bench line)")
+    parser.add_argument("--requests", type=int, default=REQUESTS)
+    parser.add_argument("--layers", type=int, default=LAYERS)
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the verify-step kernels have no CPU fallback")
+    if args.only == "attention":
+        run_attention_only(args)
+        return
     run_gpu(args)
 
 

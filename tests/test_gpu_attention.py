@@ -31,6 +31,17 @@ def run_gpu(kernel, q, key_pool, value_pool, layer, tables, lengths, cu=None):
     return out.cpu()
 
 
+def chunk_count(length):
+    """Python mirror of the kernel's fixed context chunking (512-token chunks up to 8192,
+    then four chunks per power-of-two octave)."""
+    if length <= 0:
+        return 0
+    if length <= 8192:
+        return -(-length // 512)
+    k = ((length - 1) >> 13).bit_length() - 1
+    return 16 + 4 * k + (length - 1 - (8192 << k)) // (2048 << k) + 1
+
+
 def check(got, want, dtype):
     tol = attention_tolerance(dtype)
     if dtype == torch.float32:
@@ -88,6 +99,30 @@ def test_tiled_kernel_matches_oracle_on_verify_shapes(kernel, dtype, layout):
     got = run_gpu(kernel, q, pool["key_pool"], pool["value_pool"], 2, pool["tables"], pool["lengths"])
     want = oracle.paged_attention(q, pool["key"], pool["value"], pool["tables"].clamp_min(0), pool["lengths"])
     check(got, want, dtype)
+    # Every group was found (its K/V is streamed once, not once per row) and no wait gave up.
+    status = kernel.last_status()
+    assert status["error"] == 0 and status["claimed"] >= status["items"]
+    assert status["items"] == sum(16 * chunk_count(max(lengths)) for lengths in row_lengths)
+
+
+def test_long_contexts_use_octave_chunks(kernel):
+    dtype = torch.bfloat16
+    row_lengths = [[8190, 8191, 8192, 8193, 8194], [20000], [40003, 40004]]
+    pool = make_pool([8194, 20000, 40004], kv_heads=2, head_dim=128, block=16, dtype=dtype, seed=13,
+                     row_lengths=row_lengths)
+    g = torch.Generator().manual_seed(14)
+    q = torch.randn(pool["tables"].shape[0], 4, 128, generator=g).to(dtype)
+    got = run_gpu(kernel, q, pool["key_pool"], pool["value_pool"], 0, pool["tables"], pool["lengths"])
+    want = oracle.paged_attention(q, pool["key"], pool["value"], pool["tables"].clamp_min(0), pool["lengths"])
+    check(got, want, dtype)
+    status = kernel.last_status()
+    assert status["error"] == 0
+    assert status["items"] == 2 * (chunk_count(8194) + chunk_count(20000) + chunk_count(40004))
+    for row in (0, 3, 5, 7):
+        one = slice(row, row + 1)
+        alone = run_gpu(kernel, q[one], pool["key_pool"], pool["value_pool"], 0, pool["tables"][one],
+                        pool["lengths"][one])
+        assert torch.equal(alone[0], got[row]), row
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -1,28 +1,34 @@
 // Verify attention for sm_100a: head_dim 128, 16-token pages, fp16 / bf16.
 //
 // Data flow
-//   plan kernel   one warp per query row: finds the rows that share a block-table row
-//                 (the k+1 rows of one request at one depth plane; k x depths rows in a
-//                 shared-plane layout), zero-fills empty rows, and the last CTA to finish
-//                 turns the groups into a work list of (group, context chunk, kv head).
-//   main kernel   persistent, 2 CTAs per SM.  A producer warp pulls work items and streams
-//                 the item's K/V pages into a ring of shared-memory stages with TMA
-//                 (cp.async.bulk.tensor, 128-byte swizzle, page id = TMA block coordinate,
-//                 so every page is read from HBM once per group, not once per row).  Four
-//                 consumer warps score up to 16 query rows against each page on tensor
-//                 cores (m16n8k16, Q in registers, K/V fragments by ldmatrix) with an fp32
-//                 online softmax, are merged in warp order, and either finish the row or
-//                 store an fp32 partial; the CTA that stores the last partial of a group
-//                 merges the chunks in chunk order.
+//   plan kernel   one warp per query row finds the rows that share a block-table row (the k+1
+//                 rows of one request at one depth plane; k x depths rows in a shared-plane
+//                 layout) and zero-fills empty rows; the last CTA to finish turns the groups
+//                 into a work list of (group, context chunk, kv head) items, full-size chunks
+//                 first and the ragged last chunk of every group at the end.
+//   main kernel   persistent, one CTA per SM, every warp an independent worker.  A warp claims
+//                 an item and streams that head's K/V pages through its own ring of shared
+//                 memory stages with TMA (cp.async.bulk.tensor, 128-byte swizzle, page id =
+//                 TMA block coordinate), always kStages-1 pages ahead of the page it is
+//                 scoring, across item boundaries.  Each page is scored for up to 16 query
+//                 rows at once on tensor cores (m16n8k16; Q in registers, K/V fragments by
+//                 ldmatrix) with an fp32 online softmax, so a page is read from HBM once per
+//                 group instead of once per row.  A row whose context fits one chunk is
+//                 finished from registers; otherwise the warp stores an fp32 partial and the
+//                 warp that stores the last partial of a group merges the chunks in chunk order.
 //
-// Batch invariance: tile -> warp assignment, chunk boundaries and both merge orders are
-// functions of absolute token positions only, and a tensor-core output row depends only on
-// its own input row, so a row's bits do not depend on its group or batch.
+// There is no cross-warp reduction and no CTA-wide barrier after start-up; the only
+// synchronisation is each warp's own mbarrier ring and one atomic per multi-chunk item.
+//
+// Batch invariance: chunk boundaries and the merge order are functions of absolute token
+// positions only, and a tensor-core output row depends only on its own input row, so a row's
+// bits do not depend on its group or batch.
 //
 // HBM traffic per call = each group's K/V once + Q + O (+ fp32 partials for contexts of more
 // than one chunk), which is what the roofline of this kernel is measured against.
 #include <cuda.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include <mutex>
 #include <type_traits>
@@ -34,21 +40,16 @@ namespace {
 
 constexpr int kHeadDim = 128;
 constexpr int kPage = 16;
-constexpr int kStages = 8;                    // ring of (K page, V page) tiles
 constexpr int kTileBytes = kPage * kHeadDim * 2;  // one page of one head: 4 KiB
-constexpr int kStageBytes = 2 * kTileBytes;
-constexpr int kConsumerWarps = 4;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;
-constexpr int kItemSlots = 4;
-constexpr int kMergeStride = 132;             // floats per merged row (128 + pad)
-constexpr int kPartialStride = 132;           // floats per stored partial: O[128], m, l, pad
-constexpr int kPlanWarps = 8;
-constexpr long long kWaitCycles = 4000000000ll;  // bounded waits (about 2 s): give up instead of hanging
+constexpr int kStageBytes = 2 * kTileBytes;       // K page + V page
+constexpr int kPartialStride = 132;               // floats per stored partial: O[128], m, l, pad
+constexpr int kPlanThreads = 1024;
+constexpr int kMaxGroupRows = 16;
+constexpr long long kWaitCycles = 4000000000ll;   // bounded waits (about 2 s): give up instead of hanging
 
 // ---- context chunks -------------------------------------------------------------------
-// Fixed, position-only chunk boundaries: eight 512-token chunks up to 4096, then every
-// power-of-two octave [4096 * 2^k, 4096 * 2^(k+1)) in four equal chunks.
+// Fixed, position-only chunk boundaries: sixteen 512-token chunks up to 8192, then every
+// power-of-two octave [8192 * 2^k, 8192 * 2^(k+1)) in four equal chunks.
 __host__ __device__ inline int floor_log2(unsigned x) {
 #ifdef __CUDA_ARCH__
   return 31 - __clz(x);
@@ -59,28 +60,29 @@ __host__ __device__ inline int floor_log2(unsigned x) {
 
 __host__ __device__ inline int chunk_count(int len) {
   if (len <= 0) return 0;
-  if (len <= 4096) return (len + 511) >> 9;
-  const int k = floor_log2(static_cast<unsigned>((len - 1) >> 12));
-  return 8 + 4 * k + (len - 1 - (4096 << k)) / (1024 << k) + 1;
+  if (len <= 8192) return (len + 511) >> 9;
+  const int k = floor_log2(static_cast<unsigned>((len - 1) >> 13));
+  return 16 + 4 * k + (len - 1 - (8192 << k)) / (2048 << k) + 1;
 }
 
 __host__ __device__ inline void chunk_range(int c, int* start, int* end) {
-  if (c < 8) {
+  if (c < 16) {
     *start = c << 9;
     *end = *start + 512;
   } else {
-    const int k = (c - 8) >> 2, j = (c - 8) & 3;
-    *start = (4096 << k) + j * (1024 << k);
-    *end = *start + (1024 << k);
+    const int k = (c - 16) >> 2, j = (c - 16) & 3;
+    *start = (8192 << k) + j * (2048 << k);
+    *end = *start + (2048 << k);
   }
 }
 
 // ---- workspace ------------------------------------------------------------------------
 struct Header {
-  unsigned item_count;
-  unsigned next_item;
-  unsigned error;      // nonzero: a bounded wait gave up (bit 0 producer, bit 1 consumer)
-  unsigned plan_done;  // CTAs of the plan kernel that finished phase 1
+  unsigned full_items;   // items of list A (full-size chunks)
+  unsigned last_items;   // items of list B (last chunk of every group)
+  unsigned next_item;    // claim counter of the main kernel
+  unsigned error;        // nonzero: a bounded wait gave up
+  unsigned plan_done;    // CTAs of the plan kernel that finished phase 1
 };
 
 struct Item {
@@ -91,7 +93,7 @@ struct Item {
 };
 
 struct Layout {
-  size_t header, row_len, row_table, link, counters, items, partials, total;
+  size_t header, row_len, row_table, link, counters, items_a, items_b, partials, total;
   int max_chunks;
 };
 
@@ -108,7 +110,8 @@ Layout make_layout(int rows, int q_heads, int kv_heads, int block_size, int tabl
   l.row_table = off; off += align256(sizeof(int) * rows);
   l.link = off; off += align256(sizeof(int) * rows);
   l.counters = off; off += align256(sizeof(unsigned) * rows * kv_heads);
-  l.items = off; off += align256(sizeof(Item) * static_cast<size_t>(rows) * kv_heads * l.max_chunks);
+  l.items_a = off; off += align256(sizeof(Item) * static_cast<size_t>(rows) * kv_heads * (l.max_chunks - 1) + 16);
+  l.items_b = off; off += align256(sizeof(Item) * static_cast<size_t>(rows) * kv_heads);
   l.partials = off;
   off += align256(sizeof(float) * kPartialStride * static_cast<size_t>(rows) * q_heads * l.max_chunks);
   l.total = off;
@@ -121,7 +124,8 @@ struct Workspace {
   int* row_table;
   int* link;
   unsigned* counters;
-  Item* items;
+  Item* items_a;
+  Item* items_b;
   float* partials;
   int max_chunks;
 };
@@ -132,9 +136,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -166,6 +167,11 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
   return p;
+}
+// Orders this thread's earlier generic-proxy accesses to shared memory before later
+// async-proxy (TMA) writes to it.
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 // One [64 dims x 16 tokens] box of one page: coordinates (element in token row, token, block).
 __device__ __forceinline__ void tma_load_page_half(uint32_t dst, const CUtensorMap* map, int x, int block,
@@ -211,19 +217,46 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
   }
 }
-__device__ __forceinline__ void consumer_barrier() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-}
 
 // ---- plan kernel ------------------------------------------------------------------------
+// Inclusive block scans over kPlanThreads threads (warp shuffles + one shared array).
+__device__ __forceinline__ int block_scan_max(int v, int* warp_totals) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int x = 1; x < 32; x <<= 1) {
+    const int o = __shfl_up_sync(0xffffffffu, v, x);
+    if (lane >= x) v = max(v, o);
+  }
+  __syncthreads();
+  if (lane == 31) warp_totals[warp] = v;
+  __syncthreads();
+  int before = -1;
+  for (int w = 0; w < warp; ++w) before = max(before, warp_totals[w]);
+  return max(v, before);
+}
+__device__ __forceinline__ unsigned long long block_scan_sum(unsigned long long v, unsigned long long* warp_totals) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int x = 1; x < 32; x <<= 1) {
+    const unsigned long long o = __shfl_up_sync(0xffffffffu, v, x);
+    if (lane >= x) v += o;
+  }
+  __syncthreads();
+  if (lane == 31) warp_totals[warp] = v;
+  __syncthreads();
+  unsigned long long before = 0;
+  for (int w = 0; w < warp; ++w) before += warp_totals[w];
+  return v + before;
+}
+
 // Rows r-1 and r are linked when both are non-empty and their table rows agree on every
 // page any of the last `cap` rows can need (that window makes agreement transitive inside
 // a group of at most `cap` rows).  Packed input states its groups through cu_seqlens_q.
 template <typename T>
-__global__ void __launch_bounds__(kPlanWarps * 32)
+__global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(AttentionArgs a, Workspace ws, int cap) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int row = blockIdx.x * kPlanWarps + warp;
+  const int row = blockIdx.x * (kPlanThreads / 32) + warp;
   if (row < a.rows) {
     int table_row, len;
     resolve_row(a, row, &table_row, &len);
@@ -235,16 +268,15 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
         if (a.cu_seqlens_q != nullptr) {
           link = prev_table == table_row;
         } else {
-          int longest = len;
-          for (int back = 1; back < cap && row - back >= 0; ++back) {
-            const int other = a.context_lengths[row - back];
-            longest = other > longest ? other : longest;
-          }
-          const int pages = (longest + a.block_size - 1) / a.block_size;
+          const int other = (lane >= 1 && lane < cap && row - lane >= 0) ? a.context_lengths[row - lane] : 0;
+          int longest = max(len, other);
+#pragma unroll
+          for (int x = 16; x > 0; x >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, x));
+          const int pages = min((longest + a.block_size - 1) / a.block_size, a.table_width);
           const int32_t* mine = a.block_tables + static_cast<int64_t>(row) * a.table_width;
           const int32_t* prev = mine - a.table_width;
           int same = 1;
-          for (int p = lane; p < pages && p < a.table_width; p += 32) same &= mine[p] == prev[p];
+          for (int p = lane; p < pages; p += 32) same &= mine[p] == prev[p];
           link = __all_sync(0xffffffffu, same);
         }
       }
@@ -261,7 +293,7 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
     for (int h = lane; h < a.kv_heads; h += 32) ws.counters[static_cast<int64_t>(row) * a.kv_heads + h] = 0;
   }
 
-  // The last CTA to get here builds the work list.
+  // The last CTA to get here builds the work lists.
   __shared__ int s_last;
   __threadfence();
   __syncthreads();
@@ -273,78 +305,75 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
   if (!s_last) return;
   __threadfence();
 
-  constexpr int kT = kPlanWarps * 32;
-  __shared__ int s_scan[kT];
-  __shared__ int s_carry_start;   // start of the run that reaches into this tile
-  __shared__ unsigned s_item_base;
-  if (threadIdx.x == 0) { s_carry_start = 0; s_item_base = 0; }
-  __syncthreads();
-  volatile int* vlink = ws.link;
-  volatile int* vlen = ws.row_len;
-  for (int base = 0; base < a.rows; base += kT) {
+  __shared__ int s_link[kPlanThreads + kMaxGroupRows];
+  __shared__ int s_len[kPlanThreads + kMaxGroupRows];
+  __shared__ int s_imax[32];
+  __shared__ unsigned long long s_usum[32];
+  __shared__ int s_carry_start;
+  __shared__ unsigned s_base_full, s_base_last;
+  if (threadIdx.x == 0) { s_carry_start = 0; s_base_full = 0; s_base_last = 0; }
+  for (int base = 0; base < a.rows; base += kPlanThreads) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < kPlanThreads + kMaxGroupRows; i += kPlanThreads) {
+      const int r = base + i;
+      s_link[i] = r < a.rows ? __ldcg(&ws.link[r]) : 0;
+      s_len[i] = r < a.rows ? __ldcg(&ws.row_len[r]) : 0;
+    }
+    __syncthreads();
     const int r = base + threadIdx.x;
     const bool in = r < a.rows;
-    const int linked = in ? vlink[r] : 0;
-    const int len = in ? vlen[r] : 0;
-    // run start of every row: max-scan of (start ? r : carry)
-    s_scan[threadIdx.x] = (in && !linked) ? r : -1;
-    __syncthreads();
-    for (int step = 1; step < kT; step <<= 1) {
-      int v = s_scan[threadIdx.x];
-      if (threadIdx.x >= step) v = max(v, s_scan[threadIdx.x - step]);
-      __syncthreads();
-      s_scan[threadIdx.x] = v;
-      __syncthreads();
-    }
-    int run_start = s_scan[threadIdx.x];
+    const int len = s_len[threadIdx.x];
+    int run_start = block_scan_max((in && !s_link[threadIdx.x]) ? r : -1, s_imax);
     if (run_start < 0) run_start = s_carry_start;
-    __syncthreads();
-    if (threadIdx.x == kT - 1) s_carry_start = run_start;
     const bool leader = in && len > 0 && ((r - run_start) % cap == 0);
     int nrows = 0, longest = 0, longest_row = r;
     if (leader) {
       nrows = 1;
       longest = len;
-      while (nrows < cap && r + nrows < a.rows && vlink[r + nrows]) {
-        const int other = vlen[r + nrows];
+      while (nrows < cap && s_link[threadIdx.x + nrows]) {  // rows beyond a.rows read as unlinked
+        const int other = s_len[threadIdx.x + nrows];
         if (other > longest) { longest = other; longest_row = r + nrows; }
         ++nrows;
       }
     }
     const int chunks = leader ? chunk_count(longest) : 0;
-    const int count = chunks * a.kv_heads;
-    // exclusive scan of item counts
-    s_scan[threadIdx.x] = count;
-    __syncthreads();
-    for (int step = 1; step < kT; step <<= 1) {
-      int v = s_scan[threadIdx.x];
-      if (threadIdx.x >= step) v += s_scan[threadIdx.x - step];
-      __syncthreads();
-      s_scan[threadIdx.x] = v;
-      __syncthreads();
-    }
-    const unsigned first = s_item_base + static_cast<unsigned>(s_scan[threadIdx.x] - count);
+    const unsigned long long mine = leader ? ((static_cast<unsigned long long>(a.kv_heads) << 32) |
+                                              static_cast<unsigned>((chunks - 1) * a.kv_heads))
+                                           : 0ull;
+    const unsigned long long inclusive = block_scan_sum(mine, s_usum);
+    const unsigned long long exclusive = inclusive - mine;
     if (leader) {
       // Pages are addressed through the table row of the group's longest member: the link
       // window guarantees every member agrees with it on all pages that member can need.
       const int table_row = __ldcg(&ws.row_table[longest_row]);
-      unsigned i = first;
-      for (int c = chunks - 1; c >= 0; --c)        // last (largest / ragged) chunks first
+      Item it;
+      it.row_start = r;
+      it.table_row = table_row;
+      Item* full = ws.items_a + s_base_full + static_cast<unsigned>(exclusive & 0xffffffffu);
+      for (int c = 0; c < chunks - 1; ++c)
         for (int h = 0; h < a.kv_heads; ++h) {
-          Item it;
-          it.row_start = r;
-          it.table_row = table_row;
           it.nrows_head = nrows | (h << 16);
           it.chunk = c;
-          ws.items[i++] = it;
+          *full++ = it;
         }
+      Item* last = ws.items_b + s_base_last + static_cast<unsigned>(exclusive >> 32);
+      for (int h = 0; h < a.kv_heads; ++h) {
+        it.nrows_head = nrows | (h << 16);
+        it.chunk = chunks - 1;
+        *last++ = it;
+      }
     }
     __syncthreads();
-    if (threadIdx.x == kT - 1) s_item_base += static_cast<unsigned>(s_scan[kT - 1]);
-    __syncthreads();
+    if (threadIdx.x == kPlanThreads - 1) {
+      s_carry_start = run_start;
+      s_base_full += static_cast<unsigned>(inclusive & 0xffffffffu);
+      s_base_last += static_cast<unsigned>(inclusive >> 32);
+    }
   }
+  __syncthreads();
   if (threadIdx.x == 0) {
-    ws.header->item_count = s_item_base;
+    ws.header->full_items = s_base_full;
+    ws.header->last_items = s_base_last;
     ws.header->next_item = 0;
     ws.header->error = 0;
     ws.header->plan_done = 0;
@@ -352,157 +381,136 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
 }
 
 // ---- main kernel ------------------------------------------------------------------------
-struct ItemSlot {
+// Per-warp view of one claimed work item.  Scalars are warp-uniform; `len` is lane-indexed
+// (lane i < nrows: visible length of group row i) and `page` holds the page id of tile
+// page_base + lane.
+struct ItemCtx {
   int valid;
   int row_start;
+  int table_row;
   int nrows;
   int kv_head;
   int chunk;
   int chunk_start;
   int ntiles;
   int group_chunks;
-  int lens[16];
+  int len;
+  int page;
+  int page_base;
 };
 
+template <int kWarps, int kStages>
 struct __align__(1024) SharedStorage {
-  unsigned char stages[kStages][kStageBytes];         // K lo | K hi | V lo | V hi, 2 KiB each
-  float merge_o[kConsumerWarps][16][kMergeStride];
-  float merge_m[kConsumerWarps][16];
-  float merge_l[kConsumerWarps][16];
-  ItemSlot slots[kItemSlots];
-  unsigned long long full[kStages];
-  unsigned long long empty[kStages];
-  unsigned long long item_full[kItemSlots];
-  unsigned long long item_empty[kItemSlots];
-  int last_flag;
+  unsigned char stages[kWarps][kStages][kStageBytes];  // per stage: K lo | K hi | V lo | V hi, 2 KiB each
+  unsigned long long full[kWarps][kStages];
 };
 
-template <bool kBF16>
-__global__ void __launch_bounds__(kThreads, 2)
+__device__ __forceinline__ ItemCtx claim_item(const AttentionArgs& a, const Workspace& ws, int lane) {
+  ItemCtx c;
+  unsigned idx = 0;
+  if (lane == 0) idx = atomicAdd(&ws.header->next_item, 1u);
+  idx = __shfl_sync(0xffffffffu, idx, 0);
+  const unsigned full = ws.header->full_items, last = ws.header->last_items;
+  c.valid = idx < full + last;
+  c.row_start = c.table_row = c.nrows = c.kv_head = c.chunk = c.chunk_start = c.ntiles = 0;
+  c.group_chunks = c.len = c.page_base = 0;
+  c.page = -1;
+  if (!c.valid) return c;
+  const Item it = idx < full ? ws.items_a[idx] : ws.items_b[idx - full];
+  c.row_start = it.row_start;
+  c.table_row = it.table_row;
+  c.nrows = it.nrows_head & 0xffff;
+  c.kv_head = it.nrows_head >> 16;
+  c.chunk = it.chunk;
+  c.len = lane < c.nrows ? ws.row_len[it.row_start + lane] : 0;
+  int longest = c.len;
+#pragma unroll
+  for (int x = 16; x > 0; x >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, x));
+  int cend;
+  chunk_range(c.chunk, &c.chunk_start, &cend);
+  const int visible = min(cend, longest) - c.chunk_start;
+  c.ntiles = visible > 0 ? (visible + kPage - 1) / kPage : 0;
+  c.group_chunks = chunk_count(longest);
+  const int32_t* table = a.block_tables + static_cast<int64_t>(c.table_row) * a.table_width + c.chunk_start / kPage;
+  c.page = lane < c.ntiles ? table[lane] : -1;
+  return c;
+}
+
+template <bool kBF16, int kWarps, int kStages>
+__global__ void __launch_bounds__(kWarps * 32, 1)
 verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                         AttentionArgs a, Workspace ws, float scale_log2) {
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
+  using Storage = SharedStorage<kWarps, kStages>;
   extern __shared__ unsigned char smem_raw[];
-  SharedStorage& sm = *reinterpret_cast<SharedStorage*>(
-      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  Storage& sm = *reinterpret_cast<Storage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gqa = a.q_heads / a.kv_heads;
+  const int g = lane >> 2, t = lane & 3;  // fragment row within 8, column pair
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&sm.full[s]), 1); mbar_init(smem_u32(&sm.empty[s]), 1); }
-    for (int s = 0; s < kItemSlots; ++s) {
-      mbar_init(smem_u32(&sm.item_full[s]), 1);
-      mbar_init(smem_u32(&sm.item_empty[s]), kConsumerWarps);
-    }
+  if (lane == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&sm.full[warp][s]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
+  __syncwarp();
+  const uint64_t policy = policy_evict_first();
+  const uint32_t stage_base = smem_u32(&sm.stages[warp][0][0]);
+  const uint32_t bar_base = smem_u32(&sm.full[warp][0]);
 
-  if (warp == kConsumerWarps) {
-    // ===================== producer warp =====================
-    const uint64_t policy = policy_evict_first();
-    unsigned tile_counter = 0;  // tiles issued so far by this CTA (ring position)
-    unsigned item_counter = 0;
-    bool failed = false;
-    for (;;) {
-      unsigned idx = 0;
-      if (lane == 0) idx = atomicAdd(&ws.header->next_item, 1u);
-      idx = __shfl_sync(0xffffffffu, idx, 0);
-      const unsigned total = ws.header->item_count;
-      const int slot = item_counter % kItemSlots;
-      const unsigned use = item_counter / kItemSlots;
-      if (use > 0 && !mbar_wait(smem_u32(&sm.item_empty[slot]), (use - 1) & 1)) { failed = true; break; }
-      if (idx >= total) {
-        if (lane == 0) { sm.slots[slot].valid = 0; mbar_arrive(smem_u32(&sm.item_full[slot])); }
-        break;
+  unsigned issued = 0, consumed = 0;  // tiles of this warp's ring
+  bool failed = false;
+  ItemCtx cur = claim_item(a, ws, lane);
+  ItemCtx nxt = cur.valid ? claim_item(a, ws, lane) : cur;
+  bool issue_in_next = false;  // the issue side has moved on to `nxt`
+  int issue_tile = 0;          // next tile of the issue side's item
+
+  // Issue side: keep every stage that is not being scored in flight.  Called when all tiles
+  // below `consumed` are finished, so tile n may go into stage n % kStages as long as
+  // n - consumed < kStages (the tile at `consumed` keeps its own stage while it is scored).
+  auto top_up = [&]() {
+    while (issued - consumed < static_cast<unsigned>(kStages)) {
+      ItemCtx& ic = issue_in_next ? nxt : cur;
+      if (!ic.valid) break;
+      if (issue_tile >= ic.ntiles) {
+        if (issue_in_next) break;  // at most one item ahead
+        issue_in_next = true;
+        issue_tile = 0;
+        continue;
       }
-      const Item it = ws.items[idx];
-      const int nrows = it.nrows_head & 0xffff, kv_head = it.nrows_head >> 16;
-      int len = (lane < nrows) ? ws.row_len[it.row_start + lane] : 0;
-      int longest = len;
-#pragma unroll
-      for (int x = 16; x > 0; x >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, x));
-      int cstart, cend;
-      chunk_range(it.chunk, &cstart, &cend);
-      const int visible = min(cend, longest) - cstart;
-      const int ntiles = visible > 0 ? (visible + kPage - 1) / kPage : 0;
-      if (lane < 16) sm.slots[slot].lens[lane] = len;
+      if (issue_tile >= ic.page_base + 32) {  // next batch of 32 page ids
+        const int32_t* table = a.block_tables + static_cast<int64_t>(ic.table_row) * a.table_width +
+                               ic.chunk_start / kPage + issue_tile;
+        ic.page = issue_tile + lane < ic.ntiles ? table[lane] : -1;
+        ic.page_base = issue_tile;
+      }
+      const int block = __shfl_sync(0xffffffffu, ic.page, issue_tile - ic.page_base);
       if (lane == 0) {
-        ItemSlot& s = sm.slots[slot];
-        s.valid = 1; s.row_start = it.row_start; s.nrows = nrows; s.kv_head = kv_head;
-        s.chunk = it.chunk; s.chunk_start = cstart; s.ntiles = ntiles;
-        s.group_chunks = chunk_count(longest);
+        const int stage = issued % kStages;
+        const uint32_t bar = bar_base + stage * 8;
+        const uint32_t dst = stage_base + stage * kStageBytes;
+        const int x0 = ic.kv_head * kHeadDim;
+        mbar_expect_tx(bar, kStageBytes);
+        tma_load_page_half(dst, &k_map, x0, block, bar, policy);
+        tma_load_page_half(dst + 2048, &k_map, x0 + 64, block, bar, policy);
+        tma_load_page_half(dst + 4096, &v_map, x0, block, bar, policy);
+        tma_load_page_half(dst + 6144, &v_map, x0 + 64, block, bar, policy);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.item_full[slot]));
-      ++item_counter;
-
-      const int32_t* table = a.block_tables + static_cast<int64_t>(it.table_row) * a.table_width + cstart / kPage;
-      const int x0 = kv_head * kHeadDim;
-      for (int tbase = 0; tbase < ntiles && !failed; tbase += 32) {
-        const int mine = tbase + lane;
-        const int page = mine < ntiles ? table[mine] : -1;
-        const int batch = min(32, ntiles - tbase);
-        for (int j = 0; j < batch; ++j) {
-          const int block = __shfl_sync(0xffffffffu, page, j);
-          if (lane == 0) {
-            const int stage = tile_counter % kStages;
-            const unsigned suse = tile_counter / kStages;
-            if (suse > 0 && !mbar_wait(smem_u32(&sm.empty[stage]), (suse - 1) & 1)) failed = true;
-            if (!failed) {
-              const uint32_t bar = smem_u32(&sm.full[stage]);
-              const uint32_t dst = smem_u32(&sm.stages[stage][0]);
-              mbar_expect_tx(bar, kStageBytes);
-              tma_load_page_half(dst, &k_map, x0, block, bar, policy);
-              tma_load_page_half(dst + 2048, &k_map, x0 + 64, block, bar, policy);
-              tma_load_page_half(dst + 4096, &v_map, x0, block, bar, policy);
-              tma_load_page_half(dst + 6144, &v_map, x0 + 64, block, bar, policy);
-            }
-          }
-          ++tile_counter;
-          failed = __shfl_sync(0xffffffffu, failed ? 1 : 0, 0) != 0;
-          if (failed) break;
-        }
-      }
-      if (failed) break;
+      ++issued;
+      ++issue_tile;
     }
-    if (failed && lane == 0) {
-      atomicOr(&ws.header->error, 1u);
-      // Tell the consumers to stop, then let copies already in flight land before the
-      // shared memory is released.
-      for (int s = 0; s < kItemSlots; ++s) sm.slots[s].valid = 0;
-      __threadfence_block();
-      for (int s = 0; s < kItemSlots; ++s) mbar_arrive(smem_u32(&sm.item_full[s]));
-      const unsigned issued = tile_counter;
-      for (unsigned n = issued > kStages ? issued - kStages : 0; n < issued; ++n)
-        mbar_wait(smem_u32(&sm.full[n % kStages]), (n / kStages) & 1);
-    }
-    return;
-  }
+  };
 
-  // ===================== consumer warps =====================
-  const int g = lane >> 2, t = lane & 3;  // fragment row within 8, column pair
-  unsigned tile_counter = 0, item_counter = 0;
-  for (;;) {
-    const int slot = item_counter % kItemSlots;
-    if (!mbar_wait(smem_u32(&sm.item_full[slot]), (item_counter / kItemSlots) & 1)) {
-      if (lane == 0) atomicOr(&ws.header->error, 2u);
-      break;
-    }
-    const ItemSlot& is = sm.slots[slot];
-    if (!is.valid) break;
-    const int row_start = is.row_start, nrows = is.nrows, kv_head = is.kv_head;
-    const int chunk = is.chunk, chunk_start = is.chunk_start, ntiles = is.ntiles;
-    const int group_chunks = is.group_chunks;
-    // fragment rows g and g+8 -> (query row, query head, visible length)
-    const int mrows = nrows * gqa;
-    const int r0 = g, r1 = g + 8;
-    const int len0 = r0 < mrows ? is.lens[r0 / gqa] : 0;
-    const int len1 = r1 < mrows ? is.lens[r1 / gqa] : 0;
-    ++item_counter;
+  while (cur.valid && !failed) {
+    const int mrows = cur.nrows * gqa;
+    const int r0 = g, r1 = g + 8;  // fragment rows -> (group row, query head)
+    const int shuffled0 = __shfl_sync(0xffffffffu, cur.len, (r0 < mrows ? r0 : 0) / gqa);
+    const int shuffled1 = __shfl_sync(0xffffffffu, cur.len, (r1 < mrows ? r1 : 0) / gqa);
+    const int len0 = r0 < mrows ? shuffled0 : 0, len1 = r1 < mrows ? shuffled1 : 0;
+    top_up();
 
-    const int64_t q0 = (static_cast<int64_t>(row_start + r0 / gqa) * a.q_heads + kv_head * gqa + r0 % gqa) * kHeadDim;
-    const int64_t q1 = (static_cast<int64_t>(row_start + r1 / gqa) * a.q_heads + kv_head * gqa + r1 % gqa) * kHeadDim;
+    const int64_t qrow0 = cur.row_start + r0 / gqa, qrow1 = cur.row_start + r1 / gqa;
+    const int qhead0 = cur.kv_head * gqa + r0 % gqa, qhead1 = cur.kv_head * gqa + r1 % gqa;
+    const int64_t q0 = (qrow0 * a.q_heads + qhead0) * kHeadDim, q1 = (qrow1 * a.q_heads + qhead1) * kHeadDim;
     const uint32_t* qp = reinterpret_cast<const uint32_t*>(a.q);
     uint32_t qa[8][4];
 #pragma unroll
@@ -518,38 +526,42 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 #pragma unroll
     for (int j = 0; j < 16; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-    bool failed = false;
 
-    for (int j = warp; j < ntiles; j += kConsumerWarps) {
-      const unsigned n = tile_counter + j;
-      const int stage = n % kStages;
-      if (!mbar_wait(smem_u32(&sm.full[stage]), (n / kStages) & 1)) { failed = true; break; }
-      const uint32_t kbase = smem_u32(&sm.stages[stage][0]);
+    for (int j = 0; j < cur.ntiles; ++j) {
+      const int stage = consumed % kStages;
+      if (!mbar_wait(bar_base + stage * 8, (consumed / kStages) & 1)) { failed = true; break; }
+      const uint32_t kbase = stage_base + stage * kStageBytes;
       const uint32_t vbase = kbase + kTileBytes;
 
-      // S = Q K^T for the 16 tokens of this page (two n8 tiles)
+      // S = Q K^T for the 16 tokens of this page (two n8 tiles, two accumulator chains each)
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       {
         const int mi = lane >> 3, token = ((mi >> 1) << 3) + (lane & 7);
+        const uint32_t row_addr = kbase + token * 128;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const int chunk16 = ((ks & 3) << 1) + (mi & 1);
-          const uint32_t addr = kbase + ((ks >> 2) << 11) + token * 128 + ((chunk16 ^ (token & 7)) << 4);
           uint32_t b[4];
-          ldmatrix_x4(addr, b);
-          mma_16816<kBF16>(s[0], qa[ks], b[0], b[1]);
-          mma_16816<kBF16>(s[1], qa[ks], b[2], b[3]);
+          ldmatrix_x4(row_addr + ((ks >> 2) << 11) + ((chunk16 ^ (token & 7)) << 4), b);
+          if (ks & 1) {
+            mma_16816<kBF16>(s2[0], qa[ks], b[0], b[1]);
+            mma_16816<kBF16>(s2[1], qa[ks], b[2], b[3]);
+          } else {
+            mma_16816<kBF16>(s[0], qa[ks], b[0], b[1]);
+            mma_16816<kBF16>(s[1], qa[ks], b[2], b[3]);
+          }
         }
       }
       // mask by each row's own length, move to the log2 domain
-      const int tok = chunk_start + j * kPage + 2 * t;
+      const int tok = cur.chunk_start + j * kPage + 2 * t;
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int pos = tok + nt * 8 + e;
-          s[nt][e] = pos < len0 ? s[nt][e] * scale_log2 : -INFINITY;
-          s[nt][2 + e] = pos < len1 ? s[nt][2 + e] * scale_log2 : -INFINITY;
+          s[nt][e] = pos < len0 ? (s[nt][e] + s2[nt][e]) * scale_log2 : -INFINITY;
+          s[nt][2 + e] = pos < len1 ? (s[nt][2 + e] + s2[nt][2 + e]) * scale_log2 : -INFINITY;
         }
       }
       float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -560,6 +572,7 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
       const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
       const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+      const bool moved = (mn0 != m0) || (mn1 != m1);
       const float al0 = fast_exp2(m0 - mu0), al1 = fast_exp2(m1 - mu1);
       m0 = mn0; m1 = mn1;
       uint32_t pa[4];
@@ -575,106 +588,118 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         pa[2] = pack2<kBF16>(p10, p11);
         pa[3] = pack2<kBF16>(p12, p13);
       }
+      // Rescale O only when some row's running maximum moved (a factor of exactly 1 otherwise).
+      if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-      for (int jn = 0; jn < 16; ++jn) { o[jn][0] *= al0; o[jn][1] *= al0; o[jn][2] *= al1; o[jn][3] *= al1; }
+        for (int jn = 0; jn < 16; ++jn) { o[jn][0] *= al0; o[jn][1] *= al0; o[jn][2] *= al1; o[jn][3] *= al1; }
+      }
       // O += P V
       {
         const int mi = lane >> 3, token = ((mi & 1) << 3) + (lane & 7);
+        const uint32_t row_addr = vbase + token * 128;
 #pragma unroll
         for (int jn = 0; jn < 16; jn += 2) {
           const int c = jn + (mi >> 1);
-          const uint32_t addr = vbase + ((c >> 3) << 11) + token * 128 + (((c & 7) ^ (token & 7)) << 4);
           uint32_t b[4];
-          ldmatrix_x4_trans(addr, b);
+          ldmatrix_x4_trans(row_addr + ((c >> 3) << 11) + (((c & 7) ^ (token & 7)) << 4), b);
           mma_16816<kBF16>(o[jn], pa, b[0], b[1]);
           mma_16816<kBF16>(o[jn + 1], pa, b[2], b[3]);
         }
       }
+      ++consumed;
+      // the stage just read is free: order our shared-memory reads before the next TMA write
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.empty[stage]));
+      if (lane == 0) fence_proxy_async();
+      top_up();
     }
-    tile_counter += ntiles;
-    if (failed) {
-      if (lane == 0) atomicOr(&ws.header->error, 2u);
-      break;
-    }
+    if (failed) break;
 
-    // ---- merge the four warps in warp order ----
+    // ---- epilogue: straight from registers ----
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    if (t == 0) {
-      sm.merge_m[warp][r0] = m0; sm.merge_l[warp][r0] = l0;
-      sm.merge_m[warp][r1] = m1; sm.merge_l[warp][r1] = l1;
-    }
+    const int chunks0 = chunk_count(len0), chunks1 = chunk_count(len1);
+    T* out = static_cast<T*>(a.out);
+    if (cur.chunk < chunks0) {
+      if (chunks0 == 1) {
+        const float inv = 1.0f / l0;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(out + q0);
 #pragma unroll
-    for (int jn = 0; jn < 16; ++jn) {
-      *reinterpret_cast<float2*>(&sm.merge_o[warp][r0][jn * 8 + 2 * t]) = make_float2(o[jn][0], o[jn][1]);
-      *reinterpret_cast<float2*>(&sm.merge_o[warp][r1][jn * 8 + 2 * t]) = make_float2(o[jn][2], o[jn][3]);
-    }
-    consumer_barrier();
-    const int d = threadIdx.x;  // one head dimension per consumer thread
-    bool stored_partial = false;
-    for (int r = 0; r < mrows; ++r) {
-      const int len = is.lens[r / gqa];
-      const int row_chunks = chunk_count(len);
-      if (chunk >= row_chunks) continue;  // this row ends before the chunk
-      float big = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) big = fmaxf(big, sm.merge_m[w][r]);
-      float acc = 0.f, total = 0.f;
-#pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) {
-        const float mw = sm.merge_m[w][r];
-        const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - big);
-        acc = fmaf(sm.merge_o[w][r][d], f, acc);
-        total = fmaf(sm.merge_l[w][r], f, total);
-      }
-      const int64_t qrow = row_start + r / gqa;
-      const int qhead = kv_head * gqa + r % gqa;
-      if (row_chunks == 1) {
-        static_cast<T*>(a.out)[(qrow * a.q_heads + qhead) * kHeadDim + d] = Elem<T>::from_float(acc / total);
+        for (int jn = 0; jn < 16; ++jn) dst[jn * 4 + t] = pack2<kBF16>(o[jn][0] * inv, o[jn][1] * inv);
       } else {
-        float* part = ws.partials + ((qrow * a.q_heads + qhead) * ws.max_chunks + chunk) * kPartialStride;
-        part[d] = acc;
-        if (d == 0) { part[kHeadDim] = big; part[kHeadDim + 1] = total; }
-        stored_partial = true;
+        float* part = ws.partials + ((qrow0 * a.q_heads + qhead0) * ws.max_chunks + cur.chunk) * kPartialStride;
+#pragma unroll
+        for (int jn = 0; jn < 16; ++jn) *reinterpret_cast<float2*>(part + jn * 8 + 2 * t) = make_float2(o[jn][0], o[jn][1]);
+        if (t == 0) { part[kHeadDim] = m0; part[kHeadDim + 1] = l0; }
       }
     }
-    // ---- the CTA that stores a group's last partial merges its chunks in chunk order ----
-    if (group_chunks > 1) {
-      (void)stored_partial;
-      __threadfence();
-      consumer_barrier();
-      if (threadIdx.x == 0) {
-        const unsigned prior = atomicAdd(&ws.counters[static_cast<int64_t>(row_start) * a.kv_heads + kv_head], 1u);
-        sm.last_flag = prior == static_cast<unsigned>(group_chunks - 1);
+    if (cur.chunk < chunks1) {
+      if (chunks1 == 1) {
+        const float inv = 1.0f / l1;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(out + q1);
+#pragma unroll
+        for (int jn = 0; jn < 16; ++jn) dst[jn * 4 + t] = pack2<kBF16>(o[jn][2] * inv, o[jn][3] * inv);
+      } else {
+        float* part = ws.partials + ((qrow1 * a.q_heads + qhead1) * ws.max_chunks + cur.chunk) * kPartialStride;
+#pragma unroll
+        for (int jn = 0; jn < 16; ++jn) *reinterpret_cast<float2*>(part + jn * 8 + 2 * t) = make_float2(o[jn][2], o[jn][3]);
+        if (t == 0) { part[kHeadDim] = m1; part[kHeadDim + 1] = l1; }
       }
-      consumer_barrier();
-      if (sm.last_flag) {
+    }
+    // ---- the warp that stores a group's last partial merges its chunks in chunk order ----
+    if (cur.group_chunks > 1) {
+      __threadfence();
+      __syncwarp();
+      unsigned prior = 0;
+      if (lane == 0) prior = atomicAdd(&ws.counters[static_cast<int64_t>(cur.row_start) * a.kv_heads + cur.kv_head], 1u);
+      prior = __shfl_sync(0xffffffffu, prior, 0);
+      if (prior == static_cast<unsigned>(cur.group_chunks - 1)) {
         __threadfence();
         for (int r = 0; r < mrows; ++r) {
-          const int row_chunks = chunk_count(is.lens[r / gqa]);
+          const int row_chunks = chunk_count(__shfl_sync(0xffffffffu, cur.len, r / gqa));
           if (row_chunks < 2) continue;
-          const int64_t qrow = row_start + r / gqa;
-          const int qhead = kv_head * gqa + r % gqa;
+          const int64_t qrow = cur.row_start + r / gqa;
+          const int qhead = cur.kv_head * gqa + r % gqa;
           const float* part = ws.partials + ((qrow * a.q_heads + qhead) * ws.max_chunks) * kPartialStride;
           float big = -INFINITY;
-          for (int c = 0; c < row_chunks; ++c) big = fmaxf(big, __ldcg(part + c * kPartialStride + kHeadDim));
-          float acc = 0.f, total = 0.f;
+          for (int c = lane; c < row_chunks; c += 32) big = fmaxf(big, __ldcg(part + c * kPartialStride + kHeadDim));
+#pragma unroll
+          for (int x = 16; x > 0; x >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, x));
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          float total = 0.f;
           for (int c = 0; c < row_chunks; ++c) {
-            const float mc = __ldcg(part + c * kPartialStride + kHeadDim);
+            const float* pc = part + c * kPartialStride;
+            const float mc = __ldcg(pc + kHeadDim);
             const float f = mc == -INFINITY ? 0.f : fast_exp2(mc - big);
-            acc = fmaf(__ldcg(part + c * kPartialStride + d), f, acc);
-            total = fmaf(__ldcg(part + c * kPartialStride + kHeadDim + 1), f, total);
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(pc) + lane);
+            acc.x = fmaf(v.x, f, acc.x); acc.y = fmaf(v.y, f, acc.y);
+            acc.z = fmaf(v.z, f, acc.z); acc.w = fmaf(v.w, f, acc.w);
+            total = fmaf(__ldcg(pc + kHeadDim + 1), f, total);
           }
-          static_cast<T*>(a.out)[(qrow * a.q_heads + qhead) * kHeadDim + d] = Elem<T>::from_float(acc / total);
+          const float inv = 1.0f / total;
+          uint2 packed;
+          packed.x = pack2<kBF16>(acc.x * inv, acc.y * inv);
+          packed.y = pack2<kBF16>(acc.z * inv, acc.w * inv);
+          reinterpret_cast<uint2*>(out + (qrow * a.q_heads + qhead) * kHeadDim)[lane] = packed;
         }
       }
     }
-    consumer_barrier();  // merge buffers and the item slot are free again
-    if (lane == 0) mbar_arrive(smem_u32(&sm.item_empty[slot]));
+
+    // ---- next item ----
+    cur = nxt;
+    if (issue_in_next) {
+      issue_in_next = false;  // the issue side is already inside the new `cur`
+    } else {
+      issue_tile = 0;
+    }
+    nxt = cur.valid ? claim_item(a, ws, lane) : cur;
+  }
+
+  if (failed) {
+    if (lane == 0) atomicOr(&ws.header->error, 1u);
+    // let copies already in flight land before the shared memory is released
+    for (unsigned n = consumed + 1; n < issued; ++n) mbar_wait(bar_base + (n % kStages) * 8, (n / kStages) & 1);
   }
 }
 
@@ -721,7 +746,18 @@ int make_page_map(CUtensorMap* map, const void* base, const AttentionArgs& a) {
   return RLT_OK;
 }
 
-int gqa_cap(const AttentionArgs& a) { return 16 / (a.q_heads / a.kv_heads); }
+int gqa_cap(const AttentionArgs& a) { return kMaxGroupRows / (a.q_heads / a.kv_heads); }
+
+template <bool kBF16, int kWarps, int kStages>
+int launch_main(const CUtensorMap& k_map, const CUtensorMap& v_map, const AttentionArgs& a, const Workspace& ws,
+                int sm_count, cudaStream_t stream) {
+  const size_t smem = sizeof(SharedStorage<kWarps, kStages>) + 1024;
+  const float scale_log2 = static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(kHeadDim)));
+  auto kernel = verify_attention_kernel<kBF16, kWarps, kStages>;
+  RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  kernel<<<sm_count, kWarps * 32, smem, stream>>>(k_map, v_map, a, ws, scale_log2);
+  return launch_status("verify_attention_kernel");
+}
 
 }  // namespace
 
@@ -737,7 +773,7 @@ bool attention_sm100_supported(const AttentionArgs& a) {
   if ((a.token_stride * 2) % 16 != 0 || (a.block_stride * 2) % 16 != 0) return false;
   if (a.block_stride < a.token_stride * kPage) return false;
   if (!aligned16(a.key_cache) || !aligned16(a.value_cache)) return false;
-  if ((reinterpret_cast<uintptr_t>(a.q) & 3u) != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(a.q) & 3u) != 0 || (reinterpret_cast<uintptr_t>(a.out) & 7u) != 0) return false;
   if (a.num_blocks > 0xffffffffll) return false;
   return true;
 }
@@ -752,7 +788,7 @@ int attention_sm100_read_status(const void* workspace, cudaStream_t stream, unsi
   Header h;
   RLT_CUDA_TRY(cudaMemcpyAsync(&h, workspace, sizeof(Header), cudaMemcpyDeviceToHost, stream));
   RLT_CUDA_TRY(cudaStreamSynchronize(stream));
-  out4[0] = h.item_count; out4[1] = h.next_item; out4[2] = h.error; out4[3] = h.plan_done;
+  out4[0] = h.full_items + h.last_items; out4[1] = h.next_item; out4[2] = h.error; out4[3] = h.plan_done;
   return RLT_OK;
 }
 
@@ -772,7 +808,8 @@ int launch_attention_sm100(const AttentionArgs& a, void* workspace, size_t works
   ws.row_table = reinterpret_cast<int*>(base + l.row_table);
   ws.link = reinterpret_cast<int*>(base + l.link);
   ws.counters = reinterpret_cast<unsigned*>(base + l.counters);
-  ws.items = reinterpret_cast<Item*>(base + l.items);
+  ws.items_a = reinterpret_cast<Item*>(base + l.items_a);
+  ws.items_b = reinterpret_cast<Item*>(base + l.items_b);
   ws.partials = reinterpret_cast<float*>(base + l.partials);
   ws.max_chunks = l.max_chunks;
 
@@ -783,32 +820,31 @@ int launch_attention_sm100(const AttentionArgs& a, void* workspace, size_t works
   if (status != RLT_OK) return status;
 
   RLT_CUDA_TRY(cudaMemsetAsync(ws.header, 0, sizeof(Header), stream));
-  const int plan_ctas = (a.rows + kPlanWarps - 1) / kPlanWarps;
+  const int plan_ctas = (a.rows + kPlanThreads / 32 - 1) / (kPlanThreads / 32);
   const int cap = gqa_cap(a);
   if (a.dtype == RLT_BF16)
-    plan_kernel<__nv_bfloat16><<<plan_ctas, kPlanWarps * 32, 0, stream>>>(a, ws, cap);
+    plan_kernel<__nv_bfloat16><<<plan_ctas, kPlanThreads, 0, stream>>>(a, ws, cap);
   else
-    plan_kernel<__half><<<plan_ctas, kPlanWarps * 32, 0, stream>>>(a, ws, cap);
+    plan_kernel<__half><<<plan_ctas, kPlanThreads, 0, stream>>>(a, ws, cap);
   status = launch_status("plan_kernel");
   if (status != RLT_OK) return status;
 
-  const size_t smem = sizeof(SharedStorage) + 1024;
-  const float scale_log2 = static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(kHeadDim)));
-  const int grid = info.sm_count * 2;
+  // Ring geometry (warps per SM x stages per warp); RLT_ATTENTION_RING selects another
+  // compiled variant for tuning runs.
+  static const int variant = [] {
+    const char* e = getenv("RLT_ATTENTION_RING");
+    return e ? atoi(e) : 0;
+  }();
   if (a.dtype == RLT_BF16) {
-    RLT_CUDA_TRY(cudaFuncSetAttribute(verify_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      static_cast<int>(smem)));
-    RLT_CUDA_TRY(cudaFuncSetAttribute(verify_attention_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                      cudaSharedmemCarveoutMaxShared));
-    verify_attention_kernel<true><<<grid, kThreads, smem, stream>>>(k_map, v_map, a, ws, scale_log2);
-  } else {
-    RLT_CUDA_TRY(cudaFuncSetAttribute(verify_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      static_cast<int>(smem)));
-    RLT_CUDA_TRY(cudaFuncSetAttribute(verify_attention_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                      cudaSharedmemCarveoutMaxShared));
-    verify_attention_kernel<false><<<grid, kThreads, smem, stream>>>(k_map, v_map, a, ws, scale_log2);
+    switch (variant) {
+      case 1: return launch_main<true, 8, 3>(k_map, v_map, a, ws, info.sm_count, stream);
+      case 2: return launch_main<true, 7, 4>(k_map, v_map, a, ws, info.sm_count, stream);
+      case 3: return launch_main<true, 5, 5>(k_map, v_map, a, ws, info.sm_count, stream);
+      case 4: return launch_main<true, 4, 6>(k_map, v_map, a, ws, info.sm_count, stream);
+      default: return launch_main<true, 6, 4>(k_map, v_map, a, ws, info.sm_count, stream);
+    }
   }
-  return launch_status("verify_attention_kernel");
+  return launch_main<false, 6, 4>(k_map, v_map, a, ws, info.sm_count, stream);
 }
 
 }  // namespace rlt
