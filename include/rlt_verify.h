@@ -136,11 +136,36 @@ RLT_API int rlt_verify_attention(const void* q, void* out, const void* key_cache
                          const int32_t* context_lengths, const int32_t* cu_seqlens_q, int rows,
                          void* workspace, size_t workspace_bytes, rlt_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * The two halves of rlt_verify_attention, for callers that score many layers against the
+ * same block tables and lengths (every layer of one recurrent depth pass shares them,
+ * vllm_rlt/models/ouro.py:283-291): plan once, run once per layer.
+ *   rlt_verify_attention_plan  groups the rows and builds the work list in `workspace`.
+ *   rlt_verify_attention_run   scores q against one layer's K/V with that plan and leaves the
+ *                              plan intact.  The block tables, lengths and packing must be the
+ *                              ones that were planned (same contents, same workspace).
+ * Both return RLT_ERR_UNSUPPORTED for shapes outside the tiled kernel (head_dim 128, 16-token
+ * pages, fp16 / bf16, GQA ratio 1/2/4/8/16); use rlt_verify_attention for those.
+ * rlt_verify_attention(...) == plan(...) followed by run(...).
+ * ---------------------------------------------------------------------- */
+RLT_API int rlt_verify_attention_plan(const int32_t* block_tables, int table_rows, int table_width,
+                              const int32_t* context_lengths, const int32_t* cu_seqlens_q, int rows,
+                              int q_heads, int kv_heads, int head_dim, int block_size, int dtype,
+                              void* workspace, size_t workspace_bytes, rlt_stream_t stream);
+
+RLT_API int rlt_verify_attention_run(const void* q, void* out, const void* key_cache, const void* value_cache,
+                             int64_t block_stride, int64_t token_stride, int64_t num_blocks,
+                             int block_size, int q_heads, int kv_heads, int head_dim, int dtype,
+                             const int32_t* block_tables, int table_rows, int table_width,
+                             const int32_t* context_lengths, const int32_t* cu_seqlens_q, int rows,
+                             void* workspace, size_t workspace_bytes, rlt_stream_t stream);
+
 /* Diagnostics for the tiled kernel (head_dim 128, 16-token pages, fp16/bf16): waits for
  * `stream` and copies four words of the workspace header to the host —
  * status4[0] = work items planned by the last call (groups x context chunks x kv heads; shows
- * whether rows were grouped), status4[1] = work items claimed, status4[2] = error bits
- * (nonzero: a bounded device-side wait gave up and the output is invalid), status4[3] = 0.
+ * whether rows were grouped), status4[1] = rows of length zero, status4[2] = error bits
+ * (nonzero: a bounded device-side wait gave up and the output is invalid), status4[3] = claim
+ * counter (0 after a clean run).
  * Synchronises; not for the hot path.  No counterpart in the reference. */
 RLT_API int rlt_verify_attention_status(const void* workspace, rlt_stream_t stream, uint32_t* status4);
 

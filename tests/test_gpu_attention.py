@@ -101,7 +101,7 @@ def test_tiled_kernel_matches_oracle_on_verify_shapes(kernel, dtype, layout):
     check(got, want, dtype)
     # Every group was found (its K/V is streamed once, not once per row) and no wait gave up.
     status = kernel.last_status()
-    assert status["error"] == 0 and status["claimed"] >= status["items"]
+    assert status["error"] == 0 and status["claim_counter"] == 0
     assert status["items"] == sum(16 * chunk_count(max(lengths)) for lengths in row_lengths)
 
 
@@ -172,6 +172,39 @@ def test_row_bits_do_not_depend_on_group_membership(kernel):
     shuffled = run_gpu(kernel, q[perm], pool["key_pool"], pool["value_pool"], 0, pool["tables"][perm],
                        pool["lengths"][perm])
     assert torch.equal(shuffled, grouped[perm])
+
+
+def test_shared_plan_runs_every_layer_with_one_plan(kernel):
+    # One plan, many runs: every layer of a pass shares block tables and lengths.  The result of
+    # each layer must equal the self-planned call bit for bit, including zero-length rows and
+    # multi-chunk rows (whose counters and claim counter must be left clean by every run).
+    dtype = torch.bfloat16
+    row_lengths = [[1290, 1291, 1292], [0], [33, 34], [513]]
+    pool = make_pool([1292, 16, 34, 513], kv_heads=16, head_dim=128, block=16, dtype=dtype, seed=21, layers=3,
+                     row_lengths=row_lengths)
+    g = torch.Generator().manual_seed(22)
+    rows = pool["tables"].shape[0]
+    qs = [(torch.randn(rows, 16, 128, generator=g) * 0.5).to(dtype).cuda() for _ in range(3)]
+    kp, vp = pool["key_pool"].cuda(), pool["value_pool"].cuda()
+    tables, lengths = pool["tables"].cuda(), pool["lengths"].cuda()
+    separate = [kernel(qs[layer], kp[:, layer], vp[:, layer], tables, lengths) for layer in range(3)]
+    with kernel.shared_plan():
+        shared = [kernel(qs[layer], kp[:, layer], vp[:, layer], tables, lengths) for layer in range(3)]
+        again = kernel(qs[0], kp[:, 0], vp[:, 0], tables, lengths)
+        status = kernel.last_status()
+    torch.cuda.synchronize()
+    for layer in range(3):
+        assert torch.equal(shared[layer], separate[layer]), layer
+    assert torch.equal(again, separate[0])
+    assert status["error"] == 0 and status["zero_rows"] == 1 and status["claim_counter"] == 0
+    assert torch.count_nonzero(shared[1][3]) == 0
+    # different lengths tensor inside the context -> replanned, not reused
+    shorter = (lengths - 1).clamp_min(0)
+    with kernel.shared_plan():
+        a = kernel(qs[0], kp[:, 0], vp[:, 0], tables, lengths)
+        b = kernel(qs[0], kp[:, 0], vp[:, 0], tables, shorter)
+    assert torch.equal(a, separate[0])
+    assert torch.equal(b, kernel(qs[0], kp[:, 0], vp[:, 0], tables, shorter))
 
 
 def test_padding_entries_are_never_dereferenced(kernel):

@@ -51,13 +51,18 @@ int launch_attention_generic(const AttentionArgs& a, cudaStream_t stream);
 
 // attention_sm100.cu: head_dim 128, 16-token pages, fp16/bf16 — TMA page streaming,
 // request-grouped rows on tensor cores, split-KV with a deterministic merge.
-bool attention_sm100_supported(const AttentionArgs& a);
+bool attention_sm100_supported(const AttentionArgs& a);        // shape and cache view
+bool attention_sm100_shape_supported(const AttentionArgs& a);  // shape only (enough to plan)
 size_t attention_sm100_workspace_bytes(int rows, int q_heads, int kv_heads, int head_dim,
                                        int block_size, int table_width);
 int launch_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes,
                            cudaStream_t stream);
+// The two halves of launch_attention_sm100: the plan depends only on the block tables, lengths
+// and packing; a run consumes it and leaves it intact for the next layer.
+int plan_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+int run_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 // Synchronous read-back of the workspace header of the last tiled call:
-// {work items planned, work items claimed, error bits, 0}.
+// {work items planned, rows of length zero, error bits, claim counter (0 after a clean run)}.
 int attention_sm100_read_status(const void* workspace, cudaStream_t stream, unsigned* out4);
 
 }  // namespace rlt

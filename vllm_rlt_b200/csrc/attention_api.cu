@@ -4,6 +4,21 @@
 namespace rlt {
 namespace {
 
+int check_metadata(const AttentionArgs& a) {
+  RLT_REQUIRE(dtype_valid(a.dtype), "verify_attention: dtype must be float32, float16 or bfloat16");
+  RLT_REQUIRE(a.rows >= 0 && a.q_heads > 0 && a.kv_heads > 0 && a.head_dim > 0 && a.block_size > 0,
+              "verify_attention: invalid shape");
+  RLT_REQUIRE(a.q_heads % a.kv_heads == 0,
+              "verify_attention: query heads must be a positive multiple of KV heads");
+  if (a.rows == 0) return RLT_OK;
+  RLT_REQUIRE(a.block_tables && a.context_lengths, "verify_attention: null pointer");
+  RLT_REQUIRE(a.table_rows > 0 && a.table_width > 0,
+              "verify_attention: block tables must be int32 [rows, pages] with pages > 0");
+  RLT_REQUIRE(a.cu_seqlens_q != nullptr || a.table_rows == a.rows,
+              "verify_attention: one block-table row per query row unless cu_seqlens_q is given");
+  return RLT_OK;
+}
+
 int check_args(const AttentionArgs& a) {
   RLT_REQUIRE(dtype_valid(a.dtype), "verify_attention: dtype must be float32, float16 or bfloat16");
   RLT_REQUIRE(a.rows >= 0 && a.q_heads > 0 && a.kv_heads > 0 && a.head_dim > 0 && a.block_size > 0,
@@ -51,6 +66,48 @@ extern "C" RLT_API int rlt_verify_attention(const void* q, void* out, const void
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (attention_sm100_supported(a)) return launch_attention_sm100(a, workspace, workspace_bytes, s);
   return launch_attention_generic(a, s);
+}
+
+extern "C" RLT_API int rlt_verify_attention_plan(const int32_t* block_tables, int table_rows, int table_width,
+                                                 const int32_t* context_lengths, const int32_t* cu_seqlens_q,
+                                                 int rows, int q_heads, int kv_heads, int head_dim, int block_size,
+                                                 int dtype, void* workspace, size_t workspace_bytes,
+                                                 rlt_stream_t stream) {
+  using namespace rlt;
+  AttentionArgs a = {};
+  a.block_tables = block_tables; a.table_rows = table_rows; a.table_width = table_width;
+  a.context_lengths = context_lengths; a.cu_seqlens_q = cu_seqlens_q; a.rows = rows;
+  a.q_heads = q_heads; a.kv_heads = kv_heads; a.head_dim = head_dim; a.block_size = block_size; a.dtype = dtype;
+  int status = check_metadata(a);
+  if (status != RLT_OK || rows == 0) return status;
+  if (!attention_sm100_shape_supported(a)) {
+    set_last_error_text("verify_attention_plan: only the tiled kernel (head_dim 128, 16-token pages, fp16/bf16) plans");
+    return RLT_ERR_UNSUPPORTED;
+  }
+  return plan_attention_sm100(a, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" RLT_API int rlt_verify_attention_run(const void* q, void* out, const void* key_cache,
+                                                const void* value_cache, int64_t block_stride, int64_t token_stride,
+                                                int64_t num_blocks, int block_size, int q_heads, int kv_heads,
+                                                int head_dim, int dtype, const int32_t* block_tables, int table_rows,
+                                                int table_width, const int32_t* context_lengths,
+                                                const int32_t* cu_seqlens_q, int rows, void* workspace,
+                                                size_t workspace_bytes, rlt_stream_t stream) {
+  using namespace rlt;
+  AttentionArgs a;
+  a.q = q; a.out = out; a.key_cache = key_cache; a.value_cache = value_cache;
+  a.block_stride = block_stride; a.token_stride = token_stride; a.num_blocks = num_blocks;
+  a.block_size = block_size; a.q_heads = q_heads; a.kv_heads = kv_heads; a.head_dim = head_dim;
+  a.dtype = dtype; a.block_tables = block_tables; a.table_rows = table_rows; a.table_width = table_width;
+  a.context_lengths = context_lengths; a.cu_seqlens_q = cu_seqlens_q; a.rows = rows;
+  int status = check_args(a);
+  if (status != RLT_OK || rows == 0) return status;
+  if (!attention_sm100_supported(a)) {
+    set_last_error_text("verify_attention_run: this shape or cache view is not covered by the tiled kernel");
+    return RLT_ERR_UNSUPPORTED;
+  }
+  return run_attention_sm100(a, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" RLT_API int rlt_verify_attention_status(const void* workspace, rlt_stream_t stream, uint32_t* status4) {

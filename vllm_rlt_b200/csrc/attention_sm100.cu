@@ -83,6 +83,8 @@ struct Header {
   unsigned next_item;    // claim counter of the main kernel
   unsigned error;        // nonzero: a bounded wait gave up
   unsigned plan_done;    // CTAs of the plan kernel that finished phase 1
+  unsigned zero_rows;    // rows of length 0 (their output is zero-filled by every run)
+  unsigned exited;       // warps of the running main kernel that have finished
 };
 
 struct Item {
@@ -93,7 +95,7 @@ struct Item {
 };
 
 struct Layout {
-  size_t header, row_len, row_table, link, counters, items_a, items_b, partials, total;
+  size_t header, row_len, row_table, link, zero_list, counters, items_a, items_b, partials, total;
   int max_chunks;
 };
 
@@ -109,6 +111,7 @@ Layout make_layout(int rows, int q_heads, int kv_heads, int block_size, int tabl
   l.row_len = off; off += align256(sizeof(int) * rows);
   l.row_table = off; off += align256(sizeof(int) * rows);
   l.link = off; off += align256(sizeof(int) * rows);
+  l.zero_list = off; off += align256(sizeof(int) * rows);
   l.counters = off; off += align256(sizeof(unsigned) * rows * kv_heads);
   l.items_a = off; off += align256(sizeof(Item) * static_cast<size_t>(rows) * kv_heads * (l.max_chunks - 1) + 16);
   l.items_b = off; off += align256(sizeof(Item) * static_cast<size_t>(rows) * kv_heads);
@@ -123,6 +126,7 @@ struct Workspace {
   int* row_len;
   int* row_table;
   int* link;
+  int* zero_list;
   unsigned* counters;
   Item* items_a;
   Item* items_b;
@@ -252,7 +256,6 @@ __device__ __forceinline__ unsigned long long block_scan_sum(unsigned long long 
 // Rows r-1 and r are linked when both are non-empty and their table rows agree on every
 // page any of the last `cap` rows can need (that window makes agreement transitive inside
 // a group of at most `cap` rows).  Packed input states its groups through cu_seqlens_q.
-template <typename T>
 __global__ void __launch_bounds__(kPlanThreads)
 plan_kernel(AttentionArgs a, Workspace ws, int cap) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -281,11 +284,8 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
         }
       }
     }
-    if (len <= 0) {  // empty row: zeros, never part of a group
-      T* out = static_cast<T*>(a.out) + static_cast<int64_t>(row) * a.q_heads * a.head_dim;
-      for (int i = lane; i < a.q_heads * a.head_dim; i += 32) out[i] = Elem<T>::from_float(0.0f);
-    }
     if (lane == 0) {
+      if (len <= 0) ws.zero_list[atomicAdd(&ws.header->zero_rows, 1u)] = row;  // empty row: never in a group
       ws.row_len[row] = len > 0 ? len : 0;
       ws.row_table[row] = table_row;
       ws.link[row] = link;
@@ -377,13 +377,14 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
     ws.header->next_item = 0;
     ws.header->error = 0;
     ws.header->plan_done = 0;
+    ws.header->exited = 0;
   }
 }
 
 // ---- main kernel ------------------------------------------------------------------------
 // Per-warp view of one claimed work item.  Scalars are warp-uniform; `len` is lane-indexed
-// (lane i < nrows: visible length of group row i) and `page` holds the page id of tile
-// page_base + lane.
+// (lane i < nrows: visible length of group row i) and `page` holds the page id of the item's
+// tile `lane` (the first 32 tiles).
 struct ItemCtx {
   int valid;
   int row_start;
@@ -396,7 +397,6 @@ struct ItemCtx {
   int group_chunks;
   int len;
   int page;
-  int page_base;
 };
 
 template <int kWarps, int kStages>
@@ -413,7 +413,7 @@ __device__ __forceinline__ ItemCtx claim_item(const AttentionArgs& a, const Work
   const unsigned full = ws.header->full_items, last = ws.header->last_items;
   c.valid = idx < full + last;
   c.row_start = c.table_row = c.nrows = c.kv_head = c.chunk = c.chunk_start = c.ntiles = 0;
-  c.group_chunks = c.len = c.page_base = 0;
+  c.group_chunks = c.len = 0;
   c.page = -1;
   if (!c.valid) return c;
   const Item it = idx < full ? ws.items_a[idx] : ws.items_b[idx - full];
@@ -453,50 +453,80 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
+  // Rows of length zero: zeros, their block table is never read.
+  {
+    const unsigned zero_rows = ws.header->zero_rows;
+    const int row_elems = a.q_heads * kHeadDim;  // multiple of 4 elements = 8 bytes
+    for (unsigned z = blockIdx.x * kWarps + warp; z < zero_rows; z += gridDim.x * kWarps) {
+      uint2* dst = reinterpret_cast<uint2*>(static_cast<T*>(a.out) + static_cast<int64_t>(ws.zero_list[z]) * row_elems);
+      for (int i = lane; i < row_elems / 4; i += 32) dst[i] = make_uint2(0u, 0u);
+    }
+  }
   const uint64_t policy = policy_evict_first();
   const uint32_t stage_base = smem_u32(&sm.stages[warp][0][0]);
   const uint32_t bar_base = smem_u32(&sm.full[warp][0]);
+
+  // ldmatrix source offsets inside a stage (lane dependent, item independent).
+  // K: matrix mi of an x4 load = (tokens 8*(mi>>1).., 8-dim chunk 2*(ks&3) + (mi&1)) of half ks>>2.
+  // V: matrix mi = (tokens 8*(mi&1).., 8-dim chunk jn + (mi>>1)), transposed on load.
+  uint32_t koff[8], voff[8];
+  {
+    const int mi = lane >> 3;
+    const int ktoken = ((mi >> 1) << 3) + (lane & 7), vtoken = ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int chunk16 = ((ks & 3) << 1) + (mi & 1);
+      koff[ks] = ((ks >> 2) << 11) + ktoken * 128 + ((chunk16 ^ (ktoken & 7)) << 4);
+    }
+#pragma unroll
+    for (int jp = 0; jp < 8; ++jp) {
+      const int c = 2 * jp + (mi >> 1);
+      voff[jp] = kTileBytes + ((c >> 3) << 11) + vtoken * 128 + (((c & 7) ^ (vtoken & 7)) << 4);
+    }
+  }
 
   unsigned issued = 0, consumed = 0;  // tiles of this warp's ring
   bool failed = false;
   ItemCtx cur = claim_item(a, ws, lane);
   ItemCtx nxt = cur.valid ? claim_item(a, ws, lane) : cur;
-  bool issue_in_next = false;  // the issue side has moved on to `nxt`
-  int issue_tile = 0;          // next tile of the issue side's item
 
-  // Issue side: keep every stage that is not being scored in flight.  Called when all tiles
-  // below `consumed` are finished, so tile n may go into stage n % kStages as long as
+  // Issue side state, all in registers: the item whose pages are being requested.
+  int iss_valid = cur.valid, iss_ntiles = cur.ntiles, iss_x0 = cur.kv_head * kHeadDim;
+  int iss_page = cur.page, iss_page_base = 0, iss_tile = 0;
+  const int32_t* iss_table = a.block_tables + static_cast<int64_t>(cur.table_row) * a.table_width + cur.chunk_start / kPage;
+  bool iss_on_next = false;  // the issue side has moved on to `nxt`
+
+  // Keep every stage that is not being scored in flight.  Called when all tiles below
+  // `consumed` are finished, so tile n may go into stage n % kStages as long as
   // n - consumed < kStages (the tile at `consumed` keeps its own stage while it is scored).
   auto top_up = [&]() {
     while (issued - consumed < static_cast<unsigned>(kStages)) {
-      ItemCtx& ic = issue_in_next ? nxt : cur;
-      if (!ic.valid) break;
-      if (issue_tile >= ic.ntiles) {
-        if (issue_in_next) break;  // at most one item ahead
-        issue_in_next = true;
-        issue_tile = 0;
+      if (!iss_valid) break;
+      if (iss_tile >= iss_ntiles) {
+        if (iss_on_next) break;  // at most one item ahead of the one being scored
+        iss_on_next = true;
+        iss_valid = nxt.valid; iss_ntiles = nxt.ntiles; iss_x0 = nxt.kv_head * kHeadDim;
+        iss_page = nxt.page; iss_page_base = 0; iss_tile = 0;
+        iss_table = a.block_tables + static_cast<int64_t>(nxt.table_row) * a.table_width + nxt.chunk_start / kPage;
         continue;
       }
-      if (issue_tile >= ic.page_base + 32) {  // next batch of 32 page ids
-        const int32_t* table = a.block_tables + static_cast<int64_t>(ic.table_row) * a.table_width +
-                               ic.chunk_start / kPage + issue_tile;
-        ic.page = issue_tile + lane < ic.ntiles ? table[lane] : -1;
-        ic.page_base = issue_tile;
+      if (iss_tile >= iss_page_base + 32) {  // next batch of 32 page ids
+        iss_page = iss_tile + lane < iss_ntiles ? iss_table[iss_tile + lane] : -1;
+        iss_page_base = iss_tile;
       }
-      const int block = __shfl_sync(0xffffffffu, ic.page, issue_tile - ic.page_base);
+      const int block = __shfl_sync(0xffffffffu, iss_page, iss_tile - iss_page_base);
       if (lane == 0) {
         const int stage = issued % kStages;
         const uint32_t bar = bar_base + stage * 8;
         const uint32_t dst = stage_base + stage * kStageBytes;
-        const int x0 = ic.kv_head * kHeadDim;
         mbar_expect_tx(bar, kStageBytes);
-        tma_load_page_half(dst, &k_map, x0, block, bar, policy);
-        tma_load_page_half(dst + 2048, &k_map, x0 + 64, block, bar, policy);
-        tma_load_page_half(dst + 4096, &v_map, x0, block, bar, policy);
-        tma_load_page_half(dst + 6144, &v_map, x0 + 64, block, bar, policy);
+        tma_load_page_half(dst, &k_map, iss_x0, block, bar, policy);
+        tma_load_page_half(dst + 2048, &k_map, iss_x0 + 64, block, bar, policy);
+        tma_load_page_half(dst + 4096, &v_map, iss_x0, block, bar, policy);
+        tma_load_page_half(dst + 6144, &v_map, iss_x0 + 64, block, bar, policy);
       }
       ++issued;
-      ++issue_tile;
+      ++iss_tile;
     }
   };
 
@@ -506,6 +536,11 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     const int shuffled0 = __shfl_sync(0xffffffffu, cur.len, (r0 < mrows ? r0 : 0) / gqa);
     const int shuffled1 = __shfl_sync(0xffffffffu, cur.len, (r1 < mrows ? r1 : 0) / gqa);
     const int len0 = r0 < mrows ? shuffled0 : 0, len1 = r1 < mrows ? shuffled1 : 0;
+    // tiles that end at or before the shortest member's length need no masking
+    int shortest = lane < cur.nrows ? cur.len : 0x7fffffff;
+#pragma unroll
+    for (int x = 16; x > 0; x >>= 1) shortest = min(shortest, __shfl_xor_sync(0xffffffffu, shortest, x));
+    const bool padded_rows = mrows < 16;
     top_up();
 
     const int64_t qrow0 = cur.row_start + r0 / gqa, qrow1 = cur.row_start + r1 / gqa;
@@ -525,43 +560,46 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     float o[16][4];
 #pragma unroll
     for (int j = 0; j < 16; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
+    // m: running maximum of score * scale_log2; l: running sum of exp2(score * scale_log2 - m)
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
     for (int j = 0; j < cur.ntiles; ++j) {
       const int stage = consumed % kStages;
       if (!mbar_wait(bar_base + stage * 8, (consumed / kStages) & 1)) { failed = true; break; }
-      const uint32_t kbase = stage_base + stage * kStageBytes;
-      const uint32_t vbase = kbase + kTileBytes;
+      const uint32_t base = stage_base + stage * kStageBytes;
 
       // S = Q K^T for the 16 tokens of this page (two n8 tiles, two accumulator chains each)
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      {
-        const int mi = lane >> 3, token = ((mi >> 1) << 3) + (lane & 7);
-        const uint32_t row_addr = kbase + token * 128;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const int chunk16 = ((ks & 3) << 1) + (mi & 1);
-          uint32_t b[4];
-          ldmatrix_x4(row_addr + ((ks >> 2) << 11) + ((chunk16 ^ (token & 7)) << 4), b);
-          if (ks & 1) {
-            mma_16816<kBF16>(s2[0], qa[ks], b[0], b[1]);
-            mma_16816<kBF16>(s2[1], qa[ks], b[2], b[3]);
-          } else {
-            mma_16816<kBF16>(s[0], qa[ks], b[0], b[1]);
-            mma_16816<kBF16>(s[1], qa[ks], b[2], b[3]);
-          }
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t b[4];
+        ldmatrix_x4(base + koff[ks], b);
+        if (ks & 1) {
+          mma_16816<kBF16>(s2[0], qa[ks], b[0], b[1]);
+          mma_16816<kBF16>(s2[1], qa[ks], b[2], b[3]);
+        } else {
+          mma_16816<kBF16>(s[0], qa[ks], b[0], b[1]);
+          mma_16816<kBF16>(s[1], qa[ks], b[2], b[3]);
         }
       }
-      // mask by each row's own length, move to the log2 domain
-      const int tok = cur.chunk_start + j * kPage + 2 * t;
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int pos = tok + nt * 8 + e;
-          s[nt][e] = pos < len0 ? (s[nt][e] + s2[nt][e]) * scale_log2 : -INFINITY;
-          s[nt][2 + e] = pos < len1 ? (s[nt][2 + e] + s2[nt][2 + e]) * scale_log2 : -INFINITY;
+        for (int e = 0; e < 4; ++e) s[nt][e] += s2[nt][e];
+      }
+      // mask by each row's own length (only tiles that reach past the shortest member)
+      const int tile_start = cur.chunk_start + j * kPage;
+      if (padded_rows || tile_start + kPage > shortest) {
+        const int tok = tile_start + 2 * t;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int pos = tok + nt * 8 + e;
+            if (pos >= len0) s[nt][e] = -INFINITY;
+            if (pos >= len1) s[nt][2 + e] = -INFINITY;
+          }
         }
       }
       float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -570,17 +608,17 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float mn0 = fmaxf(m0, mx0 * scale_log2), mn1 = fmaxf(m1, mx1 * scale_log2);
       const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
       const bool moved = (mn0 != m0) || (mn1 != m1);
       const float al0 = fast_exp2(m0 - mu0), al1 = fast_exp2(m1 - mu1);
       m0 = mn0; m1 = mn1;
       uint32_t pa[4];
       {
-        const float p00 = fast_exp2(s[0][0] - mu0), p01 = fast_exp2(s[0][1] - mu0);
-        const float p02 = fast_exp2(s[0][2] - mu1), p03 = fast_exp2(s[0][3] - mu1);
-        const float p10 = fast_exp2(s[1][0] - mu0), p11 = fast_exp2(s[1][1] - mu0);
-        const float p12 = fast_exp2(s[1][2] - mu1), p13 = fast_exp2(s[1][3] - mu1);
+        const float p00 = fast_exp2(fmaf(s[0][0], scale_log2, -mu0)), p01 = fast_exp2(fmaf(s[0][1], scale_log2, -mu0));
+        const float p02 = fast_exp2(fmaf(s[0][2], scale_log2, -mu1)), p03 = fast_exp2(fmaf(s[0][3], scale_log2, -mu1));
+        const float p10 = fast_exp2(fmaf(s[1][0], scale_log2, -mu0)), p11 = fast_exp2(fmaf(s[1][1], scale_log2, -mu0));
+        const float p12 = fast_exp2(fmaf(s[1][2], scale_log2, -mu1)), p13 = fast_exp2(fmaf(s[1][3], scale_log2, -mu1));
         l0 = l0 * al0 + ((p00 + p01) + (p10 + p11));
         l1 = l1 * al1 + ((p02 + p03) + (p12 + p13));
         pa[0] = pack2<kBF16>(p00, p01);
@@ -594,17 +632,12 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         for (int jn = 0; jn < 16; ++jn) { o[jn][0] *= al0; o[jn][1] *= al0; o[jn][2] *= al1; o[jn][3] *= al1; }
       }
       // O += P V
-      {
-        const int mi = lane >> 3, token = ((mi & 1) << 3) + (lane & 7);
-        const uint32_t row_addr = vbase + token * 128;
 #pragma unroll
-        for (int jn = 0; jn < 16; jn += 2) {
-          const int c = jn + (mi >> 1);
-          uint32_t b[4];
-          ldmatrix_x4_trans(row_addr + ((c >> 3) << 11) + (((c & 7) ^ (token & 7)) << 4), b);
-          mma_16816<kBF16>(o[jn], pa, b[0], b[1]);
-          mma_16816<kBF16>(o[jn + 1], pa, b[2], b[3]);
-        }
+      for (int jp = 0; jp < 8; ++jp) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(base + voff[jp], b);
+        mma_16816<kBF16>(o[2 * jp], pa, b[0], b[1]);
+        mma_16816<kBF16>(o[2 * jp + 1], pa, b[2], b[3]);
       }
       ++consumed;
       // the stage just read is free: order our shared-memory reads before the next TMA write
@@ -655,6 +688,8 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       if (lane == 0) prior = atomicAdd(&ws.counters[static_cast<int64_t>(cur.row_start) * a.kv_heads + cur.kv_head], 1u);
       prior = __shfl_sync(0xffffffffu, prior, 0);
       if (prior == static_cast<unsigned>(cur.group_chunks - 1)) {
+        // leave the counter at zero so the same plan can drive another run
+        if (lane == 0) ws.counters[static_cast<int64_t>(cur.row_start) * a.kv_heads + cur.kv_head] = 0;
         __threadfence();
         for (int r = 0; r < mrows; ++r) {
           const int row_chunks = chunk_count(__shfl_sync(0xffffffffu, cur.len, r / gqa));
@@ -688,10 +723,12 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 
     // ---- next item ----
     cur = nxt;
-    if (issue_in_next) {
-      issue_in_next = false;  // the issue side is already inside the new `cur`
-    } else {
-      issue_tile = 0;
+    if (iss_on_next) {
+      iss_on_next = false;  // the issue side is already inside the new `cur`
+    } else {                // (re)start the issue side at the first page of the new item
+      iss_valid = cur.valid; iss_ntiles = cur.ntiles; iss_x0 = cur.kv_head * kHeadDim;
+      iss_page = cur.page; iss_page_base = 0; iss_tile = 0;
+      iss_table = a.block_tables + static_cast<int64_t>(cur.table_row) * a.table_width + cur.chunk_start / kPage;
     }
     nxt = cur.valid ? claim_item(a, ws, lane) : cur;
   }
@@ -700,6 +737,15 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     if (lane == 0) atomicOr(&ws.header->error, 1u);
     // let copies already in flight land before the shared memory is released
     for (unsigned n = consumed + 1; n < issued; ++n) mbar_wait(bar_base + (n % kStages) * 8, (n / kStages) & 1);
+  }
+  // The last warp to finish rewinds the claim counter: the plan in the workspace stays valid
+  // for further runs over the same block tables and lengths (other layers of the same pass).
+  if (lane == 0) {
+    const unsigned before = atomicAdd(&ws.header->exited, 1u);
+    if (before == gridDim.x * kWarps - 1) {
+      ws.header->next_item = 0;
+      ws.header->exited = 0;
+    }
   }
 }
 
@@ -761,7 +807,7 @@ int launch_main(const CUtensorMap& k_map, const CUtensorMap& v_map, const Attent
 
 }  // namespace
 
-bool attention_sm100_supported(const AttentionArgs& a) {
+bool attention_sm100_shape_supported(const AttentionArgs& a) {
   if (a.dtype != RLT_BF16 && a.dtype != RLT_F16) return false;
   if (a.head_dim != kHeadDim || a.block_size != kPage) return false;
   if (a.kv_heads <= 0 || a.q_heads % a.kv_heads != 0) return false;
@@ -769,6 +815,11 @@ bool attention_sm100_supported(const AttentionArgs& a) {
   if (gqa != 1 && gqa != 2 && gqa != 4 && gqa != 8 && gqa != 16) return false;
   if (a.kv_heads > 32767) return false;
   if (static_cast<long long>(a.table_width) * a.block_size > (1 << 26)) return false;
+  return true;
+}
+
+bool attention_sm100_supported(const AttentionArgs& a) {
+  if (!attention_sm100_shape_supported(a)) return false;
   if (a.token_stride < static_cast<int64_t>(a.kv_heads) * kHeadDim) return false;
   if ((a.token_stride * 2) % 16 != 0 || (a.block_stride * 2) % 16 != 0) return false;
   if (a.block_stride < a.token_stride * kPage) return false;
@@ -788,45 +839,57 @@ int attention_sm100_read_status(const void* workspace, cudaStream_t stream, unsi
   Header h;
   RLT_CUDA_TRY(cudaMemcpyAsync(&h, workspace, sizeof(Header), cudaMemcpyDeviceToHost, stream));
   RLT_CUDA_TRY(cudaStreamSynchronize(stream));
-  out4[0] = h.full_items + h.last_items; out4[1] = h.next_item; out4[2] = h.error; out4[3] = h.plan_done;
+  out4[0] = h.full_items + h.last_items; out4[1] = h.zero_rows; out4[2] = h.error; out4[3] = h.next_item;
   return RLT_OK;
 }
 
-int launch_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+namespace {
+
+int bind_workspace(const AttentionArgs& a, void* workspace, size_t workspace_bytes, Workspace* ws) {
   const Layout l = make_layout(a.rows, a.q_heads, a.kv_heads, a.block_size, a.table_width);
   if (workspace == nullptr || workspace_bytes < l.total || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
     set_last_error_text("verify_attention: workspace missing, misaligned or too small");
     return RLT_ERR_WORKSPACE;
   }
-  DeviceInfo info;
-  int status = current_device_info(&info);
-  if (status != RLT_OK) return status;
   char* base = static_cast<char*>(workspace);
-  Workspace ws;
-  ws.header = reinterpret_cast<Header*>(base + l.header);
-  ws.row_len = reinterpret_cast<int*>(base + l.row_len);
-  ws.row_table = reinterpret_cast<int*>(base + l.row_table);
-  ws.link = reinterpret_cast<int*>(base + l.link);
-  ws.counters = reinterpret_cast<unsigned*>(base + l.counters);
-  ws.items_a = reinterpret_cast<Item*>(base + l.items_a);
-  ws.items_b = reinterpret_cast<Item*>(base + l.items_b);
-  ws.partials = reinterpret_cast<float*>(base + l.partials);
-  ws.max_chunks = l.max_chunks;
+  ws->header = reinterpret_cast<Header*>(base + l.header);
+  ws->row_len = reinterpret_cast<int*>(base + l.row_len);
+  ws->row_table = reinterpret_cast<int*>(base + l.row_table);
+  ws->link = reinterpret_cast<int*>(base + l.link);
+  ws->zero_list = reinterpret_cast<int*>(base + l.zero_list);
+  ws->counters = reinterpret_cast<unsigned*>(base + l.counters);
+  ws->items_a = reinterpret_cast<Item*>(base + l.items_a);
+  ws->items_b = reinterpret_cast<Item*>(base + l.items_b);
+  ws->partials = reinterpret_cast<float*>(base + l.partials);
+  ws->max_chunks = l.max_chunks;
+  return RLT_OK;
+}
 
+}  // namespace
+
+// Builds the work lists for (block_tables, context_lengths, cu_seqlens_q) in the workspace.
+int plan_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  Workspace ws;
+  int status = bind_workspace(a, workspace, workspace_bytes, &ws);
+  if (status != RLT_OK) return status;
+  RLT_CUDA_TRY(cudaMemsetAsync(ws.header, 0, sizeof(Header), stream));
+  const int plan_ctas = (a.rows + kPlanThreads / 32 - 1) / (kPlanThreads / 32);
+  plan_kernel<<<plan_ctas, kPlanThreads, 0, stream>>>(a, ws, gqa_cap(a));
+  return launch_status("plan_kernel");
+}
+
+// Scores q against one layer's K/V with the plan already in the workspace.
+int run_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  Workspace ws;
+  int status = bind_workspace(a, workspace, workspace_bytes, &ws);
+  if (status != RLT_OK) return status;
+  DeviceInfo info;
+  status = current_device_info(&info);
+  if (status != RLT_OK) return status;
   CUtensorMap k_map, v_map;
   status = make_page_map(&k_map, a.key_cache, a);
   if (status != RLT_OK) return status;
   status = make_page_map(&v_map, a.value_cache, a);
-  if (status != RLT_OK) return status;
-
-  RLT_CUDA_TRY(cudaMemsetAsync(ws.header, 0, sizeof(Header), stream));
-  const int plan_ctas = (a.rows + kPlanThreads / 32 - 1) / (kPlanThreads / 32);
-  const int cap = gqa_cap(a);
-  if (a.dtype == RLT_BF16)
-    plan_kernel<__nv_bfloat16><<<plan_ctas, kPlanThreads, 0, stream>>>(a, ws, cap);
-  else
-    plan_kernel<__half><<<plan_ctas, kPlanThreads, 0, stream>>>(a, ws, cap);
-  status = launch_status("plan_kernel");
   if (status != RLT_OK) return status;
 
   // Ring geometry (warps per SM x stages per warp); RLT_ATTENTION_RING selects another
@@ -837,14 +900,18 @@ int launch_attention_sm100(const AttentionArgs& a, void* workspace, size_t works
   }();
   if (a.dtype == RLT_BF16) {
     switch (variant) {
-      case 1: return launch_main<true, 8, 3>(k_map, v_map, a, ws, info.sm_count, stream);
       case 2: return launch_main<true, 7, 4>(k_map, v_map, a, ws, info.sm_count, stream);
-      case 3: return launch_main<true, 5, 5>(k_map, v_map, a, ws, info.sm_count, stream);
-      case 4: return launch_main<true, 4, 6>(k_map, v_map, a, ws, info.sm_count, stream);
-      default: return launch_main<true, 6, 4>(k_map, v_map, a, ws, info.sm_count, stream);
+      case 3: return launch_main<true, 12, 2>(k_map, v_map, a, ws, info.sm_count, stream);
+      default: return launch_main<true, 8, 3>(k_map, v_map, a, ws, info.sm_count, stream);
     }
   }
-  return launch_main<false, 6, 4>(k_map, v_map, a, ws, info.sm_count, stream);
+  return launch_main<false, 8, 3>(k_map, v_map, a, ws, info.sm_count, stream);
+}
+
+int launch_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  const int status = plan_attention_sm100(a, workspace, workspace_bytes, stream);
+  if (status != RLT_OK) return status;
+  return run_attention_sm100(a, workspace, workspace_bytes, stream);
 }
 
 }  // namespace rlt
