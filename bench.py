@@ -56,9 +56,12 @@ def measured_peaks():
 class Workload:
     """Seeded synthetic inputs of one replica (one GPU or the CPU sample)."""
 
-    def __init__(self, seed: int, requests: int = REQUESTS, layers: int = LAYERS, device="cpu"):
+    def __init__(self, seed: int, requests: int = REQUESTS, layers: int = LAYERS, device="cpu",
+                 tokens: int = TOKENS, depths: int = DEPTHS, kv_heads: int = HEADS):
         g = torch.Generator().manual_seed(seed)
         self.requests, self.layers = requests, layers
+        TOKENS, DEPTHS = tokens, depths
+        self.kv_heads = kv_heads
         self.contexts = torch.randint(512, 4097, (requests,), generator=g)
         pages = (self.contexts + BLOCK - 1) // BLOCK
         self.total_pages = int(pages.sum())
@@ -93,7 +96,7 @@ class Workload:
 
     def algorithmic_attention_bytes(self) -> int:
         """Each group's K/V once + Q + O + block tables, per layer call."""
-        kv = int(self.contexts.sum()) * HEADS * HEAD_DIM * 2 * 2
+        kv = int(self.contexts.sum()) * self.kv_heads * HEAD_DIM * 2 * 2
         qo = self.rows * HEADS * HEAD_DIM * 2 * 2
         tables = int(((self.contexts + BLOCK - 1) // BLOCK).sum()) * 4
         return kv + qo + tables
@@ -341,9 +344,10 @@ def run_attention_only(args):
 
     torch.cuda.set_device(0)
     device = torch.device("cuda", 0)
-    work = Workload(seed=1234, requests=args.requests, layers=args.layers)
+    work = Workload(seed=1234, requests=args.requests, layers=args.layers, tokens=args.tokens, depths=args.depths,
+                    kv_heads=args.kv_heads)
     g = torch.Generator(device=device).manual_seed(99)
-    pool_shape = (work.total_pages, args.layers, BLOCK, HEADS, HEAD_DIM)
+    pool_shape = (work.total_pages, args.layers, BLOCK, args.kv_heads, HEAD_DIM)
     key_pool = (torch.randn(pool_shape, device=device, generator=g) * 0.5).to(torch.bfloat16)
     value_pool = (torch.randn(pool_shape, device=device, generator=g) * 0.5).to(torch.bfloat16)
     q = (torch.randn(args.layers, work.rows, HEADS, HEAD_DIM, device=device, generator=g) * 0.5).to(torch.bfloat16)
@@ -463,6 +467,9 @@ def main():
                         help="profiling aid: run only this kernel family (not a bench line)")
     parser.add_argument("--requests", type=int, default=REQUESTS)
     parser.add_argument("--layers", type=int, default=LAYERS)
+    parser.add_argument("--tokens", type=int, default=TOKENS, help="with --only attention: new tokens per request")
+    parser.add_argument("--depths", type=int, default=DEPTHS, help="with --only attention: depth rows per token")
+    parser.add_argument("--kv-heads", type=int, default=HEADS, help="with --only attention: KV heads (query heads stay 16)")
     parser.add_argument("--shared-plan", action="store_true",
                         help="with --only attention: plan once per pass instead of once per layer call")
     args = parser.parse_args()
