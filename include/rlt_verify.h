@@ -160,6 +160,41 @@ RLT_API int rlt_verify_attention_run(const void* q, void* out, const void* key_c
                              const int32_t* context_lengths, const int32_t* cu_seqlens_q, int rows,
                              void* workspace, size_t workspace_bytes, rlt_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * rlt_verify_attention for hosts that are not allowed to allocate device memory.
+ * It has no counterpart in the reference.
+ *
+ * Who needs it: an engine that gives every free byte of HBM to its KV pool at start-up can
+ * find cudaMalloc failing for the rest of its life; a serving loop that must never stall
+ * cannot afford the device-wide synchronisation an allocation implies; and a plugin that
+ * runs under someone else's memory pool may simply have no allocator to call.  Such a caller
+ * cannot provide the scratch workspace rlt_verify_attention asks for.  This entry point takes
+ * the same inputs and outputs and no workspace: the scratch is a fixed 32 MiB block that is
+ * part of the library image (so every GPU that loads the library holds those 32 MiB until
+ * the process exits).  It calls no cudaMalloc, cudaFree or any other allocating routine.
+ *
+ * Limits and rules:
+ *   - The batch must fit the block: rlt_verify_attention_workspace_bytes(rows, q_heads,
+ *     kv_heads, head_dim, block_size, table_width) <= 32 MiB (for 16 heads x 128 that is,
+ *     e.g., 64 rows with tables of up to 512 pages, or 400 rows with up to 64 pages).
+ *     Anything larger is refused with RLT_ERR_WORKSPACE and a message in rlt_last_error();
+ *     nothing is launched.
+ *   - The first call on each device looks up the block's device address (with that device
+ *     current).  Make that first call outside any stream capture.
+ *   - All calls on a device share the one block, and it keeps whatever the previous call
+ *     left; each call re-initialises the words that must start at zero.  Two calls whose
+ *     work can overlap on the GPU (different streams, no ordering between them) race on
+ *     the block and corrupt each other: order them, or give one of them its own workspace
+ *     through rlt_verify_attention.
+ * Results are bit-identical to rlt_verify_attention on the same inputs.
+ * ---------------------------------------------------------------------- */
+RLT_API int rlt_verify_attention_noalloc(const void* q, void* out, const void* key_cache,
+                                 const void* value_cache, int64_t block_stride, int64_t token_stride,
+                                 int64_t num_blocks, int block_size, int q_heads, int kv_heads,
+                                 int head_dim, int dtype, const int32_t* block_tables, int table_rows,
+                                 int table_width, const int32_t* context_lengths,
+                                 const int32_t* cu_seqlens_q, int rows, rlt_stream_t stream);
+
 /* Diagnostics for the tiled kernel (head_dim 128, 16-token pages, fp16/bf16): waits for
  * `stream` and copies four words of the workspace header to the host —
  * status4[0] = work items planned by the last call (groups x context chunks x kv heads; shows

@@ -61,6 +61,9 @@ int launch_attention_sm100(const AttentionArgs& a, void* workspace, size_t works
 // and packing; a run consumes it and leaves it intact for the next layer.
 int plan_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 int run_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+// launch_attention_sm100 on the library's built-in 32 MiB scratch block (no allocation anywhere).
+size_t attention_sm100_builtin_scratch_bytes();
+int launch_attention_sm100_builtin(const AttentionArgs& a, cudaStream_t stream);
 // Synchronous read-back of the workspace header of the last tiled call:
 // {work items planned, rows of length zero, error bits, claim counter (0 after a clean run)}.
 int attention_sm100_read_status(const void* workspace, cudaStream_t stream, unsigned* out4);

@@ -28,6 +28,7 @@
 // than one chunk), which is what the roofline of this kernel is measured against.
 #include <cuda.h>
 #include <math.h>
+#include <stdio.h>
 #include <stdlib.h>
 
 #include <mutex>
@@ -913,5 +914,56 @@ int launch_attention_sm100(const AttentionArgs& a, void* workspace, size_t works
   if (status != RLT_OK) return status;
   return run_attention_sm100(a, workspace, workspace_bytes, stream);
 }
+
+// ---- built-in scratch for callers that must not allocate ------------------------------------
+// A fixed 32 MiB block of device memory that is part of the library image: every GPU context
+// that loads the library holds it until the process exits.  In host code the array's name is
+// only a handle; the device address the kernels need is looked up once per device.
+constexpr size_t kBuiltinScratchBytes = 32u << 20;
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+
+namespace {
+
+int builtin_scratch_address(void** address) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mutex;
+  static void* cached[kMaxDevices] = {};
+  int device = 0;
+  RLT_CUDA_TRY(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices) {
+    set_last_error_text("device index out of range");
+    return RLT_ERR_INVALID;
+  }
+  std::lock_guard<std::mutex> lock(mutex);
+  if (cached[device] == nullptr) {
+    void* found = nullptr;
+    RLT_CUDA_TRY(cudaGetSymbolAddress(&found, g_builtin_scratch));  // for the current device
+    cached[device] = found;
+  }
+  *address = cached[device];
+  return RLT_OK;
+}
+
+}  // namespace
+
+size_t attention_sm100_builtin_scratch_bytes() { return kBuiltinScratchBytes; }
+
+int launch_attention_sm100_builtin(const AttentionArgs& a, cudaStream_t stream) {
+  const size_t need = make_layout(a.rows, a.q_heads, a.kv_heads, a.block_size, a.table_width).total;
+  if (need > kBuiltinScratchBytes) {
+    char text[256];
+    snprintf(text, sizeof(text),
+             "verify_attention_noalloc: this batch needs %zu bytes of scratch but the built-in scratch holds %zu; "
+             "use rlt_verify_attention with a caller-owned workspace",
+             need, kBuiltinScratchBytes);
+    set_last_error_text(text);
+    return RLT_ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  const int status = builtin_scratch_address(&scratch);
+  if (status != RLT_OK) return status;
+  return launch_attention_sm100(a, scratch, kBuiltinScratchBytes, stream);
+}
+
 
 }  // namespace rlt
