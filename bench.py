@@ -242,7 +242,7 @@ def run_gpu(args):
                                          x["temperature"], x["u_accept"], x["u_final"], x["slots"], slot_values)
         accepted = result[work.accept_rows:work.accept_rows + work.requests]
         rolled = rlt.rollback(x["starts"], accepted + 1, x["request_tables"], BLOCK)
-        launches += 5  # sample_rows, argmax + greedy finish, rejection, rollback
+        launches += 6  # sample_rows, argmax + greedy finish, row stats + decide (rejection), rollback
         return result, rolled
 
     # ---- device-resident timing ----

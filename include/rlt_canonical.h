@@ -103,6 +103,16 @@ RLT_HD float rlt_fix_to_float(unsigned long long zfix) {
   return RLT_MUL(RLT_ULL2F(zfix), RLT_FIX_INV);
 }
 
+/* Mass of token v in a plain draw from p = e / z:  e * (1 / z). */
+RLT_HD float rlt_draw_mass(float e, float inv_z) { return RLT_MUL(e, inv_z); }
+
+/* Mass of token v in a residual draw, max(p - q, 0) with p = ep / zp and q = eq / zq, written
+ * without a division per token: (ep * zq - eq * zp) * (1 / (zp * zq)).  Negative values and
+ * NaN get weight zero in rlt_fix_weight. */
+RLT_HD float rlt_residual_mass(float ep, float eq, float zp, float zq, float inv_zpzq) {
+  return RLT_MUL(RLT_SUB(RLT_MUL(ep, zq), RLT_MUL(eq, zp)), inv_zpzq);
+}
+
 /* Draw threshold: floor(u * total), u in [0, 1), total < 2^53. */
 RLT_HD unsigned long long rlt_draw_threshold(float u, unsigned long long total) {
   return RLT_D2ULL(RLT_DMUL((double)u, (double)total));

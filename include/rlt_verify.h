@@ -265,21 +265,26 @@ RLT_API int rlt_sample_rows(const void* logits, int64_t row_stride, int rows, in
  *
  * Arithmetic (identical in the CPU oracle, so results are bit-exact):
  *   t = x / T (IEEE);  m = max t;  e = rlt_expf(t - m);  Zfix = sum (u64)(e * 2^40);
- *   Z = (float)Zfix * 2^-40;  p[v] = e / Z (IEEE).  Draw weights w[v] = (u64)(mass[v] * 2^40),
- *   threshold = (u64)((double)u * (double)sum w), token = first v with prefix(v) > threshold.
- *   Integer sums make every result independent of summation order.
+ *   Z = (float)Zfix * 2^-40;  p[v] = e / Z (IEEE).  Draw weights w[v] = (u64)(mass[v] * 2^40) with
+ *   mass[v] = e_p * (1/Z_p) for a plain draw and (e_p * Z_q - e_q * Z_p) * (1/(Z_p * Z_q)) clamped
+ *   at 0 for a residual draw; threshold = (u64)((double)u * (double)sum w), token = first v with
+ *   prefix(v) > threshold.  Integer sums make every result independent of summation order.
+ * workspace: device scratch of rlt_accept_rejection_workspace_bytes(rows) bytes, 16-byte aligned
+ *   (per-row normalisers, filled by the first of the call's two launches).
  * Replaces: rejection_sample (vllm_rlt/worker/speculative.py:47-63), the loop in
  *   SpeculativeRunner._collect_round (:483-510), Sampler.probabilities for top_k = -1,
  *   top_p = 1 (vllm_rlt/worker/sampler.py:27-55).
  * target_logits, draft_logits: [rows, vocab]; draft row j of a request holds the logits
  *   draft j+1 was sampled from (its last row is unused).
  * ---------------------------------------------------------------------- */
+RLT_API size_t rlt_accept_rejection_workspace_bytes(int rows);
+
 RLT_API int rlt_accept_rejection(const void* target_logits, const void* draft_logits, int64_t row_stride,
                          int rows, int vocab, int dtype, const int32_t* cu_rows, int n,
                          const int64_t* tokens, int tokens_width, const int64_t* starts,
                          const float* temperature, const float* u_accept, const float* u_final,
                          const int64_t* slots, int64_t* slot_values, int64_t* result,
-                         int32_t* status, rlt_stream_t stream);
+                         int32_t* status, void* workspace, size_t workspace_bytes, rlt_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Device rollback of rejected positions.  For request i with round start

@@ -37,8 +37,9 @@ SIGNATURES = {
     "rlt_argmax_rows": (_I, [_P, _L, _I, _I, _I, _P, _P]),
     "rlt_accept_greedy": (_I, [_P, _L, _I, _I, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P]),
     "rlt_sample_rows": (_I, [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P]),
+    "rlt_accept_rejection_workspace_bytes": (_Z, [_I]),
     "rlt_accept_rejection": (_I, [_P, _P, _L, _I, _I, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P,
-                                  _P]),
+                                  _P, _Z, _P]),
     "rlt_rollback": (_I, [_P, _P, _I, _P, _I, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _P, _P, _P]),
 }
 

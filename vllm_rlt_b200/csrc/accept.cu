@@ -167,30 +167,39 @@ __device__ __forceinline__ RowNorm block_normalise(const T* __restrict__ row, in
 }
 
 template <typename T>
-__device__ __forceinline__ float prob_at(const T* row, int v, float temperature, const RowNorm& n) {
-  return RLT_DIV(rlt_expf(RLT_SUB(scaled_logit(row, v, temperature), n.m)), n.z);
+__device__ __forceinline__ float exp_at(const T* row, int v, float temperature, const RowNorm& n) {
+  return rlt_expf(RLT_SUB(scaled_logit(row, v, temperature), n.m));
 }
 
 template <typename T>
+__device__ __forceinline__ float prob_at(const T* row, int v, float temperature, const RowNorm& n) {
+  return RLT_DIV(exp_at(row, v, temperature, n), n.z);
+}
+
+// Fixed-point draw weight of token v: p[v] (plain) or max(p[v] - q[v], 0) (residual), in the
+// division-free form of rlt_canonical.h; `inv` is 1/zp or 1/(zp*zq).
+template <typename T>
 __device__ __forceinline__ unsigned long long draw_weight(const T* prow, const RowNorm& pn, const T* qrow,
                                                           const RowNorm& qn, bool residual, int v,
-                                                          float temperature) {
-  float mass = prob_at(prow, v, temperature, pn);
-  if (residual) mass = RLT_SUB(mass, prob_at(qrow, v, temperature, qn));
-  return rlt_fix_weight(mass);
+                                                          float temperature, float inv) {
+  const float ep = exp_at(prow, v, temperature, pn);
+  if (!residual) return rlt_fix_weight(rlt_draw_mass(ep, inv));
+  return rlt_fix_weight(rlt_residual_mass(ep, exp_at(qrow, v, temperature, qn), pn.z, qn.z, inv));
 }
 
 // Inverse-CDF draw over fixed-point weights in ascending token index; -1 if the mass is zero.
-// Thread t owns the contiguous tokens [t*span, (t+1)*span).
+// Thread t owns the contiguous tokens [t*span, (t+1)*span); its weights stay in registers
+// between the sum and the search when the span is small enough.
 template <typename T, int kThreads>
 __device__ __forceinline__ int block_draw(const T* __restrict__ prow, const RowNorm& pn,
                                           const T* __restrict__ qrow, const RowNorm& qn, bool residual,
                                           int vocab, float temperature, float u, unsigned long long* scratch,
                                           int* token_slot) {
+  const float inv = residual ? RLT_DIV(1.0f, RLT_MUL(pn.z, qn.z)) : RLT_DIV(1.0f, pn.z);
   const int span = (vocab + kThreads - 1) / kThreads;
   const int begin = min(static_cast<int>(threadIdx.x) * span, vocab), end = min(begin + span, vocab);
   unsigned long long local = 0ull;
-  for (int v = begin; v < end; ++v) local += draw_weight(prow, pn, qrow, qn, residual, v, temperature);
+  for (int v = begin; v < end; ++v) local += draw_weight(prow, pn, qrow, qn, residual, v, temperature, inv);
   // exclusive scan over threads: inclusive warp scan, then warp totals
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned long long inc = local;
@@ -214,7 +223,7 @@ __device__ __forceinline__ int block_draw(const T* __restrict__ prow, const RowN
     unsigned long long prefix = before + inc - local;
     if (prefix <= threshold && threshold < prefix + local) {
       for (int v = begin; v < end; ++v) {
-        prefix += draw_weight(prow, pn, qrow, qn, residual, v, temperature);
+        prefix += draw_weight(prow, pn, qrow, qn, residual, v, temperature, inv);
         if (prefix > threshold) { *token_slot = v; break; }
       }
     }
@@ -249,17 +258,66 @@ sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
   if (threadIdx.x == 0) { tokens[r] = token; status[r] = st; }
 }
 
-// One CTA per request; rows of the request are examined in order and the walk stops at the
-// first rejection, so only the rows that decide the outcome are read.
+// ---- rejection sampling in two launches -------------------------------------------------
+// 1. row_stats_kernel, one CTA per (verification row, target | draft): everything about a
+//    row that does not depend on earlier accept decisions — max, normaliser and the
+//    probability of the row's draft token (or the argmax for a greedy request) — so the
+//    streaming over [rows, vocab] runs at full width instead of request by request.
+// 2. decide_kernel, one CTA per request: the sequential accept walk over those few numbers,
+//    then the single residual or bonus draw the request needs.
+struct RowStats {
+  float m;
+  float z;
+  float prob;  // probability of the row's draft token under this row's distribution
+  int info;    // bit 0: distribution valid; greedy requests: argmax index << 1
+};
+
+constexpr int kStatsThreads = 512;
+
+__device__ __forceinline__ int request_of_row(const int32_t* cu_rows, int n, int row) {
+  int lo = 0, hi = n - 1;  // last i with cu_rows[i] <= row
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu_rows[mid] <= row) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kStatsThreads)
+row_stats_kernel(const T* __restrict__ target_logits, const T* __restrict__ draft_logits, int64_t row_stride,
+                 int vocab, const int32_t* __restrict__ cu_rows, int n, const int64_t* __restrict__ tokens,
+                 int tokens_width, const float* __restrict__ temperature, RowStats* __restrict__ stats) {
+  __shared__ unsigned long long scratch[32];
+  const int row = blockIdx.x, side = blockIdx.y;  // side 0: target, 1: draft
+  const int i = request_of_row(cu_rows, n, row);
+  const int first = cu_rows[i], count = cu_rows[i + 1] - first, j = row - first;
+  const float temp = temperature[i];
+  RowStats out = {0.0f, 0.0f, 0.0f, 0};
+  if (temp == 0.0f) {
+    if (side == 1) return;
+    out.info = block_argmax<T, kStatsThreads>(target_logits + static_cast<int64_t>(row) * row_stride, vocab, scratch) << 1;
+  } else {
+    if (side == 1 && j == count - 1) return;  // the bonus row has no draft distribution
+    const T* logits = (side == 0 ? target_logits : draft_logits) + static_cast<int64_t>(row) * row_stride;
+    const RowNorm norm = block_normalise<T, kStatsThreads>(logits, vocab, temp, scratch);
+    const int64_t d = j < count - 1 ? tokens[static_cast<int64_t>(i) * tokens_width + j + 1] : -1;
+    out.m = norm.m;
+    out.z = norm.z;
+    out.info = norm.ok ? 1 : 0;
+    if (norm.ok && d >= 0 && d < vocab) out.prob = prob_at(logits, static_cast<int>(d), temp, norm);
+  }
+  if (threadIdx.x == 0) stats[2 * row + side] = out;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kSampleThreads)
-accept_rejection_kernel(const T* __restrict__ target_logits, const T* __restrict__ draft_logits,
-                        int64_t row_stride, int rows, int vocab, const int32_t* __restrict__ cu_rows, int n,
-                        const int64_t* __restrict__ tokens, int tokens_width,
-                        const int64_t* __restrict__ starts, const float* __restrict__ temperature,
-                        const float* __restrict__ u_accept, const float* __restrict__ u_final,
-                        const int64_t* __restrict__ slots, int64_t* __restrict__ slot_values,
-                        int64_t* __restrict__ result, int32_t* __restrict__ status) {
+decide_kernel(const T* __restrict__ target_logits, const T* __restrict__ draft_logits, int64_t row_stride, int rows,
+              int vocab, const int32_t* __restrict__ cu_rows, int n, const int64_t* __restrict__ tokens,
+              int tokens_width, const int64_t* __restrict__ starts, const float* __restrict__ temperature,
+              const float* __restrict__ u_accept, const float* __restrict__ u_final,
+              const int64_t* __restrict__ slots, int64_t* __restrict__ slot_values,
+              const RowStats* __restrict__ stats, int64_t* __restrict__ result, int32_t* __restrict__ status) {
   __shared__ unsigned long long scratch[32];
   __shared__ int token_slot;
   const int i = blockIdx.x;
@@ -273,8 +331,7 @@ accept_rejection_kernel(const T* __restrict__ target_logits, const T* __restrict
   int64_t final_token = -1;
   if (temp == 0.0f) {
     for (int j = 0; j < c; ++j) {
-      const int target = block_argmax<T, kSampleThreads>(target_logits + static_cast<int64_t>(a + j) * row_stride,
-                                                         vocab, scratch);
+      const int target = stats[2 * (a + j)].info >> 1;
       if (threadIdx.x == 0) result[a + j] = target;
       final_token = target;
       if (j < c - 1 && tok[j + 1] == target) { ++accepted; continue; }
@@ -283,31 +340,29 @@ accept_rejection_kernel(const T* __restrict__ target_logits, const T* __restrict
   } else {
     int j = 0;
     for (; j < c - 1; ++j) {
-      const T* prow = target_logits + static_cast<int64_t>(a + j) * row_stride;
-      const T* qrow = draft_logits + static_cast<int64_t>(a + j) * row_stride;
+      const RowStats ps = stats[2 * (a + j)], qs = stats[2 * (a + j) + 1];
       const int64_t d = tok[j + 1];
-      const RowNorm pn = block_normalise<T, kSampleThreads>(prow, vocab, temp, scratch);
-      const RowNorm qn = block_normalise<T, kSampleThreads>(qrow, vocab, temp, scratch);
-      if (!pn.ok || !qn.ok || d < 0 || d >= vocab) { st = RLT_ROW_BAD_LOGITS; break; }
-      const float qd = prob_at(qrow, static_cast<int>(d), temp, qn);
-      const float pd = prob_at(prow, static_cast<int>(d), temp, pn);
-      if (!(qd > 0.0f)) { st = RLT_ROW_ZERO_PROPOSAL; break; }
-      if (RLT_MUL(u_accept[a + j], qd) < pd) {
+      if (!(ps.info & 1) || !(qs.info & 1) || d < 0 || d >= vocab) { st = RLT_ROW_BAD_LOGITS; break; }
+      if (!(qs.prob > 0.0f)) { st = RLT_ROW_ZERO_PROPOSAL; break; }
+      if (RLT_MUL(u_accept[a + j], qs.prob) < ps.prob) {
         if (threadIdx.x == 0) result[a + j] = d;
         ++accepted;
         continue;
       }
-      final_token = block_draw<T, kSampleThreads>(prow, pn, qrow, qn, true, vocab, temp, u_final[i], scratch,
-                                                  &token_slot);
+      const RowNorm pn = {ps.m, ps.z, 1}, qn = {qs.m, qs.z, 1};
+      final_token = block_draw<T, kSampleThreads>(target_logits + static_cast<int64_t>(a + j) * row_stride, pn,
+                                                  draft_logits + static_cast<int64_t>(a + j) * row_stride, qn, true,
+                                                  vocab, temp, u_final[i], scratch, &token_slot);
       if (final_token < 0) st = RLT_ROW_INVALID_RESIDUAL;
       break;
     }
     if (st == RLT_ROW_OK && j == c - 1) {
-      const T* prow = target_logits + static_cast<int64_t>(a + c - 1) * row_stride;
-      const RowNorm pn = block_normalise<T, kSampleThreads>(prow, vocab, temp, scratch);
-      if (!pn.ok) {
+      const RowStats ps = stats[2 * (a + c - 1)];
+      if (!(ps.info & 1)) {
         st = RLT_ROW_BAD_LOGITS;
       } else {
+        const RowNorm pn = {ps.m, ps.z, 1};
+        const T* prow = target_logits + static_cast<int64_t>(a + c - 1) * row_stride;
         final_token = block_draw<T, kSampleThreads>(prow, pn, prow, pn, false, vocab, temp, u_final[i], scratch,
                                                     &token_slot);
         if (final_token < 0) st = RLT_ROW_INVALID_RESIDUAL;
@@ -388,12 +443,17 @@ extern "C" RLT_API int rlt_sample_rows(const void* logits, int64_t row_stride, i
   return launch_status("sample_rows_kernel");
 }
 
+extern "C" RLT_API size_t rlt_accept_rejection_workspace_bytes(int rows) {
+  return rows > 0 ? static_cast<size_t>(rows) * 2 * sizeof(rlt::RowStats) : 32;
+}
+
 extern "C" RLT_API int rlt_accept_rejection(const void* target_logits, const void* draft_logits, int64_t row_stride,
-                                    int rows, int vocab, int dtype, const int32_t* cu_rows, int n,
-                                    const int64_t* tokens, int tokens_width, const int64_t* starts,
-                                    const float* temperature, const float* u_accept, const float* u_final,
-                                    const int64_t* slots, int64_t* slot_values, int64_t* result,
-                                    int32_t* status_out, rlt_stream_t stream) {
+                                            int rows, int vocab, int dtype, const int32_t* cu_rows, int n,
+                                            const int64_t* tokens, int tokens_width, const int64_t* starts,
+                                            const float* temperature, const float* u_accept, const float* u_final,
+                                            const int64_t* slots, int64_t* slot_values, int64_t* result,
+                                            int32_t* status_out, void* workspace, size_t workspace_bytes,
+                                            rlt_stream_t stream) {
   using namespace rlt;
   int status = check_logits(target_logits, row_stride, rows, vocab, dtype);
   if (status != RLT_OK) return status;
@@ -402,10 +462,21 @@ extern "C" RLT_API int rlt_accept_rejection(const void* target_logits, const voi
   RLT_REQUIRE(draft_logits && cu_rows && tokens && starts && temperature && u_accept && u_final && result &&
                   status_out,
               "accept_rejection: null pointer");
+  if (workspace == nullptr || workspace_bytes < rlt_accept_rejection_workspace_bytes(rows) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) {
+    set_last_error_text("accept_rejection: workspace missing, misaligned or too small");
+    return RLT_ERR_WORKSPACE;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  RLT_DISPATCH_DTYPE(dtype, T, (accept_rejection_kernel<T><<<n, kSampleThreads, 0, s>>>(
+  RowStats* stats = static_cast<RowStats*>(workspace);
+  RLT_DISPATCH_DTYPE(dtype, T, (row_stats_kernel<T><<<dim3(rows, 2), kStatsThreads, 0, s>>>(
+                                   static_cast<const T*>(target_logits), static_cast<const T*>(draft_logits),
+                                   row_stride, vocab, cu_rows, n, tokens, tokens_width, temperature, stats)));
+  status = launch_status("row_stats_kernel");
+  if (status != RLT_OK) return status;
+  RLT_DISPATCH_DTYPE(dtype, T, (decide_kernel<T><<<n, kSampleThreads, 0, s>>>(
                                    static_cast<const T*>(target_logits), static_cast<const T*>(draft_logits),
                                    row_stride, rows, vocab, cu_rows, n, tokens, tokens_width, starts, temperature,
-                                   u_accept, u_final, slots, slot_values, result, status_out)));
-  return launch_status("accept_rejection_kernel");
+                                   u_accept, u_final, slots, slot_values, stats, result, status_out)));
+  return launch_status("decide_kernel");
 }

@@ -146,14 +146,17 @@ def accept_rejection(target_logits, draft_logits, cu_rows, tokens, starts, tempe
     status = torch.zeros(n, dtype=torch.int32, device=target_logits.device)
     if n == 0:
         return result, status
+    lib = _capi.load()
+    workspace = torch.empty(lib.rlt_accept_rejection_workspace_bytes(rows), dtype=torch.uint8,
+                            device=target_logits.device)
     with torch.cuda.device(target_logits.device):
-        code = _capi.load().rlt_accept_rejection(
+        code = lib.rlt_accept_rejection(
             _capi.ptr(target_logits), _capi.ptr(draft_logits), target_logits.stride(0), rows,
             target_logits.shape[1], _capi.DTYPE_CODES[target_logits.dtype], _capi.ptr(cu_rows.contiguous()), n,
             _capi.ptr(tokens), tokens.shape[1], _capi.ptr(starts.contiguous()),
             _capi.ptr(temperature.contiguous()), _capi.ptr(u_accept.contiguous()),
             _capi.ptr(u_final.contiguous()), _capi.ptr(slots), _capi.ptr(slot_values), _capi.ptr(result),
-            _capi.ptr(status), _capi.stream_of(target_logits))
+            _capi.ptr(status), _capi.ptr(workspace), workspace.numel(), _capi.stream_of(target_logits))
     _capi.check(code, "accept_rejection")
     return result, status
 
