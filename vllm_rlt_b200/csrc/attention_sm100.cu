@@ -437,6 +437,63 @@ __device__ __forceinline__ ItemCtx claim_item(const AttentionArgs& a, const Work
   return c;
 }
 
+// Merge of a group's per-chunk partials into its output rows, by one warp, all rows at once:
+// lanes 2r and 2r+1 own the two 64-dim halves of fragment row r and walk that row's chunks in
+// chunk order, out = sum_c O_c * 2^(m_c - M) / sum_c l_c * 2^(m_c - M) with M = max_c m_c.
+// The merge is a chain of L2 round trips; doing the (up to 16) rows side by side instead of one
+// after another makes it about (1 + 2 * chunks) trips per group instead of per row.
+template <bool kBF16>
+__device__ __forceinline__ void merge_chunks(const AttentionArgs& a, const Workspace& ws, int row_start, int kv_head,
+                                             int gqa, int mrows, int lane_len, int lane) {
+  using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
+  const int r = lane >> 1, half = lane & 1;
+  const int source = (r < mrows ? r : 0) / gqa;
+  const int len = __shfl_sync(0xffffffffu, lane_len, source);
+  int row_chunks = r < mrows ? chunk_count(len) : 0;
+  if (row_chunks < 2) row_chunks = 0;  // single-chunk rows were finished from registers
+  const int64_t qrow = row_start + source;
+  const int qhead = kv_head * gqa + (r < mrows ? r : 0) % gqa;
+  const float* part = ws.partials + ((qrow * a.q_heads + qhead) * ws.max_chunks) * kPartialStride;
+  float big = -INFINITY;
+  for (int c = 0; c < row_chunks; ++c) big = fmaxf(big, __ldcg(part + c * kPartialStride + kHeadDim));
+  T* out = static_cast<T*>(a.out) + (qrow * a.q_heads + qhead) * kHeadDim;
+#pragma unroll 1
+  for (int quarter = 0; quarter < 2; ++quarter) {
+    const int dim0 = half * 64 + quarter * 32;
+    float4 acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float total = 0.f;
+    for (int c = 0; c < row_chunks; ++c) {
+      const float* pc = part + c * kPartialStride;
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(pc + kHeadDim));
+      float4 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __ldcg(reinterpret_cast<const float4*>(pc + dim0) + i);
+      const float f = ml.x == -INFINITY ? 0.f : fast_exp2(ml.x - big);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        acc[i].x = fmaf(v[i].x, f, acc[i].x); acc[i].y = fmaf(v[i].y, f, acc[i].y);
+        acc[i].z = fmaf(v[i].z, f, acc[i].z); acc[i].w = fmaf(v[i].w, f, acc[i].w);
+      }
+      total = fmaf(ml.y, f, total);
+    }
+    if (row_chunks > 0) {
+      const float inv = 1.0f / total;
+      uint4* dst = reinterpret_cast<uint4*>(out + dim0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 packed;
+        packed.x = pack2<kBF16>(acc[2 * i].x * inv, acc[2 * i].y * inv);
+        packed.y = pack2<kBF16>(acc[2 * i].z * inv, acc[2 * i].w * inv);
+        packed.z = pack2<kBF16>(acc[2 * i + 1].x * inv, acc[2 * i + 1].y * inv);
+        packed.w = pack2<kBF16>(acc[2 * i + 1].z * inv, acc[2 * i + 1].w * inv);
+        dst[i] = packed;
+      }
+    }
+  }
+}
+
 template <bool kBF16, int kWarps, int kStages>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
@@ -692,33 +749,7 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         // leave the counter at zero so the same plan can drive another run
         if (lane == 0) ws.counters[static_cast<int64_t>(cur.row_start) * a.kv_heads + cur.kv_head] = 0;
         __threadfence();
-        for (int r = 0; r < mrows; ++r) {
-          const int row_chunks = chunk_count(__shfl_sync(0xffffffffu, cur.len, r / gqa));
-          if (row_chunks < 2) continue;
-          const int64_t qrow = cur.row_start + r / gqa;
-          const int qhead = cur.kv_head * gqa + r % gqa;
-          const float* part = ws.partials + ((qrow * a.q_heads + qhead) * ws.max_chunks) * kPartialStride;
-          float big = -INFINITY;
-          for (int c = lane; c < row_chunks; c += 32) big = fmaxf(big, __ldcg(part + c * kPartialStride + kHeadDim));
-#pragma unroll
-          for (int x = 16; x > 0; x >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, x));
-          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          float total = 0.f;
-          for (int c = 0; c < row_chunks; ++c) {
-            const float* pc = part + c * kPartialStride;
-            const float mc = __ldcg(pc + kHeadDim);
-            const float f = mc == -INFINITY ? 0.f : fast_exp2(mc - big);
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(pc) + lane);
-            acc.x = fmaf(v.x, f, acc.x); acc.y = fmaf(v.y, f, acc.y);
-            acc.z = fmaf(v.z, f, acc.z); acc.w = fmaf(v.w, f, acc.w);
-            total = fmaf(__ldcg(pc + kHeadDim + 1), f, total);
-          }
-          const float inv = 1.0f / total;
-          uint2 packed;
-          packed.x = pack2<kBF16>(acc.x * inv, acc.y * inv);
-          packed.y = pack2<kBF16>(acc.z * inv, acc.w * inv);
-          reinterpret_cast<uint2*>(out + (qrow * a.q_heads + qhead) * kHeadDim)[lane] = packed;
-        }
+        merge_chunks<kBF16>(a, ws, cur.row_start, cur.kv_head, gqa, mrows, cur.len, lane);
       }
     }
 
@@ -825,7 +856,7 @@ bool attention_sm100_supported(const AttentionArgs& a) {
   if ((a.token_stride * 2) % 16 != 0 || (a.block_stride * 2) % 16 != 0) return false;
   if (a.block_stride < a.token_stride * kPage) return false;
   if (!aligned16(a.key_cache) || !aligned16(a.value_cache)) return false;
-  if ((reinterpret_cast<uintptr_t>(a.q) & 3u) != 0 || (reinterpret_cast<uintptr_t>(a.out) & 7u) != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(a.q) & 3u) != 0 || (reinterpret_cast<uintptr_t>(a.out) & 15u) != 0) return false;
   if (a.num_blocks > 0xffffffffll) return false;
   return true;
 }
