@@ -30,7 +30,6 @@ import os
 import statistics
 import subprocess
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -130,6 +129,41 @@ class Workload:
         return inputs
 
 
+def combine_ranks(stats, world: int, steps: int, gather=None):
+    """Whole-job numbers from per-rank [timed ms, e2e ms, accepted/step, committed/step].
+
+    Replicas are independent, so the job's step time is the slowest rank's (max over ranks) and its
+    tokens are the sum over ranks.  `gather(tensor) -> [world, 4]` collects the rows
+    (torch.distributed all_gather in a multi-rank run)."""
+    table = stats[None] if gather is None or world == 1 else gather(stats)
+    max_ms, max_e2e_ms = float(table[:, 0].max()), float(table[:, 1].max())
+    accepted, committed = float(table[:, 2].sum()), float(table[:, 3].sum())
+    ms_per_step = max_ms / steps
+    return {
+        "ms_per_step": ms_per_step,
+        "e2e_ms_per_step": max_e2e_ms / steps,
+        "accepted_per_step": accepted,
+        "committed_per_step": committed,
+        "accepted_tokens_per_s": accepted / (ms_per_step / 1e3),
+        "committed_tokens_per_s": committed / (ms_per_step / 1e3),
+        "e2e_accepted_tokens_per_s": accepted / (max_e2e_ms / steps / 1e3),
+    }
+
+
+def all_gather_rows(stats):
+    """[4] per rank -> [world, 4] on every rank (any torch.distributed backend)."""
+    import torch.distributed as dist
+
+    rows = [torch.zeros_like(stats) for _ in range(dist.get_world_size())]
+    dist.all_gather(rows, stats)
+    return torch.stack(rows).cpu()
+
+
+def replica_seed(rank: int) -> int:
+    """Every replica draws its own requests: same distribution, different seed."""
+    return 1234 + rank
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
 
@@ -142,28 +176,30 @@ class ClockSampler:
             index = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
         except Exception:
             pass
-        self.index, self.samples, self.stop = index, [], threading.Event()
-        self.thread = threading.Thread(target=self.run, daemon=True)
-
-    def run(self):
-        while not self.stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
-                                     timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([x.strip() for x in out.split(",")])
-            except Exception:
-                pass
-            self.stop.wait(0.1)
+        self.index, self.samples, self.process = index, [], None
 
     def __enter__(self):
-        self.thread.start()
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.process = None
         return self
 
     def __exit__(self, *exc):
-        self.stop.set()
-        self.thread.join(timeout=6)
+        if self.process is None:
+            return
+        self.process.terminate()
+        try:
+            out, _ = self.process.communicate(timeout=5)
+        except Exception:
+            self.process.kill()
+            out = ""
+        for line in out.splitlines():
+            fields = [x.strip() for x in line.split(",")]
+            if len(fields) >= 9:
+                self.samples.append(fields)
 
     def summary(self):
         sm = [float(s[1]) for s in self.samples if len(s) > 2 and s[1].replace(".", "").isdigit()]
@@ -196,7 +232,7 @@ def run_gpu(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    work = Workload(seed=1234 + rank)
+    work = Workload(seed=replica_seed(rank))
     host = work.host_inputs(pin=True)
     dev = {name: t.to(device) for name, t in host.items()}
     g = torch.Generator(device=device).manual_seed(99 + rank)
@@ -215,12 +251,15 @@ def run_gpu(args):
     launches = 0
     attn_events = []
 
-    def hot_path(x, timed_attention):
-        """One verify pass on device tensors `x`; returns (result buffer, rollback state)."""
+    def hot_path(x, timed_attention, before_layer=None, before_accept=None):
+        """One verify pass on device tensors `x`; returns (result buffer, rollback state).
+        The two hooks let a host-driven caller wait for that layer's / the logits' upload."""
         nonlocal launches
         # all layers of the pass share the block tables and lengths: plan once, run per layer
         with backend.kernel.shared_plan():
             for layer in range(LAYERS):
+                if before_layer is not None:
+                    before_layer(layer)
                 kc, vc = key_pool[:, layer], value_pool[:, layer]
                 rlt.kv_write(kc, vc, x["k"][layer], x["v"][layer], x["write_blocks"], x["write_offsets"])
                 if timed_attention:
@@ -233,6 +272,8 @@ def run_gpu(args):
                 rlt.silu_and_mul(x["gate"][layer], x["up"][layer])
                 launches += 3  # kv_write, attention, silu_and_mul
         launches += 1  # the pass's one attention plan
+        if before_accept is not None:
+            before_accept()
         # drafts proposed from q with the explicit-uniform rule, then both acceptance modes
         drafts, _ = rlt.sample_rows(x["draft"], per_row_t, x["u_draft"])
         tokens = torch.zeros(work.requests, TOKENS, dtype=torch.int64, device=device)
@@ -250,13 +291,14 @@ def run_gpu(args):
         hot_path(dev, False)
     barrier()
     launches = 0
-    with ClockSampler(local) as clocks:
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(args.steps):
-            result, _ = hot_path(dev, True)
-        stop.record()
-        barrier()
+    clocks = ClockSampler(local)
+    clocks.__enter__()  # samples until the end of the second (host-driven) timed region
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        result, _ = hot_path(dev, True)
+    stop.record()
+    barrier()
     elapsed_ms = start.elapsed_time(stop)
     launches_per_step = launches // args.steps
     attention_ms = statistics.mean(a.elapsed_time(b) for a, b in attn_events)
@@ -264,16 +306,49 @@ def run_gpu(args):
     committed_per_step = accepted_per_step + work.requests
 
     # ---- end to end from pinned host buffers through the public API ----
-    staged = {name: torch.empty_like(t, device=device) for name, t in host.items()}
+    # Every step uploads all of its inputs from pinned host memory and reads its result back.
+    # Uploads run on a copy stream, layer by layer, into one of two staging sets, so the copy of
+    # layer l+1 (and of the next step) overlaps the kernels of layer l; the compute stream waits
+    # for exactly the tensors it is about to read.
+    per_layer = ("q", "k", "v", "gate", "up")
+    last = ("target", "draft")
+    first = [name for name in host if name not in per_layer + last]
+    sets = [{name: torch.empty_like(t, device=device) for name, t in host.items()} for _ in range(2)]
+    copy_stream = torch.cuda.Stream(device=device)
+    compute_stream = torch.cuda.current_stream(device)
+    set_free = [None, None]  # event: the compute that used this staging set has finished
     result_host = torch.empty(work.accept_rows + 2 * work.requests, dtype=torch.int64).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in host.values())
     d2h = result_host.numel() * 8
+    e2e_counter = 0
 
     def e2e_step():
-        for name, t in host.items():
-            staged[name].copy_(t, non_blocking=True)
-        result, _ = hot_path(staged, False)
+        nonlocal e2e_counter
+        which = e2e_counter % 2
+        e2e_counter += 1
+        staged = sets[which]
+        layer_ready = [torch.cuda.Event() for _ in range(LAYERS)]
+        first_ready, last_ready = torch.cuda.Event(), torch.cuda.Event()
+        with torch.cuda.stream(copy_stream):
+            if set_free[which] is not None:
+                copy_stream.wait_event(set_free[which])
+            for name in first:
+                staged[name].copy_(host[name], non_blocking=True)
+            first_ready.record(copy_stream)
+            for layer in range(LAYERS):
+                for name in per_layer:
+                    staged[name][layer].copy_(host[name][layer], non_blocking=True)
+                layer_ready[layer].record(copy_stream)
+            for name in last:
+                staged[name].copy_(host[name], non_blocking=True)
+            last_ready.record(copy_stream)
+        compute_stream.wait_event(first_ready)
+        result, _ = hot_path(staged, False, before_layer=lambda layer: compute_stream.wait_event(layer_ready[layer]),
+                             before_accept=lambda: compute_stream.wait_event(last_ready))
         result_host.copy_(result, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record(compute_stream)
+        set_free[which] = done
 
     for _ in range(min(args.warmup, 3)):
         e2e_step()
@@ -284,22 +359,16 @@ def run_gpu(args):
         e2e_step()
     e_stop.record()
     barrier()
+    clocks.__exit__(None, None, None)
     e2e_ms = e_start.elapsed_time(e_stop)
     status = backend.kernel.last_status(device)
 
     times = torch.tensor([elapsed_ms, e2e_ms, float(accepted_per_step), float(committed_per_step)],
                          dtype=torch.float64, device=device)
-    if world > 1:
-        gathered = [torch.zeros_like(times) for _ in range(world)]
-        dist.all_gather(gathered, times)
-        gathered = torch.stack(gathered).cpu()
-    else:
-        gathered = times.cpu()[None]
+    job = combine_ranks(times if world > 1 else times.cpu(), world, args.steps, all_gather_rows)
     if rank == 0:
-        max_ms, max_e2e_ms = float(gathered[:, 0].max()), float(gathered[:, 1].max())
-        accepted_total, committed_total = float(gathered[:, 2].sum()), float(gathered[:, 3].sum())
-        ms_per_step = max_ms / args.steps
-        value = accepted_total / (ms_per_step / 1e3)
+        ms_per_step, value = job["ms_per_step"], job["accepted_tokens_per_s"]
+        accepted_total, committed_total = job["accepted_per_step"], job["committed_per_step"]
         peak, peak_kind = measured_peaks()
         algorithmic = work.algorithmic_attention_bytes()
         achieved = algorithmic / (attention_ms * 1e-3) / 1e9
@@ -317,11 +386,11 @@ def run_gpu(args):
                 "l2_policy": "inputs larger than L2 (KV pool streamed once per step)",
                 "parallelism": f"{world} independent replicas, no collective",
             },
-            "committed_tokens_per_s": committed_total / (ms_per_step / 1e3),
+            "committed_tokens_per_s": job["committed_tokens_per_s"],
             "acceptance_rate": accepted_total / (world * work.requests * (TOKENS - 1)),
-            "e2e": {"value": accepted_total / (max_e2e_ms / args.steps / 1e3), "unit": "accepted tokens/s",
+            "e2e": {"value": job["e2e_accepted_tokens_per_s"], "unit": "accepted tokens/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": max_e2e_ms / args.steps},
+                    "ms_per_step": job["e2e_ms_per_step"]},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "kernel": "verify_attention_kernel (per layer call; one plan per 24-layer pass amortised in)",
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
@@ -372,6 +441,58 @@ def run_attention_only(args):
                       "avg_call_ms": ms, "algorithmic_bytes": algorithmic,
                       "achieved_gbs": algorithmic / ms / 1e6, "frac": algorithmic / ms / 1e6 / peak,
                       "peak_kind": kind, "status": backend.kernel.last_status(device)}))
+
+
+def run_small_only(args):
+    """Profiling aid: the acceptance kernels (`--only accept`) or SiLU-and-Mul (`--only silu`) at the
+    step's shapes, a few hundred MB on the device, timed per call with CUDA events."""
+    import vllm_rlt_b200 as rlt
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    work = Workload(seed=1234, requests=args.requests, layers=1)
+    out = {"only": args.only, "requests": args.requests}
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / args.steps
+
+    if args.only == "silu":
+        g = torch.Generator(device=device).manual_seed(3)
+        gate = (torch.randn(work.rows, FFN, device=device, generator=g) * 3).to(torch.bfloat16)
+        up = torch.randn(work.rows, FFN, device=device, generator=g).to(torch.bfloat16)
+        ms = timed(lambda: rlt.silu_and_mul(gate, up))
+        nbytes = 3 * gate.numel() * 2
+        out.update(rows=work.rows, ms=ms, bytes=nbytes, gbs=nbytes / ms / 1e6)
+    else:
+        x = {k: v.to(device) for k, v in work.host_inputs(pin=False).items() if k not in ("q", "k", "v", "gate", "up")}
+        per_row_t = x["temperature"].repeat_interleave(TOKENS)
+        slot_values = torch.zeros(2 * work.requests, 2, dtype=torch.int64, device=device)
+        drafts, _ = rlt.sample_rows(x["draft"], per_row_t, x["u_draft"])
+        tokens = torch.zeros(work.requests, TOKENS, dtype=torch.int64, device=device)
+        tokens[:, 1:] = drafts.view(work.requests, TOKENS)[:, :-1]
+        logits_bytes = x["target"].numel() * 4
+        out["sample_rows_ms"] = timed(lambda: rlt.sample_rows(x["draft"], per_row_t, x["u_draft"]))
+        out["accept_greedy_ms"] = timed(lambda: rlt.accept_greedy(x["target"], x["cu_rows"], tokens, x["starts"],
+                                                                  x["slots"], slot_values))
+        out["accept_rejection_ms"] = timed(lambda: rlt.accept_rejection(
+            x["target"], x["draft"], x["cu_rows"], tokens, x["starts"], x["temperature"], x["u_accept"],
+            x["u_final"], x["slots"], slot_values))
+        result, _ = rlt.accept_rejection(x["target"], x["draft"], x["cu_rows"], tokens, x["starts"],
+                                         x["temperature"], x["u_accept"], x["u_final"])
+        accepted = result[work.accept_rows:work.accept_rows + work.requests]
+        out["rollback_ms"] = timed(lambda: rlt.rollback(x["starts"], accepted + 1, x["request_tables"], BLOCK))
+        out.update(rows=work.accept_rows, vocab=VOCAB, greedy_bytes=logits_bytes, rejection_bytes=2 * logits_bytes,
+                   greedy_gbs=logits_bytes / out["accept_greedy_ms"] / 1e6,
+                   rejection_gbs=2 * logits_bytes / out["accept_rejection_ms"] / 1e6)
+    print(json.dumps(out))
 
 
 def cpu_step_seconds(threads: int, budget_s: float):
@@ -459,11 +580,11 @@ def run_reference(args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--only", default=None, choices=["attention"],
+    parser.add_argument("--only", default=None, choices=["attention", "accept", "silu"],
                         help="profiling aid: run only this kernel family (not a bench line)")
     parser.add_argument("--requests", type=int, default=REQUESTS)
     parser.add_argument("--layers", type=int, default=LAYERS)
@@ -480,6 +601,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the verify-step kernels have no CPU fallback")
     if args.only == "attention":
         run_attention_only(args)
+        return
+    if args.only in ("accept", "silu"):
+        run_small_only(args)
         return
     run_gpu(args)
 

@@ -343,25 +343,31 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
                                            : 0ull;
     const unsigned long long inclusive = block_scan_sum(mine, s_usum);
     const unsigned long long exclusive = inclusive - mine;
-    if (leader) {
-      // Pages are addressed through the table row of the group's longest member: the link
-      // window guarantees every member agrees with it on all pages that member can need.
-      const int table_row = __ldcg(&ws.row_table[longest_row]);
+    // Work items are written by the whole warp of each leader, 32 consecutive items per step.
+    // Pages are addressed through the table row of the group's longest member: the link
+    // window guarantees every member agrees with it on all pages that member can need.
+    const int table_row = leader ? __ldcg(&ws.row_table[longest_row]) : 0;
+    unsigned leaders = __ballot_sync(0xffffffffu, leader);
+    while (leaders != 0u) {
+      const int src = __ffs(leaders) - 1;
+      leaders &= leaders - 1;
       Item it;
-      it.row_start = r;
-      it.table_row = table_row;
-      Item* full = ws.items_a + s_base_full + static_cast<unsigned>(exclusive & 0xffffffffu);
-      for (int c = 0; c < chunks - 1; ++c)
-        for (int h = 0; h < a.kv_heads; ++h) {
-          it.nrows_head = nrows | (h << 16);
-          it.chunk = c;
-          *full++ = it;
-        }
-      Item* last = ws.items_b + s_base_last + static_cast<unsigned>(exclusive >> 32);
-      for (int h = 0; h < a.kv_heads; ++h) {
-        it.nrows_head = nrows | (h << 16);
-        it.chunk = chunks - 1;
-        *last++ = it;
+      it.row_start = __shfl_sync(0xffffffffu, r, src);
+      it.table_row = __shfl_sync(0xffffffffu, table_row, src);
+      const int l_nrows = __shfl_sync(0xffffffffu, nrows, src);
+      const int l_chunks = __shfl_sync(0xffffffffu, chunks, src);
+      const unsigned l_full = s_base_full + __shfl_sync(0xffffffffu, static_cast<unsigned>(exclusive & 0xffffffffu), src);
+      const unsigned l_last = s_base_last + __shfl_sync(0xffffffffu, static_cast<unsigned>(exclusive >> 32), src);
+      const int full_count = (l_chunks - 1) * a.kv_heads;
+      for (int i = lane; i < full_count; i += 32) {
+        it.nrows_head = l_nrows | ((i % a.kv_heads) << 16);
+        it.chunk = i / a.kv_heads;
+        ws.items_a[l_full + i] = it;
+      }
+      for (int h = lane; h < a.kv_heads; h += 32) {
+        it.nrows_head = l_nrows | (h << 16);
+        it.chunk = l_chunks - 1;
+        ws.items_b[l_last + h] = it;
       }
     }
     __syncthreads();
