@@ -72,21 +72,36 @@ __device__ __forceinline__ unsigned long long block_sum(unsigned long long v, un
   return warp_sum(v);
 }
 
-// Argmax of one row by the whole CTA; 16-byte loads when the row allows them.
+// Packed (value, lowest index) maximum of one row by the whole CTA.  16-byte loads when the row
+// allows them, four in flight per thread (a row is only a few hundred KB: latency, not issue
+// rate, decides how fast one CTA can stream it).
 template <typename T, int kThreads>
-__device__ __forceinline__ int block_argmax(const T* __restrict__ row, int vocab, unsigned long long* scratch) {
+__device__ __forceinline__ unsigned long long block_max_key(const T* __restrict__ row, int vocab,
+                                                           unsigned long long* scratch) {
   constexpr int kVec = 16 / sizeof(T);
+  constexpr int kDepth = 4;
   unsigned long long best = 0ull;
   if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0 && vocab % kVec == 0) {
     const uint4* rv = reinterpret_cast<const uint4*>(row);
     const int nvec = vocab / kVec;
-    for (int i = threadIdx.x; i < nvec; i += kThreads) {
-      const uint4 raw = __ldcs(rv + i);
-      const T* e = reinterpret_cast<const T*>(&raw);
+    for (int base = threadIdx.x; base < nvec; base += kThreads * kDepth) {
+      uint4 raw[kDepth];
 #pragma unroll
-      for (int j = 0; j < kVec; ++j) {
-        const unsigned long long key = argmax_key(Elem<T>::to_float(e[j]), i * kVec + j);
-        best = key > best ? key : best;
+      for (int k = 0; k < kDepth; ++k) {
+        const int i = base + k * kThreads;
+        if (i < nvec) raw[k] = __ldcs(rv + i);
+      }
+#pragma unroll
+      for (int k = 0; k < kDepth; ++k) {
+        const int i = base + k * kThreads;
+        if (i < nvec) {
+          const T* e = reinterpret_cast<const T*>(&raw[k]);
+#pragma unroll
+          for (int j = 0; j < kVec; ++j) {
+            const unsigned long long key = argmax_key(Elem<T>::to_float(e[j]), i * kVec + j);
+            best = key > best ? key : best;
+          }
+        }
       }
     }
   } else {
@@ -95,7 +110,12 @@ __device__ __forceinline__ int block_argmax(const T* __restrict__ row, int vocab
       best = key > best ? key : best;
     }
   }
-  return key_index(block_max<kThreads>(best, scratch));
+  return block_max<kThreads>(best, scratch);
+}
+
+template <typename T, int kThreads>
+__device__ __forceinline__ int block_argmax(const T* __restrict__ row, int vocab, unsigned long long* scratch) {
+  return key_index(block_max_key<T, kThreads>(row, vocab, scratch));
 }
 
 template <typename T>
@@ -139,29 +159,48 @@ __device__ __forceinline__ float scaled_logit(const T* row, int v, float tempera
   return RLT_DIV(Elem<T>::to_float(row[v]), temperature);
 }
 
+// max and normaliser of softmax(row / temperature).  Division by a positive temperature is
+// monotonic, so max_v (x_v / T) == (max_v x_v) / T exactly: the first pass is a plain maximum
+// over the raw logits (NaN counts as the maximum and is then reported), one division at the end.
 template <typename T, int kThreads>
 __device__ __forceinline__ RowNorm block_normalise(const T* __restrict__ row, int vocab, float temperature,
                                                    unsigned long long* scratch) {
-  unsigned long long best = 0ull;
-  unsigned bad = 0;
-  for (int v = threadIdx.x; v < vocab; v += kThreads) {
-    const float t = scaled_logit(row, v, temperature);
-    bad |= (t != t) || (t == INFINITY);
-    const unsigned long long key = argmax_key(t, 0);
-    best = key > best ? key : best;
-  }
-  bad = __syncthreads_or(bad);
-  best = block_max<kThreads>(best, scratch);
+  const unsigned long long best = block_max_key<T, kThreads>(row, vocab, scratch);
   RowNorm n;
   uint32_t bits = static_cast<uint32_t>(best >> 32);
   bits = (bits & 0x80000000u) ? (bits & 0x7fffffffu) : ~bits;
-  n.m = __uint_as_float(bits);
-  n.ok = !bad && best != 0ull && n.m != -INFINITY;
+  const float raw_max = __uint_as_float(bits);
+  n.m = RLT_DIV(raw_max, temperature);
+  n.ok = best != 0ull && raw_max == raw_max && n.m != INFINITY && n.m != -INFINITY;
   n.z = 0.0f;
   if (!n.ok) return n;
   unsigned long long zfix = 0ull;
-  for (int v = threadIdx.x; v < vocab; v += kThreads)
-    zfix += rlt_fix_weight(rlt_expf(RLT_SUB(scaled_logit(row, v, temperature), n.m)));
+  constexpr int kVec = 16 / sizeof(T);
+  if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0 && vocab % kVec == 0) {
+    const uint4* rv = reinterpret_cast<const uint4*>(row);
+    const int nvec = vocab / kVec;
+    for (int base = threadIdx.x; base < nvec; base += kThreads * 2) {
+      uint4 raw[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int i = base + k * kThreads;
+        if (i < nvec) raw[k] = __ldg(rv + i);
+      }
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int i = base + k * kThreads;
+        if (i < nvec) {
+          const T* e = reinterpret_cast<const T*>(&raw[k]);
+#pragma unroll
+          for (int j = 0; j < kVec; ++j)
+            zfix += rlt_fix_weight(rlt_expf(RLT_SUB(RLT_DIV(Elem<T>::to_float(e[j]), temperature), n.m)));
+        }
+      }
+    }
+  } else {
+    for (int v = threadIdx.x; v < vocab; v += kThreads)
+      zfix += rlt_fix_weight(rlt_expf(RLT_SUB(scaled_logit(row, v, temperature), n.m)));
+  }
   n.z = rlt_fix_to_float(block_sum<kThreads>(zfix, scratch));
   return n;
 }
