@@ -1,0 +1,184 @@
+"""Greedy self-speculative decoding of a looped LM on the B200 kernels (block mode).
+
+The loop of `SpeculativeRunner._submit_round` / `_collect_round`
+(`vllm_rlt/worker/speculative.py:418-511` of the reference) with the reference's round geometry
+(SURVEY: a round of request i processes `c_i = min(K+1, max_tokens - generated_i)` input
+positions starting at the last committed token; draft offset o runs loops `0..d-1` and proposes
+token o+1 from `coda(hidden_d).argmax`; the retained depth-d states of all c_i rows then run
+loops `d..D-1` and every row's argmax is a target), on a LAST_EXITED paged KV cache (one plane
+per loop depth).  Acceptance, the next token / position and the rollback frontier are computed
+on the device by `accept_greedy` / `rollback`; the host reads one small buffer per round.
+
+`native` decoding (one token per step through all loops) is provided for the token-identity
+check the reference applies to its own runner (tests/test_speculative.py:71-87 there).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from .kv_cache import rollback
+from .looped_lm import LoopedLM
+from .speculative import accept_greedy, argmax_rows
+
+
+@dataclass
+class DecodeStats:
+    """Counters of the reference's SpeculativeStats (worker/speculative.py:23-29)."""
+
+    rounds: int = 0
+    drafted_tokens: int = 0
+    accepted_tokens: int = 0
+    committed_tokens: int = 0
+    verified_rows: int = 0
+
+
+@dataclass
+class PagedKV:
+    """A LAST_EXITED paged pool: `[blocks, layers, block, kv_heads, head_dim]` K and V, and one block
+    table per (request, depth plane), `tables[n, planes, pages]` (core/kv_cache_manager.py:135-145)."""
+
+    key: torch.Tensor
+    value: torch.Tensor
+    tables: torch.Tensor
+    block: int
+
+    @classmethod
+    def allocate(cls, model: LoopedLM, capacities, block: int, *, permute_seed: int | None = 0):
+        c = model.config
+        planes = c.total_ut_steps
+        pages = [-(-n // block) for n in capacities]
+        width = max(pages)
+        total = sum(pages) * planes
+        order = torch.arange(total, dtype=torch.int32)
+        if permute_seed is not None:  # physical pages deliberately out of order
+            order = order[torch.randperm(total, generator=torch.Generator().manual_seed(permute_seed))]
+        tables = torch.full((len(capacities), planes, width), -1, dtype=torch.int32)
+        cursor = 0
+        for i, n in enumerate(pages):
+            for plane in range(planes):
+                tables[i, plane, :n] = order[cursor:cursor + n]
+                cursor += n
+        shape = (total, c.num_hidden_layers, block, c.num_key_value_heads, c.head_dim)
+        return cls(torch.zeros(shape, device=model.device, dtype=model.dtype),
+                   torch.zeros(shape, device=model.device, dtype=model.dtype), tables.to(model.device), block)
+
+    def addressing(self, requests: torch.Tensor, positions: torch.Tensor, plane: int):
+        """Write addresses, per-row block tables and context lengths of rows (request, position)."""
+        tables = self.tables[requests, plane]
+        blocks = tables.gather(1, (positions // self.block)[:, None]).squeeze(1).long()
+        return blocks, positions % self.block, tables.contiguous(), (positions + 1).int()
+
+
+@dataclass
+class _State:
+    prompts: list
+    max_tokens: int
+    generated: list = field(default_factory=list)
+
+
+class SelfSpeculativeDecoder:
+    def __init__(self, model: LoopedLM, *, block: int = 16):
+        self.model = model
+        self.block = block
+        self.stats = DecodeStats()
+
+    # ---- shared pieces -------------------------------------------------------------------
+    def _loop(self, kv: PagedKV, hidden, requests, positions, depth):
+        blocks, offsets, tables, lengths = kv.addressing(requests, positions, depth)
+        return self.model.recurrent(hidden, positions, kv.key, kv.value, blocks, offsets, tables, lengths)
+
+    def _prefill(self, kv: PagedKV, prompts):
+        """All prompt positions through every loop; returns the first generated token of each request."""
+        device = self.model.device
+        requests = torch.tensor([i for i, p in enumerate(prompts) for _ in p], device=device)
+        positions = torch.tensor([j for p in prompts for j in range(len(p))], device=device)
+        tokens = torch.tensor([t for p in prompts for t in p], device=device)
+        hidden = self.model.prelude(tokens)
+        for depth in range(self.model.config.total_ut_steps):
+            hidden = self._loop(kv, hidden, requests, positions, depth)
+        last = torch.tensor([sum(len(p) for p in prompts[:i + 1]) - 1 for i in range(len(prompts))], device=device)
+        return argmax_rows(self.model.coda(hidden[last]).float().contiguous()).tolist()
+
+    # ---- native decoding -----------------------------------------------------------------
+    @torch.no_grad()
+    def generate_native(self, prompts, max_tokens: int):
+        device = self.model.device
+        kv = PagedKV.allocate(self.model, [len(p) + max_tokens for p in prompts], self.block)
+        generated = [[t] for t in self._prefill(kv, prompts)]
+        while any(len(g) < max_tokens for g in generated):
+            active = [i for i, g in enumerate(generated) if len(g) < max_tokens]
+            requests = torch.tensor(active, device=device)
+            positions = torch.tensor([len(prompts[i]) + len(generated[i]) - 1 for i in active], device=device)
+            hidden = self.model.prelude(torch.tensor([generated[i][-1] for i in active], device=device))
+            for depth in range(self.model.config.total_ut_steps):
+                hidden = self._loop(kv, hidden, requests, positions, depth)
+            for i, token in zip(active, argmax_rows(self.model.coda(hidden).float().contiguous()).tolist()):
+                generated[i].append(token)
+        return generated
+
+    # ---- block self-speculation ----------------------------------------------------------
+    @torch.no_grad()
+    def generate(self, prompts, max_tokens: int, *, num_speculative_tokens: int, draft_loops: int = 2,
+                 target_loops: int | None = None):
+        model, device = self.model, self.model.device
+        target_loops = target_loops or model.config.total_ut_steps
+        if not 0 < draft_loops < target_loops <= model.config.total_ut_steps:
+            raise ValueError("draft_loops must be smaller than target_loops")
+        k = num_speculative_tokens
+        kv = PagedKV.allocate(model, [len(p) + max_tokens + k + 1 for p in prompts], self.block)
+        generated = [[t] for t in self._prefill(kv, prompts)]
+        slot_values = torch.zeros(len(prompts), 2, dtype=torch.int64, device=device)
+        while any(len(g) < max_tokens for g in generated):
+            active = [i for i, g in enumerate(generated) if len(g) < max_tokens]
+            counts = [min(k + 1, max_tokens - len(generated[i])) for i in active]
+            starts = [len(prompts[i]) + len(generated[i]) - 1 for i in active]
+            n, width = len(active), max(counts)
+            tokens = torch.zeros(n, width, dtype=torch.int64, device=device)
+            tokens[:, 0] = torch.tensor([generated[i][-1] for i in active], device=device)
+            retained = [[] for _ in active]
+            # draft: one new position per request and offset, loops 0 .. d-1
+            for offset in range(width):
+                rows = [j for j, c in enumerate(counts) if offset < c]
+                requests = torch.tensor([active[j] for j in rows], device=device)
+                positions = torch.tensor([starts[j] + offset for j in rows], device=device)
+                hidden = model.prelude(tokens[rows, offset])
+                for depth in range(draft_loops):
+                    hidden = self._loop(kv, hidden, requests, positions, depth)
+                for row, j in enumerate(rows):
+                    retained[j].append(hidden[row])
+                drafting = [(row, j) for row, j in enumerate(rows) if offset + 1 < counts[j]]
+                if not drafting:
+                    break
+                logits = model.coda(torch.stack([hidden[row] for row, _ in drafting]))
+                tokens[[j for _, j in drafting], offset + 1] = argmax_rows(logits.float().contiguous())
+                self.stats.drafted_tokens += len(drafting)
+            # verify: the retained depth-d states of all rows, request-major, loops d .. D-1
+            hidden = torch.stack([h for per_request in retained for h in per_request])
+            requests = torch.tensor([active[j] for j, c in enumerate(counts) for _ in range(c)], device=device)
+            positions = torch.tensor([starts[j] + o for j, c in enumerate(counts) for o in range(c)], device=device)
+            for depth in range(draft_loops, target_loops):
+                hidden = self._loop(kv, hidden, requests, positions, depth)
+            logits = model.coda(hidden).float().contiguous()
+            cu_rows = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=device)
+            start_tensor = torch.tensor(starts, device=device)
+            slots = torch.arange(n, device=device)
+            result = accept_greedy(logits, cu_rows, tokens.contiguous(), start_tensor, slots, slot_values[:n].contiguous())
+            rows_total = sum(counts)
+            accepted = result[rows_total:rows_total + n]
+            rolled = rollback(start_tensor, accepted + 1, kv.tables[torch.tensor(active, device=device)].contiguous(),
+                              self.block)
+            values = torch.cat([result, rolled.frontier]).tolist()  # the round's one host read
+            firsts = [sum(counts[:j]) for j in range(n)]
+            for j, i in enumerate(active):
+                a = values[rows_total + j]
+                emitted = values[firsts[j]:firsts[j] + a + 1]
+                generated[i].extend(emitted)
+                assert values[rows_total + n + j] == starts[j] + a + 1 == values[rows_total + 2 * n + j]
+                self.stats.accepted_tokens += a
+                self.stats.committed_tokens += len(emitted)
+            self.stats.rounds += n
+            self.stats.verified_rows += rows_total
+        return [g[:max_tokens] for g in generated]
