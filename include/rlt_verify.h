@@ -311,6 +311,23 @@ RLT_API int rlt_rollback(const int64_t* starts, const int64_t* emitted, int n, c
                  int64_t* frontier, int32_t* context_lengths, int64_t* write_blocks,
                  int64_t* write_offsets, int32_t* status, rlt_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Early-exit finalisation.  For each row (slot, exit depth e, position): copy the token's K/V
+ * of every layer from plane e's page into the pages of planes e+1 .. planes-1, so that later
+ * tokens attending at deeper loops find it.
+ * Replaces: KVCacheManager.finalize_token (vllm_rlt/core/kv_cache_manager.py:805-831) and the
+ *   Triton finalize_kernel (vllm_rlt/kernels/routing.py:147-177).
+ * key_pool / value_pool: the WHOLE pool [num_blocks, layers, block_size, kv_heads, head_dim];
+ *   block_stride, layer_stride, token_stride in elements.  tables: int32 [slots, planes, width].
+ * slots / depths / positions: int64 [rows].  Rows must not overlap each other's destinations
+ * (one row per token).  A shared-plane layout (planes == 1) is a no-op.
+ * ---------------------------------------------------------------------- */
+RLT_API int rlt_finalize_tokens(void* key_pool, void* value_pool, int64_t block_stride, int64_t layer_stride,
+                        int64_t token_stride, int64_t num_blocks, int layers, int block_size, int kv_heads,
+                        int head_dim, int dtype, const int32_t* tables, int planes, int table_width,
+                        const int64_t* slots, const int64_t* depths, const int64_t* positions, int rows,
+                        rlt_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -147,6 +147,15 @@ def accept_rejection(target_logits, draft_logits, cu_rows, tokens, starts, tempe
     return result, status
 
 
+def finalize_tokens(key_pool, value_pool, tables, slots, depths, positions):
+    assert key_pool.dim() == 5 and key_pool.stride() == value_pool.stride()
+    lib().orc_finalize_tokens(_p(key_pool), _p(value_pool), _i64(key_pool.stride(0)), _i64(key_pool.stride(1)),
+                              _i64(key_pool.stride(2)), key_pool.shape[1], key_pool.shape[2], key_pool.shape[3],
+                              key_pool.shape[4], _DTYPES[key_pool.dtype], _p(tables.contiguous()), tables.shape[1],
+                              tables.shape[2], _p(slots.contiguous()), _p(depths.contiguous()),
+                              _p(positions.contiguous()), slots.numel())
+
+
 def rollback(starts, emitted, tables, block_size, pages_used=None, refcounts=None,
              written_prefix=None):
     n, planes, width = tables.shape

@@ -95,3 +95,29 @@ def test_rollback_batch_matches_oracle_bit_for_bit():
     assert torch.equal(got.write_offsets.cpu()[ok], want[3][ok])
     assert torch.equal(got_prefix.cpu(), want_prefix)
     assert torch.equal(tables, tables.clone())  # tables are inputs only
+
+
+def test_finalize_tokens_match_the_reference_and_the_oracle(golden):
+    for case in golden("finalize.pt"):
+        key, value = case["key_before"].cuda(), case["value_before"].cuda()
+        rlt.finalize_tokens(key, value, case["tables"].cuda(), case["slots"].cuda(), case["depths"].cuda(),
+                            case["positions"].cuda())
+        assert torch.equal(key.cpu().view(torch.uint8), case["key_after"].view(torch.uint8))
+        assert torch.equal(value.cpu().view(torch.uint8), case["value_after"].view(torch.uint8))
+    # a larger seeded case against the oracle: Ouro-shaped rows, every exit depth
+    g = torch.Generator().manual_seed(4)
+    slots_n, planes, width, layers, block = 9, 4, 6, 24, 16
+    tables = torch.randperm(slots_n * planes * width, generator=g).int().view(slots_n, planes, width)
+    pool = (slots_n * planes * width, layers, block, 16, 128)
+    key = torch.randn(pool, generator=g).bfloat16()
+    value = torch.randn(pool, generator=g).bfloat16()
+    slots = torch.arange(slots_n)
+    depths = torch.tensor([0, 1, 2, 3, 0, 1, 2, 0, 1])
+    positions = torch.randint(0, width * block, (slots_n,), generator=g)
+    want_k, want_v = key.clone(), value.clone()
+    oracle.finalize_tokens(want_k, want_v, tables, slots, depths, positions)
+    got_k, got_v = key.cuda(), value.cuda()
+    rlt.finalize_tokens(got_k, got_v, tables.cuda(), slots.cuda(), depths.cuda(), positions.cuda())
+    assert torch.equal(got_k.cpu().view(torch.int16), want_k.view(torch.int16))
+    assert torch.equal(got_v.cpu().view(torch.int16), want_v.view(torch.int16))
+    assert not torch.equal(want_k, key)

@@ -246,3 +246,12 @@ def test_rollback_frontiers_and_slot_mapping(golden):
         assert int(lengths[0]) == case["context_length"]
         assert int(offsets[0]) == case["write_offset"]
         assert torch.equal(blocks[0], case["write_blocks"])
+
+
+def test_finalize_tokens_match_the_reference_pools(golden):
+    for case in golden("finalize.pt"):
+        key, value = case["key_before"].clone(), case["value_before"].clone()
+        oracle.finalize_tokens(key, value, case["tables"], case["slots"], case["depths"], case["positions"])
+        assert torch.equal(key.view(torch.uint8), case["key_after"].view(torch.uint8))
+        assert torch.equal(value.view(torch.uint8), case["value_after"].view(torch.uint8))
+        assert not torch.equal(case["key_before"], case["key_after"])

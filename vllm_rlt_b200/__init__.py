@@ -12,7 +12,7 @@ from .activation import register_torch_op, silu_and_mul
 from .attention import (B200_CAPABILITIES, AttentionBackend, B200PagedAttention, BackendCapabilities,
                         create_backend)
 from .decoder import DecodeStats, PagedKV, SelfSpeculativeDecoder
-from .kv_cache import RollbackResult, kv_write, rollback
+from .kv_cache import RollbackResult, finalize_tokens, kv_write, rollback
 from .looped_lm import LoopedLM, LoopedLMConfig, seeded_state_dict
 from .speculative import (SpeculativeResult, accept_greedy, accept_rejection, argmax_rows, decode_result,
                           raise_for_status, sample_rows)
@@ -21,6 +21,6 @@ __all__ = [
     "AttentionBackend", "B200PagedAttention", "DecodeStats", "LoopedLM", "LoopedLMConfig", "PagedKV",
     "SelfSpeculativeDecoder", "seeded_state_dict", "B200_CAPABILITIES", "BackendCapabilities",
     "NativeLibraryMissing", "RollbackResult", "SpeculativeResult", "accept_greedy", "accept_rejection",
-    "argmax_rows", "create_backend", "decode_result", "kv_write", "load_library", "raise_for_status",
+    "argmax_rows", "create_backend", "decode_result", "finalize_tokens", "kv_write", "load_library", "raise_for_status",
     "register_torch_op", "rollback", "sample_rows", "silu_and_mul",
 ]

@@ -40,6 +40,7 @@ SIGNATURES = {
     "rlt_accept_rejection_workspace_bytes": (_Z, [_I]),
     "rlt_accept_rejection": (_I, [_P, _P, _L, _I, _I, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P,
                                   _P, _Z, _P]),
+    "rlt_finalize_tokens": (_I, [_P, _P, _L, _L, _L, _L, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P]),
     "rlt_rollback": (_I, [_P, _P, _I, _P, _I, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _P, _P, _P]),
 }
 

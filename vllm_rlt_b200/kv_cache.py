@@ -56,6 +56,38 @@ def kv_write(key_cache, value_cache, k, v, write_blocks, write_offsets, write_ma
     _capi.check(status, "kv_write")
 
 
+def finalize_tokens(key_pool, value_pool, tables, slots, depths, positions) -> None:
+    """Copy each token's exit-depth K/V (all layers) into every deeper plane of its request.
+
+    The batched device form of `KVCacheManager.finalize_token` (core/kv_cache_manager.py:805-831).
+    key_pool / value_pool: the whole pool `[blocks, layers, block_size, kv_heads, head_dim]`;
+    tables: int32 `[slots, planes, pages]`; slots / depths / positions: int64 `[rows]`.
+    """
+    _capi.require_cuda(key_pool, value_pool, tables, slots, depths, positions)
+    if key_pool.dim() != 5 or value_pool.shape != key_pool.shape or key_pool.stride() != value_pool.stride():
+        raise ValueError("key_pool/value_pool must be matching [blocks, layers, block_size, kv_heads, head_dim] pools")
+    if key_pool.stride(4) != 1 or key_pool.stride(3) != key_pool.shape[4]:
+        raise ValueError("the [kv_heads, head_dim] tail of the KV pool must be contiguous")
+    if key_pool.dtype not in _capi.DTYPE_CODES or value_pool.dtype != key_pool.dtype:
+        raise ValueError("KV dtype must be float32, float16, or bfloat16")
+    if tables.dim() != 3 or tables.dtype != torch.int32:
+        raise ValueError("tables must be int32 [slots, planes, pages]")
+    rows = slots.numel()
+    for name, t in (("slots", slots), ("depths", depths), ("positions", positions)):
+        if t.dtype != torch.int64 or t.shape != (rows,):
+            raise ValueError(f"{name} must be int64 [rows]")
+    if rows == 0:
+        return
+    blocks, layers, block_size, kv_heads, head_dim = key_pool.shape
+    with torch.cuda.device(key_pool.device):
+        status = _capi.load().rlt_finalize_tokens(
+            _capi.ptr(key_pool), _capi.ptr(value_pool), key_pool.stride(0), key_pool.stride(1), key_pool.stride(2),
+            blocks, layers, block_size, kv_heads, head_dim, _capi.DTYPE_CODES[key_pool.dtype],
+            _capi.ptr(tables.contiguous()), tables.shape[1], tables.shape[2], _capi.ptr(slots.contiguous()),
+            _capi.ptr(depths.contiguous()), _capi.ptr(positions.contiguous()), rows, _capi.stream_of(key_pool))
+    _capi.check(status, "finalize_tokens")
+
+
 @dataclass
 class RollbackResult:
     """Device tensors describing the state after rollback (one entry per request)."""
