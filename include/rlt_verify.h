@@ -328,6 +328,29 @@ RLT_API int rlt_finalize_tokens(void* key_pool, void* value_pool, int64_t block_
                         const int64_t* slots, const int64_t* depths, const int64_t* positions, int rows,
                         rlt_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Pipeline-mode self-speculation: device state update of every request after one pipeline step
+ * (the retained-hidden-state rollback).  Request i keeps `width` oldest-first slots
+ * (tokens, depths, candidates, active, hidden rows); the step advanced its first widths[i] slots
+ * by draft_loops loops and produced, request-major from row row_starts[i], the LM-head argmax
+ * `choices` and the hidden rows `step_hidden`.  The head slot that reached target_loops is
+ * emitted and compared with its draft candidate: on a match the slots (and their hidden rows)
+ * shift down and a new draft slot is born at the tail; on a mismatch all descendants are dropped
+ * and the pipeline restarts from the corrected token; nothing is born at or beyond limits[i].
+ * result[6i .. 6i+5] = prediction, accepted, emitted, next position, drafted count, verified count.
+ * Replaces: the per-request tensor program of AsyncSpeculativeRunner._pipeline_step
+ *   (vllm_rlt/worker/async_speculative.py:527-580; wire layout :62-77).
+ * tokens / depths / candidates: int64 [n, width]; active: uint8/bool [n, width];
+ * hidden: [n, width, hidden_size] of `dtype`; state_token / state_position / limits: int64 [n];
+ * widths / row_starts: int32 [n]; choices: int64 [rows]; step_hidden: [rows, hidden_size].
+ * All state arrays are updated in place.  width <= 64.
+ * ---------------------------------------------------------------------- */
+RLT_API int rlt_pipeline_shift(int64_t* tokens, int64_t* depths, int64_t* candidates, uint8_t* active,
+                       void* hidden, int64_t* state_token, int64_t* state_position, const int32_t* widths,
+                       const int32_t* row_starts, const int64_t* choices, const void* step_hidden,
+                       const int64_t* limits, int n, int width, int hidden_size, int dtype, int draft_loops,
+                       int target_loops, int64_t* result, rlt_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

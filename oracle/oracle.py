@@ -156,6 +156,18 @@ def finalize_tokens(key_pool, value_pool, tables, slots, depths, positions):
                               _p(positions.contiguous()), slots.numel())
 
 
+def pipeline_shift(state, widths, row_starts, choices, step_hidden, limits, draft_loops, target_loops):
+    """In place on `state` (dict of tokens, depths, candidates, active(uint8), hidden, token, position); returns result."""
+    n, width = state["tokens"].shape
+    result = torch.zeros(6 * n, dtype=torch.int64)
+    lib().orc_pipeline_shift(_p(state["tokens"]), _p(state["depths"]), _p(state["candidates"]), _p(state["active"]),
+                             _p(state["hidden"]), _p(state["token"]), _p(state["position"]), _p(widths),
+                             _p(row_starts), _p(choices), _p(step_hidden.contiguous()), _p(limits), n, width,
+                             state["hidden"].shape[2], _DTYPES[state["hidden"].dtype], draft_loops, target_loops,
+                             _p(result))
+    return result
+
+
 def rollback(starts, emitted, tables, block_size, pages_used=None, refcounts=None,
              written_prefix=None):
     n, planes, width = tables.shape

@@ -179,3 +179,25 @@ def test_error_statuses_are_reported_not_raised_on_device():
     draft[0, 3] = 0.0
     _, status = rlt.accept_rejection(target.cuda(), draft.cuda(), *[a.cuda() for a in args])
     assert status.tolist() == [3]
+
+
+def test_pipeline_shift_matches_every_reference_step(golden):
+    data = golden("pipeline.pt")
+    for dtype in (torch.float32, torch.bfloat16):
+        for step in data["steps"]:
+            before, after = step["before"], step["after"]
+            n = before["tokens"].shape[0]
+            state = rlt.PipelineState(
+                tokens=before["tokens"].cuda(), depths=before["depths"].cuda(), candidates=before["candidates"].cuda(),
+                active=before["active"].cuda(), hidden=before["hidden"].to(dtype).cuda(), token=before["token"].cuda(),
+                position=before["position"].cuda())
+            widths = step["widths"]
+            row_starts = torch.zeros(n, dtype=torch.int32)
+            row_starts[1:] = widths.cumsum(0)[:-1].int()
+            result = rlt.pipeline_shift(state, widths.cuda(), row_starts.cuda(), step["choices"].cuda(),
+                                        step["step_hidden"].to(dtype).cuda(), data["limits"].cuda(),
+                                        draft_loops=data["draft_loops"], target_loops=data["target_loops"])
+            assert torch.equal(result.cpu().flatten(), after["result"])
+            for key in ("tokens", "depths", "candidates", "active", "token", "position"):
+                assert torch.equal(getattr(state, key).cpu(), after[key]), key
+            assert torch.equal(state.hidden.cpu(), after["hidden"].to(dtype))

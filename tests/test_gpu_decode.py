@@ -56,3 +56,40 @@ def test_bf16_ouro_shaped_heads_use_the_tiled_kernel_and_agree_with_native():
     # rows decoded one at a time; greedy tokens still have to agree almost everywhere.
     same = sum(a == b for x, y in zip(native, speculative) for a, b in zip(x, y))
     assert same >= 0.8 * 36
+
+
+def test_rejection_sampled_decoding_collapses_to_greedy_at_vanishing_temperature(golden):
+    # At T -> 0 every distribution is a point mass on its argmax, so drafts sampled from q,
+    # the u*q < p tests and the residual / bonus draws must reproduce greedy decoding exactly,
+    # whatever the uniforms are: the reference's golden tokens again, through sample_rows and
+    # accept_rejection instead of argmax and accept_greedy.
+    case = golden("decode.pt")["config1"]
+    model = build(case)
+    for seed in (0, 7):
+        decoder = rlt.SelfSpeculativeDecoder(model, block=case["block"])
+        tokens = decoder.generate(case["prompts"], case["max_tokens"], num_speculative_tokens=case["k"],
+                                  draft_loops=case["draft_loops"], target_loops=case["target_loops"],
+                                  temperature=1e-5, seed=seed)
+        assert tokens == case["tokens"]
+        assert decoder.stats.committed_tokens == case["stats"]["committed"]
+
+
+def test_rejection_sampled_decoding_is_reproducible_and_seed_dependent(golden):
+    case = golden("decode.pt")["tiny_k3"]
+    model = build(case)
+
+    def run(seed):
+        decoder = rlt.SelfSpeculativeDecoder(model, block=case["block"])
+        tokens = decoder.generate(case["prompts"], case["max_tokens"], num_speculative_tokens=3, temperature=0.8,
+                                  seed=seed)
+        return tokens, decoder.stats
+
+    first, stats = run(3)
+    again, _ = run(3)
+    other, _ = run(4)
+    assert first == again and first != other
+    assert all(len(t) == case["max_tokens"] for t in first)
+    assert all(0 <= x < case["config"]["vocab_size"] for t in first for x in t)
+    assert stats.committed_tokens == sum(len(t) - 1 for t in first)
+    # the first token of every request comes from the prefill argmax, so it matches greedy
+    assert [t[0] for t in first] == [t[0] for t in case["tokens"]]

@@ -255,3 +255,31 @@ def test_finalize_tokens_match_the_reference_pools(golden):
         assert torch.equal(key.view(torch.uint8), case["key_after"].view(torch.uint8))
         assert torch.equal(value.view(torch.uint8), case["value_after"].view(torch.uint8))
         assert not torch.equal(case["key_before"], case["key_after"])
+
+
+def _pipeline_inputs(step, n):
+    widths = step["widths"]
+    row_starts = torch.zeros(n, dtype=torch.int32)
+    row_starts[1:] = widths.cumsum(0)[:-1].int()
+    return widths, row_starts
+
+
+def test_pipeline_shift_matches_every_reference_step(golden):
+    data = golden("pipeline.pt")
+    seen = set()
+    for step in data["steps"]:
+        before, after = step["before"], step["after"]
+        n = before["tokens"].shape[0]
+        state = {k: before[k].clone() for k in ("tokens", "depths", "candidates", "hidden", "token", "position")}
+        state["active"] = before["active"].to(torch.uint8)
+        widths, row_starts = _pipeline_inputs(step, n)
+        result = oracle.pipeline_shift(state, widths, row_starts, step["choices"], step["step_hidden"],
+                                       data["limits"], data["draft_loops"], data["target_loops"])
+        assert torch.equal(result, after["result"])
+        for key in ("tokens", "depths", "candidates", "token", "position"):
+            assert torch.equal(state[key], after[key]), key
+        assert torch.equal(state["active"].bool(), after["active"])
+        assert torch.equal(state["hidden"], after["hidden"])
+        for row in after["result"].view(n, 6).tolist():
+            seen.add((row[1], row[2]))
+    assert seen == {(0, 0), (0, 1), (1, 1)}  # waiting, rejected and accepted steps all occur

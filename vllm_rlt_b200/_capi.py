@@ -41,6 +41,7 @@ SIGNATURES = {
     "rlt_accept_rejection": (_I, [_P, _P, _L, _I, _I, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P,
                                   _P, _Z, _P]),
     "rlt_finalize_tokens": (_I, [_P, _P, _L, _L, _L, _L, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P]),
+    "rlt_pipeline_shift": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P]),
     "rlt_rollback": (_I, [_P, _P, _I, _P, _I, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _P, _P, _P]),
 }
 

@@ -21,7 +21,7 @@ import torch
 
 from .kv_cache import rollback
 from .looped_lm import LoopedLM
-from .speculative import accept_greedy, argmax_rows
+from .speculative import accept_greedy, accept_rejection, argmax_rows, raise_for_status, sample_rows
 
 
 @dataclass
@@ -122,14 +122,21 @@ class SelfSpeculativeDecoder:
     # ---- block self-speculation ----------------------------------------------------------
     @torch.no_grad()
     def generate(self, prompts, max_tokens: int, *, num_speculative_tokens: int, draft_loops: int = 2,
-                 target_loops: int | None = None):
+                 target_loops: int | None = None, temperature: float = 0.0, seed: int = 0):
+        """Block self-speculation.  `temperature == 0` is greedy acceptance; otherwise drafts are
+        sampled from softmax(draft logits / T) and verified by rejection sampling with residual
+        resampling (worker/speculative.py:47-63, 483-510 of the reference), with every uniform
+        drawn from one seeded device generator in the reference's order per round: the draft
+        draws, then the accept tests, then the final (residual or bonus) draw."""
         model, device = self.model, self.model.device
+        sampled = temperature > 0
+        generator = torch.Generator(device=device).manual_seed(seed) if sampled else None
         target_loops = target_loops or model.config.total_ut_steps
         if not 0 < draft_loops < target_loops <= model.config.total_ut_steps:
             raise ValueError("draft_loops must be smaller than target_loops")
         k = num_speculative_tokens
         kv = PagedKV.allocate(model, [len(p) + max_tokens + k + 1 for p in prompts], self.block)
-        generated = [[t] for t in self._prefill(kv, prompts)]
+        generated = [[t] for t in self._prefill(kv, prompts)]  # the first token is the prefill's argmax
         slot_values = torch.zeros(len(prompts), 2, dtype=torch.int64, device=device)
         while any(len(g) < max_tokens for g in generated):
             active = [i for i, g in enumerate(generated) if len(g) < max_tokens]
@@ -139,6 +146,12 @@ class SelfSpeculativeDecoder:
             tokens = torch.zeros(n, width, dtype=torch.int64, device=device)
             tokens[:, 0] = torch.tensor([generated[i][-1] for i in active], device=device)
             retained = [[] for _ in active]
+            firsts = [sum(counts[:j]) for j in range(n)]
+            rows_total = sum(counts)
+            draft_logits = None
+            if sampled:  # row j of a request keeps the logits its draft j+1 was sampled from
+                draft_logits = torch.zeros(rows_total, model.config.vocab_size, dtype=torch.float32, device=device)
+                u_draft = torch.rand(n, width, generator=generator, device=device)
             # draft: one new position per request and offset, loops 0 .. d-1
             for offset in range(width):
                 rows = [j for j, c in enumerate(counts) if offset < c]
@@ -152,8 +165,15 @@ class SelfSpeculativeDecoder:
                 drafting = [(row, j) for row, j in enumerate(rows) if offset + 1 < counts[j]]
                 if not drafting:
                     break
-                logits = model.coda(torch.stack([hidden[row] for row, _ in drafting]))
-                tokens[[j for _, j in drafting], offset + 1] = argmax_rows(logits.float().contiguous())
+                logits = model.coda(torch.stack([hidden[row] for row, _ in drafting])).float().contiguous()
+                drafting_requests = [j for _, j in drafting]
+                if sampled:
+                    draft_logits[[firsts[j] + offset for j in drafting_requests]] = logits
+                    proposed, status = sample_rows(logits, torch.full((len(drafting),), temperature, device=device),
+                                                   u_draft[drafting_requests, offset].contiguous())
+                else:
+                    proposed = argmax_rows(logits)
+                tokens[drafting_requests, offset + 1] = proposed
                 self.stats.drafted_tokens += len(drafting)
             # verify: the retained depth-d states of all rows, request-major, loops d .. D-1
             hidden = torch.stack([h for per_request in retained for h in per_request])
@@ -165,13 +185,20 @@ class SelfSpeculativeDecoder:
             cu_rows = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=device)
             start_tensor = torch.tensor(starts, device=device)
             slots = torch.arange(n, device=device)
-            result = accept_greedy(logits, cu_rows, tokens.contiguous(), start_tensor, slots, slot_values[:n].contiguous())
-            rows_total = sum(counts)
+            if sampled:
+                result, status = accept_rejection(
+                    logits, draft_logits, cu_rows, tokens.contiguous(), start_tensor,
+                    torch.full((n,), temperature, device=device), torch.rand(rows_total, generator=generator, device=device),
+                    torch.rand(n, generator=generator, device=device), slots, slot_values[:n].contiguous())
+            else:
+                status = torch.zeros(n, dtype=torch.int32, device=device)
+                result = accept_greedy(logits, cu_rows, tokens.contiguous(), start_tensor, slots,
+                                       slot_values[:n].contiguous())
             accepted = result[rows_total:rows_total + n]
             rolled = rollback(start_tensor, accepted + 1, kv.tables[torch.tensor(active, device=device)].contiguous(),
                               self.block)
-            values = torch.cat([result, rolled.frontier]).tolist()  # the round's one host read
-            firsts = [sum(counts[:j]) for j in range(n)]
+            values = torch.cat([result, rolled.frontier, status.long()]).tolist()  # the round's one host read
+            raise_for_status(values[rows_total + 3 * n:])
             for j, i in enumerate(active):
                 a = values[rows_total + j]
                 emitted = values[firsts[j]:firsts[j] + a + 1]

@@ -161,6 +161,66 @@ def accept_rejection(target_logits, draft_logits, cu_rows, tokens, starts, tempe
     return result, status
 
 
+@dataclass
+class PipelineState:
+    """Batched form of the reference's DevicePipelineState + per-request (token, position)
+    (worker/async_speculative.py:28-50): `width` oldest-first slots per request, all on the device."""
+
+    tokens: torch.Tensor       # int64 [n, width]
+    depths: torch.Tensor       # int64 [n, width]
+    candidates: torch.Tensor   # int64 [n, width]
+    active: torch.Tensor       # bool  [n, width]
+    hidden: torch.Tensor       # model dtype [n, width, hidden_size]
+    token: torch.Tensor        # int64 [n]  last committed token
+    position: torch.Tensor     # int64 [n]  its position
+
+
+def pipeline_shift(state: PipelineState, widths, row_starts, choices, step_hidden, limits, *, draft_loops: int,
+                   target_loops: int, result=None):
+    """Apply one pipeline step's outcome to every request's device state, in place.
+
+    The fused form of the per-request program at the end of `AsyncSpeculativeRunner._pipeline_step`
+    (async_speculative.py:527-580): emit the head slot that reached `target_loops`, accept or reject its
+    draft candidate, shift the surviving slots and their retained hidden rows, start the next draft slot
+    (or restart from the corrected token), honour the output limit.  Returns the int64 wire buffer
+    `[n, 6]` = prediction, accepted, emitted, next position, drafted count, verified count.
+    """
+    _capi.require_cuda(state.tokens, state.depths, state.candidates, state.active, state.hidden, state.token,
+                       state.position, widths, row_starts, choices, step_hidden, limits, result)
+    n, width = state.tokens.shape
+    for name, t in (("tokens", state.tokens), ("depths", state.depths), ("candidates", state.candidates)):
+        if t.dtype != torch.int64 or t.shape != (n, width) or not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous int64 [requests, width]")
+    if state.active.dtype != torch.bool or state.active.shape != (n, width) or not state.active.is_contiguous():
+        raise ValueError("active must be contiguous bool [requests, width]")
+    if state.hidden.dim() != 3 or state.hidden.shape[:2] != (n, width) or not state.hidden.is_contiguous() \
+            or state.hidden.dtype not in _capi.DTYPE_CODES:
+        raise ValueError("hidden must be contiguous [requests, width, hidden_size]")
+    for name, t in (("token", state.token), ("position", state.position), ("limits", limits)):
+        if t.dtype != torch.int64 or t.shape != (n,) or not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous int64 [requests]")
+    for name, t in (("widths", widths), ("row_starts", row_starts)):
+        if t.dtype != torch.int32 or t.shape != (n,):
+            raise ValueError(f"{name} must be int32 [requests]")
+    if choices.dtype != torch.int64 or step_hidden.dtype != state.hidden.dtype \
+            or step_hidden.shape != (choices.numel(), state.hidden.shape[2]):
+        raise ValueError("choices must be int64 [rows] and step_hidden [rows, hidden_size] of the state dtype")
+    if result is None:
+        result = torch.empty(6 * n, dtype=torch.int64, device=state.tokens.device)
+    if n == 0:
+        return result.view(0, 6)
+    with torch.cuda.device(state.tokens.device):
+        status = _capi.load().rlt_pipeline_shift(
+            _capi.ptr(state.tokens), _capi.ptr(state.depths), _capi.ptr(state.candidates), _capi.ptr(state.active),
+            _capi.ptr(state.hidden), _capi.ptr(state.token), _capi.ptr(state.position),
+            _capi.ptr(widths.contiguous()), _capi.ptr(row_starts.contiguous()), _capi.ptr(choices.contiguous()),
+            _capi.ptr(step_hidden.contiguous()), _capi.ptr(limits), n, width, state.hidden.shape[2],
+            _capi.DTYPE_CODES[state.hidden.dtype], draft_loops, target_loops, _capi.ptr(result),
+            _capi.stream_of(state.tokens))
+    _capi.check(status, "pipeline_shift")
+    return result[: 6 * n].view(n, 6)
+
+
 def raise_for_status(status_values) -> None:
     """Raise what the reference raises for a per-request status list already on the host."""
     for i, code in enumerate(status_values):
