@@ -501,6 +501,44 @@ def run_small_only(args):
     print(json.dumps(out))
 
 
+def run_decode_workload(args):
+    """Secondary workload (`--workload decode`): self-speculative decoding of a random-init
+    Ouro-1.4B-shaped model (24 layers, hidden 2048, 16 x 128 MHA, FFN 5632, vocab 49152, 4 loops, bf16)
+    through `vllm_rlt_b200.SelfSpeculativeDecoder` — BASELINE configs[2] with the output length set by
+    `--output-tokens`.  GEMMs / norms / RoPE are eager PyTorch around the kernels, so this number is
+    launch-bound like the reference's eager mode; the prefill is outside the timed region."""
+    import vllm_rlt_b200 as rlt
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    config = rlt.LoopedLMConfig()
+    model = rlt.LoopedLM(config, rlt.seeded_state_dict(config, 3, device=device), device, torch.bfloat16)
+    g = torch.Generator().manual_seed(11)
+    lengths = torch.randint(128, 1025, (args.requests,), generator=g).tolist()
+    prompts = [torch.randint(1, config.vocab_size, (n,), generator=g).tolist() for n in lengths]
+    decoder = rlt.SelfSpeculativeDecoder(model)
+    clock = {}
+
+    def start_clock():
+        torch.cuda.synchronize()
+        clock["start"] = time.perf_counter()
+
+    tokens = decoder.generate(prompts, args.output_tokens, num_speculative_tokens=4, draft_loops=2, target_loops=4,
+                              temperature=args.temperature, seed=1, after_prefill=start_clock)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - clock["start"]
+    stats = decoder.stats
+    print(json.dumps({
+        "workload": "decode: Ouro-1.4B-shaped random-init bf16, self-spec k=4 from depth 2, "
+                    f"{args.requests} requests, prompts U[128,1024], {args.output_tokens} output tokens, T={args.temperature}",
+        "decode_seconds": seconds, "committed_tokens": stats.committed_tokens, "accepted_tokens": stats.accepted_tokens,
+        "drafted_tokens": stats.drafted_tokens, "request_rounds": stats.rounds,
+        "committed_tokens_per_s": stats.committed_tokens / seconds,
+        "accepted_tokens_per_s": stats.accepted_tokens / seconds,
+        "acceptance_rate": stats.accepted_tokens / max(stats.drafted_tokens, 1),
+        "tokens_out": sum(len(t) for t in tokens), "attention_status": model.attention.last_status(device)}))
+
+
 def cpu_step_seconds(threads: int, budget_s: float):
     """Times the CPU oracle on a bounded sample of the same workload and extrapolates linearly
     to one full step.  Returns (estimated seconds per step, accepted tokens per step, sample text)."""
@@ -592,6 +630,10 @@ def main():
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--only", default=None, choices=["attention", "accept", "silu"],
                         help="profiling aid: run only this kernel family (not a bench line)")
+    parser.add_argument("--workload", default="step", choices=["step", "decode"],
+                        help="step: the verify-step microbench (the bench line); decode: whole-model decoding (secondary)")
+    parser.add_argument("--output-tokens", type=int, default=32)
+    parser.add_argument("--temperature", type=float, default=0.8)
     parser.add_argument("--requests", type=int, default=REQUESTS)
     parser.add_argument("--layers", type=int, default=LAYERS)
     parser.add_argument("--tokens", type=int, default=TOKENS, help="with --only attention: new tokens per request")
@@ -605,6 +647,9 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the verify-step kernels have no CPU fallback")
+    if args.workload == "decode":
+        run_decode_workload(args)
+        return
     if args.only == "attention":
         run_attention_only(args)
         return

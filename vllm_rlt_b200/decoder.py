@@ -122,12 +122,13 @@ class SelfSpeculativeDecoder:
     # ---- block self-speculation ----------------------------------------------------------
     @torch.no_grad()
     def generate(self, prompts, max_tokens: int, *, num_speculative_tokens: int, draft_loops: int = 2,
-                 target_loops: int | None = None, temperature: float = 0.0, seed: int = 0):
+                 target_loops: int | None = None, temperature: float = 0.0, seed: int = 0, after_prefill=None):
         """Block self-speculation.  `temperature == 0` is greedy acceptance; otherwise drafts are
         sampled from softmax(draft logits / T) and verified by rejection sampling with residual
         resampling (worker/speculative.py:47-63, 483-510 of the reference), with every uniform
         drawn from one seeded device generator in the reference's order per round: the draft
-        draws, then the accept tests, then the final (residual or bonus) draw."""
+        draws, then the accept tests, then the final (residual or bonus) draw.  `after_prefill`, if
+        given, is called once the prompts are in the cache (benchmarks start their clock there)."""
         model, device = self.model, self.model.device
         sampled = temperature > 0
         generator = torch.Generator(device=device).manual_seed(seed) if sampled else None
@@ -137,53 +138,66 @@ class SelfSpeculativeDecoder:
         k = num_speculative_tokens
         kv = PagedKV.allocate(model, [len(p) + max_tokens + k + 1 for p in prompts], self.block)
         generated = [[t] for t in self._prefill(kv, prompts)]  # the first token is the prefill's argmax
+        if after_prefill is not None:
+            after_prefill()
         slot_values = torch.zeros(len(prompts), 2, dtype=torch.int64, device=device)
         while any(len(g) < max_tokens for g in generated):
             active = [i for i, g in enumerate(generated) if len(g) < max_tokens]
             counts = [min(k + 1, max_tokens - len(generated[i])) for i in active]
             starts = [len(prompts[i]) + len(generated[i]) - 1 for i in active]
             n, width = len(active), max(counts)
+            rows_total = sum(counts)
+            counts_t = torch.tensor(counts)
+            active_t = torch.tensor(active, device=device)
+            starts_t = torch.tensor(starts, device=device)
             tokens = torch.zeros(n, width, dtype=torch.int64, device=device)
             tokens[:, 0] = torch.tensor([generated[i][-1] for i in active], device=device)
-            retained = [[] for _ in active]
-            firsts = [sum(counts[:j]) for j in range(n)]
-            rows_total = sum(counts)
+            # which (request, offset) cells exist, and where each lands among the retained rows
+            present = counts_t[:, None] > torch.arange(width)[None, :]                 # [n, width]
+            per_offset = present.sum(0)                                                # rows of draft pass o
+            rank = present.long().cumsum(0) - 1                                        # row of request j in pass o
+            base = torch.cat([torch.zeros(1, dtype=torch.long), per_offset.cumsum(0)[:-1]])
+            firsts = [0] + counts_t.cumsum(0).tolist()[:-1]
+            gather = (base[None, :] + rank)[present].to(device)                         # request-major order
             draft_logits = None
             if sampled:  # row j of a request keeps the logits its draft j+1 was sampled from
                 draft_logits = torch.zeros(rows_total, model.config.vocab_size, dtype=torch.float32, device=device)
                 u_draft = torch.rand(n, width, generator=generator, device=device)
+                first_row = torch.tensor(firsts, device=device)
+            retained = []
             # draft: one new position per request and offset, loops 0 .. d-1
             for offset in range(width):
-                rows = [j for j, c in enumerate(counts) if offset < c]
-                requests = torch.tensor([active[j] for j in rows], device=device)
-                positions = torch.tensor([starts[j] + offset for j in rows], device=device)
-                hidden = model.prelude(tokens[rows, offset])
+                in_pass = present[:, offset].nonzero().flatten().to(device)             # requests with c > offset
+                hidden = model.prelude(tokens[in_pass, offset])
                 for depth in range(draft_loops):
-                    hidden = self._loop(kv, hidden, requests, positions, depth)
-                for row, j in enumerate(rows):
-                    retained[j].append(hidden[row])
-                drafting = [(row, j) for row, j in enumerate(rows) if offset + 1 < counts[j]]
-                if not drafting:
+                    hidden = self._loop(kv, hidden, active_t[in_pass], starts_t[in_pass] + offset, depth)
+                retained.append(hidden)
+                if offset + 1 >= width:
                     break
-                logits = model.coda(torch.stack([hidden[row] for row, _ in drafting])).float().contiguous()
-                drafting_requests = [j for _, j in drafting]
+                drafting = present[present[:, offset], offset + 1].to(device)           # of this pass's rows
+                if not bool(drafting.any()):
+                    break
+                drafting_requests = in_pass[drafting]
+                logits = model.coda(hidden[drafting]).float().contiguous()
                 if sampled:
-                    draft_logits[[firsts[j] + offset for j in drafting_requests]] = logits
-                    proposed, status = sample_rows(logits, torch.full((len(drafting),), temperature, device=device),
-                                                   u_draft[drafting_requests, offset].contiguous())
+                    draft_logits[first_row[drafting_requests] + offset] = logits
+                    proposed, _ = sample_rows(logits, torch.full((logits.shape[0],), temperature, device=device),
+                                              u_draft[drafting_requests, offset].contiguous())
                 else:
                     proposed = argmax_rows(logits)
                 tokens[drafting_requests, offset + 1] = proposed
-                self.stats.drafted_tokens += len(drafting)
+                self.stats.drafted_tokens += int(logits.shape[0])
             # verify: the retained depth-d states of all rows, request-major, loops d .. D-1
-            hidden = torch.stack([h for per_request in retained for h in per_request])
-            requests = torch.tensor([active[j] for j, c in enumerate(counts) for _ in range(c)], device=device)
-            positions = torch.tensor([starts[j] + o for j, c in enumerate(counts) for o in range(c)], device=device)
+            hidden = torch.cat(retained)[gather]
+            row_request = torch.repeat_interleave(torch.arange(n), counts_t)
+            row_offset = torch.cat([torch.arange(c) for c in counts])
+            requests = active_t[row_request.to(device)]
+            positions = starts_t[row_request.to(device)] + row_offset.to(device)
             for depth in range(draft_loops, target_loops):
                 hidden = self._loop(kv, hidden, requests, positions, depth)
             logits = model.coda(hidden).float().contiguous()
-            cu_rows = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=device)
-            start_tensor = torch.tensor(starts, device=device)
+            cu_rows = torch.tensor([0] + counts_t.cumsum(0).tolist(), dtype=torch.int32, device=device)
+            start_tensor = starts_t
             slots = torch.arange(n, device=device)
             if sampled:
                 result, status = accept_rejection(
@@ -195,8 +209,7 @@ class SelfSpeculativeDecoder:
                 result = accept_greedy(logits, cu_rows, tokens.contiguous(), start_tensor, slots,
                                        slot_values[:n].contiguous())
             accepted = result[rows_total:rows_total + n]
-            rolled = rollback(start_tensor, accepted + 1, kv.tables[torch.tensor(active, device=device)].contiguous(),
-                              self.block)
+            rolled = rollback(start_tensor, accepted + 1, kv.tables[active_t].contiguous(), self.block)
             values = torch.cat([result, rolled.frontier, status.long()]).tolist()  # the round's one host read
             raise_for_status(values[rows_total + 3 * n:])
             for j, i in enumerate(active):
