@@ -118,4 +118,31 @@ RLT_HD unsigned long long rlt_draw_threshold(float u, unsigned long long total) 
   return RLT_D2ULL(RLT_DMUL((double)u, (double)total));
 }
 
+/*
+ * Support filters (strict top-k by index, then top-p;
+ * vllm_rlt/worker/sampler.py:40-54).  Tokens are ranked by (scaled logit descending, token
+ * index ascending); both filters keep a prefix of that ranking, so the support of a row is
+ * described by one cut (key, limit): token v with scaled logit t is kept iff
+ *     rlt_order_key(t) > key  ||  (rlt_order_key(t) == key && v <= limit).
+ * The reference leaves the order among tied logits unspecified; this definition fixes it.
+ * top-k keeps the first k ranks.  top-p keeps rank i iff the probability mass of the ranks
+ * before it (exclusive prefix, as 2^-40 fixed-point integers of e * (1 / z) with z the
+ * normaliser over the top-k support) is <= rlt_top_p_limit(top_p) — the integer form of the
+ * reference's "drop a token once the cumulative probability before it exceeds top_p".
+ */
+RLT_HD uint32_t rlt_order_key(float t) {
+  if (t == 0.0f) t = 0.0f; /* -0 ranks with +0 */
+  uint32_t b = rlt_float_to_bits(t);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+RLT_HD unsigned long long rlt_top_p_limit(float top_p) {
+  if (!(top_p > 0.0f)) return 0ull;
+  return RLT_D2ULL(RLT_DMUL((double)top_p, 1099511627776.0));
+}
+
+RLT_HD int rlt_in_support(uint32_t order_key, int v, uint32_t cut_key, int cut_limit) {
+  return order_key > cut_key || (order_key == cut_key && v <= cut_limit);
+}
+
 #endif /* RLT_CANONICAL_H_ */

@@ -237,22 +237,41 @@ RLT_API int rlt_accept_greedy(const void* logits, int64_t row_stride, int rows, 
                       int64_t* result, rlt_stream_t stream);
 
 /* ------------------------------------------------------------------------
- * Token draw from softmax(logits / temperature) with a supplied uniform:
+ * Sampling distribution of every row: softmax(float(logits) / temperature) restricted to
+ * the strict top-k tokens (by rank, ties broken by the lower token index) and then to the
+ * top-p nucleus (rank i stays iff the probability mass of the ranks before it is <= top_p,
+ * probabilities taken over the top-k support), renormalised.  probs: float32 [rows, vocab],
+ * zero outside the support.  top_k (int32 [rows]) and top_p (float [rows]) may be NULL;
+ * top_k[r] <= 0 or >= vocab and top_p[r] >= 1 switch that filter off.  The host validates
+ * temperature > 0 and 0 < top_p <= 1 (vllm_rlt/sampling_params.py:30-35); a row with
+ * temperature <= 0, NaN / +inf logits or all -inf logits gets status RLT_ROW_BAD_LOGITS and
+ * zeros.  Arithmetic: include/rlt_canonical.h (same bits as the CPU oracle).
+ * Replaces: Sampler.probabilities (vllm_rlt/worker/sampler.py:27-55).
+ * ---------------------------------------------------------------------- */
+RLT_API int rlt_probabilities(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
+                      const float* temperature, const int32_t* top_k, const float* top_p,
+                      float* probs, int32_t* status, rlt_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Token draw from the row's sampling distribution (see rlt_probabilities) with a supplied
+ * uniform:
  *   tokens[r] = first index whose inclusive fixed-point prefix mass exceeds
  *   floor(u[r] * total)   (see rlt_accept_rejection for the arithmetic).
- * temperature[r] == 0 gives argmax.  Used for draft proposals and bonus draws.
+ * temperature[r] == 0 gives argmax.  top_k / top_p: per row, may be NULL.
+ * Used for draft proposals and bonus draws.
  * Replaces: Sampler.sample / Sampler.draw (vllm_rlt/worker/sampler.py:57-81) with the
  *   generator replaced by an explicit uniform.
  * ---------------------------------------------------------------------- */
 RLT_API int rlt_sample_rows(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
-                    const float* temperature, const float* uniforms, int64_t* tokens,
-                    int32_t* status, rlt_stream_t stream);
+                    const float* temperature, const int32_t* top_k, const float* top_p,
+                    const float* uniforms, int64_t* tokens, int32_t* status, rlt_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Rejection-sampling acceptance (sequential per request, parallel over requests).
  * For request i with rows cu_rows[i]..cu_rows[i+1]-1 (c_i rows, c_i-1 drafts) and
  * temperature T_i > 0:
- *   p_j = softmax(target_logits[row_j] / T_i),  q_j = softmax(draft_logits[row_j] / T_i)
+ *   p_j = softmax(target_logits[row_j] / T_i),  q_j = softmax(draft_logits[row_j] / T_i),
+ *         both restricted to top_k[i] / top_p[i] as rlt_probabilities does (NULL: no filter)
  *   for j = 0 .. c_i-2, d = tokens[i, j+1]:
  *       accept iff  u_accept[row_j] * q_j[d] < p_j[d]          (fp32, strict)
  *       on the first rejection emit a draw from max(p_j - q_j, 0) / sum with u_final[i]; stop
@@ -272,8 +291,8 @@ RLT_API int rlt_sample_rows(const void* logits, int64_t row_stride, int rows, in
  * workspace: device scratch of rlt_accept_rejection_workspace_bytes(rows) bytes, 16-byte aligned
  *   (per-row normalisers, filled by the first of the call's two launches).
  * Replaces: rejection_sample (vllm_rlt/worker/speculative.py:47-63), the loop in
- *   SpeculativeRunner._collect_round (:483-510), Sampler.probabilities for top_k = -1,
- *   top_p = 1 (vllm_rlt/worker/sampler.py:27-55).
+ *   SpeculativeRunner._collect_round (:483-510), Sampler.probabilities
+ *   (vllm_rlt/worker/sampler.py:27-55).
  * target_logits, draft_logits: [rows, vocab]; draft row j of a request holds the logits
  *   draft j+1 was sampled from (its last row is unused).
  * ---------------------------------------------------------------------- */
@@ -282,9 +301,10 @@ RLT_API size_t rlt_accept_rejection_workspace_bytes(int rows);
 RLT_API int rlt_accept_rejection(const void* target_logits, const void* draft_logits, int64_t row_stride,
                          int rows, int vocab, int dtype, const int32_t* cu_rows, int n,
                          const int64_t* tokens, int tokens_width, const int64_t* starts,
-                         const float* temperature, const float* u_accept, const float* u_final,
-                         const int64_t* slots, int64_t* slot_values, int64_t* result,
-                         int32_t* status, void* workspace, size_t workspace_bytes, rlt_stream_t stream);
+                         const float* temperature, const int32_t* top_k, const float* top_p,
+                         const float* u_accept, const float* u_final, const int64_t* slots,
+                         int64_t* slot_values, int64_t* result, int32_t* status, void* workspace,
+                         size_t workspace_bytes, rlt_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Device rollback of rejected positions.  For request i with round start

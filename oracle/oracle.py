@@ -115,26 +115,26 @@ def accept_greedy(logits, cu_rows, tokens, starts, slots=None, slot_values=None)
     return result
 
 
-def probabilities(logits_row, temperature):
+def probabilities(logits_row, temperature, top_k=-1, top_p=1.0):
     probs = torch.empty(logits_row.numel(), dtype=torch.float32)
     status = lib().orc_probabilities(_p(logits_row.contiguous()), logits_row.numel(),
                                      _DTYPES[logits_row.dtype], ctypes.c_float(temperature),
-                                     _p(probs))
+                                     int(top_k), ctypes.c_float(top_p), _p(probs))
     return probs, status
 
 
-def sample_rows(logits, temperature, uniforms):
+def sample_rows(logits, temperature, uniforms, top_k=None, top_p=None):
     rows = logits.shape[0]
     tokens = torch.empty(rows, dtype=torch.int64)
     status = torch.empty(rows, dtype=torch.int32)
     lib().orc_sample_rows(_p(logits), _i64(logits.stride(0)), rows, logits.shape[1],
-                          _DTYPES[logits.dtype], _p(temperature), _p(uniforms), _p(tokens),
-                          _p(status))
+                          _DTYPES[logits.dtype], _p(temperature), _p(top_k), _p(top_p), _p(uniforms),
+                          _p(tokens), _p(status))
     return tokens, status
 
 
 def accept_rejection(target_logits, draft_logits, cu_rows, tokens, starts, temperature, u_accept,
-                     u_final, slots=None, slot_values=None):
+                     u_final, slots=None, slot_values=None, top_k=None, top_p=None):
     rows, n = target_logits.shape[0], cu_rows.numel() - 1
     assert target_logits.stride() == draft_logits.stride()
     result = torch.empty(rows + 2 * n, dtype=torch.int64)
@@ -142,7 +142,7 @@ def accept_rejection(target_logits, draft_logits, cu_rows, tokens, starts, tempe
     lib().orc_accept_rejection(_p(target_logits), _p(draft_logits), _i64(target_logits.stride(0)),
                                rows, target_logits.shape[1], _DTYPES[target_logits.dtype],
                                _p(cu_rows), n, _p(tokens), tokens.shape[1], _p(starts),
-                               _p(temperature), _p(u_accept), _p(u_final), _p(slots),
+                               _p(temperature), _p(top_k), _p(top_p), _p(u_accept), _p(u_final), _p(slots),
                                _p(slot_values), _p(result), _p(status))
     return result, status
 

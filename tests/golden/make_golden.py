@@ -162,7 +162,7 @@ def golden_async_accept():
 
 
 def golden_sampler():
-    out = dict(probabilities=[], rejection=[], distribution=[])
+    out = dict(probabilities=[], rejection=[], distribution=[], filtered=[])
     g = torch.Generator().manual_seed(5)
     for vocab, temperature, scale in ((4, 1.0, 1.0), (64, 0.7, 1.0), (1024, 0.8, 3.0), (4099, 1.3, 3.0)):
         logits = torch.randn(vocab, generator=g) * scale
@@ -196,6 +196,29 @@ def golden_sampler():
     for p, q in (([0.1, 0.6, 0.3], [0.7, 0.2, 0.1]), ([0.0, 1.0, 0.0], [1.0, 0.0, 0.0]),
                  ([0.2, 0.3, 0.5], [0.2, 0.3, 0.5])):
         out["distribution"].append(dict(p=torch.tensor(p), q=torch.tensor(q)))
+    # top-k / top-p supports and distributions (Sampler.probabilities, worker/sampler.py:40-54), drawn
+    # after everything above so the earlier cases keep their generator stream.
+    def filtered(logits, temperature, top_k, top_p, tied=False):
+        params = SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p)
+        out["filtered"].append(dict(logits=logits, temperature=temperature, top_k=top_k, top_p=top_p, tied=tied,
+                                    probs=Sampler.probabilities(logits, params)))
+    # the reference's own cases: tests/test_sampler.py:87-166, tests/test_speculative.py:423-434
+    filtered(torch.tensor([5.0, 4.0, 4.0, 1.0]), 1.0, 2, 1.0, tied=True)
+    filtered(torch.zeros(4), 1.0, 1, 1.0, tied=True)
+    filtered(torch.tensor([1.0, 2.0, 3.0]), 1.0, 3, 1.0)
+    filtered(torch.tensor([1.0, 2.0, 3.0]), 1.0, 5, 1.0)
+    filtered(torch.tensor([4.0, 3.0, 2.0, 1.0]), 1.0, 3, 0.8)
+    filtered(torch.linspace(1.0, 0.0, 100), 1.0, -1, 0.005)
+    filtered(torch.tensor([1.0, 0.9, 0.8, 0.7]), 1.0, -1, 0.5)
+    filtered(torch.tensor([0.50, 0.25, 0.15, 0.10]).log(), 1.0, -1, 0.8)
+    filtered(torch.tensor([0.50, 0.25, 0.15, 0.10]).log(), 0.5, 2, 1.0)
+    for vocab, temperature, scale, top_k, top_p in (
+            (64, 0.7, 1.0, 8, 1.0), (64, 0.7, 1.0, -1, 0.9), (64, 1.0, 2.0, 16, 0.5),
+            (1024, 0.8, 3.0, 50, 1.0), (1024, 0.8, 3.0, -1, 0.95), (1024, 0.8, 3.0, 40, 0.9),
+            (1024, 1.5, 1.0, -1, 0.3), (1024, 1.5, 1.0, 1000, 0.999), (1024, 0.3, 3.0, 5, 0.99),
+            (4099, 1.3, 3.0, 257, 0.9), (4099, 0.8, 3.0, -1, 0.8), (4099, 2.0, 0.5, 4098, 0.6),
+            (4099, 1.0, 3.0, 1, 0.5), (4099, 1.0, 3.0, -1, 0.01)):
+        filtered(torch.randn(vocab, generator=g) * scale, temperature, top_k, top_p)
     torch.save(out, HERE / "sampler.pt")
 
 

@@ -144,6 +144,127 @@ def test_rejection_round_matches_oracle_bit_for_bit(noise, dtype):
         assert int(accepted.sum()) < int(drafts_per_request.sum()) // 2
 
 
+def _oracle_probabilities(logits, temperature, top_k, top_p):
+    rows = []
+    for r in range(logits.shape[0]):
+        probs, status = oracle.probabilities(logits[r], float(temperature[r]), int(top_k[r]), float(top_p[r]))
+        assert status == 0
+        rows.append(probs)
+    return torch.stack(rows)
+
+
+def test_filtered_probabilities_of_the_reference(golden):
+    """Sampler.probabilities with top-k / top-p: support exact, values to fp32 rounding."""
+    for case in golden("sampler.pt")["filtered"]:
+        probs, status = rlt.probabilities(case["logits"][None].cuda(), torch.tensor([case["temperature"]]).cuda(),
+                                          torch.tensor([case["top_k"]], dtype=torch.int32).cuda(),
+                                          torch.tensor([case["top_p"]]).cuda())
+        assert int(status[0]) == 0
+        probs = probs[0].cpu()
+        if case["tied"]:
+            torch.testing.assert_close(probs.sort().values, case["probs"].sort().values, rtol=2e-6, atol=1e-12)
+        else:
+            assert torch.equal(probs > 0, case["probs"] > 0), (case["top_k"], case["top_p"])
+            torch.testing.assert_close(probs, case["probs"], rtol=4e-6, atol=1e-12)
+
+
+@pytest.mark.parametrize("vocab,dtype,levels", [(49152, torch.float32, 0), (49152, torch.bfloat16, 0),
+                                                (4099, torch.float32, 0), (1027, torch.float32, 9),
+                                                (49152, torch.float32, 33), (300, torch.float16, 0)])
+def test_filtered_probabilities_match_oracle_bit_for_bit(vocab, dtype, levels):
+    """The radix-select cut equals the oracle's full sort: same support, same bits.  `levels`
+    quantises the logits so that cuts fall inside large tie groups."""
+    g = torch.Generator().manual_seed(vocab + levels)
+    rows = 20
+    logits = torch.randn(rows, vocab, generator=g) * 3
+    if levels:
+        logits = (logits * levels / 12).round() * (12 / levels)
+    logits = logits.to(dtype)
+    logits[3, : vocab // 2] = float("-inf")
+    temperature = torch.tensor([0.8, 1.0, 0.3, 1.7, 5.0] * 4)
+    top_k = torch.tensor([-1, 1, 2, 50, vocab - 1, vocab, 7, 1000, -1, 40] * 2, dtype=torch.int32)
+    top_p = torch.tensor([0.9, 1.0, 0.5, 0.95, 0.999, 0.3, 1.0, 0.01, 0.6, 0.8,
+                          1.0, 0.7, 1.0, 1.0, 0.2, 1.0, 0.99, 0.9999999, 1e-6, 0.5])
+    want = _oracle_probabilities(logits, temperature, top_k, top_p)
+    got, status = rlt.probabilities(logits.cuda(), temperature.cuda(), top_k.cuda(), top_p.cuda())
+    assert not status.any()
+    assert torch.equal(got.cpu(), want)
+    # no filters at all: the unfiltered distribution, whichever way it is requested
+    plain, _ = rlt.probabilities(logits.cuda(), temperature.cuda())
+    off, _ = rlt.probabilities(logits.cuda(), temperature.cuda(), torch.full((rows,), -1, dtype=torch.int32).cuda(),
+                               torch.ones(rows).cuda())
+    assert torch.equal(plain, off)
+    assert torch.equal(plain.cpu(), _oracle_probabilities(logits, temperature, [-1] * rows, [1.0] * rows))
+
+
+def test_probabilities_reject_greedy_and_bad_rows():
+    logits = torch.randn(3, 64)
+    logits[2, 5] = float("nan")
+    probs, status = rlt.probabilities(logits.cuda(), torch.tensor([0.0, 1.0, 1.0]).cuda())
+    assert status.tolist() == [3, 0, 3]
+    assert not probs[0].any() and not probs[2].any()
+
+
+@pytest.mark.parametrize("vocab,dtype", [(49152, torch.float32), (4099, torch.bfloat16)])
+def test_filtered_sample_rows_match_oracle_bit_for_bit(vocab, dtype):
+    g = torch.Generator().manual_seed(18)
+    rows = 24
+    logits = (torch.randn(rows, vocab, generator=g) * 3).to(dtype)
+    temperature = torch.tensor([0.8, 1.0, 0.0, 1.7] * 6)
+    top_k = torch.tensor([-1, 50, 3, 1] * 6, dtype=torch.int32)
+    top_p = torch.tensor([0.9, 1.0, 0.5, 0.95, 0.3, 0.99] * 4)
+    uniforms = torch.rand(rows, generator=g)
+    uniforms[0], uniforms[1] = 0.0, 0.99999994
+    want_tokens, want_status = oracle.sample_rows(logits, temperature, uniforms, top_k, top_p)
+    got_tokens, got_status = rlt.sample_rows(logits.cuda(), temperature.cuda(), uniforms.cuda(), top_k.cuda(),
+                                             top_p.cuda())
+    assert torch.equal(got_tokens.cpu(), want_tokens) and torch.equal(got_status.cpu(), want_status)
+    assert int(want_status.abs().sum()) == 0
+    plain_tokens, _ = oracle.sample_rows(logits, temperature, uniforms)
+    assert not torch.equal(plain_tokens, want_tokens)      # the filters change the draws
+
+
+@pytest.mark.parametrize("noise,dtype", [(0.5, torch.float32), (3.0, torch.float32), (0.5, torch.bfloat16)])
+def test_filtered_rejection_round_matches_oracle_bit_for_bit(noise, dtype):
+    """Per-request top-k / top-p filter both p and q; drafts are drawn from the filtered q."""
+    n, k, vocab = 24, 4, 49152
+    r = make_round(n, k, vocab, torch.float32, seed=35, agree=False)
+    g = r["g"]
+    target = r["logits"]
+    draft = target + torch.randn(r["rows"], vocab, generator=g) * noise if noise < 3 else \
+        torch.randn(r["rows"], vocab, generator=g) * 3
+    target, draft = target.to(dtype), draft.to(dtype)
+    temperature = torch.full((n,), 0.8)
+    temperature[::7] = 0.0
+    top_k = torch.tensor([-1, 50, 8, 2000] * 6, dtype=torch.int32)
+    top_p = torch.tensor([0.9, 1.0, 0.95] * 8)
+    rep = lambda t: torch.repeat_interleave(t, r["counts"])
+    drafts, _ = oracle.sample_rows(draft, rep(temperature), torch.rand(r["rows"], generator=g), rep(top_k),
+                                   rep(top_p))
+    tokens = r["tokens"]
+    for i in range(n):
+        a, c = int(r["cu"][i]), int(r["counts"][i])
+        tokens[i, 1:c] = drafts[a:a + c - 1]
+    u_accept, u_final = torch.rand(r["rows"], generator=g), torch.rand(n, generator=g)
+    want_slots = torch.full((2 * n, 2), -1, dtype=torch.int64)
+    want, want_status = oracle.accept_rejection(target, draft, r["cu"], tokens, r["starts"], temperature,
+                                                u_accept, u_final, r["slots"], want_slots, top_k, top_p)
+    got_slots = torch.full((2 * n, 2), -1, dtype=torch.int64).cuda()
+    got, got_status = rlt.accept_rejection(target.cuda(), draft.cuda(), r["cu"].cuda(), tokens.cuda(),
+                                           r["starts"].cuda(), temperature.cuda(), u_accept.cuda(),
+                                           u_final.cuda(), r["slots"].cuda(), got_slots, top_k=top_k.cuda(),
+                                           top_p=top_p.cuda())
+    assert torch.equal(got_status.cpu(), want_status)
+    assert torch.equal(got.cpu(), want)
+    assert torch.equal(got_slots.cpu(), want_slots)
+    # a draft outside the target's support has p = 0 and is rejected; one outside q's support
+    # would be a zero-probability proposal: drafts drawn from the filtered q never are
+    assert not (want_status == 1).any()
+    unfiltered, _ = oracle.accept_rejection(target, draft, r["cu"], tokens, r["starts"], temperature, u_accept,
+                                            u_final)
+    assert not torch.equal(unfiltered, want)
+
+
 def test_rejection_decisions_of_the_reference(golden):
     for case in golden("sampler.pt")["rejection"]:
         vocab = case["target_logits"].numel()

@@ -93,3 +93,23 @@ def test_rejection_sampled_decoding_is_reproducible_and_seed_dependent(golden):
     assert stats.committed_tokens == sum(len(t) - 1 for t in first)
     # the first token of every request comes from the prefill argmax, so it matches greedy
     assert [t[0] for t in first] == [t[0] for t in case["tokens"]]
+
+
+def test_top_k_one_sampling_is_greedy_and_top_p_restricts_the_emitted_tokens(golden):
+    # top_k = 1 leaves a point mass on the argmax at any temperature (tests/test_sampler.py:76-84
+    # of the reference pins the same for Sampler.sample), so sampled decoding gives the golden
+    # greedy tokens; a tiny top_p does the same through the nucleus filter.
+    case = golden("decode.pt")["config1"]
+    model = build(case)
+    for filters in (dict(top_k=1), dict(top_p=1e-6)):
+        decoder = rlt.SelfSpeculativeDecoder(model, block=case["block"])
+        tokens = decoder.generate(case["prompts"], case["max_tokens"], num_speculative_tokens=case["k"],
+                                  draft_loops=case["draft_loops"], target_loops=case["target_loops"],
+                                  temperature=1.3, seed=11, **filters)
+        assert tokens == case["tokens"]
+    # a wider filter still changes what is sampled
+    plain = rlt.SelfSpeculativeDecoder(model, block=case["block"]).generate(
+        case["prompts"], 24, num_speculative_tokens=case["k"], temperature=1.3, seed=11)
+    narrow = rlt.SelfSpeculativeDecoder(model, block=case["block"]).generate(
+        case["prompts"], 24, num_speculative_tokens=case["k"], temperature=1.3, seed=11, top_k=5, top_p=0.9)
+    assert plain != narrow

@@ -129,6 +129,54 @@ def test_probabilities_match_reference_sampler(golden):
         assert abs(float(probs.double().sum()) - 1.0) < 1e-5
 
 
+def test_top_k_top_p_supports_and_distributions_match_reference_sampler(golden):
+    """Sampler.probabilities with filters: the support (which tokens stay) is exact, the
+    probabilities agree to fp32 rounding.  Among tied logits the reference leaves the
+    survivor unspecified (tests/test_sampler.py:101-103); the canonical order keeps the lower
+    index, so tied cases compare the sorted values."""
+    cases = golden("sampler.pt")["filtered"]
+    assert len(cases) >= 20
+    for case in cases:
+        probs, status = oracle.probabilities(case["logits"], case["temperature"], case["top_k"], case["top_p"])
+        assert status == 0
+        if case["tied"]:
+            torch.testing.assert_close(probs.sort().values, case["probs"].sort().values, rtol=2e-6, atol=1e-12)
+            support = probs.nonzero().flatten().tolist()
+            assert support == sorted(support)[:len(support)] and support[0] == 0
+        else:
+            assert torch.equal(probs > 0, case["probs"] > 0), (case["top_k"], case["top_p"])
+            torch.testing.assert_close(probs, case["probs"], rtol=4e-6, atol=1e-12)
+        assert abs(float(probs.double().sum()) - 1.0) < 1e-5
+
+
+def test_top_k_ties_keep_the_lowest_indices_and_top_p_cuts_inside_a_tie_group():
+    # canonical tie order: (logit descending, index ascending)
+    probs, _ = oracle.probabilities(torch.tensor([5.0, 4.0, 4.0, 1.0]), 1.0, 2, 1.0)
+    assert probs.nonzero().flatten().tolist() == [0, 1]
+    probs, _ = oracle.probabilities(torch.zeros(8), 1.0, 3, 1.0)
+    assert probs.nonzero().flatten().tolist() == [0, 1, 2]
+    # eight tied tokens of mass 1/8: the ranks whose preceding mass is <= 0.3 are 0, 1, 2
+    probs, _ = oracle.probabilities(torch.zeros(8), 1.0, -1, 0.3)
+    assert probs.nonzero().flatten().tolist() == [0, 1, 2]
+    torch.testing.assert_close(probs[:3], torch.full((3,), 1 / 3))
+    # top-k first, then top-p over the top-k distribution
+    probs, _ = oracle.probabilities(torch.tensor([0.0, 1.0, 1.0, 1.0, 1.0, -1.0]), 1.0, 3, 0.5)
+    assert probs.nonzero().flatten().tolist() == [1, 2]
+
+
+def test_filtered_sampling_never_leaves_the_support():
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn(32, 777, generator=g) * 2
+    temperature = torch.full((32,), 0.9)
+    top_k = torch.randint(1, 40, (32,), generator=g, dtype=torch.int32)
+    top_p = torch.rand(32, generator=g) * 0.9 + 0.05
+    tokens, status = oracle.sample_rows(logits, temperature, torch.rand(32, generator=g), top_k, top_p)
+    assert not status.any()
+    for r in range(32):
+        probs, _ = oracle.probabilities(logits[r], 0.9, int(top_k[r]), float(top_p[r]))
+        assert probs[tokens[r]] > 0 and int((probs > 0).sum()) <= int(top_k[r])
+
+
 def test_rejection_decisions_match_reference(golden):
     data = golden("sampler.pt")
     accepted_count = 0

@@ -15,12 +15,12 @@ from .decoder import DecodeStats, PagedKV, SelfSpeculativeDecoder
 from .kv_cache import RollbackResult, finalize_tokens, kv_write, rollback
 from .looped_lm import LoopedLM, LoopedLMConfig, seeded_state_dict
 from .speculative import (PipelineState, SpeculativeResult, accept_greedy, accept_rejection, argmax_rows,
-                          decode_result, pipeline_shift, raise_for_status, sample_rows)
+                          decode_result, pipeline_shift, probabilities, raise_for_status, sample_rows)
 
 __all__ = [
     "AttentionBackend", "B200PagedAttention", "DecodeStats", "LoopedLM", "LoopedLMConfig", "PagedKV",
     "SelfSpeculativeDecoder", "seeded_state_dict", "B200_CAPABILITIES", "BackendCapabilities",
     "NativeLibraryMissing", "RollbackResult", "SpeculativeResult", "accept_greedy", "accept_rejection",
-    "argmax_rows", "PipelineState", "create_backend", "decode_result", "finalize_tokens", "pipeline_shift", "kv_write", "load_library", "raise_for_status",
+    "argmax_rows", "PipelineState", "create_backend", "decode_result", "finalize_tokens", "pipeline_shift", "kv_write", "load_library", "probabilities", "raise_for_status",
     "register_torch_op", "rollback", "sample_rows", "silu_and_mul",
 ]

@@ -148,10 +148,19 @@ __global__ void greedy_finish_kernel(const int32_t* __restrict__ cu_rows, int n,
 }
 
 // ---- canonical distributions ----------------------------------------------------------
+// Support of a row after top-k / top-p: the prefix of the ranking (scaled logit descending,
+// token index ascending) that ends at (key, limit); see rlt_in_support.
+struct Cut {
+  uint32_t key;
+  int limit;
+};
+__device__ __forceinline__ Cut whole_row() { return Cut{0u, 0x7fffffff}; }
+
 struct RowNorm {
   float m;   // max of logits / T
-  float z;   // normaliser (from the fixed-point sum)
+  float z;   // normaliser over the support (from the fixed-point sum)
   int ok;    // 0: NaN / +inf / all -inf
+  Cut cut;   // support of the distribution
 };
 
 template <typename T>
@@ -159,12 +168,12 @@ __device__ __forceinline__ float scaled_logit(const T* row, int v, float tempera
   return RLT_DIV(Elem<T>::to_float(row[v]), temperature);
 }
 
-// max and normaliser of softmax(row / temperature).  Division by a positive temperature is
-// monotonic, so max_v (x_v / T) == (max_v x_v) / T exactly: the first pass is a plain maximum
-// over the raw logits (NaN counts as the maximum and is then reported), one division at the end.
+// max of row / temperature.  Division by a positive temperature is monotonic, so
+// max_v (x_v / T) == (max_v x_v) / T exactly: the pass is a plain maximum over the raw logits
+// (NaN counts as the maximum and is then reported), one division at the end.
 template <typename T, int kThreads>
-__device__ __forceinline__ RowNorm block_normalise(const T* __restrict__ row, int vocab, float temperature,
-                                                   unsigned long long* scratch) {
+__device__ __forceinline__ RowNorm block_row_max(const T* __restrict__ row, int vocab, float temperature,
+                                                 unsigned long long* scratch) {
   const unsigned long long best = block_max_key<T, kThreads>(row, vocab, scratch);
   RowNorm n;
   uint32_t bits = static_cast<uint32_t>(best >> 32);
@@ -173,7 +182,14 @@ __device__ __forceinline__ RowNorm block_normalise(const T* __restrict__ row, in
   n.m = RLT_DIV(raw_max, temperature);
   n.ok = best != 0ull && raw_max == raw_max && n.m != INFINITY && n.m != -INFINITY;
   n.z = 0.0f;
-  if (!n.ok) return n;
+  n.cut = whole_row();
+  return n;
+}
+
+// Normaliser of softmax(row / temperature) over the whole row.
+template <typename T, int kThreads>
+__device__ __forceinline__ float block_full_sum(const T* __restrict__ row, int vocab, float temperature, float m,
+                                                unsigned long long* scratch) {
   unsigned long long zfix = 0ull;
   constexpr int kVec = 16 / sizeof(T);
   if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0 && vocab % kVec == 0) {
@@ -193,21 +209,205 @@ __device__ __forceinline__ RowNorm block_normalise(const T* __restrict__ row, in
           const T* e = reinterpret_cast<const T*>(&raw[k]);
 #pragma unroll
           for (int j = 0; j < kVec; ++j)
-            zfix += rlt_fix_weight(rlt_expf(RLT_SUB(RLT_DIV(Elem<T>::to_float(e[j]), temperature), n.m)));
+            zfix += rlt_fix_weight(rlt_expf(RLT_SUB(RLT_DIV(Elem<T>::to_float(e[j]), temperature), m)));
         }
       }
     }
   } else {
     for (int v = threadIdx.x; v < vocab; v += kThreads)
-      zfix += rlt_fix_weight(rlt_expf(RLT_SUB(scaled_logit(row, v, temperature), n.m)));
+      zfix += rlt_fix_weight(rlt_expf(RLT_SUB(scaled_logit(row, v, temperature), m)));
   }
-  n.z = rlt_fix_to_float(block_sum<kThreads>(zfix, scratch));
+  return rlt_fix_to_float(block_sum<kThreads>(zfix, scratch));
+}
+
+// Normaliser over the tokens inside `cut`.
+template <typename T, int kThreads>
+__device__ __forceinline__ float block_cut_sum(const T* __restrict__ row, int vocab, float temperature, float m,
+                                               Cut cut, unsigned long long* scratch) {
+  unsigned long long zfix = 0ull;
+  for (int v = threadIdx.x; v < vocab; v += kThreads) {
+    const float t = scaled_logit(row, v, temperature);
+    if (rlt_in_support(rlt_order_key(t), v, cut.key, cut.limit)) zfix += rlt_fix_weight(rlt_expf(RLT_SUB(t, m)));
+  }
+  return rlt_fix_to_float(block_sum<kThreads>(zfix, scratch));
+}
+
+// ---- top-k / top-p: radix select over the ranking ------------------------------------------
+// Both filters keep the ranks whose exclusive prefix WEIGHT is <= a limit: weight 1 per token
+// and limit k - 1 for top-k, the fixed-point probability mass and rlt_top_p_limit for top-p.
+// The cut is found digit by digit (four 8-bit digits of the order key, most significant first):
+// a histogram of weight per digit over the tokens that match the digits chosen so far, then the
+// digit in which the running weight, accumulated from the top, first exceeds the limit.  Equal
+// keys have equal weights, so inside the final tie group the kept count follows by division and
+// the cut index is the n-th matching token in index order.  A row is a few hundred KB and stays
+// in L2 between the passes.
+struct SelectScratch {
+  unsigned long long mass[256];
+  unsigned int count[256];
+  unsigned long long above;
+  int digit;
+  int found;
+  int warp_counts[32];
+};
+
+template <bool kByMass>
+__device__ __forceinline__ void hist_add(SelectScratch& h, int bucket, unsigned long long w, bool valid) {
+  const int lane = threadIdx.x & 31;
+  unsigned todo = __ballot_sync(0xffffffffu, valid);
+  bool pending = valid;
+  // Most tokens of a warp fall into a few digits of the leading byte: add those once per warp.
+  for (int it = 0; todo != 0u && it < 3; ++it) {
+    const int leader = __ffs(todo) - 1;
+    const int b = __shfl_sync(0xffffffffu, bucket, leader);
+    const bool mine = pending && bucket == b;
+    const unsigned peers = __ballot_sync(0xffffffffu, mine);
+    if (kByMass) {
+      const unsigned long long s = warp_sum(mine ? w : 0ull);
+      if (lane == leader) atomicAdd(&h.mass[b], s);
+    }
+    if (lane == leader) atomicAdd(&h.count[b], static_cast<unsigned int>(__popc(peers)));
+    pending = pending && !mine;
+    todo &= ~peers;
+  }
+  if (pending) {
+    if (kByMass) atomicAdd(&h.mass[bucket], w);
+    atomicAdd(&h.count[bucket], 1u);
+  }
+}
+
+// Index of the n-th (1-based) token in ascending index order with order key `key` inside `outer`.
+template <typename T, int kThreads>
+__device__ __forceinline__ int block_nth_index(const T* __restrict__ row, int vocab, float temperature,
+                                               uint32_t key, Cut outer, unsigned int n, SelectScratch& h) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) h.found = 0x7fffffff;
+  unsigned int running = 0;
+  for (int base = 0; base < vocab; base += kThreads) {
+    const int v = base + static_cast<int>(threadIdx.x);
+    bool flag = false;
+    if (v < vocab) {
+      const uint32_t k = rlt_order_key(scaled_logit(row, v, temperature));
+      flag = k == key && rlt_in_support(k, v, outer.key, outer.limit);
+    }
+    const unsigned ballot = __ballot_sync(0xffffffffu, flag);
+    __syncthreads();
+    if (lane == 0) h.warp_counts[warp] = __popc(ballot);
+    __syncthreads();
+    unsigned int before = running, total = 0;
+    for (int w = 0; w < kThreads / 32; ++w) {
+      const unsigned int c = h.warp_counts[w];
+      if (w < warp) before += c;
+      total += c;
+    }
+    if (flag && before + __popc(ballot & ((1u << lane) - 1u)) + 1u == n) h.found = v;
+    running += total;
+    if (running >= n) break;  // uniform: every thread computes the same totals
+  }
+  __syncthreads();
+  return h.found;
+}
+
+template <typename T, int kThreads, bool kByMass>
+__device__ __forceinline__ Cut block_select(const T* __restrict__ row, int vocab, float temperature, float m,
+                                            float inv, Cut outer, unsigned long long limit, SelectScratch& h) {
+  uint32_t prefix = 0u;
+  unsigned long long above = 0ull;
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    __syncthreads();
+    for (int i = threadIdx.x; i < 256; i += kThreads) { h.mass[i] = 0ull; h.count[i] = 0u; }
+    __syncthreads();
+    for (int base = 0; base < vocab; base += kThreads) {
+      const int v = base + static_cast<int>(threadIdx.x);
+      bool valid = false;
+      int bucket = 0;
+      unsigned long long w = 0ull;
+      if (v < vocab) {
+        const float t = scaled_logit(row, v, temperature);
+        const uint32_t key = rlt_order_key(t);
+        valid = rlt_in_support(key, v, outer.key, outer.limit) &&
+                (pass == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8)));
+        bucket = static_cast<int>((key >> shift) & 255u);
+        if (kByMass && valid) w = rlt_fix_weight(rlt_draw_mass(rlt_expf(RLT_SUB(t, m)), inv));
+      }
+      hist_add<kByMass>(h, bucket, w, valid);
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      // lane l scans digits 255 - 8l down to 248 - 8l
+      const int lane = threadIdx.x, hi = 255 - 8 * lane;
+      unsigned long long local = 0ull;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) local += kByMass ? h.mass[hi - j] : static_cast<unsigned long long>(h.count[hi - j]);
+      unsigned long long inc = local;
+#pragma unroll
+      for (int x = 1; x < 32; x <<= 1) {
+        const unsigned long long o = __shfl_up_sync(0xffffffffu, inc, x);
+        if (lane >= x) inc += o;
+      }
+      const unsigned crossing = __ballot_sync(0xffffffffu, above + inc > limit);
+      if (crossing == 0u) {
+        if (lane == 0) h.digit = -1;
+      } else if (lane == __ffs(crossing) - 1) {
+        unsigned long long acc = above + inc - local;
+        int digit = hi;
+        for (int j = 0; j < 8; ++j) {
+          const unsigned long long wd = kByMass ? h.mass[hi - j] : static_cast<unsigned long long>(h.count[hi - j]);
+          digit = hi - j;
+          if (acc + wd > limit) break;
+          acc += wd;
+        }
+        h.digit = digit;
+        h.above = acc;
+      }
+    }
+    __syncthreads();
+    if (h.digit < 0) return outer;  // the whole of `outer` stays (its weight never exceeds the limit)
+    prefix |= static_cast<uint32_t>(h.digit) << shift;
+    above = h.above;
+  }
+  const unsigned int ties = h.count[prefix & 255u];
+  const unsigned long long each = kByMass ? h.mass[prefix & 255u] / ties : 1ull;
+  const unsigned long long keep = (limit - above) / each + 1ull;
+  __syncthreads();
+  if (keep >= ties) return Cut{prefix, prefix == outer.key ? outer.limit : 0x7fffffff};
+  return Cut{prefix, block_nth_index<T, kThreads>(row, vocab, temperature, prefix, outer,
+                                                  static_cast<unsigned int>(keep), h)};
+}
+
+// max, support and normaliser of the distribution Sampler.probabilities builds for one row
+// (vllm_rlt/worker/sampler.py:37-55): softmax(row / T) restricted to top-k, then to top-p.
+// top_k <= 0 or >= vocab and top_p >= 1 switch the filters off.
+template <typename T, int kThreads>
+__device__ __forceinline__ RowNorm block_normalise(const T* __restrict__ row, int vocab, float temperature,
+                                                   int top_k, float top_p, unsigned long long* scratch,
+                                                   SelectScratch& h) {
+  RowNorm n = block_row_max<T, kThreads>(row, vocab, temperature, scratch);
+  if (!n.ok) return n;
+  const bool use_k = top_k > 0 && top_k < vocab, use_p = top_p < 1.0f;
+  if (use_k) {
+    n.cut = block_select<T, kThreads, false>(row, vocab, temperature, n.m, 0.0f, whole_row(),
+                                             static_cast<unsigned long long>(top_k - 1), h);
+    n.z = block_cut_sum<T, kThreads>(row, vocab, temperature, n.m, n.cut, scratch);
+  } else {
+    n.z = block_full_sum<T, kThreads>(row, vocab, temperature, n.m, scratch);
+  }
+  if (use_p) {
+    const Cut outer = n.cut;
+    n.cut = block_select<T, kThreads, true>(row, vocab, temperature, n.m, RLT_DIV(1.0f, n.z), outer,
+                                            rlt_top_p_limit(top_p), h);
+    if (n.cut.key != outer.key || n.cut.limit != outer.limit)
+      n.z = block_cut_sum<T, kThreads>(row, vocab, temperature, n.m, n.cut, scratch);
+  }
   return n;
 }
 
+// exp(t_v - max) for a token of the support, 0 outside it.
 template <typename T>
 __device__ __forceinline__ float exp_at(const T* row, int v, float temperature, const RowNorm& n) {
-  return rlt_expf(RLT_SUB(scaled_logit(row, v, temperature), n.m));
+  const float t = scaled_logit(row, v, temperature);
+  if (!rlt_in_support(rlt_order_key(t), v, n.cut.key, n.cut.limit)) return 0.0f;
+  return rlt_expf(RLT_SUB(t, n.m));
 }
 
 template <typename T>
@@ -274,9 +474,11 @@ __device__ __forceinline__ int block_draw(const T* __restrict__ prow, const RowN
 template <typename T>
 __global__ void __launch_bounds__(kSampleThreads)
 sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
-                   const float* __restrict__ temperature, const float* __restrict__ uniforms,
+                   const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
+                   const float* __restrict__ top_p, const float* __restrict__ uniforms,
                    int64_t* __restrict__ tokens, int32_t* __restrict__ status) {
   __shared__ unsigned long long scratch[32];
+  __shared__ SelectScratch select;
   __shared__ int token_slot;
   const int r = blockIdx.x;
   const T* row = logits + static_cast<int64_t>(r) * row_stride;
@@ -286,7 +488,8 @@ sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
   if (temp == 0.0f) {
     token = block_argmax<T, kSampleThreads>(row, vocab, scratch);
   } else {
-    const RowNorm n = block_normalise<T, kSampleThreads>(row, vocab, temp, scratch);
+    const RowNorm n = block_normalise<T, kSampleThreads>(row, vocab, temp, top_k ? top_k[r] : -1,
+                                                         top_p ? top_p[r] : 1.0f, scratch, select);
     if (!n.ok) {
       st = RLT_ROW_BAD_LOGITS;
     } else {
@@ -295,6 +498,27 @@ sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
     }
   }
   if (threadIdx.x == 0) { tokens[r] = token; status[r] = st; }
+}
+
+// Sampler.probabilities for every row: fp32 [rows, vocab], zero outside the support.
+template <typename T>
+__global__ void __launch_bounds__(kSampleThreads)
+probabilities_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
+                     const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
+                     const float* __restrict__ top_p, float* __restrict__ probs, int32_t* __restrict__ status) {
+  __shared__ unsigned long long scratch[32];
+  __shared__ SelectScratch select;
+  const int r = blockIdx.x;
+  const T* row = logits + static_cast<int64_t>(r) * row_stride;
+  float* out = probs + static_cast<int64_t>(r) * vocab;
+  const float temp = temperature[r];
+  RowNorm n;
+  n.ok = 0;
+  if (temp > 0.0f)
+    n = block_normalise<T, kSampleThreads>(row, vocab, temp, top_k ? top_k[r] : -1, top_p ? top_p[r] : 1.0f,
+                                           scratch, select);
+  for (int v = threadIdx.x; v < vocab; v += kSampleThreads) out[v] = n.ok ? prob_at(row, v, temp, n) : 0.0f;
+  if (threadIdx.x == 0) status[r] = n.ok ? RLT_ROW_OK : RLT_ROW_BAD_LOGITS;
 }
 
 // ---- rejection sampling in two launches -------------------------------------------------
@@ -309,6 +533,7 @@ struct RowStats {
   float z;
   float prob;  // probability of the row's draft token under this row's distribution
   int info;    // bit 0: distribution valid; greedy requests: argmax index << 1
+  Cut cut;     // support after top-k / top-p
 };
 
 constexpr int kStatsThreads = 512;
@@ -326,24 +551,28 @@ template <typename T>
 __global__ void __launch_bounds__(kStatsThreads)
 row_stats_kernel(const T* __restrict__ target_logits, const T* __restrict__ draft_logits, int64_t row_stride,
                  int vocab, const int32_t* __restrict__ cu_rows, int n, const int64_t* __restrict__ tokens,
-                 int tokens_width, const float* __restrict__ temperature, RowStats* __restrict__ stats) {
+                 int tokens_width, const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
+                 const float* __restrict__ top_p, RowStats* __restrict__ stats) {
   __shared__ unsigned long long scratch[32];
+  __shared__ SelectScratch select;
   const int row = blockIdx.x, side = blockIdx.y;  // side 0: target, 1: draft
   const int i = request_of_row(cu_rows, n, row);
   const int first = cu_rows[i], count = cu_rows[i + 1] - first, j = row - first;
   const float temp = temperature[i];
-  RowStats out = {0.0f, 0.0f, 0.0f, 0};
+  RowStats out = {0.0f, 0.0f, 0.0f, 0, whole_row()};
   if (temp == 0.0f) {
     if (side == 1) return;
     out.info = block_argmax<T, kStatsThreads>(target_logits + static_cast<int64_t>(row) * row_stride, vocab, scratch) << 1;
   } else {
     if (side == 1 && j == count - 1) return;  // the bonus row has no draft distribution
     const T* logits = (side == 0 ? target_logits : draft_logits) + static_cast<int64_t>(row) * row_stride;
-    const RowNorm norm = block_normalise<T, kStatsThreads>(logits, vocab, temp, scratch);
+    const RowNorm norm = block_normalise<T, kStatsThreads>(logits, vocab, temp, top_k ? top_k[i] : -1,
+                                                           top_p ? top_p[i] : 1.0f, scratch, select);
     const int64_t d = j < count - 1 ? tokens[static_cast<int64_t>(i) * tokens_width + j + 1] : -1;
     out.m = norm.m;
     out.z = norm.z;
     out.info = norm.ok ? 1 : 0;
+    out.cut = norm.cut;
     if (norm.ok && d >= 0 && d < vocab) out.prob = prob_at(logits, static_cast<int>(d), temp, norm);
   }
   if (threadIdx.x == 0) stats[2 * row + side] = out;
@@ -388,7 +617,7 @@ decide_kernel(const T* __restrict__ target_logits, const T* __restrict__ draft_l
         ++accepted;
         continue;
       }
-      const RowNorm pn = {ps.m, ps.z, 1}, qn = {qs.m, qs.z, 1};
+      const RowNorm pn = {ps.m, ps.z, 1, ps.cut}, qn = {qs.m, qs.z, 1, qs.cut};
       final_token = block_draw<T, kSampleThreads>(target_logits + static_cast<int64_t>(a + j) * row_stride, pn,
                                                   draft_logits + static_cast<int64_t>(a + j) * row_stride, qn, true,
                                                   vocab, temp, u_final[i], scratch, &token_slot);
@@ -400,7 +629,7 @@ decide_kernel(const T* __restrict__ target_logits, const T* __restrict__ draft_l
       if (!(ps.info & 1)) {
         st = RLT_ROW_BAD_LOGITS;
       } else {
-        const RowNorm pn = {ps.m, ps.z, 1};
+        const RowNorm pn = {ps.m, ps.z, 1, ps.cut};
         const T* prow = target_logits + static_cast<int64_t>(a + c - 1) * row_stride;
         final_token = block_draw<T, kSampleThreads>(prow, pn, prow, pn, false, vocab, temp, u_final[i], scratch,
                                                     &token_slot);
@@ -469,17 +698,31 @@ extern "C" RLT_API int rlt_accept_greedy(const void* logits, int64_t row_stride,
 }
 
 extern "C" RLT_API int rlt_sample_rows(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
-                               const float* temperature, const float* uniforms, int64_t* tokens,
-                               int32_t* status_out, rlt_stream_t stream) {
+                               const float* temperature, const int32_t* top_k, const float* top_p,
+                               const float* uniforms, int64_t* tokens, int32_t* status_out, rlt_stream_t stream) {
   using namespace rlt;
   int status = check_logits(logits, row_stride, rows, vocab, dtype);
   if (status != RLT_OK || rows == 0) return status;
   RLT_REQUIRE(temperature && uniforms && tokens && status_out, "sample_rows: null pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   RLT_DISPATCH_DTYPE(dtype, T, (sample_rows_kernel<T><<<rows, kSampleThreads, 0, s>>>(
-                                   static_cast<const T*>(logits), row_stride, vocab, temperature, uniforms,
-                                   tokens, status_out)));
+                                   static_cast<const T*>(logits), row_stride, vocab, temperature, top_k, top_p,
+                                   uniforms, tokens, status_out)));
   return launch_status("sample_rows_kernel");
+}
+
+extern "C" RLT_API int rlt_probabilities(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
+                                         const float* temperature, const int32_t* top_k, const float* top_p,
+                                         float* probs, int32_t* status_out, rlt_stream_t stream) {
+  using namespace rlt;
+  int status = check_logits(logits, row_stride, rows, vocab, dtype);
+  if (status != RLT_OK || rows == 0) return status;
+  RLT_REQUIRE(temperature && probs && status_out, "probabilities: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RLT_DISPATCH_DTYPE(dtype, T, (probabilities_kernel<T><<<rows, kSampleThreads, 0, s>>>(
+                                   static_cast<const T*>(logits), row_stride, vocab, temperature, top_k, top_p,
+                                   probs, status_out)));
+  return launch_status("probabilities_kernel");
 }
 
 extern "C" RLT_API size_t rlt_accept_rejection_workspace_bytes(int rows) {
@@ -489,9 +732,10 @@ extern "C" RLT_API size_t rlt_accept_rejection_workspace_bytes(int rows) {
 extern "C" RLT_API int rlt_accept_rejection(const void* target_logits, const void* draft_logits, int64_t row_stride,
                                             int rows, int vocab, int dtype, const int32_t* cu_rows, int n,
                                             const int64_t* tokens, int tokens_width, const int64_t* starts,
-                                            const float* temperature, const float* u_accept, const float* u_final,
-                                            const int64_t* slots, int64_t* slot_values, int64_t* result,
-                                            int32_t* status_out, void* workspace, size_t workspace_bytes,
+                                            const float* temperature, const int32_t* top_k, const float* top_p,
+                                            const float* u_accept, const float* u_final, const int64_t* slots,
+                                            int64_t* slot_values, int64_t* result, int32_t* status_out,
+                                            void* workspace, size_t workspace_bytes,
                                             rlt_stream_t stream) {
   using namespace rlt;
   int status = check_logits(target_logits, row_stride, rows, vocab, dtype);
@@ -510,7 +754,8 @@ extern "C" RLT_API int rlt_accept_rejection(const void* target_logits, const voi
   RowStats* stats = static_cast<RowStats*>(workspace);
   RLT_DISPATCH_DTYPE(dtype, T, (row_stats_kernel<T><<<dim3(rows, 2), kStatsThreads, 0, s>>>(
                                    static_cast<const T*>(target_logits), static_cast<const T*>(draft_logits),
-                                   row_stride, vocab, cu_rows, n, tokens, tokens_width, temperature, stats)));
+                                   row_stride, vocab, cu_rows, n, tokens, tokens_width, temperature, top_k, top_p,
+                                   stats)));
   status = launch_status("row_stats_kernel");
   if (status != RLT_OK) return status;
   RLT_DISPATCH_DTYPE(dtype, T, (decide_kernel<T><<<n, kSampleThreads, 0, s>>>(

@@ -122,9 +122,11 @@ class SelfSpeculativeDecoder:
     # ---- block self-speculation ----------------------------------------------------------
     @torch.no_grad()
     def generate(self, prompts, max_tokens: int, *, num_speculative_tokens: int, draft_loops: int = 2,
-                 target_loops: int | None = None, temperature: float = 0.0, seed: int = 0, after_prefill=None):
+                 target_loops: int | None = None, temperature: float = 0.0, top_k: int = -1, top_p: float = 1.0,
+                 seed: int = 0, after_prefill=None):
         """Block self-speculation.  `temperature == 0` is greedy acceptance; otherwise drafts are
-        sampled from softmax(draft logits / T) and verified by rejection sampling with residual
+        sampled from the draft distribution (softmax(draft logits / T) after top-k / top-p, as
+        Sampler.probabilities builds it) and verified by rejection sampling with residual
         resampling (worker/speculative.py:47-63, 483-510 of the reference), with every uniform
         drawn from one seeded device generator in the reference's order per round: the draft
         draws, then the accept tests, then the final (residual or bonus) draw.  `after_prefill`, if
@@ -132,6 +134,15 @@ class SelfSpeculativeDecoder:
         model, device = self.model, self.model.device
         sampled = temperature > 0
         generator = torch.Generator(device=device).manual_seed(seed) if sampled else None
+        if not 0 < top_p <= 1 or (top_k != -1 and top_k < 1):
+            raise ValueError("top_p must be in (0, 1] and top_k must be -1 or positive")
+        filtered = sampled and (top_k > 0 or top_p < 1)
+
+        def filters(count):
+            if not filtered:
+                return None, None
+            return (torch.full((count,), top_k, dtype=torch.int32, device=device),
+                    torch.full((count,), top_p, dtype=torch.float32, device=device))
         target_loops = target_loops or model.config.total_ut_steps
         if not 0 < draft_loops < target_loops <= model.config.total_ut_steps:
             raise ValueError("draft_loops must be smaller than target_loops")
@@ -182,7 +193,7 @@ class SelfSpeculativeDecoder:
                 if sampled:
                     draft_logits[first_row[drafting_requests] + offset] = logits
                     proposed, _ = sample_rows(logits, torch.full((logits.shape[0],), temperature, device=device),
-                                              u_draft[drafting_requests, offset].contiguous())
+                                              u_draft[drafting_requests, offset].contiguous(), *filters(logits.shape[0]))
                 else:
                     proposed = argmax_rows(logits)
                 tokens[drafting_requests, offset + 1] = proposed
@@ -203,7 +214,8 @@ class SelfSpeculativeDecoder:
                 result, status = accept_rejection(
                     logits, draft_logits, cu_rows, tokens.contiguous(), start_tensor,
                     torch.full((n,), temperature, device=device), torch.rand(rows_total, generator=generator, device=device),
-                    torch.rand(n, generator=generator, device=device), slots, slot_values[:n].contiguous())
+                    torch.rand(n, generator=generator, device=device), slots, slot_values[:n].contiguous(),
+                    None, *filters(n))
             else:
                 status = torch.zeros(n, dtype=torch.int32, device=device)
                 result = accept_greedy(logits, cu_rows, tokens.contiguous(), start_tensor, slots,

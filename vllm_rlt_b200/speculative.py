@@ -95,17 +95,56 @@ def accept_greedy(logits, cu_rows, tokens, starts, slots=None, slot_values=None,
     return result
 
 
-def sample_rows(logits, temperature, uniforms):
-    """One draw per row from ``softmax(logits / temperature)``; temperature 0 is argmax.
+def _check_filters(top_k, top_p, count, what):
+    """top_k int32 [count] (<= 0 or >= vocab: off) and top_p float32 [count] (>= 1: off), or None."""
+    if top_k is not None and (top_k.dtype != torch.int32 or top_k.shape != (count,)):
+        raise ValueError(f"top_k must be int32 [{what}]")
+    if top_p is not None and (top_p.dtype != torch.float32 or top_p.shape != (count,)):
+        raise ValueError(f"top_p must be float32 [{what}]")
+    return (None if top_k is None else top_k.contiguous()), (None if top_p is None else top_p.contiguous())
+
+
+def probabilities(logits, temperature, top_k=None, top_p=None):
+    """``Sampler.probabilities`` (``vllm_rlt/worker/sampler.py:27-55``) for every row at once.
+
+    ``softmax(float(logits) / temperature)`` over the strict top-k support (ties to the lower
+    index), trimmed to the top-p nucleus, renormalised.  Returns ``(probs float32 [rows, vocab],
+    status int32 [rows])``.  ``temperature`` must be positive: greedy decoding has no
+    temperature-scaled distribution (such rows get status 3 and zeros; the reference raises
+    ``ValueError``).
+    """
+    _capi.require_cuda(logits, temperature, top_k, top_p)
+    _check_logits(logits)
+    rows, vocab = logits.shape
+    if temperature.dtype != torch.float32 or temperature.shape != (rows,):
+        raise ValueError("temperature must be float32 [rows]")
+    top_k, top_p = _check_filters(top_k, top_p, rows, "rows")
+    probs = torch.empty(rows, vocab, dtype=torch.float32, device=logits.device)
+    status = torch.zeros(rows, dtype=torch.int32, device=logits.device)
+    if rows == 0:
+        return probs, status
+    with torch.cuda.device(logits.device):
+        code = _capi.load().rlt_probabilities(
+            _capi.ptr(logits), logits.stride(0), rows, vocab, _capi.DTYPE_CODES[logits.dtype],
+            _capi.ptr(temperature.contiguous()), _capi.ptr(top_k), _capi.ptr(top_p), _capi.ptr(probs),
+            _capi.ptr(status), _capi.stream_of(logits))
+    _capi.check(code, "probabilities")
+    return probs, status
+
+
+def sample_rows(logits, temperature, uniforms, top_k=None, top_p=None):
+    """One draw per row from the row's sampling distribution (see ``probabilities``);
+    temperature 0 is argmax.
 
     Returns ``(tokens int64 [rows], status int32 [rows])``.
     """
-    _capi.require_cuda(logits, temperature, uniforms)
+    _capi.require_cuda(logits, temperature, uniforms, top_k, top_p)
     _check_logits(logits)
     rows = logits.shape[0]
     for name, t in (("temperature", temperature), ("uniforms", uniforms)):
         if t.dtype != torch.float32 or t.shape != (rows,):
             raise ValueError(f"{name} must be float32 [rows]")
+    top_k, top_p = _check_filters(top_k, top_p, rows, "rows")
     tokens = torch.empty(rows, dtype=torch.int64, device=logits.device)
     status = torch.zeros(rows, dtype=torch.int32, device=logits.device)
     if rows == 0:
@@ -113,24 +152,26 @@ def sample_rows(logits, temperature, uniforms):
     with torch.cuda.device(logits.device):
         code = _capi.load().rlt_sample_rows(
             _capi.ptr(logits), logits.stride(0), rows, logits.shape[1], _capi.DTYPE_CODES[logits.dtype],
-            _capi.ptr(temperature.contiguous()), _capi.ptr(uniforms.contiguous()), _capi.ptr(tokens),
-            _capi.ptr(status), _capi.stream_of(logits))
+            _capi.ptr(temperature.contiguous()), _capi.ptr(top_k), _capi.ptr(top_p),
+            _capi.ptr(uniforms.contiguous()), _capi.ptr(tokens), _capi.ptr(status), _capi.stream_of(logits))
     _capi.check(code, "sample_rows")
     return tokens, status
 
 
 def accept_rejection(target_logits, draft_logits, cu_rows, tokens, starts, temperature, u_accept, u_final,
-                     slots=None, slot_values=None, result=None):
+                     slots=None, slot_values=None, result=None, top_k=None, top_p=None):
     """Rejection-sampling acceptance of a whole round; returns ``(result, status)``.
 
     ``result[cu_rows[i] : cu_rows[i] + accepted_i + 1]`` are request i's emitted tokens (its
     other rows hold -1); ``status[i]`` is 0, or 1 (zero proposal probability: ``ValueError`` in
     the reference), 2 (invalid residual mass: ``RuntimeError``), 3 (NaN / +inf logits).
     Use ``raise_for_status`` to turn them into those exceptions after the one host read of a
-    round.  ``temperature[i] == 0`` takes the greedy branch for that request.
+    round.  ``temperature[i] == 0`` takes the greedy branch for that request.  ``top_k`` /
+    ``top_p`` are per request and filter both the target and the proposal distribution, as the
+    reference builds both with the request's ``SamplingParams``.
     """
     _capi.require_cuda(target_logits, draft_logits, cu_rows, tokens, starts, temperature, u_accept, u_final,
-                       slots, slot_values, result)
+                       slots, slot_values, result, top_k, top_p)
     _check_logits(target_logits)
     _check_logits(draft_logits)
     if target_logits.shape != draft_logits.shape or target_logits.stride() != draft_logits.stride() \
@@ -141,6 +182,7 @@ def accept_rejection(target_logits, draft_logits, cu_rows, tokens, starts, tempe
     for name, t, count in (("temperature", temperature, n), ("u_accept", u_accept, rows), ("u_final", u_final, n)):
         if t.dtype != torch.float32 or t.shape != (count,):
             raise ValueError(f"{name} must be float32 [{count}]")
+    top_k, top_p = _check_filters(top_k, top_p, n, "requests")
     if result is None:
         result = torch.empty(rows + 2 * n, dtype=torch.int64, device=target_logits.device)
     status = torch.zeros(n, dtype=torch.int32, device=target_logits.device)
@@ -154,8 +196,8 @@ def accept_rejection(target_logits, draft_logits, cu_rows, tokens, starts, tempe
             _capi.ptr(target_logits), _capi.ptr(draft_logits), target_logits.stride(0), rows,
             target_logits.shape[1], _capi.DTYPE_CODES[target_logits.dtype], _capi.ptr(cu_rows.contiguous()), n,
             _capi.ptr(tokens), tokens.shape[1], _capi.ptr(starts.contiguous()),
-            _capi.ptr(temperature.contiguous()), _capi.ptr(u_accept.contiguous()),
-            _capi.ptr(u_final.contiguous()), _capi.ptr(slots), _capi.ptr(slot_values), _capi.ptr(result),
+            _capi.ptr(temperature.contiguous()), _capi.ptr(top_k), _capi.ptr(top_p),
+            _capi.ptr(u_accept.contiguous()), _capi.ptr(u_final.contiguous()), _capi.ptr(slots), _capi.ptr(slot_values), _capi.ptr(result),
             _capi.ptr(status), _capi.ptr(workspace), workspace.numel(), _capi.stream_of(target_logits))
     _capi.check(code, "accept_rejection")
     return result, status
