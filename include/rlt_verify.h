@@ -371,6 +371,50 @@ RLT_API int rlt_pipeline_shift(int64_t* tokens, int64_t* depths, int64_t* candid
                        const int64_t* limits, int n, int width, int hidden_size, int dtype, int draft_loops,
                        int target_loops, int64_t* result, rlt_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Rotary embedding of q and k fused with the KV write of one layer.
+ *   q_out[r]              = q[r] * cos[r] + rotate_half(q[r]) * sin[r]      (per head)
+ *   cache_k[block, off]   = k[r] * cos[r] + rotate_half(k[r]) * sin[r]
+ *   cache_v[block, off]   = v[r]
+ * with rotate_half(x) = (-x[d/2:], x[:d/2]) and every product and sum rounded to `dtype`
+ * as the tensor expression rounds, so the results are bit-identical to it.  Rows that
+ * rlt_kv_write would skip (mask, active_rows, out-of-pool address) write nothing to the
+ * cache; q_out is written for every row.
+ * Replaces: apply_rotary_pos_emb (vllm_rlt/layers/rotary_embedding.py:15-24) followed by
+ *   KVCacheManager._write_prepared in OuroAttention.forward (vllm_rlt/models/ouro.py:179-186).
+ * q: [rows, q_heads, head_dim] with row stride q_row_stride (elements; the [heads, head_dim]
+ *   tail contiguous, so slices of one fused QKV projection are accepted); k, v likewise.
+ * cos_table / sin_table: [rows, head_dim] of `dtype`, contiguous (RotaryEmbedding.forward,
+ *   rotary_embedding.py:54-64, computed once per pass).  q_out: [rows, q_heads, head_dim]
+ *   contiguous.  Cache arguments as rlt_kv_write.  head_dim must be even.
+ * ---------------------------------------------------------------------- */
+RLT_API int rlt_rope_kv_write(const void* q, int64_t q_row_stride, const void* k, int64_t k_row_stride,
+                      const void* v, int64_t v_row_stride, const void* cos_table, const void* sin_table,
+                      void* q_out, void* key_cache, void* value_cache, int64_t block_stride,
+                      int64_t token_stride, int64_t num_blocks, int block_size, int q_heads, int kv_heads,
+                      int head_dim, int dtype, const int64_t* write_blocks, const int64_t* write_offsets,
+                      const uint8_t* write_mask, const int32_t* active_rows, int rows, rlt_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * RMSNorm of a sandwich-norm sublayer, optionally fused with the residual add and with the
+ * norm that opens the next sublayer.  Per row:
+ *   y = weight * T(x * rsqrt(mean(x^2) + eps))           (T: round to `dtype`)
+ *   s = residual + y        (s = y when residual is NULL)         -> sum_out  (if not NULL)
+ *   n = weight2 * T(s * rsqrt(mean(s^2) + eps))                   -> norm_out (if weight2 not NULL)
+ * The squares are fp32, their sum is accumulated in double, the reciprocal square root is
+ * correctly rounded; products and sums round to `dtype` where the tensor expressions round.
+ * (PyTorch's fp32 mean sums in an unspecified order, so agreement with it is to the last
+ * place of `dtype`, not bit for bit.)
+ * Replaces: RMSNorm.forward (vllm_rlt/layers/normalization.py:20-23) and the residual adds of
+ *   OuroDecoderLayer.forward (vllm_rlt/models/ouro.py:217-221).
+ * x, residual, sum_out, norm_out: [rows, hidden] contiguous; weight, weight2: [hidden].
+ * sum_out may alias residual (in-place residual stream); x must not alias an output.
+ * hidden <= 8192.
+ * ---------------------------------------------------------------------- */
+RLT_API int rlt_sandwich_norm(const void* x, const void* weight, const void* residual, void* sum_out,
+                      const void* weight2, void* norm_out, int rows, int hidden, float eps, int dtype,
+                      rlt_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -183,3 +183,31 @@ def rollback(starts, emitted, tables, block_size, pages_used=None, refcounts=Non
                        layers, _p(frontier), _p(context_lengths), _p(write_blocks),
                        _p(write_offsets), _p(status))
     return frontier, context_lengths, write_blocks, write_offsets, status
+
+
+def rope_kv_write(q, k, v, cos, sin, key_cache, value_cache, write_blocks, write_offsets, write_mask=None,
+                  active_rows=None):
+    """q, k, v: [rows, heads, head_dim] views with contiguous [heads, head_dim] tails; returns rotated q."""
+    bs, ts = _cache_geometry(key_cache)
+    assert _cache_geometry(value_cache) == (bs, ts)
+    for t in (q, k, v):
+        assert t.stride(2) == 1 and t.stride(1) == t.shape[2]
+    q_out = torch.empty(q.shape, dtype=q.dtype)
+    mask = None if write_mask is None else write_mask.to(torch.uint8).contiguous()
+    lib().orc_rope_kv_write(_p(q), _i64(q.stride(0)), _p(k), _i64(k.stride(0)), _p(v), _i64(v.stride(0)),
+                            _p(cos.contiguous()), _p(sin.contiguous()), _p(q_out), _p(key_cache), _p(value_cache),
+                            _i64(bs), _i64(ts), q.shape[1], k.shape[1], q.shape[2], _DTYPES[q.dtype],
+                            _p(write_blocks.contiguous()), _p(write_offsets.contiguous()), _p(mask),
+                            _p(active_rows), q.shape[0])
+    return q_out
+
+
+def sandwich_norm(x, weight, eps, residual=None, weight2=None):
+    """Returns (sum, norm): sum = [residual +] weight * T(rmsnorm(x)); norm = weight2 * T(rmsnorm(sum)) or None."""
+    x = x.contiguous()
+    total = torch.empty_like(x)
+    norm = None if weight2 is None else torch.empty_like(x)
+    lib().orc_sandwich_norm(_p(x), _p(weight.contiguous()), _p(None if residual is None else residual.contiguous()),
+                            _p(total), _p(None if weight2 is None else weight2.contiguous()), _p(norm), x.shape[0],
+                            x.shape[1], ctypes.c_float(eps), _DTYPES[x.dtype])
+    return total, norm

@@ -113,3 +113,32 @@ def test_top_k_one_sampling_is_greedy_and_top_p_restricts_the_emitted_tokens(gol
     narrow = rlt.SelfSpeculativeDecoder(model, block=case["block"]).generate(
         case["prompts"], 24, num_speculative_tokens=case["k"], temperature=1.3, seed=11, top_k=5, top_p=0.9)
     assert plain != narrow
+
+
+@pytest.mark.parametrize("dtype,tolerance", [(torch.float32, 2e-5), (torch.bfloat16, 4e-2)])
+def test_fused_layer_kernels_agree_with_the_tensor_expressions(dtype, tolerance):
+    # one recurrent loop with rope_kv_write + sandwich_norm against RMSNorm / RoPE / KV write as
+    # separate tensor expressions: same K/V pool contents and hidden state to the dtype's tolerance
+    # (the fused path also runs q, k and v as one projection, so the GEMM bits differ).
+    config = rlt.LoopedLMConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=3,
+                                num_attention_heads=2, num_key_value_heads=2, head_dim=128, rope_theta=10000.0)
+    state = rlt.seeded_state_dict(config, 9)
+    fused = rlt.LoopedLM(config, state, "cuda", dtype)
+    plain = rlt.LoopedLM(config, state, "cuda", dtype, fused=False)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(1, 512, (n,), generator=g).tolist() for n in (33, 5, 18)]
+    outputs = []
+    for model in (fused, plain):
+        kv = rlt.PagedKV.allocate(model, [len(p) + 4 for p in prompts], 16)
+        requests = torch.tensor([i for i, p in enumerate(prompts) for _ in p], device="cuda")
+        positions = torch.tensor([j for p in prompts for j in range(len(p))], device="cuda")
+        hidden = model.prelude(torch.tensor([t for p in prompts for t in p], device="cuda"))
+        before = hidden.clone()
+        blocks, offsets, tables, lengths = kv.addressing(requests, positions, 0)
+        out = model.recurrent(hidden, positions, kv.key, kv.value, blocks, offsets, tables, lengths)
+        assert torch.equal(hidden, before)                      # the caller's tensor is not the residual stream
+        outputs.append((out.float(), kv.key.float(), kv.value.float()))
+    (a, ka, va), (b, kb, vb) = outputs
+    torch.testing.assert_close(a, b, rtol=tolerance, atol=tolerance)
+    torch.testing.assert_close(ka, kb, rtol=tolerance, atol=tolerance)
+    torch.testing.assert_close(va, vb, rtol=tolerance, atol=tolerance)

@@ -331,3 +331,31 @@ def test_pipeline_shift_matches_every_reference_step(golden):
         for row in after["result"].view(n, 6).tolist():
             seen.add((row[1], row[2]))
     assert seen == {(0, 0), (0, 1), (1, 1)}  # waiting, rejected and accepted steps all occur
+
+
+def test_rope_and_sandwich_norm_match_the_reference_layers(golden):
+    """apply_rotary_pos_emb is reproduced bit for bit; RMSNorm and the sandwich residual flow to
+    the last place of the dtype (the reference's fp32 mean has no specified summation order)."""
+    data = golden("layers.pt")
+    for case in data["rope"]:
+        q, k = case["q"], case["k"]
+        rows, kv_heads, dim = k.shape
+        key_cache = torch.zeros(rows, 1, kv_heads, dim, dtype=q.dtype)
+        value_cache = torch.zeros_like(key_cache)
+        blocks, offsets = torch.arange(rows), torch.zeros(rows, dtype=torch.int64)
+        q_rot = oracle.rope_kv_write(q, k, k, case["cos"], case["sin"], key_cache, value_cache, blocks, offsets)
+        assert torch.equal(q_rot, case["q_rot"]) and torch.equal(key_cache[:, 0], case["k_rot"])
+        assert torch.equal(value_cache[:, 0], k)
+    ulp = {torch.float32: 2.0 ** -23, torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7}
+    for case in data["norm"]:
+        dtype = case["x"].dtype
+        plain, _ = oracle.sandwich_norm(case["x"], case["weight"], case["eps"])
+        total, following = oracle.sandwich_norm(case["x"], case["weight"], case["eps"], case["residual"], case["weight2"])
+        for got, want in ((plain, case["plain"]), (total, case["total"])):
+            # the residual add cancels, so the last place is that of the operands, not of the sum
+            torch.testing.assert_close(got.float(), want.float(), rtol=2 * ulp[dtype],
+                                       atol=2 * ulp[dtype] * float(want.abs().max()))
+            if dtype != torch.float32:   # a last-place difference of the fp32 scale rarely survives the rounding
+                assert float((got == want).float().mean()) > 0.99
+        torch.testing.assert_close(following.float(), case["following"].float(), rtol=4 * ulp[dtype],
+                                   atol=4 * ulp[dtype] * float(case["following"].abs().max()))

@@ -13,6 +13,7 @@ from .attention import (B200_CAPABILITIES, AttentionBackend, B200PagedAttention,
                         create_backend)
 from .decoder import DecodeStats, PagedKV, SelfSpeculativeDecoder
 from .kv_cache import RollbackResult, finalize_tokens, kv_write, rollback
+from .layers import rope_kv_write, sandwich_norm
 from .looped_lm import LoopedLM, LoopedLMConfig, seeded_state_dict
 from .speculative import (PipelineState, SpeculativeResult, accept_greedy, accept_rejection, argmax_rows,
                           decode_result, pipeline_shift, probabilities, raise_for_status, sample_rows)
@@ -22,5 +23,5 @@ __all__ = [
     "SelfSpeculativeDecoder", "seeded_state_dict", "B200_CAPABILITIES", "BackendCapabilities",
     "NativeLibraryMissing", "RollbackResult", "SpeculativeResult", "accept_greedy", "accept_rejection",
     "argmax_rows", "PipelineState", "create_backend", "decode_result", "finalize_tokens", "pipeline_shift", "kv_write", "load_library", "probabilities", "raise_for_status",
-    "register_torch_op", "rollback", "sample_rows", "silu_and_mul",
+    "register_torch_op", "rollback", "rope_kv_write", "sample_rows", "sandwich_norm", "silu_and_mul",
 ]

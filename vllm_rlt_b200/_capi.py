@@ -7,7 +7,7 @@ built, or a call fails, the caller gets an exception.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
 import torch
@@ -20,7 +20,7 @@ ROW_OK, ROW_ZERO_PROPOSAL, ROW_INVALID_RESIDUAL, ROW_BAD_LOGITS, ROW_SHARED_PAGE
 DTYPE_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 # name -> (restype, argtypes); mirrors include/rlt_verify.h one to one.
-_P, _I, _L, _Z = c_void_p, c_int, c_int64, c_size_t
+_P, _I, _L, _Z, _F = c_void_p, c_int, c_int64, c_size_t, c_float
 SIGNATURES = {
     "rlt_version": (c_char_p, []),
     "rlt_last_error": (c_char_p, []),
@@ -43,6 +43,9 @@ SIGNATURES = {
                                   _P, _Z, _P]),
     "rlt_finalize_tokens": (_I, [_P, _P, _L, _L, _L, _L, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P]),
     "rlt_pipeline_shift": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P]),
+    "rlt_rope_kv_write": (_I, [_P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P,
+                               _I, _P]),
+    "rlt_sandwich_norm": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _F, _I, _P]),
     "rlt_rollback": (_I, [_P, _P, _I, _P, _I, _I, _I, _P, _P, _L, _P, _I, _P, _P, _P, _P, _P, _P]),
 }
 

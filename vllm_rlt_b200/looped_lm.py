@@ -2,10 +2,11 @@
 
 This is the call-site side of the path (`vllm_rlt/models/ouro.py:171-291` of the reference):
 embedding prelude, a stack of sandwich-norm decoder layers that is applied once per recurrent
-loop with shared weights, final norm inside the recurrence, LM-head coda.  GEMMs, RMSNorm and
-RoPE are plain PyTorch (cuBLAS) with the reference's formulas; the KV write, the paged attention
-and SiLU-and-Mul are this package's kernels.  Parameter names are the reference's
-(checkpoint-compatible), so a reference `state_dict()` loads unchanged.
+loop with shared weights, final norm inside the recurrence, LM-head coda.  The GEMMs are
+PyTorch (cuBLAS); everything between them is this package's kernels: fused RoPE + KV write,
+paged attention, SiLU-and-Mul and the fused sandwich RMSNorm + residual (`fused=False` keeps
+RMSNorm and RoPE as the reference's tensor expressions, for comparison).  Parameter names are
+the reference's (checkpoint-compatible), so a reference `state_dict()` loads unchanged.
 """
 
 from __future__ import annotations
@@ -19,6 +20,7 @@ import torch.nn.functional as F
 from .activation import silu_and_mul
 from .attention import B200PagedAttention
 from .kv_cache import kv_write
+from .layers import rope_kv_write, sandwich_norm
 
 
 @dataclass(frozen=True)
@@ -91,7 +93,7 @@ class LoopedLM:
     """Inference-only looped LM: `prelude`, one `recurrent` loop over all layers, `coda`."""
 
     def __init__(self, config: LoopedLMConfig, state_dict: dict, device, dtype: torch.dtype,
-                 attention: B200PagedAttention | None = None):
+                 attention: B200PagedAttention | None = None, fused: bool = True):
         self.config = config
         self.device = torch.device(device)
         self.dtype = dtype
@@ -100,6 +102,10 @@ class LoopedLM:
             raise ValueError(f"state dict lacks {sorted(missing)[:3]}...")
         self.w = {name: state_dict[name].to(device=self.device, dtype=dtype) for name in parameter_shapes(config)}
         self.attention = attention or B200PagedAttention()
+        self.fused = fused
+        # one projection for q, k and v: the rotary kernel reads its three column slices in place
+        self.qkv = [torch.cat([self.w[f"model.layers.{layer}.self_attn.{n}_proj.weight"] for n in "qkv"])
+                    for layer in range(config.num_hidden_layers)] if fused else None
         self.inv_freq = 1.0 / (config.rope_theta ** (
             torch.arange(0, config.head_dim, 2, dtype=torch.float32, device=self.device) / config.head_dim))
 
@@ -120,6 +126,9 @@ class LoopedLM:
         tensors select the depth plane (they are the same for all layers of the loop, so the
         attention work list is planned once).  Returns the normalised hidden state, which is the
         next loop's input and the coda's input (models/ouro.py:283-291)."""
+        if self.fused:
+            return self._recurrent_fused(hidden, positions, key_pool, value_pool, write_blocks, write_offsets,
+                                         block_tables, context_lengths)
         c, w = self.config, self.w
         cos, sin = self.rope(positions)
         rows = hidden.shape[0]
@@ -143,6 +152,41 @@ class LoopedLM:
                 mlp = F.linear(silu_and_mul(gate, up), w[p + "mlp.down_proj.weight"])
                 hidden = hidden + rms_norm(mlp, w[p + "post_attention_layernorm_2.weight"], c.rms_norm_eps)
         return rms_norm(hidden, w["model.norm.weight"], c.rms_norm_eps)
+
+    def _recurrent_fused(self, hidden, positions, key_pool, value_pool, write_blocks, write_offsets, block_tables,
+                         context_lengths, active_rows=None):
+        """The same loop with ten launches per layer: QKV GEMM, rope_kv_write, attention, O GEMM,
+        sandwich_norm (residual add + the MLP's input norm), gate and up GEMMs, silu_and_mul, down
+        GEMM, sandwich_norm (residual add + the next layer's input norm, or the final norm).
+        `active_rows` (0-dim int32) marks padding rows of a captured graph: they write no K/V."""
+        c, w = self.config, self.w
+        cos, sin = self.rope(positions)
+        rows = hidden.shape[0]
+        q_width, kv_width = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
+        stream = None                                                  # residual stream, owned by this call
+        x, _ = sandwich_norm(hidden, w["model.layers.0.input_layernorm.weight"], c.rms_norm_eps)
+        with self.attention.shared_plan():
+            for layer in range(c.num_hidden_layers):
+                p = f"model.layers.{layer}."
+                qkv = F.linear(x, self.qkv[layer])
+                q = qkv[:, :q_width].view(rows, -1, c.head_dim)
+                k = qkv[:, q_width:q_width + kv_width].view(rows, -1, c.head_dim)
+                v = qkv[:, q_width + kv_width:].view(rows, -1, c.head_dim)
+                kc, vc = key_pool[:, layer], value_pool[:, layer]
+                q = rope_kv_write(q, k, v, cos, sin, kc, vc, write_blocks, write_offsets, active_rows=active_rows)
+                attended = self.attention(q, kc, vc, block_tables, context_lengths)
+                attended = F.linear(attended.view(rows, -1), w[p + "self_attn.o_proj.weight"])
+                stream, x = sandwich_norm(attended, w[p + "input_layernorm_2.weight"], c.rms_norm_eps,
+                                          hidden if stream is None else stream,
+                                          w[p + "post_attention_layernorm.weight"], in_place=stream is not None)
+                gate = F.linear(x, w[p + "mlp.gate_proj.weight"])
+                up = F.linear(x, w[p + "mlp.up_proj.weight"])
+                mlp = F.linear(silu_and_mul(gate, up), w[p + "mlp.down_proj.weight"])
+                following = (w[f"model.layers.{layer + 1}.input_layernorm.weight"]
+                             if layer + 1 < c.num_hidden_layers else w["model.norm.weight"])
+                stream, x = sandwich_norm(mlp, w[p + "post_attention_layernorm_2.weight"], c.rms_norm_eps, stream,
+                                          following, in_place=True)
+        return x
 
     def coda(self, hidden: torch.Tensor) -> torch.Tensor:
         return F.linear(hidden, self.w["lm_head.weight"])
