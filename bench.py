@@ -60,12 +60,12 @@ class Workload:
     """Seeded synthetic inputs of one replica (one GPU or the CPU sample)."""
 
     def __init__(self, seed: int, requests: int = REQUESTS, layers: int = LAYERS, device="cpu",
-                 tokens: int = TOKENS, depths: int = DEPTHS, kv_heads: int = HEADS):
+                 tokens: int = TOKENS, depths: int = DEPTHS, kv_heads: int = HEADS, context_range=(512, 4096)):
         g = torch.Generator().manual_seed(seed)
         self.requests, self.layers = requests, layers
         TOKENS, DEPTHS = tokens, depths
         self.kv_heads = kv_heads
-        self.contexts = torch.randint(512, 4097, (requests,), generator=g)
+        self.contexts = torch.randint(context_range[0], context_range[1] + 1, (requests,), generator=g)
         pages = (self.contexts + BLOCK - 1) // BLOCK
         self.total_pages = int(pages.sum())
         order = torch.randperm(self.total_pages, generator=g).int()
@@ -420,6 +420,7 @@ def run_attention_only(args):
     torch.cuda.set_device(0)
     device = torch.device("cuda", 0)
     work = Workload(seed=1234, requests=args.requests, layers=args.layers, tokens=args.tokens, depths=args.depths,
+                    context_range=(args.context_min, args.context_max),
                     kv_heads=args.kv_heads)
     g = torch.Generator(device=device).manual_seed(99)
     pool_shape = (work.total_pages, args.layers, BLOCK, args.kv_heads, HEAD_DIM)
@@ -505,8 +506,8 @@ def run_decode_workload(args):
     """Secondary workload (`--workload decode`): self-speculative decoding of a random-init
     Ouro-1.4B-shaped model (24 layers, hidden 2048, 16 x 128 MHA, FFN 5632, vocab 49152, 4 loops, bf16)
     through `vllm_rlt_b200.SelfSpeculativeDecoder` — BASELINE configs[2] with the output length set by
-    `--output-tokens`.  GEMMs / norms / RoPE are eager PyTorch around the kernels, so this number is
-    launch-bound like the reference's eager mode; the prefill is outside the timed region."""
+    `--output-tokens`.  The GEMMs are cuBLAS; every recurrent loop is replayed from a CUDA graph per
+    row bucket unless `--eager` is given.  The prefill and the graph captures are outside the timed region."""
     import vllm_rlt_b200 as rlt
 
     torch.cuda.set_device(0)
@@ -516,7 +517,7 @@ def run_decode_workload(args):
     g = torch.Generator().manual_seed(11)
     lengths = torch.randint(128, 1025, (args.requests,), generator=g).tolist()
     prompts = [torch.randint(1, config.vocab_size, (n,), generator=g).tolist() for n in lengths]
-    decoder = rlt.SelfSpeculativeDecoder(model)
+    decoder = rlt.SelfSpeculativeDecoder(model, cuda_graphs=not args.eager)
     clock = {}
 
     def start_clock():
@@ -530,7 +531,8 @@ def run_decode_workload(args):
     stats = decoder.stats
     print(json.dumps({
         "workload": "decode: Ouro-1.4B-shaped random-init bf16, self-spec k=4 from depth 2, "
-                    f"{args.requests} requests, prompts U[128,1024], {args.output_tokens} output tokens, T={args.temperature}",
+                    f"{args.requests} requests, prompts U[128,1024], {args.output_tokens} output tokens, T={args.temperature}, "
+                    + ("eager launches" if args.eager else "recurrent loops replayed from CUDA graphs"),
         "decode_seconds": seconds, "committed_tokens": stats.committed_tokens, "accepted_tokens": stats.accepted_tokens,
         "drafted_tokens": stats.drafted_tokens, "request_rounds": stats.rounds,
         "committed_tokens_per_s": stats.committed_tokens / seconds,
@@ -633,11 +635,14 @@ def main():
     parser.add_argument("--workload", default="step", choices=["step", "decode"],
                         help="step: the verify-step microbench (the bench line); decode: whole-model decoding (secondary)")
     parser.add_argument("--output-tokens", type=int, default=32)
+    parser.add_argument("--eager", action="store_true", help="decode workload: launch every kernel from the host")
     parser.add_argument("--temperature", type=float, default=0.8)
     parser.add_argument("--requests", type=int, default=REQUESTS)
     parser.add_argument("--layers", type=int, default=LAYERS)
     parser.add_argument("--tokens", type=int, default=TOKENS, help="with --only attention: new tokens per request")
     parser.add_argument("--depths", type=int, default=DEPTHS, help="with --only attention: depth rows per token")
+    parser.add_argument("--context-min", type=int, default=512, help="with --only attention: shortest context")
+    parser.add_argument("--context-max", type=int, default=4096, help="with --only attention: longest context")
     parser.add_argument("--kv-heads", type=int, default=HEADS, help="with --only attention: KV heads (query heads stay 16)")
     parser.add_argument("--shared-plan", action="store_true",
                         help="with --only attention: plan once per pass instead of once per layer call")

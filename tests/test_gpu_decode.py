@@ -142,3 +142,50 @@ def test_fused_layer_kernels_agree_with_the_tensor_expressions(dtype, tolerance)
     torch.testing.assert_close(a, b, rtol=tolerance, atol=tolerance)
     torch.testing.assert_close(ka, kb, rtol=tolerance, atol=tolerance)
     torch.testing.assert_close(va, vb, rtol=tolerance, atol=tolerance)
+
+
+@pytest.mark.parametrize("name", ["tiny_k3", "config1"])
+def test_graph_captured_loops_give_the_reference_tokens_and_counters(golden, name):
+    # every recurrent loop replayed from a CUDA graph per row bucket (padding rows write no K/V
+    # and attend to nothing): the reference engine's tokens and counters again
+    case = golden("decode.pt")[name]
+    decoder = rlt.SelfSpeculativeDecoder(build(case), block=case["block"], cuda_graphs=True)
+    speculative = decoder.generate(case["prompts"], case["max_tokens"], num_speculative_tokens=case["k"],
+                                   draft_loops=case["draft_loops"], target_loops=case["target_loops"])
+    assert speculative == case["tokens"]
+    stats, want = decoder.stats, case["stats"]
+    assert (stats.rounds, stats.drafted_tokens, stats.accepted_tokens, stats.committed_tokens,
+            stats.verified_rows) == (want["rounds"], want["drafted"], want["accepted"], want["committed"],
+                                     want["verified_rows"])
+
+
+def test_graph_replay_equals_the_eager_loop_bit_for_bit():
+    config = rlt.LoopedLMConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                                num_attention_heads=2, num_key_value_heads=2, head_dim=128, rope_theta=10000.0)
+    model = rlt.LoopedLM(config, rlt.seeded_state_dict(config, 5), "cuda", torch.bfloat16)
+    g = torch.Generator().manual_seed(4)
+    lengths = [40, 3, 17, 70, 9]
+    results = []
+    for graphed in (False, True):
+        kv = rlt.PagedKV.allocate(model, [n + 8 for n in lengths], 16)
+        loops = rlt.GraphedLoops(model, kv, granularity=32) if graphed else None
+        g.manual_seed(4)
+        outs = []
+        for step in range(3):                                   # growing contexts, three row counts, one bucket reused
+            rows = [(i, p) for i, n in enumerate(lengths) for p in range(n if step == 0 else 1)]
+            if step:
+                rows = [(i, lengths[i] + step - 1) for i in range(len(lengths) - step + 1)]
+            requests = torch.tensor([r for r, _ in rows], device="cuda")
+            positions = torch.tensor([p for _, p in rows], device="cuda")
+            hidden = model.prelude(torch.randint(1, 512, (len(rows),), generator=g).cuda())
+            blocks, offsets, tables, lens = kv.addressing(requests, positions, 0)
+            if graphed:
+                outs.append(loops(hidden, positions, blocks, offsets, tables, lens))
+            else:
+                outs.append(model.recurrent(hidden, positions, kv.key, kv.value, blocks, offsets, tables, lens))
+        results.append((outs, kv.key.clone(), kv.value.clone()))
+    (eager, ke, ve), (replayed, kg, vg) = results
+    for a, b in zip(eager, replayed):
+        assert torch.equal(a, b)
+    assert torch.equal(ke, kg) and torch.equal(ve, vg)
+    assert model.attention.last_status  # the wrapper stays usable after captures

@@ -187,6 +187,17 @@ __device__ __forceinline__ void tma_load_page_half(uint32_t dst, const CUtensorM
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(0), "r"(block), "r"(bar), "l"(policy)
       : "memory");
 }
+// Both 64-dim halves of one head of one page in a single copy: coordinates (element in half,
+// token, half-head index, block); lands as [half][token][64 dims], the layout two half copies give.
+__device__ __forceinline__ void tma_load_page(uint32_t dst, const CUtensorMap* map, int half_head, int block,
+                                              uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3, %4, %5}], [%6], %7;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(0), "r"(half_head), "r"(block), "r"(bar),
+        "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -206,6 +217,11 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
+}
+__device__ __forceinline__ unsigned arrive_acq_rel(unsigned* counter) {
+  unsigned prior;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prior) : "l"(counter) : "memory");
+  return prior;
 }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -460,7 +476,9 @@ __device__ __forceinline__ void merge_chunks(const AttentionArgs& a, const Works
   const int64_t qrow = row_start + source;
   const int qhead = kv_head * gqa + (r < mrows ? r : 0) % gqa;
   const float* part = ws.partials + ((qrow * a.q_heads + qhead) * ws.max_chunks) * kPartialStride;
+  // (m, l) of every chunk first, four loads in flight
   float big = -INFINITY;
+#pragma unroll 4
   for (int c = 0; c < row_chunks; ++c) big = fmaxf(big, __ldcg(part + c * kPartialStride + kHeadDim));
   T* out = static_cast<T*>(a.out) + (qrow * a.q_heads + qhead) * kHeadDim;
 #pragma unroll 1
@@ -470,19 +488,36 @@ __device__ __forceinline__ void merge_chunks(const AttentionArgs& a, const Works
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     float total = 0.f;
-    for (int c = 0; c < row_chunks; ++c) {
-      const float* pc = part + c * kPartialStride;
-      const float2 ml = __ldcg(reinterpret_cast<const float2*>(pc + kHeadDim));
-      float4 v[8];
+    // two chunks per step: their 18 loads are issued before either is folded in, so a step
+    // costs one L2 round trip (the accumulators of the finished item are dead here, which
+    // leaves the registers for it)
+    for (int c = 0; c < row_chunks; c += 2) {
+      const bool pair = c + 1 < row_chunks;
+      const float* pc0 = part + c * kPartialStride;
+      const float* pc1 = pc0 + (pair ? kPartialStride : 0);
+      const float2 ml0 = __ldcg(reinterpret_cast<const float2*>(pc0 + kHeadDim));
+      const float2 ml1 = __ldcg(reinterpret_cast<const float2*>(pc1 + kHeadDim));
+      float4 v0[8], v1[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = __ldcg(reinterpret_cast<const float4*>(pc + dim0) + i);
-      const float f = ml.x == -INFINITY ? 0.f : fast_exp2(ml.x - big);
+      for (int i = 0; i < 8; ++i) v0[i] = __ldcg(reinterpret_cast<const float4*>(pc0 + dim0) + i);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v1[i] = __ldcg(reinterpret_cast<const float4*>(pc1 + dim0) + i);
+      const float f0 = ml0.x == -INFINITY ? 0.f : fast_exp2(ml0.x - big);
+      const float f1 = (!pair || ml1.x == -INFINITY) ? 0.f : fast_exp2(ml1.x - big);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        acc[i].x = fmaf(v[i].x, f, acc[i].x); acc[i].y = fmaf(v[i].y, f, acc[i].y);
-        acc[i].z = fmaf(v[i].z, f, acc[i].z); acc[i].w = fmaf(v[i].w, f, acc[i].w);
+        acc[i].x = fmaf(v0[i].x, f0, acc[i].x); acc[i].y = fmaf(v0[i].y, f0, acc[i].y);
+        acc[i].z = fmaf(v0[i].z, f0, acc[i].z); acc[i].w = fmaf(v0[i].w, f0, acc[i].w);
       }
-      total = fmaf(ml.y, f, total);
+      total = fmaf(ml0.y, f0, total);
+      if (pair) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          acc[i].x = fmaf(v1[i].x, f1, acc[i].x); acc[i].y = fmaf(v1[i].y, f1, acc[i].y);
+          acc[i].z = fmaf(v1[i].z, f1, acc[i].z); acc[i].w = fmaf(v1[i].w, f1, acc[i].w);
+        }
+        total = fmaf(ml1.y, f1, total);
+      }
     }
     if (row_chunks > 0) {
       const float inv = 1.0f / total;
@@ -500,7 +535,9 @@ __device__ __forceinline__ void merge_chunks(const AttentionArgs& a, const Works
   }
 }
 
-template <bool kBF16, int kWarps, int kStages>
+// kWholeHead: the tensor maps are the 4-D form (one copy per K or V head slice of a page)
+// instead of the 3-D form (one copy per 64-dim half).
+template <bool kBF16, int kWarps, int kStages, bool kWholeHead>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                         AttentionArgs a, Workspace ws, float scale_log2) {
@@ -584,10 +621,15 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         const uint32_t bar = bar_base + stage * 8;
         const uint32_t dst = stage_base + stage * kStageBytes;
         mbar_expect_tx(bar, kStageBytes);
-        tma_load_page_half(dst, &k_map, iss_x0, block, bar, policy);
-        tma_load_page_half(dst + 2048, &k_map, iss_x0 + 64, block, bar, policy);
-        tma_load_page_half(dst + 4096, &v_map, iss_x0, block, bar, policy);
-        tma_load_page_half(dst + 6144, &v_map, iss_x0 + 64, block, bar, policy);
+        if constexpr (kWholeHead) {
+          tma_load_page(dst, &k_map, iss_x0 >> 6, block, bar, policy);
+          tma_load_page(dst + 4096, &v_map, iss_x0 >> 6, block, bar, policy);
+        } else {
+          tma_load_page_half(dst, &k_map, iss_x0, block, bar, policy);
+          tma_load_page_half(dst + 2048, &k_map, iss_x0 + 64, block, bar, policy);
+          tma_load_page_half(dst + 4096, &v_map, iss_x0, block, bar, policy);
+          tma_load_page_half(dst + 6144, &v_map, iss_x0 + 64, block, bar, policy);
+        }
       }
       ++issued;
       ++iss_tile;
@@ -704,9 +746,11 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         mma_16816<kBF16>(o[2 * jp + 1], pa, b[2], b[3]);
       }
       ++consumed;
-      // the stage just read is free: order our shared-memory reads before the next TMA write
+      // The stage just read is free.  Every lane's ldmatrix results have been consumed by its
+      // MMAs, so the reads are complete before lane 0 passes this barrier and issues the copy
+      // that overwrites the stage (the consumer-release step of a TMA pipeline needs no
+      // proxy fence: only generic WRITES must be fenced before async-proxy accesses).
       __syncwarp();
-      if (lane == 0) fence_proxy_async();
       top_up();
     }
     if (failed) break;
@@ -745,16 +789,18 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       }
     }
     // ---- the warp that stores a group's last partial merges its chunks in chunk order ----
+    // The arrival is one acquire-release add by lane 0: the warp barrier before it orders every
+    // lane's partial stores before the release, the one after it extends lane 0's acquire to
+    // the lanes that read the other warps' partials (no sequentially consistent fence needed).
     if (cur.group_chunks > 1) {
-      __threadfence();
       __syncwarp();
       unsigned prior = 0;
-      if (lane == 0) prior = atomicAdd(&ws.counters[static_cast<int64_t>(cur.row_start) * a.kv_heads + cur.kv_head], 1u);
+      if (lane == 0) prior = arrive_acq_rel(&ws.counters[static_cast<int64_t>(cur.row_start) * a.kv_heads + cur.kv_head]);
       prior = __shfl_sync(0xffffffffu, prior, 0);
       if (prior == static_cast<unsigned>(cur.group_chunks - 1)) {
         // leave the counter at zero so the same plan can drive another run
         if (lane == 0) ws.counters[static_cast<int64_t>(cur.row_start) * a.kv_heads + cur.kv_head] = 0;
-        __threadfence();
+        __syncwarp();
         merge_chunks<kBF16>(a, ws, cur.row_start, cur.kv_head, gqa, mrows, cur.len, lane);
       }
     }
@@ -830,14 +876,33 @@ int make_page_map(CUtensorMap* map, const void* base, const AttentionArgs& a) {
   return RLT_OK;
 }
 
+// The same view as [num_blocks][kv_heads * 2 half-heads][16 tokens][64] elements: box = 64
+// elements x 16 tokens x 2 halves x 1 block.  The half-head stride (128 bytes) is smaller than
+// the token stride before it; returns RLT_ERR_UNSUPPORTED if the driver refuses that order.
+int make_head_map(CUtensorMap* map, const void* base, const AttentionArgs& a) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return RLT_ERR_UNSUPPORTED;
+  const cuuint64_t dims[4] = {64, kPage, static_cast<cuuint64_t>(a.kv_heads) * 2,
+                              static_cast<cuuint64_t>(a.num_blocks)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(a.token_stride) * 2, 128,
+                                 static_cast<cuuint64_t>(a.block_stride) * 2};
+  const cuuint32_t box[4] = {64, kPage, 2, 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  const CUresult r = fn(map, a.dtype == RLT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        4, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RLT_OK : RLT_ERR_UNSUPPORTED;
+}
+
 int gqa_cap(const AttentionArgs& a) { return kMaxGroupRows / (a.q_heads / a.kv_heads); }
 
-template <bool kBF16, int kWarps, int kStages>
+template <bool kBF16, int kWarps, int kStages, bool kWholeHead>
 int launch_main(const CUtensorMap& k_map, const CUtensorMap& v_map, const AttentionArgs& a, const Workspace& ws,
                 int sm_count, cudaStream_t stream) {
   const size_t smem = sizeof(SharedStorage<kWarps, kStages>) + 1024;
   const float scale_log2 = static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(kHeadDim)));
-  auto kernel = verify_attention_kernel<kBF16, kWarps, kStages>;
+  auto kernel = verify_attention_kernel<kBF16, kWarps, kStages, kWholeHead>;
   RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   kernel<<<sm_count, kWarps * 32, smem, stream>>>(k_map, v_map, a, ws, scale_log2);
   return launch_status("verify_attention_kernel");
@@ -924,26 +989,31 @@ int run_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspac
   DeviceInfo info;
   status = current_device_info(&info);
   if (status != RLT_OK) return status;
-  CUtensorMap k_map, v_map;
-  status = make_page_map(&k_map, a.key_cache, a);
-  if (status != RLT_OK) return status;
-  status = make_page_map(&v_map, a.value_cache, a);
-  if (status != RLT_OK) return status;
-
-  // Ring geometry (warps per SM x stages per warp); RLT_ATTENTION_RING selects another
-  // compiled variant for tuning runs.
+  // RLT_ATTENTION_RING selects another compiled variant for tuning runs: 1 = one copy per
+  // 64-dim half (the 3-D maps), 2 and 3 = other ring geometries (warps per SM x stages per warp).
   static const int variant = [] {
     const char* e = getenv("RLT_ATTENTION_RING");
     return e ? atoi(e) : 0;
   }();
+  CUtensorMap k_map, v_map;
+  bool whole_head = variant != 1 && make_head_map(&k_map, a.key_cache, a) == RLT_OK &&
+                    make_head_map(&v_map, a.value_cache, a) == RLT_OK;
+  if (!whole_head) {
+    status = make_page_map(&k_map, a.key_cache, a);
+    if (status != RLT_OK) return status;
+    status = make_page_map(&v_map, a.value_cache, a);
+    if (status != RLT_OK) return status;
+  }
   if (a.dtype == RLT_BF16) {
+    if (!whole_head) return launch_main<true, 8, 3, false>(k_map, v_map, a, ws, info.sm_count, stream);
     switch (variant) {
-      case 2: return launch_main<true, 7, 4>(k_map, v_map, a, ws, info.sm_count, stream);
-      case 3: return launch_main<true, 12, 2>(k_map, v_map, a, ws, info.sm_count, stream);
-      default: return launch_main<true, 8, 3>(k_map, v_map, a, ws, info.sm_count, stream);
+      case 2: return launch_main<true, 7, 4, true>(k_map, v_map, a, ws, info.sm_count, stream);
+      case 3: return launch_main<true, 12, 2, true>(k_map, v_map, a, ws, info.sm_count, stream);
+      default: return launch_main<true, 8, 3, true>(k_map, v_map, a, ws, info.sm_count, stream);
     }
   }
-  return launch_main<false, 8, 3>(k_map, v_map, a, ws, info.sm_count, stream);
+  if (!whole_head) return launch_main<false, 8, 3, false>(k_map, v_map, a, ws, info.sm_count, stream);
+  return launch_main<false, 8, 3, true>(k_map, v_map, a, ws, info.sm_count, stream);
 }
 
 int launch_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {

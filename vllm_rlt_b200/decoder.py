@@ -15,7 +15,7 @@ check the reference applies to its own runner (tests/test_speculative.py:71-87 t
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 
@@ -72,22 +72,87 @@ class PagedKV:
         return blocks, positions % self.block, tables.contiguous(), (positions + 1).int()
 
 
-@dataclass
-class _State:
-    prompts: list
-    max_tokens: int
-    generated: list = field(default_factory=list)
+class GraphedLoops:
+    """One recurrent loop (all layers) as a CUDA graph per row-count bucket.
+
+    The reference captures its decode passes the same way (`worker/cuda_graph.py:338-404`):
+    static input buffers, batch sizes rounded up to a bucket, padding rows that neither write
+    K/V (they lie at or beyond `active_rows`) nor read any (context length 0, so the attention
+    plan gives them no work and zeros as output).  Row grouping is planned on the device inside
+    the graph, so a replay follows whatever tables and lengths the buffers hold.
+    """
+
+    def __init__(self, model: LoopedLM, kv: PagedKV, *, granularity: int = 64):
+        if not model.fused:
+            raise ValueError("graph capture needs the fused layer path")
+        self.model, self.kv, self.granularity = model, kv, granularity
+        self.pool = torch.cuda.graph_pool_handle()
+        self.graphs = {}
+
+    def _capture(self, bucket: int):
+        model, kv, device = self.model, self.kv, self.model.device
+        buffers = dict(
+            hidden=torch.zeros(bucket, model.config.hidden_size, dtype=model.dtype, device=device),
+            positions=torch.zeros(bucket, dtype=torch.int64, device=device),
+            blocks=torch.zeros(bucket, dtype=torch.int64, device=device),
+            offsets=torch.zeros(bucket, dtype=torch.int64, device=device),
+            tables=torch.zeros(bucket, kv.tables.shape[2], dtype=torch.int32, device=device),
+            lengths=torch.zeros(bucket, dtype=torch.int32, device=device),
+            active=torch.zeros((), dtype=torch.int32, device=device))
+
+        def run():
+            return model._recurrent_fused(buffers["hidden"], buffers["positions"], kv.key, kv.value, buffers["blocks"],
+                                          buffers["offsets"], buffers["tables"], buffers["lengths"],
+                                          active_rows=buffers["active"])
+
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):                      # library handles and workspaces exist before capture
+            run()
+        torch.cuda.current_stream(device).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self.pool):
+            buffers["out"] = run()
+        self.graphs[bucket] = (graph, buffers)
+        return self.graphs[bucket]
+
+    def bucket_of(self, rows: int) -> int:
+        return -(-rows // self.granularity) * self.granularity
+
+    def prepare(self, max_rows: int):
+        """Capture every bucket up to `max_rows` now (benchmarks do this before their clock starts)."""
+        for bucket in range(self.bucket_of(max_rows), 0, -self.granularity):   # largest first: scratch is sized once
+            if bucket not in self.graphs:
+                self._capture(bucket)
+
+    def __call__(self, hidden, positions, blocks, offsets, tables, lengths):
+        rows = hidden.shape[0]
+        graph, b = self.graphs.get(self.bucket_of(rows)) or self._capture(self.bucket_of(rows))
+        b["hidden"][:rows] = hidden
+        b["positions"][:rows] = positions
+        b["blocks"][:rows] = blocks
+        b["offsets"][:rows] = offsets
+        b["tables"][:rows] = tables
+        b["lengths"][:rows] = lengths
+        b["lengths"][rows:] = 0
+        b["active"].fill_(rows)
+        graph.replay()
+        return b["out"][:rows].clone()
 
 
 class SelfSpeculativeDecoder:
-    def __init__(self, model: LoopedLM, *, block: int = 16):
+    def __init__(self, model: LoopedLM, *, block: int = 16, cuda_graphs: bool = False):
         self.model = model
         self.block = block
+        self.cuda_graphs = cuda_graphs
         self.stats = DecodeStats()
+        self._graphs = None
 
     # ---- shared pieces -------------------------------------------------------------------
     def _loop(self, kv: PagedKV, hidden, requests, positions, depth):
         blocks, offsets, tables, lengths = kv.addressing(requests, positions, depth)
+        if self._graphs is not None and self._graphs.kv is kv:
+            return self._graphs(hidden, positions, blocks, offsets, tables, lengths)
         return self.model.recurrent(hidden, positions, kv.key, kv.value, blocks, offsets, tables, lengths)
 
     def _prefill(self, kv: PagedKV, prompts):
@@ -149,6 +214,9 @@ class SelfSpeculativeDecoder:
         k = num_speculative_tokens
         kv = PagedKV.allocate(model, [len(p) + max_tokens + k + 1 for p in prompts], self.block)
         generated = [[t] for t in self._prefill(kv, prompts)]  # the first token is the prefill's argmax
+        if self.cuda_graphs:
+            self._graphs = GraphedLoops(model, kv)
+            self._graphs.prepare(len(prompts) * (k + 1))
         if after_prefill is not None:
             after_prefill()
         slot_values = torch.zeros(len(prompts), 2, dtype=torch.int64, device=device)
@@ -233,4 +301,5 @@ class SelfSpeculativeDecoder:
                 self.stats.committed_tokens += len(emitted)
             self.stats.rounds += n
             self.stats.verified_rows += rows_total
+        self._graphs = None
         return [g[:max_tokens] for g in generated]
