@@ -14,11 +14,15 @@
 //                 rows at once on tensor cores (m16n8k16; Q in registers, K/V fragments by
 //                 ldmatrix) with an fp32 online softmax, so a page is read from HBM once per
 //                 group instead of once per row.  A row whose context fits one chunk is
-//                 finished from registers; otherwise the warp stores an fp32 partial and the
-//                 warp that stores the last partial of a group merges the chunks in chunk order.
+//                 finished from registers; otherwise the warp stores an fp32 partial.
+//   merge kernel  one warp per (row, query head) whose context spans more than one chunk folds
+//                 that row's partials in chunk order.  The kernel boundary is the only ordering
+//                 between the partial stores and their readers: a device-scope fence inside the
+//                 streaming kernel waits for the warp's pages in flight, a full memory latency
+//                 per work item, which costs more than this launch.
 //
-// There is no cross-warp reduction and no CTA-wide barrier after start-up; the only
-// synchronisation is each warp's own mbarrier ring and one atomic per multi-chunk item.
+// The main kernel has no cross-warp reduction, no CTA-wide barrier after start-up and no
+// atomics besides the work-item claim; its only synchronisation is each warp's mbarrier ring.
 //
 // Batch invariance: chunk boundaries and the merge order are functions of absolute token
 // positions only, and a tensor-core output row depends only on its own input row, so a row's
@@ -96,7 +100,7 @@ struct Item {
 };
 
 struct Layout {
-  size_t header, row_len, row_table, link, zero_list, counters, items_a, items_b, partials, total;
+  size_t header, row_len, row_table, link, zero_list, items_a, items_b, partials, total;
   int max_chunks;
 };
 
@@ -113,7 +117,6 @@ Layout make_layout(int rows, int q_heads, int kv_heads, int block_size, int tabl
   l.row_table = off; off += align256(sizeof(int) * rows);
   l.link = off; off += align256(sizeof(int) * rows);
   l.zero_list = off; off += align256(sizeof(int) * rows);
-  l.counters = off; off += align256(sizeof(unsigned) * rows * kv_heads);
   l.items_a = off; off += align256(sizeof(Item) * static_cast<size_t>(rows) * kv_heads * (l.max_chunks - 1) + 16);
   l.items_b = off; off += align256(sizeof(Item) * static_cast<size_t>(rows) * kv_heads);
   l.partials = off;
@@ -128,7 +131,6 @@ struct Workspace {
   int* row_table;
   int* link;
   int* zero_list;
-  unsigned* counters;
   Item* items_a;
   Item* items_b;
   float* partials;
@@ -173,11 +175,6 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
-// Orders this thread's earlier generic-proxy accesses to shared memory before later
-// async-proxy (TMA) writes to it.
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 // One [64 dims x 16 tokens] box of one page: coordinates (element in token row, token, block).
 __device__ __forceinline__ void tma_load_page_half(uint32_t dst, const CUtensorMap* map, int x, int block,
                                                    uint32_t bar, uint64_t policy) {
@@ -195,6 +192,17 @@ __device__ __forceinline__ void tma_load_page(uint32_t dst, const CUtensorMap* m
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
       " [%0], [%1, {%2, %3, %4, %5}], [%6], %7;"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(0), "r"(half_head), "r"(block), "r"(bar),
+        "l"(policy)
+      : "memory");
+}
+// K and V head slices of one page in a single copy through a map whose fourth dimension steps
+// from one cache to the other: coordinates (element, token, half-head index, cache, block).
+__device__ __forceinline__ void tma_load_page_kv(uint32_t dst, const CUtensorMap* map, int half_head, int block,
+                                                 uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3, %4, %5, %6}], [%7], %8;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(0), "r"(half_head), "r"(0), "r"(block), "r"(bar),
         "l"(policy)
       : "memory");
 }
@@ -217,11 +225,6 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
-}
-__device__ __forceinline__ unsigned arrive_acq_rel(unsigned* counter) {
-  unsigned prior;
-  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(prior) : "l"(counter) : "memory");
-  return prior;
 }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -307,7 +310,6 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
       ws.row_table[row] = table_row;
       ws.link[row] = link;
     }
-    for (int h = lane; h < a.kv_heads; h += 32) ws.counters[static_cast<int64_t>(row) * a.kv_heads + h] = 0;
   }
 
   // The last CTA to get here builds the work lists.
@@ -417,7 +419,6 @@ struct ItemCtx {
   int chunk;
   int chunk_start;
   int ntiles;
-  int group_chunks;
   int len;
   int page;
 };
@@ -436,7 +437,7 @@ __device__ __forceinline__ ItemCtx claim_item(const AttentionArgs& a, const Work
   const unsigned full = ws.header->full_items, last = ws.header->last_items;
   c.valid = idx < full + last;
   c.row_start = c.table_row = c.nrows = c.kv_head = c.chunk = c.chunk_start = c.ntiles = 0;
-  c.group_chunks = c.len = 0;
+  c.len = 0;
   c.page = -1;
   if (!c.valid) return c;
   const Item it = idx < full ? ws.items_a[idx] : ws.items_b[idx - full];
@@ -453,94 +454,78 @@ __device__ __forceinline__ ItemCtx claim_item(const AttentionArgs& a, const Work
   chunk_range(c.chunk, &c.chunk_start, &cend);
   const int visible = min(cend, longest) - c.chunk_start;
   c.ntiles = visible > 0 ? (visible + kPage - 1) / kPage : 0;
-  c.group_chunks = chunk_count(longest);
   const int32_t* table = a.block_tables + static_cast<int64_t>(c.table_row) * a.table_width + c.chunk_start / kPage;
   c.page = lane < c.ntiles ? table[lane] : -1;
   return c;
 }
 
-// Merge of a group's per-chunk partials into its output rows, by one warp, all rows at once:
-// lanes 2r and 2r+1 own the two 64-dim halves of fragment row r and walk that row's chunks in
-// chunk order, out = sum_c O_c * 2^(m_c - M) / sum_c l_c * 2^(m_c - M) with M = max_c m_c.
-// The merge is a chain of L2 round trips; doing the (up to 16) rows side by side instead of one
-// after another makes it about (1 + 2 * chunks) trips per group instead of per row.
+// Merge of one row's per-chunk partials, one warp per (row, query head), lane l owning dims
+// 4l .. 4l+3:  out = sum_c O_c * 2^(m_c - M) / sum_c l_c * 2^(m_c - M), folded in chunk order with
+// M the maximum over the first eight chunks (all chunks, for contexts up to 4096 tokens), raised
+// and the sums rescaled when a later group of eight chunks brings a larger one.  Rows of one chunk were finished by the main kernel and are skipped.  The
+// partials were written moments ago and are read from L2.
+constexpr int kMergeWarps = 4;
+
 template <bool kBF16>
-__device__ __forceinline__ void merge_chunks(const AttentionArgs& a, const Workspace& ws, int row_start, int kv_head,
-                                             int gqa, int mrows, int lane_len, int lane) {
+__global__ void __launch_bounds__(kMergeWarps * 32)
+merge_kernel(AttentionArgs a, Workspace ws) {
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
-  const int r = lane >> 1, half = lane & 1;
-  const int source = (r < mrows ? r : 0) / gqa;
-  const int len = __shfl_sync(0xffffffffu, lane_len, source);
-  int row_chunks = r < mrows ? chunk_count(len) : 0;
-  if (row_chunks < 2) row_chunks = 0;  // single-chunk rows were finished from registers
-  const int64_t qrow = row_start + source;
-  const int qhead = kv_head * gqa + (r < mrows ? r : 0) % gqa;
-  const float* part = ws.partials + ((qrow * a.q_heads + qhead) * ws.max_chunks) * kPartialStride;
-  // (m, l) of every chunk first, four loads in flight
-  float big = -INFINITY;
-#pragma unroll 4
-  for (int c = 0; c < row_chunks; ++c) big = fmaxf(big, __ldcg(part + c * kPartialStride + kHeadDim));
-  T* out = static_cast<T*>(a.out) + (qrow * a.q_heads + qhead) * kHeadDim;
-#pragma unroll 1
-  for (int quarter = 0; quarter < 2; ++quarter) {
-    const int dim0 = half * 64 + quarter * 32;
-    float4 acc[8];
+  const int lane = threadIdx.x & 31;
+  const int64_t pair = static_cast<int64_t>(blockIdx.x) * kMergeWarps + (threadIdx.x >> 5);
+  if (pair >= static_cast<int64_t>(a.rows) * a.q_heads) return;
+  const int64_t row = pair / a.q_heads;
+  const int chunks = chunk_count(ws.row_len[row]);
+  if (chunks < 2) return;
+  const float* part = ws.partials + pair * ws.max_chunks * kPartialStride;
+  // Eight chunks per step, all sixteen loads of a step in flight together: a context of up to
+  // 4096 tokens is one L2 round trip.  Across steps the running maximum M only grows, and the
+  // accumulators are rescaled by 2^(M_old - M_new) — exactly 1 when it did not grow.
+  float big = -INFINITY, total = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c0 = 0; c0 < chunks; c0 += 8) {
+    float2 ml[8];
+    float4 v[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    float total = 0.f;
-    // two chunks per step: their 18 loads are issued before either is folded in, so a step
-    // costs one L2 round trip (the accumulators of the finished item are dead here, which
-    // leaves the registers for it)
-    for (int c = 0; c < row_chunks; c += 2) {
-      const bool pair = c + 1 < row_chunks;
-      const float* pc0 = part + c * kPartialStride;
-      const float* pc1 = pc0 + (pair ? kPartialStride : 0);
-      const float2 ml0 = __ldcg(reinterpret_cast<const float2*>(pc0 + kHeadDim));
-      const float2 ml1 = __ldcg(reinterpret_cast<const float2*>(pc1 + kHeadDim));
-      float4 v0[8], v1[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v0[i] = __ldcg(reinterpret_cast<const float4*>(pc0 + dim0) + i);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v1[i] = __ldcg(reinterpret_cast<const float4*>(pc1 + dim0) + i);
-      const float f0 = ml0.x == -INFINITY ? 0.f : fast_exp2(ml0.x - big);
-      const float f1 = (!pair || ml1.x == -INFINITY) ? 0.f : fast_exp2(ml1.x - big);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        acc[i].x = fmaf(v0[i].x, f0, acc[i].x); acc[i].y = fmaf(v0[i].y, f0, acc[i].y);
-        acc[i].z = fmaf(v0[i].z, f0, acc[i].z); acc[i].w = fmaf(v0[i].w, f0, acc[i].w);
-      }
-      total = fmaf(ml0.y, f0, total);
-      if (pair) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          acc[i].x = fmaf(v1[i].x, f1, acc[i].x); acc[i].y = fmaf(v1[i].y, f1, acc[i].y);
-          acc[i].z = fmaf(v1[i].z, f1, acc[i].z); acc[i].w = fmaf(v1[i].w, f1, acc[i].w);
-        }
-        total = fmaf(ml1.y, f1, total);
-      }
+    for (int i = 0; i < 8; ++i) {
+      const float* pc = part + min(c0 + i, chunks - 1) * kPartialStride;
+      ml[i] = __ldcg(reinterpret_cast<const float2*>(pc + kHeadDim));
+      v[i] = __ldcg(reinterpret_cast<const float4*>(pc) + lane);
     }
-    if (row_chunks > 0) {
-      const float inv = 1.0f / total;
-      uint4* dst = reinterpret_cast<uint4*>(out + dim0);
+    float step_big = big;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint4 packed;
-        packed.x = pack2<kBF16>(acc[2 * i].x * inv, acc[2 * i].y * inv);
-        packed.y = pack2<kBF16>(acc[2 * i].z * inv, acc[2 * i].w * inv);
-        packed.z = pack2<kBF16>(acc[2 * i + 1].x * inv, acc[2 * i + 1].y * inv);
-        packed.w = pack2<kBF16>(acc[2 * i + 1].z * inv, acc[2 * i + 1].w * inv);
-        dst[i] = packed;
+    for (int i = 0; i < 8; ++i)
+      if (c0 + i < chunks) step_big = fmaxf(step_big, ml[i].x);
+    if (step_big != big) {
+      const float r = big == -INFINITY ? 0.f : fast_exp2(big - step_big);
+      acc.x *= r; acc.y *= r; acc.z *= r; acc.w *= r;
+      total *= r;
+      big = step_big;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (c0 + i < chunks) {
+        const float f = ml[i].x == -INFINITY ? 0.f : fast_exp2(ml[i].x - big);
+        acc.x = fmaf(v[i].x, f, acc.x); acc.y = fmaf(v[i].y, f, acc.y);
+        acc.z = fmaf(v[i].z, f, acc.z); acc.w = fmaf(v[i].w, f, acc.w);
+        total = fmaf(ml[i].y, f, total);
       }
     }
   }
+  const float inv = 1.0f / total;
+  uint2 packed;
+  packed.x = pack2<kBF16>(acc.x * inv, acc.y * inv);
+  packed.y = pack2<kBF16>(acc.z * inv, acc.w * inv);
+  reinterpret_cast<uint2*>(static_cast<T*>(a.out) + pair * kHeadDim)[lane] = packed;
 }
 
-// kWholeHead: the tensor maps are the 4-D form (one copy per K or V head slice of a page)
-// instead of the 3-D form (one copy per 64-dim half).
-template <bool kBF16, int kWarps, int kStages, bool kWholeHead>
+// kCopies: TMA copies per page.  4: 3-D maps, one copy per 64-dim half of K and of V.  2: 4-D
+// maps, one copy per K or V head slice.  1: one 5-D map over both caches (k_map; v_map unused),
+// one copy per page; `k_first` tells which cache lies at the lower address and therefore lands
+// in the first half of a stage.
+template <bool kBF16, int kWarps, int kStages, int kCopies>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                        AttentionArgs a, Workspace ws, float scale_log2) {
+                        AttentionArgs a, Workspace ws, float scale_log2, int k_first) {
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
   using Storage = SharedStorage<kWarps, kStages>;
   extern __shared__ unsigned char smem_raw[];
@@ -577,12 +562,12 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
       const int chunk16 = ((ks & 3) << 1) + (mi & 1);
-      koff[ks] = ((ks >> 2) << 11) + ktoken * 128 + ((chunk16 ^ (ktoken & 7)) << 4);
+      koff[ks] = (k_first ? 0 : kTileBytes) + ((ks >> 2) << 11) + ktoken * 128 + ((chunk16 ^ (ktoken & 7)) << 4);
     }
 #pragma unroll
     for (int jp = 0; jp < 8; ++jp) {
       const int c = 2 * jp + (mi >> 1);
-      voff[jp] = kTileBytes + ((c >> 3) << 11) + vtoken * 128 + (((c & 7) ^ (vtoken & 7)) << 4);
+      voff[jp] = (k_first ? kTileBytes : 0) + ((c >> 3) << 11) + vtoken * 128 + (((c & 7) ^ (vtoken & 7)) << 4);
     }
   }
 
@@ -621,7 +606,9 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         const uint32_t bar = bar_base + stage * 8;
         const uint32_t dst = stage_base + stage * kStageBytes;
         mbar_expect_tx(bar, kStageBytes);
-        if constexpr (kWholeHead) {
+        if constexpr (kCopies == 1) {
+          tma_load_page_kv(dst, &k_map, iss_x0 >> 6, block, bar, policy);
+        } else if constexpr (kCopies == 2) {
           tma_load_page(dst, &k_map, iss_x0 >> 6, block, bar, policy);
           tma_load_page(dst + 4096, &v_map, iss_x0 >> 6, block, bar, policy);
         } else {
@@ -789,22 +776,6 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       }
     }
     // ---- the warp that stores a group's last partial merges its chunks in chunk order ----
-    // The arrival is one acquire-release add by lane 0: the warp barrier before it orders every
-    // lane's partial stores before the release, the one after it extends lane 0's acquire to
-    // the lanes that read the other warps' partials (no sequentially consistent fence needed).
-    if (cur.group_chunks > 1) {
-      __syncwarp();
-      unsigned prior = 0;
-      if (lane == 0) prior = arrive_acq_rel(&ws.counters[static_cast<int64_t>(cur.row_start) * a.kv_heads + cur.kv_head]);
-      prior = __shfl_sync(0xffffffffu, prior, 0);
-      if (prior == static_cast<unsigned>(cur.group_chunks - 1)) {
-        // leave the counter at zero so the same plan can drive another run
-        if (lane == 0) ws.counters[static_cast<int64_t>(cur.row_start) * a.kv_heads + cur.kv_head] = 0;
-        __syncwarp();
-        merge_chunks<kBF16>(a, ws, cur.row_start, cur.kv_head, gqa, mrows, cur.len, lane);
-      }
-    }
-
     // ---- next item ----
     cur = nxt;
     if (iss_on_next) {
@@ -895,17 +866,44 @@ int make_head_map(CUtensorMap* map, const void* base, const AttentionArgs& a) {
   return r == CUDA_SUCCESS ? RLT_OK : RLT_ERR_UNSUPPORTED;
 }
 
+// Both caches as one tensor [num_blocks][2 caches][kv_heads * 2][16 tokens][64]: the cache
+// dimension's stride is the distance between the two base addresses, so it exists only when
+// that distance is a positive multiple of 16 below 2^40 from `base` (the lower of the two).
+int make_joint_map(CUtensorMap* map, const AttentionArgs& a, bool* k_first) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return RLT_ERR_UNSUPPORTED;
+  const uintptr_t k = reinterpret_cast<uintptr_t>(a.key_cache), v = reinterpret_cast<uintptr_t>(a.value_cache);
+  *k_first = k < v;
+  const uintptr_t lower = k < v ? k : v, distance = k < v ? v - k : k - v;
+  if (distance == 0 || distance % 16 != 0 || distance >= (1ull << 40)) return RLT_ERR_UNSUPPORTED;
+  const cuuint64_t dims[5] = {64, kPage, static_cast<cuuint64_t>(a.kv_heads) * 2, 2,
+                              static_cast<cuuint64_t>(a.num_blocks)};
+  const cuuint64_t strides[4] = {static_cast<cuuint64_t>(a.token_stride) * 2, 128, distance,
+                                 static_cast<cuuint64_t>(a.block_stride) * 2};
+  const cuuint32_t box[5] = {64, kPage, 2, 2, 1};
+  const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+  const CUresult r = fn(map, a.dtype == RLT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        5, reinterpret_cast<void*>(lower), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RLT_OK : RLT_ERR_UNSUPPORTED;
+}
+
 int gqa_cap(const AttentionArgs& a) { return kMaxGroupRows / (a.q_heads / a.kv_heads); }
 
-template <bool kBF16, int kWarps, int kStages, bool kWholeHead>
+template <bool kBF16, int kWarps, int kStages, int kCopies>
 int launch_main(const CUtensorMap& k_map, const CUtensorMap& v_map, const AttentionArgs& a, const Workspace& ws,
-                int sm_count, cudaStream_t stream) {
+                int sm_count, cudaStream_t stream, bool k_first = true) {
   const size_t smem = sizeof(SharedStorage<kWarps, kStages>) + 1024;
   const float scale_log2 = static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(kHeadDim)));
-  auto kernel = verify_attention_kernel<kBF16, kWarps, kStages, kWholeHead>;
+  auto kernel = verify_attention_kernel<kBF16, kWarps, kStages, kCopies>;
   RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  kernel<<<sm_count, kWarps * 32, smem, stream>>>(k_map, v_map, a, ws, scale_log2);
-  return launch_status("verify_attention_kernel");
+  kernel<<<sm_count, kWarps * 32, smem, stream>>>(k_map, v_map, a, ws, scale_log2, k_first ? 1 : 0);
+  int status = launch_status("verify_attention_kernel");
+  if (status != RLT_OK || ws.max_chunks < 2) return status;  // no context can span two chunks
+  const int64_t pairs = static_cast<int64_t>(a.rows) * a.q_heads;
+  merge_kernel<kBF16><<<static_cast<unsigned>((pairs + kMergeWarps - 1) / kMergeWarps), kMergeWarps * 32, 0, stream>>>(a, ws);
+  return launch_status("merge_kernel");
 }
 
 }  // namespace
@@ -960,7 +958,6 @@ int bind_workspace(const AttentionArgs& a, void* workspace, size_t workspace_byt
   ws->row_table = reinterpret_cast<int*>(base + l.row_table);
   ws->link = reinterpret_cast<int*>(base + l.link);
   ws->zero_list = reinterpret_cast<int*>(base + l.zero_list);
-  ws->counters = reinterpret_cast<unsigned*>(base + l.counters);
   ws->items_a = reinterpret_cast<Item*>(base + l.items_a);
   ws->items_b = reinterpret_cast<Item*>(base + l.items_b);
   ws->partials = reinterpret_cast<float*>(base + l.partials);
@@ -989,31 +986,37 @@ int run_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspac
   DeviceInfo info;
   status = current_device_info(&info);
   if (status != RLT_OK) return status;
-  // RLT_ATTENTION_RING selects another compiled variant for tuning runs: 1 = one copy per
-  // 64-dim half (the 3-D maps), 2 and 3 = other ring geometries (warps per SM x stages per warp).
-  static const int variant = [] {
-    const char* e = getenv("RLT_ATTENTION_RING");
+  // RLT_ATTENTION_COPIES (4, 2 or 1 TMA copies per page) pins a variant for tuning runs.  By
+  // default the fewest copies the driver accepts a map for are used.
+  static const int pinned = [] {
+    const char* e = getenv("RLT_ATTENTION_COPIES");
     return e ? atoi(e) : 0;
   }();
   CUtensorMap k_map, v_map;
-  bool whole_head = variant != 1 && make_head_map(&k_map, a.key_cache, a) == RLT_OK &&
-                    make_head_map(&v_map, a.value_cache, a) == RLT_OK;
-  if (!whole_head) {
+  bool k_first = true;
+  int copies = 4;
+  if ((pinned == 0 || pinned == 1) && make_joint_map(&k_map, a, &k_first) == RLT_OK) {
+    copies = 1;
+    v_map = k_map;
+  } else if (pinned != 4 && make_head_map(&k_map, a.key_cache, a) == RLT_OK &&
+             make_head_map(&v_map, a.value_cache, a) == RLT_OK) {
+    copies = 2;
+    k_first = true;
+  } else {
+    k_first = true;
     status = make_page_map(&k_map, a.key_cache, a);
     if (status != RLT_OK) return status;
     status = make_page_map(&v_map, a.value_cache, a);
     if (status != RLT_OK) return status;
   }
   if (a.dtype == RLT_BF16) {
-    if (!whole_head) return launch_main<true, 8, 3, false>(k_map, v_map, a, ws, info.sm_count, stream);
-    switch (variant) {
-      case 2: return launch_main<true, 7, 4, true>(k_map, v_map, a, ws, info.sm_count, stream);
-      case 3: return launch_main<true, 12, 2, true>(k_map, v_map, a, ws, info.sm_count, stream);
-      default: return launch_main<true, 8, 3, true>(k_map, v_map, a, ws, info.sm_count, stream);
-    }
+    if (copies == 1) return launch_main<true, 8, 3, 1>(k_map, v_map, a, ws, info.sm_count, stream, k_first);
+    if (copies == 2) return launch_main<true, 8, 3, 2>(k_map, v_map, a, ws, info.sm_count, stream);
+    return launch_main<true, 8, 3, 4>(k_map, v_map, a, ws, info.sm_count, stream);
   }
-  if (!whole_head) return launch_main<false, 8, 3, false>(k_map, v_map, a, ws, info.sm_count, stream);
-  return launch_main<false, 8, 3, true>(k_map, v_map, a, ws, info.sm_count, stream);
+  if (copies == 1) return launch_main<false, 8, 3, 1>(k_map, v_map, a, ws, info.sm_count, stream, k_first);
+  if (copies == 2) return launch_main<false, 8, 3, 2>(k_map, v_map, a, ws, info.sm_count, stream);
+  return launch_main<false, 8, 3, 4>(k_map, v_map, a, ws, info.sm_count, stream);
 }
 
 int launch_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
