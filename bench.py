@@ -46,7 +46,7 @@ METRIC = "accepted tokens/s/GPU, Ouro-1.4B self-spec decode; verify-attn % HBM p
 # DRAM bytes (read + write) per algorithmic byte of verify_attention_kernel, from the ncu capture
 # summarised in profiles/verify_attention_kernel_config2.md (32-request case; traffic grows in
 # proportion to the K/V read, so the ratio carries over to a full launch).
-ATTENTION_TRAFFIC_RATIO = 1.0228
+ATTENTION_TRAFFIC_RATIO = 1.0128
 
 
 def measured_peaks():
