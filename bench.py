@@ -450,6 +450,46 @@ def run_attention_only(args):
                       "peak_kind": kind, "status": backend.kernel.last_status(device)}))
 
 
+def run_prefill_only(args):
+    """Profiling aid (`--only prefill`): packed causal prefill of `--requests` prompts of `--tokens`
+    tokens each (16 x 128 MHA, bf16, 16-token pages, pages in random order) through
+    `AttentionBackend.prefill`, timed per call with CUDA events.  Tensor-bound: reports TFLOP/s
+    (4 * head_dim flops per visible (query, key) pair and head) against the measured bf16 peak."""
+    import vllm_rlt_b200 as rlt
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    g = torch.Generator(device=device).manual_seed(17)
+    n, seqs = args.tokens, args.requests
+    pages = -(-n // BLOCK)
+    total = pages * seqs
+    shape = (total, 1, BLOCK, args.kv_heads, HEAD_DIM)
+    both = (torch.randn((2,) + shape, device=device, generator=g) * 0.5).to(torch.bfloat16)
+    key, value = both[0][:, 0], both[1][:, 0]
+    tables = torch.randperm(total, device=device, generator=g).int().view(seqs, pages)
+    lengths = torch.full((seqs,), n, dtype=torch.int32, device=device)
+    cu = (torch.arange(seqs + 1, device=device) * n).int()
+    q = (torch.randn(seqs * n, HEADS, HEAD_DIM, device=device, generator=g) * 0.5).to(torch.bfloat16)
+    kernel = rlt.B200PagedAttention()
+    max_new = n if not args.eager else 0          # --eager: the same rows through the grouped verify kernel
+    for _ in range(args.warmup):
+        kernel.prefill(q, key, value, tables, lengths, cu, max_new)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        kernel.prefill(q, key, value, tables, lengths, cu, max_new)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    flops = 4.0 * HEAD_DIM * HEADS * seqs * (n * (n + 1) / 2)
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    print(json.dumps({"only": "prefill", "kernel": "grouped verify kernel" if args.eager else "prefill kernel",
+                      "sequences": seqs, "tokens": n, "kv_heads": args.kv_heads, "ms_per_call": ms,
+                      "algorithmic_flops": flops, "tflops": flops / ms / 1e9, "peak_tflops": peak,
+                      "peak_kind": "measured" if peaks else "fallback", "frac": flops / ms / 1e9 / peak}))
+
+
 def run_small_only(args):
     """Profiling aid: the acceptance kernels (`--only accept`) or SiLU-and-Mul (`--only silu`) at the
     step's shapes, a few hundred MB on the device, timed per call with CUDA events."""
@@ -524,6 +564,8 @@ def run_decode_workload(args):
         torch.cuda.synchronize()
         clock["start"] = time.perf_counter()
 
+    torch.cuda.synchronize()
+    clock["begin"] = time.perf_counter()
     tokens = decoder.generate(prompts, args.output_tokens, num_speculative_tokens=4, draft_loops=2, target_loops=4,
                               temperature=args.temperature, seed=1, after_prefill=start_clock)
     torch.cuda.synchronize()
@@ -533,6 +575,7 @@ def run_decode_workload(args):
         "workload": "decode: Ouro-1.4B-shaped random-init bf16, self-spec k=4 from depth 2, "
                     f"{args.requests} requests, prompts U[128,1024], {args.output_tokens} output tokens, T={args.temperature}, "
                     + ("eager launches" if args.eager else "recurrent loops replayed from CUDA graphs"),
+        "prefill_and_capture_seconds": clock["start"] - clock["begin"], "prompt_tokens": sum(lengths),
         "decode_seconds": seconds, "committed_tokens": stats.committed_tokens, "accepted_tokens": stats.accepted_tokens,
         "drafted_tokens": stats.drafted_tokens, "request_rounds": stats.rounds,
         "committed_tokens_per_s": stats.committed_tokens / seconds,
@@ -630,7 +673,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--only", default=None, choices=["attention", "accept", "silu"],
+    parser.add_argument("--only", default=None, choices=["attention", "accept", "silu", "prefill"],
                         help="profiling aid: run only this kernel family (not a bench line)")
     parser.add_argument("--workload", default="step", choices=["step", "decode"],
                         help="step: the verify-step microbench (the bench line); decode: whole-model decoding (secondary)")
@@ -657,6 +700,9 @@ def main():
         return
     if args.only == "attention":
         run_attention_only(args)
+        return
+    if args.only == "prefill":
+        run_prefill_only(args)
         return
     if args.only in ("accept", "silu"):
         run_small_only(args)

@@ -195,6 +195,32 @@ RLT_API int rlt_verify_attention_noalloc(const void* q, void* out, const void* k
                                  int table_width, const int32_t* context_lengths,
                                  const int32_t* cu_seqlens_q, int rows, rlt_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Packed causal prefill: the same result as rlt_verify_attention with cu_seqlens_q (query i of
+ * the n_s new tokens of sequence s sees keys 0 .. context_lengths[s] - n_s + i), computed for
+ * prompt-sized n_s: one CTA per 64 query tokens and query head walks the sequence's pages
+ * once (head_dim 128, 16-token pages, fp16 / bf16, both caches addressable through one tensor
+ * map).  Other shapes, and cache placements the map cannot express, are scored by the kernels
+ * behind rlt_verify_attention.  The results agree with rlt_verify_attention to the tolerance
+ * of the dtype, not bit for bit (no split-KV merge here), so verification rows that must match
+ * decode rows exactly stay on rlt_verify_attention.
+ * Replaces: paged_prefill_attention (vllm_rlt/kernels/triton_attention.py:205-366) behind
+ *   AttentionBackend.prefill (vllm_rlt/attention/backend.py:30-55).
+ * block_tables: int32 [sequences, table_width]; context_lengths: int32 [sequences] (keys in the
+ * cache including the new tokens); cu_seqlens_q: int32 [sequences + 1].  workspace: device
+ * scratch of rlt_prefill_attention_workspace_bytes(...) bytes, 256-byte aligned; its second
+ * 32-bit word is nonzero after a run in which a bounded device-side wait gave up.
+ * ---------------------------------------------------------------------- */
+RLT_API size_t rlt_prefill_attention_workspace_bytes(int rows, int sequences, int q_heads, int kv_heads,
+                                             int head_dim, int block_size, int table_width);
+
+RLT_API int rlt_prefill_attention(const void* q, void* out, const void* key_cache, const void* value_cache,
+                          int64_t block_stride, int64_t token_stride, int64_t num_blocks, int block_size,
+                          int q_heads, int kv_heads, int head_dim, int dtype, const int32_t* block_tables,
+                          int sequences, int table_width, const int32_t* context_lengths,
+                          const int32_t* cu_seqlens_q, int rows, void* workspace, size_t workspace_bytes,
+                          rlt_stream_t stream);
+
 /* Diagnostics for the tiled kernel (head_dim 128, 16-token pages, fp16/bf16): waits for
  * `stream` and copies four words of the workspace header to the host —
  * status4[0] = work items planned by the last call (groups x context chunks x kv heads; shows

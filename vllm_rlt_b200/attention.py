@@ -210,9 +210,43 @@ class B200PagedAttention:
         return self._run(q, key_cache, value_cache, block_tables, context_lengths, None)
 
     def prefill(self, q, key_cache, value_cache, block_tables, context_lengths, cu_seqlens_q, max_seqlen_q):
-        """Packed rows: one block-table row per sequence, bottom-right causal lengths."""
-        del max_seqlen_q  # the kernels size nothing by it
-        return self._run(q, key_cache, value_cache, block_tables, context_lengths, cu_seqlens_q)
+        """Packed rows: one block-table row per sequence, bottom-right causal lengths.
+
+        Sequences of at most 16 new tokens (verification rows in packed form) go through the
+        grouped verify kernel and are bit-identical to the same rows scored one at a time
+        (`packed_matches_decode`); longer ones (prompts) through the prefill kernel, 64 query
+        tokens per CTA, which agrees with it to the dtype's tolerance.
+        """
+        if int(max_seqlen_q) <= 16:
+            return self._run(q, key_cache, value_cache, block_tables, context_lengths, cu_seqlens_q)
+        device = _capi.require_cuda(q, key_cache, value_cache, block_tables, context_lengths, cu_seqlens_q)
+        self._check_cache(q, key_cache, value_cache)
+        if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or not block_tables.is_contiguous():
+            raise ValueError("block tables must be contiguous int32 [sequences, pages]")
+        sequences, width = block_tables.shape
+        if context_lengths.dtype != torch.int32 or context_lengths.shape != (sequences,):
+            raise ValueError("context_lengths must be int32 [sequences]")
+        if cu_seqlens_q.dtype != torch.int32 or cu_seqlens_q.shape != (sequences + 1,):
+            raise ValueError("cu_seqlens_q must be int32 [sequences + 1]")
+        q = q.contiguous()
+        out = torch.empty_like(q)
+        rows = q.shape[0]
+        if rows == 0 or sequences == 0:
+            return out
+        lib = _capi.load()
+        blocks, block_size, kv_heads, head_dim = key_cache.shape
+        with torch.cuda.device(device):
+            stream = _capi.stream_of(q)
+            nbytes = lib.rlt_prefill_attention_workspace_bytes(rows, sequences, q.shape[1], kv_heads, head_dim,
+                                                               block_size, max(width, 1))
+            workspace = self._workspace(device, stream.value or 0, nbytes)
+            status = lib.rlt_prefill_attention(
+                _capi.ptr(q), _capi.ptr(out), _capi.ptr(key_cache), _capi.ptr(value_cache), key_cache.stride(0),
+                key_cache.stride(1), blocks, block_size, q.shape[1], kv_heads, head_dim, _capi.DTYPE_CODES[q.dtype],
+                _capi.ptr(block_tables), sequences, width, _capi.ptr(context_lengths.contiguous()),
+                _capi.ptr(cu_seqlens_q.contiguous()), rows, _capi.ptr(workspace), workspace.numel(), stream)
+        _capi.check(status, "prefill_attention")
+        return out
 
 
 def create_backend(device, dtype: torch.dtype, head_dim: int, block_size: int) -> AttentionBackend:

@@ -64,6 +64,10 @@ int run_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspac
 // launch_attention_sm100 on the library's built-in 32 MiB scratch block (no allocation anywhere).
 size_t attention_sm100_builtin_scratch_bytes();
 int launch_attention_sm100_builtin(const AttentionArgs& a, cudaStream_t stream);
+// attention_prefill_sm100.cu: packed causal prefill, 64 query tokens per CTA, the same shapes.
+bool prefill_sm100_supported(const AttentionArgs& a);
+size_t prefill_sm100_workspace_bytes(int rows, int seqs);
+int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 // Synchronous read-back of the workspace header of the last tiled call:
 // {work items planned, rows of length zero, error bits, claim counter (0 after a clean run)}.
 int attention_sm100_read_status(const void* workspace, cudaStream_t stream, unsigned* out4);

@@ -136,3 +136,37 @@ extern "C" RLT_API int rlt_verify_attention_noalloc(const void* q, void* out, co
   if (attention_sm100_supported(a)) return launch_attention_sm100_builtin(a, s);
   return launch_attention_generic(a, s);  // shapes outside the tiled kernel use no scratch at all
 }
+
+extern "C" RLT_API size_t rlt_prefill_attention_workspace_bytes(int rows, int sequences, int q_heads, int kv_heads,
+                                                                int head_dim, int block_size, int table_width) {
+  if (rows <= 0 || sequences <= 0) return 256;
+  const size_t tiled = rlt::prefill_sm100_workspace_bytes(rows, sequences);
+  const size_t grouped = rlt_verify_attention_workspace_bytes(rows, q_heads, kv_heads, head_dim, block_size, table_width);
+  return tiled > grouped ? tiled : grouped;
+}
+
+extern "C" RLT_API int rlt_prefill_attention(const void* q, void* out, const void* key_cache, const void* value_cache,
+                                             int64_t block_stride, int64_t token_stride, int64_t num_blocks,
+                                             int block_size, int q_heads, int kv_heads, int head_dim, int dtype,
+                                             const int32_t* block_tables, int sequences, int table_width,
+                                             const int32_t* context_lengths, const int32_t* cu_seqlens_q, int rows,
+                                             void* workspace, size_t workspace_bytes, rlt_stream_t stream) {
+  using namespace rlt;
+  AttentionArgs a;
+  a.q = q; a.out = out; a.key_cache = key_cache; a.value_cache = value_cache;
+  a.block_stride = block_stride; a.token_stride = token_stride; a.num_blocks = num_blocks;
+  a.block_size = block_size; a.q_heads = q_heads; a.kv_heads = kv_heads; a.head_dim = head_dim;
+  a.dtype = dtype; a.block_tables = block_tables; a.table_rows = sequences; a.table_width = table_width;
+  a.context_lengths = context_lengths; a.cu_seqlens_q = cu_seqlens_q; a.rows = rows;
+  RLT_REQUIRE(cu_seqlens_q != nullptr || rows == 0, "prefill_attention: cu_seqlens_q is required");
+  int status = check_args(a);
+  if (status != RLT_OK || rows == 0) return status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (prefill_sm100_supported(a)) {
+    status = launch_prefill_sm100(a, workspace, workspace_bytes, s);
+    if (status != RLT_ERR_UNSUPPORTED) return status;
+  }
+  // shapes or cache placements outside the tiled prefill kernel: the grouped verify kernel, or the generic one
+  if (attention_sm100_supported(a)) return launch_attention_sm100(a, workspace, workspace_bytes, s);
+  return launch_attention_generic(a, s);
+}

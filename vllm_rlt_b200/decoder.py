@@ -156,14 +156,21 @@ class SelfSpeculativeDecoder:
         return self.model.recurrent(hidden, positions, kv.key, kv.value, blocks, offsets, tables, lengths)
 
     def _prefill(self, kv: PagedKV, prompts):
-        """All prompt positions through every loop; returns the first generated token of each request."""
+        """All prompt positions through every loop, packed (one table row per prompt, causal inside
+        it); returns the first generated token of each request."""
         device = self.model.device
+        lengths = [len(p) for p in prompts]
         requests = torch.tensor([i for i, p in enumerate(prompts) for _ in p], device=device)
         positions = torch.tensor([j for p in prompts for j in range(len(p))], device=device)
         tokens = torch.tensor([t for p in prompts for t in p], device=device)
+        cu = torch.tensor([0] + torch.tensor(lengths).cumsum(0).tolist(), dtype=torch.int32, device=device)
+        context = torch.tensor(lengths, dtype=torch.int32, device=device)
         hidden = self.model.prelude(tokens)
         for depth in range(self.model.config.total_ut_steps):
-            hidden = self._loop(kv, hidden, requests, positions, depth)
+            tables = kv.tables[:, depth]
+            blocks = tables[requests].gather(1, (positions // self.block)[:, None]).squeeze(1).long()
+            hidden = self.model.recurrent(hidden, positions, kv.key, kv.value, blocks, positions % self.block,
+                                          tables.contiguous(), context, packed=(cu, max(lengths)))
         last = torch.tensor([sum(len(p) for p in prompts[:i + 1]) - 1 for i in range(len(prompts))], device=device)
         return argmax_rows(self.model.coda(hidden[last]).float().contiguous()).tolist()
 

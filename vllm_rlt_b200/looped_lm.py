@@ -119,16 +119,20 @@ class LoopedLM:
         return angles.cos().to(self.dtype).unsqueeze(1), angles.sin().to(self.dtype).unsqueeze(1)
 
     def recurrent(self, hidden, positions, key_pool, value_pool, write_blocks, write_offsets, block_tables,
-                  context_lengths):
+                  context_lengths, packed=None):
         """One recurrent loop: every layer writes its K/V rows, attends, and runs the MLP.
 
         key_pool / value_pool: `[blocks, layers, block_size, kv_heads, head_dim]`; the addressing
         tensors select the depth plane (they are the same for all layers of the loop, so the
         attention work list is planned once).  Returns the normalised hidden state, which is the
-        next loop's input and the coda's input (models/ouro.py:283-291)."""
+        next loop's input and the coda's input (models/ouro.py:283-291).
+
+        `packed = (cu_seqlens_q, max_seqlen_q)` switches to the packed form for prompts: one
+        block-table row and one context length per sequence, rows of a sequence consecutive
+        (`AttentionBackend.prefill`)."""
         if self.fused:
             return self._recurrent_fused(hidden, positions, key_pool, value_pool, write_blocks, write_offsets,
-                                         block_tables, context_lengths)
+                                         block_tables, context_lengths, packed=packed)
         c, w = self.config, self.w
         cos, sin = self.rope(positions)
         rows = hidden.shape[0]
@@ -143,7 +147,7 @@ class LoopedLM:
                 k = k * cos + rotate_half(k) * sin
                 kc, vc = key_pool[:, layer], value_pool[:, layer]
                 kv_write(kc, vc, k, v, write_blocks, write_offsets)
-                attended = self.attention(q.contiguous(), kc, vc, block_tables, context_lengths)
+                attended = self._attend(q.contiguous(), kc, vc, block_tables, context_lengths, packed)
                 attended = F.linear(attended.reshape(rows, -1), w[p + "self_attn.o_proj.weight"])
                 hidden = hidden + rms_norm(attended, w[p + "input_layernorm_2.weight"], c.rms_norm_eps)
                 x = rms_norm(hidden, w[p + "post_attention_layernorm.weight"], c.rms_norm_eps)
@@ -153,8 +157,13 @@ class LoopedLM:
                 hidden = hidden + rms_norm(mlp, w[p + "post_attention_layernorm_2.weight"], c.rms_norm_eps)
         return rms_norm(hidden, w["model.norm.weight"], c.rms_norm_eps)
 
+    def _attend(self, q, key_cache, value_cache, block_tables, context_lengths, packed):
+        if packed is None:
+            return self.attention(q, key_cache, value_cache, block_tables, context_lengths)
+        return self.attention.prefill(q, key_cache, value_cache, block_tables, context_lengths, *packed)
+
     def _recurrent_fused(self, hidden, positions, key_pool, value_pool, write_blocks, write_offsets, block_tables,
-                         context_lengths, active_rows=None):
+                         context_lengths, active_rows=None, packed=None):
         """The same loop with ten launches per layer: QKV GEMM, rope_kv_write, attention, O GEMM,
         sandwich_norm (residual add + the MLP's input norm), gate and up GEMMs, silu_and_mul, down
         GEMM, sandwich_norm (residual add + the next layer's input norm, or the final norm).
@@ -174,7 +183,7 @@ class LoopedLM:
                 v = qkv[:, q_width + kv_width:].view(rows, -1, c.head_dim)
                 kc, vc = key_pool[:, layer], value_pool[:, layer]
                 q = rope_kv_write(q, k, v, cos, sin, kc, vc, write_blocks, write_offsets, active_rows=active_rows)
-                attended = self.attention(q, kc, vc, block_tables, context_lengths)
+                attended = self._attend(q, kc, vc, block_tables, context_lengths, packed)
                 attended = F.linear(attended.view(rows, -1), w[p + "self_attn.o_proj.weight"])
                 stream, x = sandwich_norm(attended, w[p + "input_layernorm_2.weight"], c.rms_norm_eps,
                                           hidden if stream is None else stream,
