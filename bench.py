@@ -536,6 +536,15 @@ def run_small_only(args):
                                          x["temperature"], x["u_accept"], x["u_final"])
         accepted = result[work.accept_rows:work.accept_rows + work.requests]
         out["rollback_ms"] = timed(lambda: rlt.rollback(x["starts"], accepted + 1, x["request_tables"], BLOCK))
+        # the same draws and acceptance with top-k = 50 / top-p = 0.9 on every request (radix-select cut)
+        n = work.requests
+        top_k, top_p = torch.full((n,), 50, dtype=torch.int32, device=device), torch.full((n,), 0.9, device=device)
+        row_k, row_p = top_k.repeat_interleave(TOKENS), top_p.repeat_interleave(TOKENS)
+        out["sample_rows_top_k_top_p_ms"] = timed(lambda: rlt.sample_rows(x["draft"], per_row_t, x["u_draft"], row_k, row_p))
+        out["accept_rejection_top_k_top_p_ms"] = timed(lambda: rlt.accept_rejection(
+            x["target"], x["draft"], x["cu_rows"], tokens, x["starts"], x["temperature"], x["u_accept"], x["u_final"],
+            top_k=top_k, top_p=top_p))
+        out["probabilities_top_p_ms"] = timed(lambda: rlt.probabilities(x["target"], per_row_t, None, row_p))
         out.update(rows=work.accept_rows, vocab=VOCAB, greedy_bytes=logits_bytes, rejection_bytes=2 * logits_bytes,
                    greedy_gbs=logits_bytes / out["accept_greedy_ms"] / 1e6,
                    rejection_gbs=2 * logits_bytes / out["accept_rejection_ms"] / 1e6)

@@ -70,6 +70,66 @@ sandwich_norm_kernel(const T* __restrict__ x, const T* __restrict__ weight, cons
   }
 }
 
+// The same arithmetic with the row held in registers: thread i owns kPer 16-byte vectors of the
+// row (hidden = 256 * kPer * 16 / sizeof(T)), every global access is one 16-byte vector, and the
+// weight / residual loads are issued before the first reduction so that the kernel is two block
+// reductions long.
+template <typename T, int kPer>
+__global__ void __launch_bounds__(kNormThreads)
+sandwich_norm_vec_kernel(const T* __restrict__ x, const T* __restrict__ weight, const T* residual, T* sum_out,
+                         const T* __restrict__ weight2, T* __restrict__ norm_out, int hidden, float eps) {
+  constexpr int kVec = 16 / sizeof(T);
+  struct alignas(16) Vec { T e[kVec]; };
+  __shared__ double scratch[32];
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * hidden;
+  Vec xv[kPer], wv[kPer], rv[kPer], w2v[kPer];
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) {
+    const int i = (k * kNormThreads + threadIdx.x) * kVec;
+    xv[k] = *reinterpret_cast<const Vec*>(x + base + i);
+    wv[k] = *reinterpret_cast<const Vec*>(weight + i);
+    if (residual != nullptr) rv[k] = *reinterpret_cast<const Vec*>(residual + base + i);
+    if (weight2 != nullptr) w2v[k] = *reinterpret_cast<const Vec*>(weight2 + i);
+  }
+  double ss = 0.0;
+#pragma unroll
+  for (int k = 0; k < kPer; ++k)
+#pragma unroll
+    for (int e = 0; e < kVec; ++e) {
+      const float v = Elem<T>::to_float(xv[k].e[e]);
+      ss += static_cast<double>(__fmul_rn(v, v));
+    }
+  float r = inverse_rms(block_sum_double(ss, scratch), hidden, eps);
+  float sv[kPer][kVec];
+  ss = 0.0;
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) {
+    Vec out;
+#pragma unroll
+    for (int e = 0; e < kVec; ++e) {
+      const float normed = Elem<T>::to_float(Elem<T>::from_float(__fmul_rn(Elem<T>::to_float(xv[k].e[e]), r)));
+      float s = Elem<T>::to_float(Elem<T>::from_float(__fmul_rn(Elem<T>::to_float(wv[k].e[e]), normed)));
+      if (residual != nullptr) s = Elem<T>::to_float(Elem<T>::from_float(__fadd_rn(Elem<T>::to_float(rv[k].e[e]), s)));
+      out.e[e] = Elem<T>::from_float(s);
+      sv[k][e] = s;
+      ss += static_cast<double>(__fmul_rn(s, s));
+    }
+    if (sum_out != nullptr) *reinterpret_cast<Vec*>(sum_out + base + (k * kNormThreads + threadIdx.x) * kVec) = out;
+  }
+  if (weight2 == nullptr) return;
+  r = inverse_rms(block_sum_double(ss, scratch), hidden, eps);
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) {
+    Vec out;
+#pragma unroll
+    for (int e = 0; e < kVec; ++e) {
+      const float normed = Elem<T>::to_float(Elem<T>::from_float(__fmul_rn(sv[k][e], r)));
+      out.e[e] = Elem<T>::from_float(__fmul_rn(Elem<T>::to_float(w2v[k].e[e]), normed));
+    }
+    *reinterpret_cast<Vec*>(norm_out + base + (k * kNormThreads + threadIdx.x) * kVec) = out;
+  }
+}
+
 // out = T(T(a * cos) + T(rot * sin)): the two products and the sum round separately, as
 // `x * cos + rotate_half(x) * sin` does on tensors of type T.
 template <typename T>
@@ -154,6 +214,24 @@ extern "C" RLT_API int rlt_sandwich_norm(const void* x, const void* weight, cons
     return RLT_ERR_UNSUPPORTED;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // rows that are a whole number of 16-byte vectors per thread stay in registers
+  const int per_thread = hidden * static_cast<int>(dtype_size(dtype)) / (kNormThreads * 16);
+  const bool vectors = hidden * static_cast<int>(dtype_size(dtype)) == per_thread * kNormThreads * 16 &&
+                       (per_thread == 1 || per_thread == 2 || per_thread == 4) && aligned16(x) && aligned16(weight) &&
+                       aligned16(residual) && aligned16(sum_out) && aligned16(weight2) && aligned16(norm_out);
+  if (vectors) {
+#define RLT_NORM_LAUNCH(T, P)                                                                                   \
+  sandwich_norm_vec_kernel<T, P><<<rows, kNormThreads, 0, s>>>(                                                 \
+      static_cast<const T*>(x), static_cast<const T*>(weight), static_cast<const T*>(residual),                 \
+      static_cast<T*>(sum_out), static_cast<const T*>(weight2), static_cast<T*>(norm_out), hidden, eps)
+    RLT_DISPATCH_DTYPE(dtype, T, {
+      if (per_thread == 1) RLT_NORM_LAUNCH(T, 1);
+      else if (per_thread == 2) RLT_NORM_LAUNCH(T, 2);
+      else RLT_NORM_LAUNCH(T, 4);
+    });
+#undef RLT_NORM_LAUNCH
+    return launch_status("sandwich_norm_vec_kernel");
+  }
   RLT_DISPATCH_DTYPE(dtype, T, (sandwich_norm_kernel<T><<<rows, kNormThreads, smem, s>>>(
                                    static_cast<const T*>(x), static_cast<const T*>(weight),
                                    static_cast<const T*>(residual), static_cast<T*>(sum_out),
