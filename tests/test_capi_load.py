@@ -81,3 +81,40 @@ def test_silu_argument_checks_match_the_reference_errors():
     for dtype in (torch.int32, torch.float64):
         with pytest.raises(TypeError, match="supports float32"):
             rlt.silu_and_mul(torch.ones(7, dtype=dtype), torch.ones(7, dtype=dtype))
+
+
+def test_header_is_plain_c_and_a_c_program_links_against_the_library(library, tmp_path):
+    """The boundary is a C ABI: the header compiles as C99 without CUDA or C++ headers, and a C
+    translation unit that takes the address of every entry point links against the library
+    (calls that need no GPU run: version string, workspace sizes, argument errors)."""
+    import subprocess
+
+    names = declared_symbols()
+    source = tmp_path / "abi.c"
+    table = ",\n  ".join(f'{{"{n}", (void (*)(void)){n}}}' for n in names)
+    source.write_text(f'''
+#include <stdio.h>
+#include <string.h>
+#include "rlt_verify.h"
+struct entry {{ const char* name; void (*address)(void); }};
+static const struct entry entries[] = {{
+  {table}
+}};
+int main(void) {{
+  size_t n = sizeof(entries) / sizeof(entries[0]);
+  for (size_t i = 0; i < n; ++i) if (entries[i].address == 0) return 2;
+  if (strstr(rlt_version(), "sm_100a") == 0) return 3;
+  if (rlt_verify_attention_workspace_bytes(16, 16, 16, 128, 16, 64) == 0) return 4;
+  /* invalid arguments come back as a status and a message, never as a crash or an exception */
+  if (rlt_silu_and_mul(0, 0, 0, 8, 99, 0) != RLT_ERR_INVALID) return 5;
+  if (strlen(rlt_last_error()) == 0) return 6;
+  printf("%zu entry points\\n", n);
+  return 0;
+}}
+''')
+    binary = tmp_path / "abi"
+    lib_dir = ROOT / "vllm_rlt_b200"
+    subprocess.run(["/usr/bin/gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", str(ROOT / "include"), str(source),
+                    "-o", str(binary), f"-L{lib_dir}", "-lrlt_verify", f"-Wl,-rpath,{lib_dir}"], check=True)
+    done = subprocess.run([str(binary)], check=True, capture_output=True, text=True)
+    assert done.stdout.strip() == f"{len(names)} entry points"

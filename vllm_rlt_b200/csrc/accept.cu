@@ -75,7 +75,8 @@ __device__ __forceinline__ unsigned long long block_sum(unsigned long long v, un
 // Packed (value, lowest index) maximum of one row by the whole CTA.  16-byte loads when the row
 // allows them, four in flight per thread (a row is only a few hundred KB: latency, not issue
 // rate, decides how fast one CTA can stream it).
-template <typename T, int kThreads>
+// kPlain: `row` may point to shared memory (a staged row), so no global-only load forms.
+template <typename T, int kThreads, bool kPlain = false>
 __device__ __forceinline__ unsigned long long block_max_key(const T* __restrict__ row, int vocab,
                                                            unsigned long long* scratch) {
   constexpr int kVec = 16 / sizeof(T);
@@ -89,7 +90,7 @@ __device__ __forceinline__ unsigned long long block_max_key(const T* __restrict_
 #pragma unroll
       for (int k = 0; k < kDepth; ++k) {
         const int i = base + k * kThreads;
-        if (i < nvec) raw[k] = __ldcs(rv + i);
+        if (i < nvec) raw[k] = kPlain ? rv[i] : __ldcs(rv + i);
       }
 #pragma unroll
       for (int k = 0; k < kDepth; ++k) {
@@ -171,10 +172,10 @@ __device__ __forceinline__ float scaled_logit(const T* row, int v, float tempera
 // max of row / temperature.  Division by a positive temperature is monotonic, so
 // max_v (x_v / T) == (max_v x_v) / T exactly: the pass is a plain maximum over the raw logits
 // (NaN counts as the maximum and is then reported), one division at the end.
-template <typename T, int kThreads>
+template <typename T, int kThreads, bool kPlain = false>
 __device__ __forceinline__ RowNorm block_row_max(const T* __restrict__ row, int vocab, float temperature,
                                                  unsigned long long* scratch) {
-  const unsigned long long best = block_max_key<T, kThreads>(row, vocab, scratch);
+  const unsigned long long best = block_max_key<T, kThreads, kPlain>(row, vocab, scratch);
   RowNorm n;
   uint32_t bits = static_cast<uint32_t>(best >> 32);
   bits = (bits & 0x80000000u) ? (bits & 0x7fffffffu) : ~bits;
@@ -187,7 +188,7 @@ __device__ __forceinline__ RowNorm block_row_max(const T* __restrict__ row, int 
 }
 
 // Normaliser of softmax(row / temperature) over the whole row.
-template <typename T, int kThreads>
+template <typename T, int kThreads, bool kPlain = false>
 __device__ __forceinline__ float block_full_sum(const T* __restrict__ row, int vocab, float temperature, float m,
                                                 unsigned long long* scratch) {
   unsigned long long zfix = 0ull;
@@ -200,7 +201,7 @@ __device__ __forceinline__ float block_full_sum(const T* __restrict__ row, int v
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         const int i = base + k * kThreads;
-        if (i < nvec) raw[k] = __ldg(rv + i);
+        if (i < nvec) raw[k] = kPlain ? rv[i] : __ldg(rv + i);
       }
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
@@ -378,11 +379,11 @@ __device__ __forceinline__ Cut block_select(const T* __restrict__ row, int vocab
 // max, support and normaliser of the distribution Sampler.probabilities builds for one row
 // (vllm_rlt/worker/sampler.py:37-55): softmax(row / T) restricted to top-k, then to top-p.
 // top_k <= 0 or >= vocab and top_p >= 1 switch the filters off.
-template <typename T, int kThreads>
+template <typename T, int kThreads, bool kPlain = false>
 __device__ __forceinline__ RowNorm block_normalise(const T* __restrict__ row, int vocab, float temperature,
                                                    int top_k, float top_p, unsigned long long* scratch,
                                                    SelectScratch& h) {
-  RowNorm n = block_row_max<T, kThreads>(row, vocab, temperature, scratch);
+  RowNorm n = block_row_max<T, kThreads, kPlain>(row, vocab, temperature, scratch);
   if (!n.ok) return n;
   const bool use_k = top_k > 0 && top_k < vocab, use_p = top_p < 1.0f;
   if (use_k) {
@@ -390,7 +391,7 @@ __device__ __forceinline__ RowNorm block_normalise(const T* __restrict__ row, in
                                              static_cast<unsigned long long>(top_k - 1), h);
     n.z = block_cut_sum<T, kThreads>(row, vocab, temperature, n.m, n.cut, scratch);
   } else {
-    n.z = block_full_sum<T, kThreads>(row, vocab, temperature, n.m, scratch);
+    n.z = block_full_sum<T, kThreads, kPlain>(row, vocab, temperature, n.m, scratch);
   }
   if (use_p) {
     const Cut outer = n.cut;
@@ -400,6 +401,16 @@ __device__ __forceinline__ RowNorm block_normalise(const T* __restrict__ row, in
       n.z = block_cut_sum<T, kThreads>(row, vocab, temperature, n.m, n.cut, scratch);
   }
   return n;
+}
+
+// A row copied to shared memory as fp32 (exact for all three storage types).  The filters make a
+// dozen passes over a row; from shared memory a pass costs a few microseconds instead of one L2
+// round trip per element and thread.  Used when the caller passes filters and the row fits.
+template <typename T, int kThreads>
+__device__ __forceinline__ const float* stage_row(const T* __restrict__ row, int vocab, float* staged) {
+  for (int v = threadIdx.x; v < vocab; v += kThreads) staged[v] = Elem<T>::to_float(row[v]);
+  __syncthreads();
+  return staged;
 }
 
 // exp(t_v - max) for a token of the support, 0 outside it.
@@ -471,7 +482,7 @@ __device__ __forceinline__ int block_draw(const T* __restrict__ prow, const RowN
   return *token_slot;
 }
 
-template <typename T>
+template <typename T, bool kStaged>
 __global__ void __launch_bounds__(kSampleThreads)
 sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
                    const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
@@ -487,6 +498,17 @@ sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
   int token = -1;
   if (temp == 0.0f) {
     token = block_argmax<T, kSampleThreads>(row, vocab, scratch);
+  } else if constexpr (kStaged) {
+    extern __shared__ __align__(16) float staged[];
+    const float* frow = stage_row<T, kSampleThreads>(row, vocab, staged);
+    const RowNorm n = block_normalise<float, kSampleThreads, true>(frow, vocab, temp, top_k ? top_k[r] : -1,
+                                                                   top_p ? top_p[r] : 1.0f, scratch, select);
+    if (!n.ok) {
+      st = RLT_ROW_BAD_LOGITS;
+    } else {
+      token = block_draw<float, kSampleThreads>(frow, n, frow, n, false, vocab, temp, uniforms[r], scratch, &token_slot);
+      if (token < 0) st = RLT_ROW_INVALID_RESIDUAL;
+    }
   } else {
     const RowNorm n = block_normalise<T, kSampleThreads>(row, vocab, temp, top_k ? top_k[r] : -1,
                                                          top_p ? top_p[r] : 1.0f, scratch, select);
@@ -501,7 +523,7 @@ sample_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
 }
 
 // Sampler.probabilities for every row: fp32 [rows, vocab], zero outside the support.
-template <typename T>
+template <typename T, bool kStaged>
 __global__ void __launch_bounds__(kSampleThreads)
 probabilities_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab,
                      const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
@@ -514,10 +536,19 @@ probabilities_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab
   const float temp = temperature[r];
   RowNorm n;
   n.ok = 0;
-  if (temp > 0.0f)
-    n = block_normalise<T, kSampleThreads>(row, vocab, temp, top_k ? top_k[r] : -1, top_p ? top_p[r] : 1.0f,
-                                           scratch, select);
-  for (int v = threadIdx.x; v < vocab; v += kSampleThreads) out[v] = n.ok ? prob_at(row, v, temp, n) : 0.0f;
+  if constexpr (kStaged) {
+    extern __shared__ __align__(16) float staged[];
+    const float* frow = stage_row<T, kSampleThreads>(row, vocab, staged);
+    if (temp > 0.0f)
+      n = block_normalise<float, kSampleThreads, true>(frow, vocab, temp, top_k ? top_k[r] : -1,
+                                                       top_p ? top_p[r] : 1.0f, scratch, select);
+    for (int v = threadIdx.x; v < vocab; v += kSampleThreads) out[v] = n.ok ? prob_at(frow, v, temp, n) : 0.0f;
+  } else {
+    if (temp > 0.0f)
+      n = block_normalise<T, kSampleThreads>(row, vocab, temp, top_k ? top_k[r] : -1, top_p ? top_p[r] : 1.0f,
+                                             scratch, select);
+    for (int v = threadIdx.x; v < vocab; v += kSampleThreads) out[v] = n.ok ? prob_at(row, v, temp, n) : 0.0f;
+  }
   if (threadIdx.x == 0) status[r] = n.ok ? RLT_ROW_OK : RLT_ROW_BAD_LOGITS;
 }
 
@@ -547,8 +578,8 @@ __device__ __forceinline__ int request_of_row(const int32_t* cu_rows, int n, int
   return lo;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kStatsThreads)
+template <typename T, int kThreads, bool kStaged>
+__global__ void __launch_bounds__(kThreads)
 row_stats_kernel(const T* __restrict__ target_logits, const T* __restrict__ draft_logits, int64_t row_stride,
                  int vocab, const int32_t* __restrict__ cu_rows, int n, const int64_t* __restrict__ tokens,
                  int tokens_width, const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
@@ -562,12 +593,19 @@ row_stats_kernel(const T* __restrict__ target_logits, const T* __restrict__ draf
   RowStats out = {0.0f, 0.0f, 0.0f, 0, whole_row()};
   if (temp == 0.0f) {
     if (side == 1) return;
-    out.info = block_argmax<T, kStatsThreads>(target_logits + static_cast<int64_t>(row) * row_stride, vocab, scratch) << 1;
+    out.info = block_argmax<T, kThreads>(target_logits + static_cast<int64_t>(row) * row_stride, vocab, scratch) << 1;
   } else {
     if (side == 1 && j == count - 1) return;  // the bonus row has no draft distribution
     const T* logits = (side == 0 ? target_logits : draft_logits) + static_cast<int64_t>(row) * row_stride;
-    const RowNorm norm = block_normalise<T, kStatsThreads>(logits, vocab, temp, top_k ? top_k[i] : -1,
-                                                           top_p ? top_p[i] : 1.0f, scratch, select);
+    RowNorm norm;
+    if constexpr (kStaged) {
+      extern __shared__ __align__(16) float staged[];
+      norm = block_normalise<float, kThreads, true>(stage_row<T, kThreads>(logits, vocab, staged), vocab, temp,
+                                                    top_k ? top_k[i] : -1, top_p ? top_p[i] : 1.0f, scratch, select);
+    } else {
+      norm = block_normalise<T, kThreads>(logits, vocab, temp, top_k ? top_k[i] : -1, top_p ? top_p[i] : 1.0f,
+                                          scratch, select);
+    }
     const int64_t d = j < count - 1 ? tokens[static_cast<int64_t>(i) * tokens_width + j + 1] : -1;
     out.m = norm.m;
     out.z = norm.z;
@@ -650,6 +688,11 @@ decide_kernel(const T* __restrict__ target_logits, const T* __restrict__ draft_l
   }
 }
 
+// Filters were passed and an fp32 copy of a row fits beside the kernels' static shared memory.
+bool stage_rows(const int32_t* top_k, const float* top_p, int vocab) {
+  return (top_k != nullptr || top_p != nullptr) && static_cast<size_t>(vocab) * sizeof(float) <= 200u * 1024u;
+}
+
 int check_logits(const void* logits, int64_t row_stride, int rows, int vocab, int dtype) {
   RLT_REQUIRE(dtype_valid(dtype), "acceptance: logits must be float32, float16 or bfloat16");
   RLT_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "acceptance: invalid logits shape");
@@ -705,9 +748,19 @@ extern "C" RLT_API int rlt_sample_rows(const void* logits, int64_t row_stride, i
   if (status != RLT_OK || rows == 0) return status;
   RLT_REQUIRE(temperature && uniforms && tokens && status_out, "sample_rows: null pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  RLT_DISPATCH_DTYPE(dtype, T, (sample_rows_kernel<T><<<rows, kSampleThreads, 0, s>>>(
-                                   static_cast<const T*>(logits), row_stride, vocab, temperature, top_k, top_p,
-                                   uniforms, tokens, status_out)));
+  if (stage_rows(top_k, top_p, vocab)) {
+    const size_t smem = static_cast<size_t>(vocab) * sizeof(float);
+    RLT_DISPATCH_DTYPE(dtype, T, {
+      auto kernel = sample_rows_kernel<T, true>;
+      RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      kernel<<<rows, kSampleThreads, smem, s>>>(static_cast<const T*>(logits), row_stride, vocab, temperature, top_k,
+                                                top_p, uniforms, tokens, status_out);
+    });
+  } else {
+    RLT_DISPATCH_DTYPE(dtype, T, (sample_rows_kernel<T, false><<<rows, kSampleThreads, 0, s>>>(
+                                     static_cast<const T*>(logits), row_stride, vocab, temperature, top_k, top_p,
+                                     uniforms, tokens, status_out)));
+  }
   return launch_status("sample_rows_kernel");
 }
 
@@ -719,9 +772,19 @@ extern "C" RLT_API int rlt_probabilities(const void* logits, int64_t row_stride,
   if (status != RLT_OK || rows == 0) return status;
   RLT_REQUIRE(temperature && probs && status_out, "probabilities: null pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  RLT_DISPATCH_DTYPE(dtype, T, (probabilities_kernel<T><<<rows, kSampleThreads, 0, s>>>(
-                                   static_cast<const T*>(logits), row_stride, vocab, temperature, top_k, top_p,
-                                   probs, status_out)));
+  if (stage_rows(top_k, top_p, vocab)) {
+    const size_t smem = static_cast<size_t>(vocab) * sizeof(float);
+    RLT_DISPATCH_DTYPE(dtype, T, {
+      auto kernel = probabilities_kernel<T, true>;
+      RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      kernel<<<rows, kSampleThreads, smem, s>>>(static_cast<const T*>(logits), row_stride, vocab, temperature, top_k,
+                                                top_p, probs, status_out);
+    });
+  } else {
+    RLT_DISPATCH_DTYPE(dtype, T, (probabilities_kernel<T, false><<<rows, kSampleThreads, 0, s>>>(
+                                     static_cast<const T*>(logits), row_stride, vocab, temperature, top_k, top_p,
+                                     probs, status_out)));
+  }
   return launch_status("probabilities_kernel");
 }
 
@@ -752,10 +815,21 @@ extern "C" RLT_API int rlt_accept_rejection(const void* target_logits, const voi
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   RowStats* stats = static_cast<RowStats*>(workspace);
-  RLT_DISPATCH_DTYPE(dtype, T, (row_stats_kernel<T><<<dim3(rows, 2), kStatsThreads, 0, s>>>(
-                                   static_cast<const T*>(target_logits), static_cast<const T*>(draft_logits),
-                                   row_stride, vocab, cu_rows, n, tokens, tokens_width, temperature, top_k, top_p,
-                                   stats)));
+  if (stage_rows(top_k, top_p, vocab)) {
+    const size_t smem = static_cast<size_t>(vocab) * sizeof(float);
+    RLT_DISPATCH_DTYPE(dtype, T, {
+      auto kernel = row_stats_kernel<T, kSampleThreads, true>;
+      RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      kernel<<<dim3(rows, 2), kSampleThreads, smem, s>>>(static_cast<const T*>(target_logits),
+                                                         static_cast<const T*>(draft_logits), row_stride, vocab, cu_rows,
+                                                         n, tokens, tokens_width, temperature, top_k, top_p, stats);
+    });
+  } else {
+    RLT_DISPATCH_DTYPE(dtype, T, (row_stats_kernel<T, kStatsThreads, false><<<dim3(rows, 2), kStatsThreads, 0, s>>>(
+                                     static_cast<const T*>(target_logits), static_cast<const T*>(draft_logits),
+                                     row_stride, vocab, cu_rows, n, tokens, tokens_width, temperature, top_k, top_p,
+                                     stats)));
+  }
   status = launch_status("row_stats_kernel");
   if (status != RLT_OK) return status;
   RLT_DISPATCH_DTYPE(dtype, T, (decide_kernel<T><<<n, kSampleThreads, 0, s>>>(
