@@ -251,29 +251,21 @@ struct SelectScratch {
   int warp_counts[32];
 };
 
+// One shared-memory atomic per distinct digit in the warp: lanes with the same digit find each
+// other with match.any and add their weights with two integer warp reductions (a weight is below
+// 2^41: 20 low and 21 high bits, so 32 of them cannot overflow a 32-bit partial sum).  The leading
+// byte of the key has only a few populated values, so plain per-lane atomics would serialise.
 template <bool kByMass>
 __device__ __forceinline__ void hist_add(SelectScratch& h, int bucket, unsigned long long w, bool valid) {
   const int lane = threadIdx.x & 31;
-  unsigned todo = __ballot_sync(0xffffffffu, valid);
-  bool pending = valid;
-  // Most tokens of a warp fall into a few digits of the leading byte: add those once per warp.
-  for (int it = 0; todo != 0u && it < 3; ++it) {
-    const int leader = __ffs(todo) - 1;
-    const int b = __shfl_sync(0xffffffffu, bucket, leader);
-    const bool mine = pending && bucket == b;
-    const unsigned peers = __ballot_sync(0xffffffffu, mine);
-    if (kByMass) {
-      const unsigned long long s = warp_sum(mine ? w : 0ull);
-      if (lane == leader) atomicAdd(&h.mass[b], s);
-    }
-    if (lane == leader) atomicAdd(&h.count[b], static_cast<unsigned int>(__popc(peers)));
-    pending = pending && !mine;
-    todo &= ~peers;
+  const unsigned peers = __match_any_sync(0xffffffffu, valid ? bucket : 0x7fff);
+  const bool leader = valid && lane == __ffs(peers) - 1;
+  if (kByMass) {
+    const unsigned low = __reduce_add_sync(peers, static_cast<unsigned>(w & 0xfffffu));
+    const unsigned high = __reduce_add_sync(peers, static_cast<unsigned>(w >> 20));
+    if (leader) atomicAdd(&h.mass[bucket], (static_cast<unsigned long long>(high) << 20) + low);
   }
-  if (pending) {
-    if (kByMass) atomicAdd(&h.mass[bucket], w);
-    atomicAdd(&h.count[bucket], 1u);
-  }
+  if (leader) atomicAdd(&h.count[bucket], static_cast<unsigned int>(__popc(peers)));
 }
 
 // Index of the n-th (1-based) token in ascending index order with order key `key` inside `outer`.
