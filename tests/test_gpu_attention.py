@@ -288,3 +288,46 @@ def test_graph_capture_and_replay_with_device_lengths(kernel):
     torch.cuda.synchronize()
     want = oracle.paged_attention(q.cpu(), pool["key"], pool["value"], pool["tables"].clamp_min(0), lengths.cpu())
     check(out.cpu(), want, dtype)
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_batches_match_oracle_and_replay_identically(kernel, seed):
+    """Seeded random batches: group sizes 1..16 / gqa, GQA ratios 1..16, contexts from one token to
+    beyond the first chunk octave, empty rows in between, fp16 or bf16, a layer-strided view, K below
+    or above V in memory.  Checked against the oracle; a second run over the same plan gives the same
+    bits (the plan survives a run) and so does every row scored alone."""
+    g = torch.Generator().manual_seed(1000 + seed)
+    dtype = (torch.bfloat16, torch.float16)[seed % 2]
+    kv_heads = (1, 2, 4, 16)[int(torch.randint(0, 4, (1,), generator=g))]
+    gqa = (1, 2, 4, 8, 16)[int(torch.randint(0, 5, (1,), generator=g))]
+    q_heads = kv_heads * gqa
+    cap = 16 // gqa
+    groups = int(torch.randint(2, 9, (1,), generator=g))
+    contexts, row_lengths = [], []
+    for _ in range(groups):
+        scale = (40, 600, 3000, 9500)[int(torch.randint(0, 4, (1,), generator=g))]
+        ctx = int(torch.randint(1, scale + 1, (1,), generator=g))
+        rows = int(torch.randint(1, min(cap, ctx) + 1, (1,), generator=g)) if cap > 1 else 1
+        contexts.append(ctx)
+        row_lengths.append([ctx - rows + 1 + t for t in range(rows)])
+    layers, layer = 2, seed % 2
+    pool = make_pool(contexts, kv_heads=kv_heads, head_dim=128, block=16, dtype=dtype, seed=seed, layers=layers,
+                     layer=layer, row_lengths=row_lengths, pad=0 if seed % 3 else -1)
+    tables, lengths = pool["tables"], pool["lengths"].clone()
+    if seed % 4 == 0:                                  # an empty row inside a group breaks it in two
+        lengths[int(torch.randint(0, lengths.numel(), (1,), generator=g))] = 0
+    q = (torch.randn(tables.shape[0], q_heads, 128, generator=g) * 0.7).to(dtype)
+    both = torch.stack([pool["key_pool"], pool["value_pool"]] if seed % 2 else [pool["value_pool"], pool["key_pool"]]).cuda()
+    key, value = (both[0], both[1]) if seed % 2 else (both[1], both[0])
+    args = (q.cuda(), key[:, layer], value[:, layer], tables.cuda(), lengths.cuda())
+    with kernel.shared_plan():
+        first = kernel(*args)
+        again = kernel(*args)
+    want = oracle.paged_attention(q, pool["key"], pool["value"], tables.clamp_min(0), lengths)
+    check(first.cpu(), want, dtype)
+    assert torch.equal(first, again)
+    assert kernel.last_status()["error"] == 0
+    for row in range(0, tables.shape[0], 3):
+        one = slice(row, row + 1)
+        alone = kernel(args[0][one], args[1], args[2], args[3][one], args[4][one])
+        assert torch.equal(alone[0], first[row]), row
