@@ -580,6 +580,18 @@ def run_decode_workload(args):
     torch.cuda.synchronize()
     seconds = time.perf_counter() - clock["start"]
     stats = decoder.stats
+    # HBM roofline of the decode loop: every recurrent pass streams the layer weights once and the
+    # K/V of every active request's context once per layer; every LM-head call streams lm_head once
+    # (counted per draft pass and per round).  Activations and logits are left out (a few percent).
+    c = config
+    layer_params = (c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim
+                    + c.num_attention_heads * c.head_dim * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
+    weight_bytes = 2.0 * c.num_hidden_layers * layer_params * stats.loop_passes
+    kv_bytes = 2.0 * 2 * c.num_key_value_heads * c.head_dim * c.num_hidden_layers * stats.context_tokens_read
+    head_calls = stats.rounds / max(args.requests, 1) * 5          # upper bound: k draft calls + 1 verify call per round
+    head_bytes = 2.0 * c.vocab_size * c.hidden_size * head_calls
+    peak, peak_kind = measured_peaks()
+    roofline_s = (weight_bytes + kv_bytes + head_bytes) / (peak * 1e9)
     print(json.dumps({
         "workload": "decode: Ouro-1.4B-shaped random-init bf16, self-spec k=4 from depth 2, "
                     f"{args.requests} requests, prompts U[128,1024], {args.output_tokens} output tokens, T={args.temperature}, "
@@ -590,6 +602,10 @@ def run_decode_workload(args):
         "committed_tokens_per_s": stats.committed_tokens / seconds,
         "accepted_tokens_per_s": stats.accepted_tokens / seconds,
         "acceptance_rate": stats.accepted_tokens / max(stats.drafted_tokens, 1),
+        "loop_passes": stats.loop_passes,
+        "hbm_roofline": {"kv_bytes": kv_bytes, "weight_bytes": weight_bytes, "lm_head_bytes": head_bytes,
+                         "peak_gbs": peak, "peak_kind": peak_kind, "seconds_at_peak": roofline_s,
+                         "frac": roofline_s / seconds},
         "tokens_out": sum(len(t) for t in tokens), "attention_status": model.attention.last_status(device)}))
 
 

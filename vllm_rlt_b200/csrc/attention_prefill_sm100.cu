@@ -29,7 +29,10 @@ namespace {
 
 constexpr int kTileRows = 64;                  // query tokens per CTA
 constexpr int kTilePages = 4;                  // pages per stage (64 keys)
-constexpr int kPrefillStages = 2;
+#ifndef RLT_PREFILL_STAGES
+#define RLT_PREFILL_STAGES 2
+#endif
+constexpr int kPrefillStages = RLT_PREFILL_STAGES;
 constexpr int kPrefillWarps = kTileRows / 16;
 constexpr int kPrefillPlanThreads = 1024;
 

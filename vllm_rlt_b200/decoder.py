@@ -33,6 +33,11 @@ class DecodeStats:
     accepted_tokens: int = 0
     committed_tokens: int = 0
     verified_rows: int = 0
+    # work accounting of the decode loop (not in the reference): recurrent passes over all layers,
+    # context tokens whose K/V those passes had to read (once per request and pass), LM-head rows
+    loop_passes: int = 0
+    context_tokens_read: int = 0
+    coda_rows: int = 0
 
 
 @dataclass
@@ -257,6 +262,8 @@ class SelfSpeculativeDecoder:
                 hidden = model.prelude(tokens[in_pass, offset])
                 for depth in range(draft_loops):
                     hidden = self._loop(kv, hidden, active_t[in_pass], starts_t[in_pass] + offset, depth)
+                self.stats.loop_passes += draft_loops
+                self.stats.context_tokens_read += draft_loops * sum(s + offset + 1 for s, c in zip(starts, counts) if c > offset)
                 retained.append(hidden)
                 if offset + 1 >= width:
                     break
@@ -273,6 +280,7 @@ class SelfSpeculativeDecoder:
                     proposed = argmax_rows(logits)
                 tokens[drafting_requests, offset + 1] = proposed
                 self.stats.drafted_tokens += int(logits.shape[0])
+                self.stats.coda_rows += int(logits.shape[0])
             # verify: the retained depth-d states of all rows, request-major, loops d .. D-1
             hidden = torch.cat(retained)[gather]
             row_request = torch.repeat_interleave(torch.arange(n), counts_t)
@@ -281,6 +289,9 @@ class SelfSpeculativeDecoder:
             positions = starts_t[row_request.to(device)] + row_offset.to(device)
             for depth in range(draft_loops, target_loops):
                 hidden = self._loop(kv, hidden, requests, positions, depth)
+            self.stats.loop_passes += target_loops - draft_loops
+            self.stats.context_tokens_read += (target_loops - draft_loops) * sum(s + c for s, c in zip(starts, counts))
+            self.stats.coda_rows += rows_total
             logits = model.coda(hidden).float().contiguous()
             cu_rows = torch.tensor([0] + counts_t.cumsum(0).tolist(), dtype=torch.int32, device=device)
             start_tensor = starts_t
