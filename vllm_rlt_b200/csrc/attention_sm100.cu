@@ -5,7 +5,7 @@
 //                 rows of one request at one depth plane; k x depths rows in a shared-plane
 //                 layout) and zero-fills empty rows; the last CTA to finish turns the groups
 //                 into a work list of (group, context chunk, kv head) items, full-size chunks
-//                 first and the ragged last chunk of every group at the end.
+//                 first and then the ragged last chunk of every group, longest first.
 //   main kernel   persistent, one CTA per SM, every warp an independent worker.  A warp claims
 //                 an item and streams that head's K/V pages through its own ring of shared
 //                 memory stages with TMA (cp.async.bulk.tensor, 128-byte swizzle, page id =
@@ -47,6 +47,7 @@ namespace {
 constexpr int kPartialStride = 132;               // floats per stored partial: O[128], m, l, pad
 constexpr int kPlanThreads = 1024;
 constexpr int kMaxGroupRows = 16;
+constexpr int kSizeClasses = 64;                  // list B is bucketed by pages in the last chunk (64 or more share a class)
 
 // ---- context chunks -------------------------------------------------------------------
 // Fixed, position-only chunk boundaries: sixteen 512-token chunks up to 8192, then every
@@ -221,7 +222,20 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
   __shared__ unsigned long long s_usum[32];
   __shared__ int s_carry_start;
   __shared__ unsigned s_base_full, s_base_last;
-  if (threadIdx.x == 0) { s_carry_start = 0; s_base_full = 0; s_base_last = 0; }
+  // List B is ordered longest first (a counting sort of the groups by the pages of their last
+  // chunk): the schedule then ends with the smallest items and the warps finish together.
+  // Phase 0 counts the groups per size class, phase 1 writes the items.
+  __shared__ unsigned s_class[kSizeClasses];
+  for (int i = threadIdx.x; i < kSizeClasses; i += kPlanThreads) s_class[i] = 0u;
+  for (int phase = 0; phase < 2; ++phase) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s_carry_start = 0; s_base_full = 0; s_base_last = 0;
+    if (phase == 1) {  // counts -> first slot of every class, largest class first
+      unsigned running = 0;
+      for (int c = 0; c < kSizeClasses; ++c) { const unsigned n = s_class[c]; s_class[c] = running; running += n; }
+    }
+  }
   for (int base = 0; base < a.rows; base += kPlanThreads) {
     __syncthreads();
     for (int i = threadIdx.x; i < kPlanThreads + kMaxGroupRows; i += kPlanThreads) {
@@ -247,6 +261,14 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
       }
     }
     const int chunks = leader ? chunk_count(longest) : 0;
+    unsigned last_slot = 0;
+    if (leader) {
+      int last_start, last_end;
+      chunk_range(chunks - 1, &last_start, &last_end);
+      const int pages = (longest - last_start + kPage - 1) / kPage;
+      const int size_class = kSizeClasses - 1 - min(pages - 1, kSizeClasses - 1);
+      last_slot = atomicAdd(&s_class[size_class], static_cast<unsigned>(a.kv_heads));  // phase 0: count; phase 1: slot
+    }
     const unsigned long long mine = leader ? ((static_cast<unsigned long long>(a.kv_heads) << 32) |
                                               static_cast<unsigned>((chunks - 1) * a.kv_heads))
                                            : 0ull;
@@ -256,7 +278,7 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
     // Pages are addressed through the table row of the group's longest member: the link
     // window guarantees every member agrees with it on all pages that member can need.
     const int table_row = leader ? __ldcg(&ws.row_table[longest_row]) : 0;
-    unsigned leaders = __ballot_sync(0xffffffffu, leader);
+    unsigned leaders = __ballot_sync(0xffffffffu, leader && phase == 1);
     while (leaders != 0u) {
       const int src = __ffs(leaders) - 1;
       leaders &= leaders - 1;
@@ -266,7 +288,7 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
       const int l_nrows = __shfl_sync(0xffffffffu, nrows, src);
       const int l_chunks = __shfl_sync(0xffffffffu, chunks, src);
       const unsigned l_full = s_base_full + __shfl_sync(0xffffffffu, static_cast<unsigned>(exclusive & 0xffffffffu), src);
-      const unsigned l_last = s_base_last + __shfl_sync(0xffffffffu, static_cast<unsigned>(exclusive >> 32), src);
+      const unsigned l_last = __shfl_sync(0xffffffffu, last_slot, src);
       const int full_count = (l_chunks - 1) * a.kv_heads;
       for (int i = lane; i < full_count; i += 32) {
         it.nrows_head = l_nrows | ((i % a.kv_heads) << 16);
@@ -285,6 +307,7 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
       s_base_full += static_cast<unsigned>(inclusive & 0xffffffffu);
       s_base_last += static_cast<unsigned>(inclusive >> 32);
     }
+  }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
