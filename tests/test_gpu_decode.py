@@ -189,3 +189,17 @@ def test_graph_replay_equals_the_eager_loop_bit_for_bit():
         assert torch.equal(a, b)
     assert torch.equal(ke, kg) and torch.equal(ve, vg)
     assert model.attention.last_status  # the wrapper stays usable after captures
+
+
+@pytest.mark.parametrize("name", ["tiny_k3", "config1"])
+def test_pipeline_mode_decoding_gives_the_reference_tokens(golden, name):
+    # Pipeline self-speculation (every slot advances d loops per step at its own depth plane, the
+    # device state is updated by pipeline_shift) is lossless: the reference engine's greedy tokens.
+    case = golden("decode.pt")[name]
+    decoder = rlt.SelfSpeculativeDecoder(build(case), block=case["block"])
+    tokens = decoder.generate_pipeline(case["prompts"], case["max_tokens"], num_speculative_tokens=case["k"],
+                                       draft_loops=case["draft_loops"], target_loops=case["target_loops"])
+    assert tokens == case["tokens"]
+    stats = decoder.stats
+    assert stats.committed_tokens == sum(len(t) - 1 for t in tokens)
+    assert 0 <= stats.accepted_tokens <= stats.committed_tokens and stats.drafted_tokens >= stats.accepted_tokens

@@ -21,7 +21,8 @@ import torch
 
 from .kv_cache import rollback
 from .looped_lm import LoopedLM
-from .speculative import accept_greedy, accept_rejection, argmax_rows, raise_for_status, sample_rows
+from .speculative import (PipelineState, accept_greedy, accept_rejection, argmax_rows, pipeline_shift,
+                          raise_for_status, sample_rows)
 
 
 @dataclass
@@ -195,6 +196,72 @@ class SelfSpeculativeDecoder:
             for i, token in zip(active, argmax_rows(self.model.coda(hidden).float().contiguous()).tolist()):
                 generated[i].append(token)
         return generated
+
+    # ---- pipeline self-speculation --------------------------------------------------------
+    @torch.no_grad()
+    def generate_pipeline(self, prompts, max_tokens: int, *, num_speculative_tokens: int, draft_loops: int = 2,
+                          target_loops: int | None = None):
+        """Pipeline-mode self-speculation, greedy (`AsyncSpeculativeRunner._pipeline_step`,
+        worker/async_speculative.py:502-584 of the reference).
+
+        Every request keeps `width = min(k + 1, D // d)` oldest-first token slots on the device.  A
+        step advances every active slot by `d` loops at its own depth plane (slot j sits at
+        position `position + j`), takes the LM-head argmax of every slot, and `pipeline_shift`
+        applies the outcome: a slot that reached depth d proposes the next token (born at the tail),
+        the head slot that reached depth D is emitted and checked against the candidate it was
+        drafted from; a mismatch drops its descendants and restarts from the corrected token.  The
+        host reads six integers per request and step."""
+        model, device = self.model, self.model.device
+        target_loops = target_loops or model.config.total_ut_steps
+        if not 0 < draft_loops <= target_loops <= model.config.total_ut_steps or target_loops % draft_loops:
+            raise ValueError("target_loops must be a positive multiple of draft_loops")
+        width = min(num_speculative_tokens + 1, target_loops // draft_loops)
+        n = len(prompts)
+        kv = PagedKV.allocate(model, [len(p) + max_tokens + width + 1 for p in prompts], self.block)
+        first = self._prefill(kv, prompts)
+        generated = [[t] for t in first]
+        token = torch.tensor(first, device=device)
+        state = PipelineState(
+            tokens=token[:, None].repeat(1, width).contiguous(),
+            depths=torch.zeros(n, width, dtype=torch.int64, device=device),
+            candidates=torch.zeros(n, width, dtype=torch.int64, device=device),
+            active=(torch.arange(width, device=device) == 0)[None, :].repeat(n, 1).contiguous(),
+            hidden=torch.zeros(n, width, model.config.hidden_size, dtype=model.dtype, device=device),
+            token=token.clone(),
+            position=torch.tensor([len(p) for p in prompts], device=device))
+        limits = torch.tensor([len(p) + max_tokens - 1 for p in prompts], device=device)
+        widths = torch.full((n,), width, dtype=torch.int32, device=device)
+        row_starts = (torch.arange(n, device=device) * width).int()
+        request_of_row = torch.arange(n, device=device).repeat_interleave(width)
+        slot_of_row = torch.arange(width, device=device).repeat(n)
+        for _ in range(max_tokens * (target_loops // draft_loops) + 8):      # each step emits or advances
+            if all(len(g) >= max_tokens for g in generated):
+                break
+            active = state.active.view(-1)
+            depths = state.depths.view(-1)
+            positions = torch.where(active, state.position[request_of_row] + slot_of_row, 0)
+            hidden = torch.where((depths == 0)[:, None], model.prelude(state.tokens.view(-1)),
+                                 state.hidden.view(n * width, -1))
+            lengths = torch.where(active, positions + 1, 0).int()
+            for offset in range(draft_loops):
+                plane = torch.where(active, depths + offset, 0)
+                tables = kv.tables[request_of_row, plane].contiguous()
+                blocks = tables.gather(1, (positions // self.block)[:, None]).squeeze(1).long()
+                hidden = model.recurrent(hidden, positions, kv.key, kv.value, blocks, positions % self.block, tables,
+                                         lengths, write_mask=active)
+            self.stats.loop_passes += draft_loops
+            choices = argmax_rows(model.coda(hidden).float().contiguous())
+            wire = pipeline_shift(state, widths, row_starts, choices, hidden.contiguous(), limits,
+                                  draft_loops=draft_loops, target_loops=target_loops)
+            for i, (prediction, accepted, emitted, _, drafted, verified) in enumerate(wire.tolist()):  # the step's one host read
+                if emitted and len(generated[i]) < max_tokens:
+                    generated[i].append(prediction)
+                    self.stats.committed_tokens += 1
+                    self.stats.accepted_tokens += accepted
+                self.stats.drafted_tokens += drafted
+                self.stats.verified_rows += verified
+            self.stats.rounds += n
+        return [g[:max_tokens] for g in generated]
 
     # ---- block self-speculation ----------------------------------------------------------
     @torch.no_grad()

@@ -119,7 +119,7 @@ class LoopedLM:
         return angles.cos().to(self.dtype).unsqueeze(1), angles.sin().to(self.dtype).unsqueeze(1)
 
     def recurrent(self, hidden, positions, key_pool, value_pool, write_blocks, write_offsets, block_tables,
-                  context_lengths, packed=None):
+                  context_lengths, packed=None, write_mask=None):
         """One recurrent loop: every layer writes its K/V rows, attends, and runs the MLP.
 
         key_pool / value_pool: `[blocks, layers, block_size, kv_heads, head_dim]`; the addressing
@@ -129,10 +129,11 @@ class LoopedLM:
 
         `packed = (cu_seqlens_q, max_seqlen_q)` switches to the packed form for prompts: one
         block-table row and one context length per sequence, rows of a sequence consecutive
-        (`AttentionBackend.prefill`)."""
+        (`AttentionBackend.prefill`).  `write_mask` (bool [rows]) keeps inactive rows from writing K/V
+        (their context length should be 0 so that they attend to nothing)."""
         if self.fused:
             return self._recurrent_fused(hidden, positions, key_pool, value_pool, write_blocks, write_offsets,
-                                         block_tables, context_lengths, packed=packed)
+                                         block_tables, context_lengths, packed=packed, write_mask=write_mask)
         c, w = self.config, self.w
         cos, sin = self.rope(positions)
         rows = hidden.shape[0]
@@ -146,7 +147,7 @@ class LoopedLM:
                 q = q * cos + rotate_half(q) * sin
                 k = k * cos + rotate_half(k) * sin
                 kc, vc = key_pool[:, layer], value_pool[:, layer]
-                kv_write(kc, vc, k, v, write_blocks, write_offsets)
+                kv_write(kc, vc, k, v, write_blocks, write_offsets, write_mask=write_mask)
                 attended = self._attend(q.contiguous(), kc, vc, block_tables, context_lengths, packed)
                 attended = F.linear(attended.reshape(rows, -1), w[p + "self_attn.o_proj.weight"])
                 hidden = hidden + rms_norm(attended, w[p + "input_layernorm_2.weight"], c.rms_norm_eps)
@@ -163,7 +164,7 @@ class LoopedLM:
         return self.attention.prefill(q, key_cache, value_cache, block_tables, context_lengths, *packed)
 
     def _recurrent_fused(self, hidden, positions, key_pool, value_pool, write_blocks, write_offsets, block_tables,
-                         context_lengths, active_rows=None, packed=None):
+                         context_lengths, active_rows=None, packed=None, write_mask=None):
         """The same loop with ten launches per layer: QKV GEMM, rope_kv_write, attention, O GEMM,
         sandwich_norm (residual add + the MLP's input norm), gate and up GEMMs, silu_and_mul, down
         GEMM, sandwich_norm (residual add + the next layer's input norm, or the final norm).
@@ -182,7 +183,8 @@ class LoopedLM:
                 k = qkv[:, q_width:q_width + kv_width].view(rows, -1, c.head_dim)
                 v = qkv[:, q_width + kv_width:].view(rows, -1, c.head_dim)
                 kc, vc = key_pool[:, layer], value_pool[:, layer]
-                q = rope_kv_write(q, k, v, cos, sin, kc, vc, write_blocks, write_offsets, active_rows=active_rows)
+                q = rope_kv_write(q, k, v, cos, sin, kc, vc, write_blocks, write_offsets, write_mask=write_mask,
+                                  active_rows=active_rows)
                 attended = self._attend(q, kc, vc, block_tables, context_lengths, packed)
                 attended = F.linear(attended.view(rows, -1), w[p + "self_attn.o_proj.weight"])
                 stream, x = sandwich_norm(attended, w[p + "input_layernorm_2.weight"], c.rms_norm_eps,
