@@ -155,6 +155,17 @@ class SelfSpeculativeDecoder:
         self._graphs = None
 
     # ---- shared pieces -------------------------------------------------------------------
+    def _upload(self, host_tensors):
+        """int64 CPU tensors -> device tensors through one pinned staging buffer and one
+        asynchronous copy.  The buffer is reused by the next call, which the decoder makes only
+        after it has read a round's results back (so the copy has completed)."""
+        sizes = [t.numel() for t in host_tensors]
+        total = sum(sizes)
+        if getattr(self, "_staging", None) is None or self._staging.numel() < total:
+            self._staging = torch.empty(max(total, 4096) * 2, dtype=torch.int64, pin_memory=True)
+        torch.cat([t.reshape(-1).long() for t in host_tensors], out=self._staging[:total])
+        return self._staging[:total].to(self.model.device, non_blocking=True).split(sizes)
+
     def _loop(self, kv: PagedKV, hidden, requests, positions, depth):
         blocks, offsets, tables, lengths = kv.addressing(requests, positions, depth)
         if self._graphs is not None and self._graphs.kv is kv:
@@ -306,26 +317,35 @@ class SelfSpeculativeDecoder:
             n, width = len(active), max(counts)
             rows_total = sum(counts)
             counts_t = torch.tensor(counts)
-            active_t = torch.tensor(active, device=device)
-            starts_t = torch.tensor(starts, device=device)
-            tokens = torch.zeros(n, width, dtype=torch.int64, device=device)
-            tokens[:, 0] = torch.tensor([generated[i][-1] for i in active], device=device)
             # which (request, offset) cells exist, and where each lands among the retained rows
             present = counts_t[:, None] > torch.arange(width)[None, :]                 # [n, width]
             per_offset = present.sum(0)                                                # rows of draft pass o
             rank = present.long().cumsum(0) - 1                                        # row of request j in pass o
             base = torch.cat([torch.zeros(1, dtype=torch.long), per_offset.cumsum(0)[:-1]])
             firsts = [0] + counts_t.cumsum(0).tolist()[:-1]
-            gather = (base[None, :] + rank)[present].to(device)                         # request-major order
+            in_pass_host = [present[:, o].nonzero().flatten() for o in range(width)]
+            drafting_host = [present[present[:, o], o + 1].nonzero().flatten() if o + 1 < width
+                             else torch.zeros(0, dtype=torch.long) for o in range(width)]
+            row_request = torch.repeat_interleave(torch.arange(n), counts_t)
+            row_offset = torch.cat([torch.arange(c) for c in counts])
+            # every index tensor of the round goes to the device in one pinned, asynchronous copy:
+            # a pageable upload in the middle of a round would wait for the GPU and stall the launches
+            (active_t, starts_t, last_t, gather, first_row, row_request_t, row_offset_t, cu_rows64, *per_pass) = \
+                self._upload([torch.tensor(active), torch.tensor(starts),
+                              torch.tensor([generated[i][-1] for i in active]), (base[None, :] + rank)[present],
+                              torch.tensor(firsts), row_request, row_offset,
+                              torch.tensor([0] + counts_t.cumsum(0).tolist()), *in_pass_host, *drafting_host])
+            in_pass_dev, drafting_dev = per_pass[:width], per_pass[width:]
+            tokens = torch.zeros(n, width, dtype=torch.int64, device=device)
+            tokens[:, 0] = last_t
             draft_logits = None
             if sampled:  # row j of a request keeps the logits its draft j+1 was sampled from
                 draft_logits = torch.zeros(rows_total, model.config.vocab_size, dtype=torch.float32, device=device)
                 u_draft = torch.rand(n, width, generator=generator, device=device)
-                first_row = torch.tensor(firsts, device=device)
             retained = []
             # draft: one new position per request and offset, loops 0 .. d-1
             for offset in range(width):
-                in_pass = present[:, offset].nonzero().flatten().to(device)             # requests with c > offset
+                in_pass = in_pass_dev[offset]                                           # requests with c > offset
                 hidden = model.prelude(tokens[in_pass, offset])
                 for depth in range(draft_loops):
                     hidden = self._loop(kv, hidden, active_t[in_pass], starts_t[in_pass] + offset, depth)
@@ -334,8 +354,8 @@ class SelfSpeculativeDecoder:
                 retained.append(hidden)
                 if offset + 1 >= width:
                     break
-                drafting = present[present[:, offset], offset + 1].to(device)           # of this pass's rows
-                if not bool(drafting.any()):
+                drafting = drafting_dev[offset]                                         # rows of this pass that draft on
+                if drafting.numel() == 0:
                     break
                 drafting_requests = in_pass[drafting]
                 logits = model.coda(hidden[drafting]).float().contiguous()
@@ -350,17 +370,15 @@ class SelfSpeculativeDecoder:
                 self.stats.coda_rows += int(logits.shape[0])
             # verify: the retained depth-d states of all rows, request-major, loops d .. D-1
             hidden = torch.cat(retained)[gather]
-            row_request = torch.repeat_interleave(torch.arange(n), counts_t)
-            row_offset = torch.cat([torch.arange(c) for c in counts])
-            requests = active_t[row_request.to(device)]
-            positions = starts_t[row_request.to(device)] + row_offset.to(device)
+            requests = active_t[row_request_t]
+            positions = starts_t[row_request_t] + row_offset_t
             for depth in range(draft_loops, target_loops):
                 hidden = self._loop(kv, hidden, requests, positions, depth)
             self.stats.loop_passes += target_loops - draft_loops
             self.stats.context_tokens_read += (target_loops - draft_loops) * sum(s + c for s, c in zip(starts, counts))
             self.stats.coda_rows += rows_total
             logits = model.coda(hidden).float().contiguous()
-            cu_rows = torch.tensor([0] + counts_t.cumsum(0).tolist(), dtype=torch.int32, device=device)
+            cu_rows = cu_rows64.int()
             start_tensor = starts_t
             slots = torch.arange(n, device=device)
             if sampled:
