@@ -20,6 +20,14 @@ through the public Python API (H2D of every input and D2H of the result inside t
 region).  One process per GPU; every rank runs an independent replica on its own requests
 (no collective on the path), the timed region is bracketed by a barrier, and the step time is
 the maximum over ranks.
+
+Other entry points (each prints its own JSON line; none is the contract line above):
+    --workload decode [--requests R --output-tokens T --temperature X --eager]
+                      whole-model self-speculative decoding of a random-init Ouro-1.4B-shaped model
+                      (BASELINE configs[2]) with its HBM roofline
+    --only attention  [--requests --layers --tokens --depths --kv-heads --context-min --context-max --shared-plan]
+    --only prefill    [--requests --tokens --kv-heads --eager]   packed causal prefill, TFLOP/s
+    --only accept | --only silu                                  the small kernels at the step's shapes
 """
 
 from __future__ import annotations

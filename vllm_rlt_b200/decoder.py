@@ -2,7 +2,7 @@
 
 The loop of `SpeculativeRunner._submit_round` / `_collect_round`
 (`vllm_rlt/worker/speculative.py:418-511` of the reference) with the reference's round geometry
-(SURVEY: a round of request i processes `c_i = min(K+1, max_tokens - generated_i)` input
+(a round of request i processes `c_i = min(K+1, max_tokens - generated_i)` input
 positions starting at the last committed token; draft offset o runs loops `0..d-1` and proposes
 token o+1 from `coda(hidden_d).argmax`; the retained depth-d states of all c_i rows then run
 loops `d..D-1` and every row's argmax is a target), on a LAST_EXITED paged KV cache (one plane
