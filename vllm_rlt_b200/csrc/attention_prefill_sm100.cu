@@ -20,6 +20,7 @@
 // key read once per 64 queries, about 128 flop/byte — tensor-bound, unlike the verify path.
 #include <cuda.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include "attention.cuh"
 #include "sm100_primitives.cuh"
@@ -57,9 +58,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// Tile list: sequence s contributes ceil(n_s / 64) tiles, written last tile first.
+// Tile list: sequence s contributes ceil(n_s / tile_rows) tiles, written last tile first.
 __global__ void __launch_bounds__(kPrefillPlanThreads)
-prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens_q, int seqs, PrefillHeader* header,
+prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens_q, int seqs, int tile_rows, PrefillHeader* header,
                     PrefillTile* tiles) {
   __shared__ int warp_totals[32];
   __shared__ int carry;
@@ -69,7 +70,7 @@ prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens_q, int seqs, PrefillH
     __syncthreads();
     const int s = base + threadIdx.x;
     const int n = s < seqs ? max(cu_seqlens_q[s + 1] - cu_seqlens_q[s], 0) : 0;
-    const int mine = (n + kTileRows - 1) / kTileRows;
+    const int mine = (n + tile_rows - 1) / tile_rows;
     int inc = mine;
 #pragma unroll
     for (int x = 1; x < 32; x <<= 1) {
@@ -82,8 +83,8 @@ prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens_q, int seqs, PrefillH
     for (int w = 0; w < warp; ++w) before += warp_totals[w];
     const int start = before + inc - mine;
     for (int t = 0; t < mine; ++t) {
-      const int first = (mine - 1 - t) * kTileRows;
-      tiles[start + t] = PrefillTile{s, first, min(kTileRows, n - first), 0};
+      const int first = (mine - 1 - t) * tile_rows;
+      tiles[start + t] = PrefillTile{s, first, min(tile_rows, n - first), 0};
     }
     __syncthreads();
     if (threadIdx.x == kPrefillPlanThreads - 1) carry = before + inc;
@@ -310,6 +311,251 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap kv_map, AttentionAr
   }
 }
 
+// ---- the same tile on the 5th-generation tensor cores (tcgen05 / TMEM) ----------------------
+// 128 query tokens of one query head per CTA, 64 keys per stage.  Q sits in shared memory as two
+// K-major 64-dim halves, every K / V page lands as four 2 KiB TMA copies so that a stage holds
+// K as [half][64 keys][64 dims] (K-major B operand of S = Q K^T) and V in the same shape, which is
+// the MN-major B operand of O = P V.  One thread issues the MMAs: S (128 x 64, fp32) and the
+// stage's P V product (128 x 128, fp32) accumulate in tensor memory, tcgen05.commit signals an
+// mbarrier, and the 128 threads — one query row each, the row that is their TMEM lane — read S
+// with tcgen05.ld, run the online softmax without any shuffle, write P (bf16) over the stage's K
+// (16 KiB, dead once S is complete) for the second MMA and fold the P V tile into their 128 fp32
+// output registers.  97 KiB of shared memory and 256 TMEM columns per CTA: two CTAs per SM, so one
+// CTA's MMAs run under the other's softmax.  The QK^T MMA of the
+// next stage is issued right behind the P V MMA, so it runs while the rows are being folded.
+constexpr int kUmmaRows = 128;
+constexpr int kUmmaKeys = 64;
+constexpr int kUmmaStages = 2;
+constexpr uint32_t kTmemColumns = 256;   // S: columns 0..63, P V tile: 64..191
+
+struct __align__(1024) UmmaShared {
+  unsigned char q[2][kUmmaRows * 128];                   // [half][row][64 dims], 128-byte swizzle
+  unsigned char k[kUmmaStages][2][kUmmaKeys * 128];      // [half][key][64 dims]
+  unsigned char v[kUmmaStages][2][kUmmaKeys * 128];      // [half][key][64 dims]
+  unsigned long long full[kUmmaStages];
+  unsigned long long s_ready, o_ready;
+  uint32_t tmem_base;
+};
+
+// Shared-memory matrix descriptor, 128-byte swizzle: start address, leading and stride byte
+// offsets in 16-byte units, descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t leading_bytes, uint32_t stride_bytes) {
+  return static_cast<uint64_t>((saddr >> 4) & 0x3fffu) | (static_cast<uint64_t>((leading_bytes >> 4) & 0x3fffu) << 16) |
+         (static_cast<uint64_t>((stride_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
+}
+// D[tmem] (+)= A[smem] * B[smem], one elected thread.
+__device__ __forceinline__ void umma_issue(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+               ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <bool kBF16>
+__global__ void __launch_bounds__(kUmmaRows)
+prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                    AttentionArgs a, const PrefillHeader* header, const PrefillTile* tiles, unsigned* error,
+                    float scale_log2) {
+  using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
+  if (blockIdx.x >= header->tiles) return;
+  extern __shared__ unsigned char smem_raw[];
+  UmmaShared& sm = *reinterpret_cast<UmmaShared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, row = threadIdx.x;
+  const PrefillTile tile = tiles[blockIdx.x];
+  const int q_head = blockIdx.y, kv_head = q_head / (a.q_heads / a.kv_heads);
+  const int seq_first = a.cu_seqlens_q[tile.seq];
+  const int n_new = a.cu_seqlens_q[tile.seq + 1] - seq_first;
+  const int base_len = a.context_lengths[tile.seq] - n_new + 1;
+  const int len = row < tile.count ? max(base_len + tile.first + row, 0) : 0;   // keys this thread's row sees
+  const int kv_end = max(base_len + tile.first + tile.count - 1, 0);
+  const int total_pages = (kv_end + kPage - 1) / kPage;
+  const int kv_tiles = (total_pages + 3) / 4;
+  const int64_t q_offset = ((static_cast<int64_t>(seq_first) + tile.first + row) * a.q_heads + q_head) * kHeadDim;
+
+  // ---- prologue: barriers, tensor memory, Q into its swizzled halves, V stages zeroed (a partial
+  // last stage multiplies P = 0 with whatever lies behind its last page: that must be finite) ----
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kUmmaStages; ++s) mbar_init(smem_u32(&sm.full[s]), 1);
+    mbar_init(smem_u32(&sm.s_ready), 1);
+    mbar_init(smem_u32(&sm.o_ready), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemColumns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  {
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    uint4* vz = reinterpret_cast<uint4*>(&sm.v[0][0][0]);
+    for (int i = threadIdx.x; i < static_cast<int>(sizeof(sm.v) / 16); i += kUmmaRows) vz[i] = zero;
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(a.q) + q_offset);
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      const uint4 value = len > 0 ? __ldg(src + c) : zero;
+      *reinterpret_cast<uint4*>(&sm.q[c >> 3][row * 128 + (((c & 7) ^ (row & 7)) << 4)]) = value;
+    }
+  }
+  fence_async_proxy();
+  tcgen05_before_sync();
+  __syncthreads();
+  tcgen05_after_sync();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+  const uint64_t policy = policy_evict_first();
+  const int32_t* table = a.block_tables + static_cast<int64_t>(tile.seq) * a.table_width;
+  constexpr uint32_t kFormat = kBF16 ? 1u : 0u;
+  constexpr uint32_t kIdesc = (1u << 4) | (kFormat << 7) | (kFormat << 10) | (static_cast<uint32_t>(kUmmaRows >> 4) << 24);
+  constexpr uint32_t kIdescQK = kIdesc | (static_cast<uint32_t>(kUmmaKeys >> 3) << 17);            // N = 64 keys
+  constexpr uint32_t kIdescPV = kIdesc | (static_cast<uint32_t>(kHeadDim >> 3) << 17) | (1u << 16);  // N = 128 dims, B MN-major
+
+  // warp 0: the sixteen 2 KiB copies of key tile jt (4 pages x K lo, K hi, V lo, V hi), one per lane
+  auto issue_copies = [&](int jt) {
+    const int stage = jt % kUmmaStages;
+    const int pages = min(4, total_pages - jt * 4);
+    const uint32_t bar = smem_u32(&sm.full[stage]);
+    if (lane == 0) mbar_expect_tx(bar, pages * kStageBytes);
+    __syncwarp();
+    const int page = lane >> 2, part = lane & 3;
+    if (lane < 16 && page < pages) {
+      const int block = table[jt * 4 + page];
+      unsigned char* dst = (part < 2 ? &sm.k[stage][part & 1][0] : &sm.v[stage][part & 1][0]) + page * 2048;
+      tma_load_page_half(smem_u32(dst), part < 2 ? &k_map : &v_map, kv_head * kHeadDim + (part & 1) * 64, block, bar, policy);
+    }
+  };
+  auto issue_qk = [&](int jt) {   // thread 0: S = Q K^T over the 128 dims in eight K = 16 steps
+    const int stage = jt % kUmmaStages;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const uint64_t da = umma_desc(smem_u32(&sm.q[ks >> 2][0]) + (ks & 3) * 32, 16, 1024);
+      const uint64_t db = umma_desc(smem_u32(&sm.k[stage][ks >> 2][0]) + (ks & 3) * 32, 16, 1024);
+      umma_issue(tmem, da, db, kIdescQK, ks > 0);
+    }
+    umma_commit(smem_u32(&sm.s_ready));
+  };
+  bool failed = false;
+  if (warp == 0) {
+    for (int jt = 0; jt < min(kUmmaStages, kv_tiles); ++jt) issue_copies(jt);
+    if (lane == 0 && kv_tiles > 0) {
+      if (mbar_wait(smem_u32(&sm.full[0]), 0)) { tcgen05_after_sync(); issue_qk(0); } else failed = true;
+    }
+  }
+
+  float o[kHeadDim];
+#pragma unroll
+  for (int d = 0; d < kHeadDim; ++d) o[d] = 0.f;
+  float m = -INFINITY, l = 0.f;
+
+  for (int jt = 0; jt < kv_tiles; ++jt) {
+    const uint32_t parity = jt & 1;
+    if (!mbar_wait(smem_u32(&sm.s_ready), parity)) { failed = true; break; }
+    tcgen05_after_sync();
+    // ---- this row's 64 scores ----
+    float s[kUmmaKeys];
+    {
+      uint32_t r0[32], r1[32];
+      tmem_load32(tmem_row, r0);
+      tmem_load32(tmem_row + 32, r1);
+      tmem_load_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) { s[j] = __uint_as_float(r0[j]); s[32 + j] = __uint_as_float(r1[j]); }
+    }
+    const int first_key = jt * kUmmaKeys;
+    unsigned char* p_tile = &sm.k[jt % kUmmaStages][0][0];   // S is complete: this stage's K is dead
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kUmmaKeys; ++j) {
+      if (first_key + j >= len) s[j] = -INFINITY;
+      mx = fmaxf(mx, s[j]);
+    }
+    const float mn = fmaxf(m, mx * scale_log2);
+    const float mu = mn == -INFINITY ? 0.f : mn;
+    const float alpha = fast_exp2(m - mu);
+    const bool moved = mn != m;
+    m = mn;
+    float sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint32_t packed[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p0 = fast_exp2(fmaf(s[c * 8 + 2 * e], scale_log2, -mu));
+        const float p1 = fast_exp2(fmaf(s[c * 8 + 2 * e + 1], scale_log2, -mu));
+        sum += p0 + p1;
+        packed[e] = pack2<kBF16>(p0, p1);
+      }
+      *reinterpret_cast<uint4*>(&p_tile[row * 128 + ((c ^ (row & 7)) << 4)]) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+    l = l * alpha + sum;
+    if (moved) {
+#pragma unroll
+      for (int d = 0; d < kHeadDim; ++d) o[d] *= alpha;
+    }
+    fence_async_proxy();       // P (generic writes) before the MMA's reads
+    tcgen05_before_sync();     // this thread's S reads before the next MMA overwrites S
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      tcgen05_after_sync();
+      const int stage = jt % kUmmaStages;
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {   // O tile = P V over the 64 keys in four K = 16 steps
+        const uint64_t da = umma_desc(smem_u32(&sm.k[stage][0][0]) + ks * 32, 16, 1024);
+        const uint64_t db = umma_desc(smem_u32(&sm.v[stage][0][0]) + ks * 2048, 8192, 1024);
+        umma_issue(tmem + 64, da, db, kIdescPV, ks > 0);
+      }
+      umma_commit(smem_u32(&sm.o_ready));
+      if (jt + 1 < kv_tiles) {           // the next stage's scores run behind it
+        if (mbar_wait(smem_u32(&sm.full[(jt + 1) % kUmmaStages]), ((jt + 1) / kUmmaStages) & 1)) {
+          tcgen05_after_sync();
+          issue_qk(jt + 1);
+        } else {
+          failed = true;
+        }
+      }
+    }
+    if (!mbar_wait(smem_u32(&sm.o_ready), parity)) { failed = true; break; }
+    tcgen05_after_sync();
+    if (warp == 0 && jt + kUmmaStages < kv_tiles) issue_copies(jt + kUmmaStages);   // K / V of this stage are consumed
+    // ---- fold the P V tile into the row ----
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r[32];
+      tmem_load32(tmem_row + 64 + c * 32, r);
+      tmem_load_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) o[c * 32 + j] += __uint_as_float(r[j]);
+    }
+    tcgen05_before_sync();
+  }
+  failed = __any_sync(0xffffffffu, failed);
+  if (failed && lane == 0) atomicOr(error, 1u);
+  if (!failed && row < tile.count) {
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(a.out) + q_offset);
+#pragma unroll
+    for (int c = 0; c < 16; ++c)
+      dst[c] = make_uint4(pack2<kBF16>(o[c * 8] * inv, o[c * 8 + 1] * inv), pack2<kBF16>(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
+                          pack2<kBF16>(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack2<kBF16>(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
+  }
+  tcgen05_before_sync();
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
+}
+
 size_t tile_capacity(int rows, int seqs) { return static_cast<size_t>(rows) / kTileRows + static_cast<size_t>(seqs) + 1; }
 
 }  // namespace
@@ -322,7 +568,8 @@ size_t prefill_sm100_workspace_bytes(int rows, int seqs) {
   return 256 + sizeof(PrefillTile) * tile_capacity(rows, seqs);
 }
 
-// RLT_ERR_UNSUPPORTED when the two caches cannot share one tensor map (the caller then scores
+// The tcgen05 kernel by default; RLT_PREFILL_KERNEL=mma selects the mma.sync kernel.
+// RLT_ERR_UNSUPPORTED when no tiled prefill kernel can address the caches (the caller then scores
 // the rows with the verify kernel).
 int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   if (workspace == nullptr || workspace_bytes < prefill_sm100_workspace_bytes(a.rows, a.table_rows) ||
@@ -330,16 +577,38 @@ int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspa
     set_last_error_text("prefill_attention: workspace missing, misaligned or too small");
     return RLT_ERR_WORKSPACE;
   }
+  static const bool use_mma_sync = [] {
+    const char* e = getenv("RLT_PREFILL_KERNEL");
+    return e != nullptr && e[0] == 'm';
+  }();
+  PrefillHeader* header = static_cast<PrefillHeader*>(workspace);
+  PrefillTile* tiles = reinterpret_cast<PrefillTile*>(static_cast<unsigned char*>(workspace) + 256);
+  const float scale_log2 = static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(kHeadDim)));
+  CUtensorMap k_map, v_map;
+  if (!use_mma_sync && make_page_map(&k_map, a.key_cache, a) == RLT_OK && make_page_map(&v_map, a.value_cache, a) == RLT_OK) {
+    prefill_plan_kernel<<<1, kPrefillPlanThreads, 0, stream>>>(a.cu_seqlens_q, a.table_rows, kUmmaRows, header, tiles);
+    int status = launch_status("prefill_plan_kernel");
+    if (status != RLT_OK) return status;
+    const size_t smem = sizeof(UmmaShared) + 1024;
+    const dim3 grid(static_cast<unsigned>(tile_capacity(a.rows, a.table_rows)), static_cast<unsigned>(a.q_heads));
+    if (a.dtype == RLT_BF16) {
+      auto kernel = prefill_umma_kernel<true>;
+      RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      kernel<<<grid, kUmmaRows, smem, stream>>>(k_map, v_map, a, header, tiles, &header->error, scale_log2);
+    } else {
+      auto kernel = prefill_umma_kernel<false>;
+      RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      kernel<<<grid, kUmmaRows, smem, stream>>>(k_map, v_map, a, header, tiles, &header->error, scale_log2);
+    }
+    return launch_status("prefill_umma_kernel");
+  }
   CUtensorMap kv_map;
   bool k_first = true;
   if (make_joint_map(&kv_map, a, &k_first) != RLT_OK) return RLT_ERR_UNSUPPORTED;
-  PrefillHeader* header = static_cast<PrefillHeader*>(workspace);
-  PrefillTile* tiles = reinterpret_cast<PrefillTile*>(static_cast<unsigned char*>(workspace) + 256);
-  prefill_plan_kernel<<<1, kPrefillPlanThreads, 0, stream>>>(a.cu_seqlens_q, a.table_rows, header, tiles);
+  prefill_plan_kernel<<<1, kPrefillPlanThreads, 0, stream>>>(a.cu_seqlens_q, a.table_rows, kTileRows, header, tiles);
   int status = launch_status("prefill_plan_kernel");
   if (status != RLT_OK) return status;
   const size_t smem = sizeof(PrefillShared) + 1024;
-  const float scale_log2 = static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(kHeadDim)));
   const dim3 grid(static_cast<unsigned>(tile_capacity(a.rows, a.table_rows)), static_cast<unsigned>(a.q_heads));
   if (a.dtype == RLT_BF16) {
     auto kernel = prefill_attention_kernel<true>;
