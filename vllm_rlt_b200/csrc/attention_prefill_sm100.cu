@@ -318,9 +318,9 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap kv_map, AttentionAr
 // the MN-major B operand of O = P V.  One thread issues the MMAs: S (128 x 64, fp32) and the
 // stage's P V product (128 x 128, fp32) accumulate in tensor memory, tcgen05.commit signals an
 // mbarrier, and the 128 threads — one query row each, the row that is their TMEM lane — read S
-// with tcgen05.ld, run the online softmax without any shuffle, write P (bf16) over the stage's K
-// (16 KiB, dead once S is complete) for the second MMA and fold the P V tile into their 128 fp32
-// output registers.  97 KiB of shared memory and 256 TMEM columns per CTA: two CTAs per SM, so one
+// with tcgen05.ld, run the online softmax without any shuffle and write P (bf16) over the stage's K
+// (16 KiB, dead once S is complete) for the second MMA, which accumulates onto the output tile in
+// tensor memory; a row of that tile is rescaled in place only when its running maximum is raised.  97 KiB of shared memory and 256 TMEM columns per CTA: two CTAs per SM, so one
 // CTA's MMAs run under the other's softmax.  The QK^T MMA of the
 // next stage is issued right behind the P V MMA, so it runs while the rows are being folded.
 constexpr int kUmmaRows = 128;
@@ -361,6 +361,16 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&r)[32]) {
                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+               "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                 "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                 "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -455,16 +465,19 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     }
   }
 
-  float o[kHeadDim];
-#pragma unroll
-  for (int d = 0; d < kHeadDim; ++d) o[d] = 0.f;
+  // The output tile stays in tensor memory: every stage's P V product accumulates onto it.  A
+  // row's running maximum m is raised — and its TMEM row rescaled by 2^(m_old - m_new) — only
+  // when the stage's maximum exceeds it by more than 8 (log2 units): until then P is taken
+  // against the old m (values up to 2^8, exact in the fp32 sums), and l follows the same m.
+  constexpr float kRaise = 8.0f;
   float m = -INFINITY, l = 0.f;
 
   for (int jt = 0; jt < kv_tiles; ++jt) {
-    const uint32_t parity = jt & 1;
-    if (!mbar_wait(smem_u32(&sm.s_ready), parity)) { failed = true; break; }
+    if (!mbar_wait(smem_u32(&sm.s_ready), jt & 1)) { failed = true; break; }
     tcgen05_after_sync();
-    // ---- this row's 64 scores ----
+    // S(jt) is complete, and so is every MMA issued before it — the P V product of stage jt - 1:
+    // its K / V stage can take the copies of key tile jt + 1
+    if (warp == 0 && jt >= 1 && jt + 1 < kv_tiles) issue_copies(jt + 1);
     float s[kUmmaKeys];
     {
       uint32_t r0[32], r1[32];
@@ -482,11 +495,23 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       if (first_key + j >= len) s[j] = -INFINITY;
       mx = fmaxf(mx, s[j]);
     }
-    const float mn = fmaxf(m, mx * scale_log2);
-    const float mu = mn == -INFINITY ? 0.f : mn;
-    const float alpha = fast_exp2(m - mu);
-    const bool moved = mn != m;
-    m = mn;
+    const float candidate = mx * scale_log2;
+    const bool raise = candidate > m + kRaise || (m == -INFINITY && candidate > -INFINITY);
+    const float alpha = (raise && m != -INFINITY) ? fast_exp2(m - candidate) : 1.0f;
+    if (raise) m = candidate;
+    const float mu = m == -INFINITY ? 0.f : m;
+    if (jt > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {   // rescale this warp's 32 output rows in place
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_load32(tmem_row + 64 + c * 32, r);
+        tmem_load_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+        tmem_store32(tmem_row + 64 + c * 32, r);
+      }
+      tmem_store_wait();
+    }
     float sum = 0.f;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
@@ -501,23 +526,18 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       *reinterpret_cast<uint4*>(&p_tile[row * 128 + ((c ^ (row & 7)) << 4)]) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
     l = l * alpha + sum;
-    if (moved) {
-#pragma unroll
-      for (int d = 0; d < kHeadDim; ++d) o[d] *= alpha;
-    }
     fence_async_proxy();       // P (generic writes) before the MMA's reads
-    tcgen05_before_sync();     // this thread's S reads before the next MMA overwrites S
+    tcgen05_before_sync();     // this thread's TMEM reads and writes before the MMAs that follow the barrier
     __syncthreads();
     if (threadIdx.x == 0) {
       tcgen05_after_sync();
       const int stage = jt % kUmmaStages;
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {   // O tile = P V over the 64 keys in four K = 16 steps
+      for (int ks = 0; ks < 4; ++ks) {   // O += P V over the 64 keys in four K = 16 steps
         const uint64_t da = umma_desc(smem_u32(&sm.k[stage][0][0]) + ks * 32, 16, 1024);
         const uint64_t db = umma_desc(smem_u32(&sm.v[stage][0][0]) + ks * 2048, 8192, 1024);
-        umma_issue(tmem + 64, da, db, kIdescPV, ks > 0);
+        umma_issue(tmem + 64, da, db, kIdescPV, (jt > 0 || ks > 0) ? 1u : 0u);
       }
-      umma_commit(smem_u32(&sm.o_ready));
       if (jt + 1 < kv_tiles) {           // the next stage's scores run behind it
         if (mbar_wait(smem_u32(&sm.full[(jt + 1) % kUmmaStages]), ((jt + 1) / kUmmaStages) & 1)) {
           tcgen05_after_sync();
@@ -525,31 +545,37 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         } else {
           failed = true;
         }
+      } else {
+        umma_commit(smem_u32(&sm.o_ready));   // the last product: the output tile is complete
       }
     }
-    if (!mbar_wait(smem_u32(&sm.o_ready), parity)) { failed = true; break; }
-    tcgen05_after_sync();
-    if (warp == 0 && jt + kUmmaStages < kv_tiles) issue_copies(jt + kUmmaStages);   // K / V of this stage are consumed
-    // ---- fold the P V tile into the row ----
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r[32];
-      tmem_load32(tmem_row + 64 + c * 32, r);
-      tmem_load_wait();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) o[c * 32 + j] += __uint_as_float(r[j]);
-    }
-    tcgen05_before_sync();
   }
+  if (!failed && kv_tiles > 0 && !mbar_wait(smem_u32(&sm.o_ready), 0)) failed = true;
+  tcgen05_after_sync();
   failed = __any_sync(0xffffffffu, failed);
   if (failed && lane == 0) atomicOr(error, 1u);
-  if (!failed && row < tile.count) {
+  if (!failed) {
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(a.out) + q_offset);
 #pragma unroll
-    for (int c = 0; c < 16; ++c)
-      dst[c] = make_uint4(pack2<kBF16>(o[c * 8] * inv, o[c * 8 + 1] * inv), pack2<kBF16>(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
-                          pack2<kBF16>(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack2<kBF16>(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r[32];
+      if (kv_tiles > 0) {
+        tmem_load32(tmem_row + 64 + c * 32, r);
+        tmem_load_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = 0u;
+      }
+      if (row < tile.count) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const float* f = reinterpret_cast<const float*>(&r[q4 * 8]);
+          dst[c * 4 + q4] = make_uint4(pack2<kBF16>(f[0] * inv, f[1] * inv), pack2<kBF16>(f[2] * inv, f[3] * inv),
+                                       pack2<kBF16>(f[4] * inv, f[5] * inv), pack2<kBF16>(f[6] * inv, f[7] * inv));
+        }
+      }
+    }
   }
   tcgen05_before_sync();
   __syncthreads();
