@@ -312,28 +312,35 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap kv_map, AttentionAr
 }
 
 // ---- the same tile on the 5th-generation tensor cores (tcgen05 / TMEM) ----------------------
-// 128 query tokens of one query head per CTA, 64 keys per stage.  Q sits in shared memory as two
-// K-major 64-dim halves, every K / V page lands as four 2 KiB TMA copies so that a stage holds
-// K as [half][64 keys][64 dims] (K-major B operand of S = Q K^T) and V in the same shape, which is
-// the MN-major B operand of O = P V.  One thread issues the MMAs: S (128 x 64, fp32) and the
-// stage's P V product (128 x 128, fp32) accumulate in tensor memory, tcgen05.commit signals an
-// mbarrier, and the 128 threads — one query row each, the row that is their TMEM lane — read S
-// with tcgen05.ld, run the online softmax without any shuffle and write P (bf16) over the stage's K
-// (16 KiB, dead once S is complete) for the second MMA, which accumulates onto the output tile in
-// tensor memory; a row of that tile is rescaled in place only when its running maximum is raised.  97 KiB of shared memory and 256 TMEM columns per CTA: two CTAs per SM, so one
-// CTA's MMAs run under the other's softmax.  The QK^T MMA of the
-// next stage is issued right behind the P V MMA, so it runs while the rows are being folded.
+// 128 query tokens of one query head per CTA, 64 keys per stage, five warps.  Q sits in shared
+// memory as two K-major 64-dim halves; every K / V page lands as four 2 KiB TMA copies so that a
+// stage holds K as [half][64 keys][64 dims] (K-major B operand of S = Q K^T) and V in the same
+// shape, which is the MN-major B operand of O += P V.
+//   warp 4       issues the copies and, from one thread, every MMA.  Scores are double-buffered
+//                in tensor memory (columns 0..63 and 64..127) and the output tile accumulates in
+//                columns 128..255.  In steady state it waits for P(j), issues O += P(j) V(j) and
+//                right behind it S(j + 2) = Q K(j + 2)^T into the buffer P(j) is read from.
+//   warps 0..3   one query row per thread (the row that is its TMEM lane): tcgen05.ld of S(j),
+//                online softmax without any shuffle, P(j) as packed bf16 pairs stored with
+//                tcgen05.st over the first 32 columns of the same buffer — the A operand of the
+//                P V MMA is read from tensor memory — then an arrival on the buffer's barrier.
+//                S(j + 1) is complete by then, so these warps never wait for an MMA in steady
+//                state.  A row of the output tile is rescaled in place only when its running
+//                maximum is raised, after the previous P V product has been committed.
+// 97 KiB of shared memory and 256 TMEM columns per CTA: two CTAs per SM.
 constexpr int kUmmaRows = 128;
+constexpr int kUmmaThreads = 160;
 constexpr int kUmmaKeys = 64;
 constexpr int kUmmaStages = 2;
-constexpr uint32_t kTmemColumns = 256;   // S: columns 0..63, P V tile: 64..191
+constexpr uint32_t kTmemColumns = 256;
+constexpr uint32_t kTmemOut = 128;       // first column of the output tile
 
 struct __align__(1024) UmmaShared {
   unsigned char q[2][kUmmaRows * 128];                   // [half][row][64 dims], 128-byte swizzle
   unsigned char k[kUmmaStages][2][kUmmaKeys * 128];      // [half][key][64 dims]
   unsigned char v[kUmmaStages][2][kUmmaKeys * 128];      // [half][key][64 dims]
-  unsigned long long full[kUmmaStages];
-  unsigned long long s_ready, o_ready;
+  unsigned long long full_k[kUmmaStages], full_v[kUmmaStages];
+  unsigned long long s_ready[2], p_ready[2], pv_done[2];
   uint32_t tmem_base;
 };
 
@@ -376,8 +383,15 @@ __device__ __forceinline__ void tcgen05_before_sync() { asm volatile("tcgen05.fe
 __device__ __forceinline__ void tcgen05_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// D[tmem] (+)= A[tmem] * B[smem]: A as packed 16-bit pairs, one row per lane.
+__device__ __forceinline__ void umma_issue_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+
 template <bool kBF16>
-__global__ void __launch_bounds__(kUmmaRows)
+__global__ void __launch_bounds__(kUmmaThreads, 2)
 prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                     AttentionArgs a, const PrefillHeader* header, const PrefillTile* tiles, unsigned* error,
                     float scale_log2) {
@@ -385,13 +399,14 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   if (blockIdx.x >= header->tiles) return;
   extern __shared__ unsigned char smem_raw[];
   UmmaShared& sm = *reinterpret_cast<UmmaShared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, row = threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, row = threadIdx.x & (kUmmaRows - 1);
+  const bool issuer = warp == 4;
   const PrefillTile tile = tiles[blockIdx.x];
   const int q_head = blockIdx.y, kv_head = q_head / (a.q_heads / a.kv_heads);
   const int seq_first = a.cu_seqlens_q[tile.seq];
   const int n_new = a.cu_seqlens_q[tile.seq + 1] - seq_first;
   const int base_len = a.context_lengths[tile.seq] - n_new + 1;
-  const int len = row < tile.count ? max(base_len + tile.first + row, 0) : 0;   // keys this thread's row sees
+  const int len = (!issuer && row < tile.count) ? max(base_len + tile.first + row, 0) : 0;   // keys this thread's row sees
   const int kv_end = max(base_len + tile.first + tile.count - 1, 0);
   const int total_pages = (kv_end + kPage - 1) / kPage;
   const int kv_tiles = (total_pages + 3) / 4;
@@ -400,24 +415,30 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   // ---- prologue: barriers, tensor memory, Q into its swizzled halves, V stages zeroed (a partial
   // last stage multiplies P = 0 with whatever lies behind its last page: that must be finite) ----
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kUmmaStages; ++s) mbar_init(smem_u32(&sm.full[s]), 1);
-    mbar_init(smem_u32(&sm.s_ready), 1);
-    mbar_init(smem_u32(&sm.o_ready), 1);
+    for (int s = 0; s < kUmmaStages; ++s) {
+      mbar_init(smem_u32(&sm.full_k[s]), 1);
+      mbar_init(smem_u32(&sm.full_v[s]), 1);
+      mbar_init(smem_u32(&sm.s_ready[s]), 1);
+      mbar_init(smem_u32(&sm.p_ready[s]), kUmmaRows);
+      mbar_init(smem_u32(&sm.pv_done[s]), 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 0) {
+  if (issuer) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemColumns) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   {
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     uint4* vz = reinterpret_cast<uint4*>(&sm.v[0][0][0]);
-    for (int i = threadIdx.x; i < static_cast<int>(sizeof(sm.v) / 16); i += kUmmaRows) vz[i] = zero;
-    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(a.q) + q_offset);
+    for (int i = threadIdx.x; i < static_cast<int>(sizeof(sm.v) / 16); i += kUmmaThreads) vz[i] = zero;
+    if (!issuer) {
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(a.q) + q_offset);
 #pragma unroll
-    for (int c = 0; c < 16; ++c) {
-      const uint4 value = len > 0 ? __ldg(src + c) : zero;
-      *reinterpret_cast<uint4*>(&sm.q[c >> 3][row * 128 + (((c & 7) ^ (row & 7)) << 4)]) = value;
+      for (int c = 0; c < 16; ++c) {
+        const uint4 value = len > 0 ? __ldg(src + c) : zero;
+        *reinterpret_cast<uint4*>(&sm.q[c >> 3][row * 128 + (((c & 7) ^ (row & 7)) << 4)]) = value;
+      }
     }
   }
   fence_async_proxy();
@@ -425,161 +446,173 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   __syncthreads();
   tcgen05_after_sync();
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t tmem_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-  const uint64_t policy = policy_evict_first();
-  const int32_t* table = a.block_tables + static_cast<int64_t>(tile.seq) * a.table_width;
   constexpr uint32_t kFormat = kBF16 ? 1u : 0u;
   constexpr uint32_t kIdesc = (1u << 4) | (kFormat << 7) | (kFormat << 10) | (static_cast<uint32_t>(kUmmaRows >> 4) << 24);
   constexpr uint32_t kIdescQK = kIdesc | (static_cast<uint32_t>(kUmmaKeys >> 3) << 17);            // N = 64 keys
   constexpr uint32_t kIdescPV = kIdesc | (static_cast<uint32_t>(kHeadDim >> 3) << 17) | (1u << 16);  // N = 128 dims, B MN-major
-
-  // warp 0: the sixteen 2 KiB copies of key tile jt (4 pages x K lo, K hi, V lo, V hi), one per lane
-  auto issue_copies = [&](int jt) {
-    const int stage = jt % kUmmaStages;
-    const int pages = min(4, total_pages - jt * 4);
-    const uint32_t bar = smem_u32(&sm.full[stage]);
-    if (lane == 0) mbar_expect_tx(bar, pages * kStageBytes);
-    __syncwarp();
-    const int page = lane >> 2, part = lane & 3;
-    if (lane < 16 && page < pages) {
-      const int block = table[jt * 4 + page];
-      unsigned char* dst = (part < 2 ? &sm.k[stage][part & 1][0] : &sm.v[stage][part & 1][0]) + page * 2048;
-      tma_load_page_half(smem_u32(dst), part < 2 ? &k_map : &v_map, kv_head * kHeadDim + (part & 1) * 64, block, bar, policy);
-    }
-  };
-  auto issue_qk = [&](int jt) {   // thread 0: S = Q K^T over the 128 dims in eight K = 16 steps
-    const int stage = jt % kUmmaStages;
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      const uint64_t da = umma_desc(smem_u32(&sm.q[ks >> 2][0]) + (ks & 3) * 32, 16, 1024);
-      const uint64_t db = umma_desc(smem_u32(&sm.k[stage][ks >> 2][0]) + (ks & 3) * 32, 16, 1024);
-      umma_issue(tmem, da, db, kIdescQK, ks > 0);
-    }
-    umma_commit(smem_u32(&sm.s_ready));
-  };
   bool failed = false;
-  if (warp == 0) {
-    for (int jt = 0; jt < min(kUmmaStages, kv_tiles); ++jt) issue_copies(jt);
-    if (lane == 0 && kv_tiles > 0) {
-      if (mbar_wait(smem_u32(&sm.full[0]), 0)) { tcgen05_after_sync(); issue_qk(0); } else failed = true;
+
+  if (issuer) {
+    const uint64_t policy = policy_evict_first();
+    const int32_t* table = a.block_tables + static_cast<int64_t>(tile.seq) * a.table_width;
+    // the eight 2 KiB copies of one operand of key tile jt (4 pages x low / high half), one per lane
+    auto issue_copies = [&](int jt, bool keys) {
+      const int stage = jt % kUmmaStages;
+      const int pages = min(4, total_pages - jt * 4);
+      const uint32_t bar = smem_u32(keys ? &sm.full_k[stage] : &sm.full_v[stage]);
+      if (lane == 0) mbar_expect_tx(bar, pages * kTileBytes);
+      __syncwarp();
+      const int page = lane >> 1, half = lane & 1;
+      if (lane < 8 && page < pages) {
+        unsigned char* dst = (keys ? &sm.k[stage][half][0] : &sm.v[stage][half][0]) + page * 2048;
+        tma_load_page_half(smem_u32(dst), keys ? &k_map : &v_map, kv_head * kHeadDim + half * 64, table[jt * 4 + page], bar, policy);
+      }
+    };
+    // lane 0: S(jt) = Q K(jt)^T over the 128 dims in eight K = 16 steps, into score buffer jt & 1
+    auto issue_qk = [&](int jt) {
+      const int stage = jt % kUmmaStages;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t da = umma_desc(smem_u32(&sm.q[ks >> 2][0]) + (ks & 3) * 32, 16, 1024);
+        const uint64_t db = umma_desc(smem_u32(&sm.k[stage][ks >> 2][0]) + (ks & 3) * 32, 16, 1024);
+        umma_issue(tmem + (jt & 1) * kUmmaKeys, da, db, kIdescQK, ks > 0);
+      }
+      umma_commit(smem_u32(&sm.s_ready[jt & 1]));
+    };
+    // lane 0 waits, the warp learns the outcome
+    auto warp_wait = [&](unsigned long long* bar, int parity) {
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(smem_u32(bar), parity);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) failed = true;
+      return ok;
+    };
+    for (int jt = 0; jt < min(kUmmaStages, kv_tiles); ++jt) { issue_copies(jt, true); issue_copies(jt, false); }
+    for (int jt = 0; jt < min(2, kv_tiles) && !failed; ++jt) {
+      if (!warp_wait(&sm.full_k[jt], 0)) break;
+      if (lane == 0) { tcgen05_after_sync(); issue_qk(jt); }
     }
-  }
-
-  // The output tile stays in tensor memory: every stage's P V product accumulates onto it.  A
-  // row's running maximum m is raised — and its TMEM row rescaled by 2^(m_old - m_new) — only
-  // when the stage's maximum exceeds it by more than 8 (log2 units): until then P is taken
-  // against the old m (values up to 2^8, exact in the fp32 sums), and l follows the same m.
-  constexpr float kRaise = 8.0f;
-  float m = -INFINITY, l = 0.f;
-
-  for (int jt = 0; jt < kv_tiles; ++jt) {
-    if (!mbar_wait(smem_u32(&sm.s_ready), jt & 1)) { failed = true; break; }
+    for (int jt = 0; jt < kv_tiles && !failed; ++jt) {
+      const int b = jt & 1, phase = (jt >> 1) & 1;
+      if (jt + 2 < kv_tiles) {           // S(jt) is complete: its K stage takes key tile jt + 2
+        if (!warp_wait(&sm.s_ready[b], phase)) break;
+        issue_copies(jt + 2, true);
+      }
+      if (jt >= 1 && jt + 1 < kv_tiles) {   // P(jt - 1) V(jt - 1) is complete: its V stage takes key tile jt + 1
+        if (!warp_wait(&sm.pv_done[b ^ 1], ((jt - 1) >> 1) & 1)) break;
+        issue_copies(jt + 1, false);
+      }
+      if (!warp_wait(&sm.p_ready[b], phase)) break;
+      if (!warp_wait(&sm.full_v[b], phase)) break;
+      if (lane == 0) {
+        tcgen05_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {   // O += P V over the 64 keys in four K = 16 steps
+          const uint64_t db = umma_desc(smem_u32(&sm.v[b][0][0]) + ks * 2048, 8192, 1024);
+          umma_issue_ts(tmem + kTmemOut, tmem + b * kUmmaKeys + ks * 8, db, kIdescPV, (jt > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sm.pv_done[b]));
+      }
+      if (jt + 2 < kv_tiles) {           // the scores of key tile jt + 2 follow into the buffer P(jt) was read from
+        if (!warp_wait(&sm.full_k[b], ((jt + 2) >> 1) & 1)) break;
+        if (lane == 0) { tcgen05_after_sync(); issue_qk(jt + 2); }
+      }
+    }
+  } else {
+    const uint32_t tmem_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    // The output tile stays in tensor memory.  A row's running maximum m is raised — and its TMEM
+    // row rescaled by 2^(m_old - m_new) — only when the stage's maximum exceeds it by more than 8
+    // (log2 units): until then P is taken against the old m (values up to 2^8, exact in the fp32
+    // sums), and l follows the same m.
+    constexpr float kRaise = 8.0f;
+    float m = -INFINITY, l = 0.f;
+    for (int jt = 0; jt < kv_tiles; ++jt) {
+      const int b = jt & 1, phase = (jt >> 1) & 1;
+      if (!mbar_wait(smem_u32(&sm.s_ready[b]), phase)) { failed = true; break; }
+      tcgen05_after_sync();
+      float s[kUmmaKeys];
+      {
+        uint32_t r0[32], r1[32];
+        tmem_load32(tmem_row + b * kUmmaKeys, r0);
+        tmem_load32(tmem_row + b * kUmmaKeys + 32, r1);
+        tmem_load_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { s[j] = __uint_as_float(r0[j]); s[32 + j] = __uint_as_float(r1[j]); }
+      }
+      const int first_key = jt * kUmmaKeys;
+      if (first_key + kUmmaKeys > len) {
+#pragma unroll
+        for (int j = 0; j < kUmmaKeys; ++j)
+          if (first_key + j >= len) s[j] = -INFINITY;
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < kUmmaKeys; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const float candidate = mx * scale_log2;
+      const bool raise = candidate > m + kRaise || (m == -INFINITY && candidate > -INFINITY);
+      const float alpha = (raise && m != -INFINITY) ? fast_exp2(m - candidate) : 1.0f;
+      if (raise) m = candidate;
+      const float mu = m == -INFINITY ? 0.f : m;
+      if (jt > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {   // rescale this warp's 32 output rows in place
+        if (!mbar_wait(smem_u32(&sm.pv_done[b ^ 1]), ((jt - 1) >> 1) & 1)) { failed = true; break; }
+        tcgen05_after_sync();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_load32(tmem_row + kTmemOut + c * 32, r);
+          tmem_load_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+          tmem_store32(tmem_row + kTmemOut + c * 32, r);
+        }
+      }
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[32];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const float p0 = fast_exp2(fmaf(s[2 * e], scale_log2, -mu));
+        const float p1 = fast_exp2(fmaf(s[2 * e + 1], scale_log2, -mu));
+        sum4[e & 3] += p0 + p1;
+        packed[e] = pack2<kBF16>(p0, p1);
+      }
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      tmem_store32(tmem_row + b * kUmmaKeys, packed);   // P(jt) over the first half of S(jt)
+      tmem_store_wait();
+      tcgen05_before_sync();
+      mbar_arrive(smem_u32(&sm.p_ready[b]));
+    }
+    if (!failed && kv_tiles > 0 && !mbar_wait(smem_u32(&sm.pv_done[(kv_tiles - 1) & 1]), ((kv_tiles - 1) >> 1) & 1)) failed = true;
     tcgen05_after_sync();
-    // S(jt) is complete, and so is every MMA issued before it — the P V product of stage jt - 1:
-    // its K / V stage can take the copies of key tile jt + 1
-    if (warp == 0 && jt >= 1 && jt + 1 < kv_tiles) issue_copies(jt + 1);
-    float s[kUmmaKeys];
-    {
-      uint32_t r0[32], r1[32];
-      tmem_load32(tmem_row, r0);
-      tmem_load32(tmem_row + 32, r1);
-      tmem_load_wait();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) { s[j] = __uint_as_float(r0[j]); s[32 + j] = __uint_as_float(r1[j]); }
-    }
-    const int first_key = jt * kUmmaKeys;
-    unsigned char* p_tile = &sm.k[jt % kUmmaStages][0][0];   // S is complete: this stage's K is dead
-    float mx = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < kUmmaKeys; ++j) {
-      if (first_key + j >= len) s[j] = -INFINITY;
-      mx = fmaxf(mx, s[j]);
-    }
-    const float candidate = mx * scale_log2;
-    const bool raise = candidate > m + kRaise || (m == -INFINITY && candidate > -INFINITY);
-    const float alpha = (raise && m != -INFINITY) ? fast_exp2(m - candidate) : 1.0f;
-    if (raise) m = candidate;
-    const float mu = m == -INFINITY ? 0.f : m;
-    if (jt > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {   // rescale this warp's 32 output rows in place
+    failed = __any_sync(0xffffffffu, failed);
+    if (!failed) {
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(a.out) + q_offset);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
-        tmem_load32(tmem_row + 64 + c * 32, r);
-        tmem_load_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
-        tmem_store32(tmem_row + 64 + c * 32, r);
-      }
-      tmem_store_wait();
-    }
-    float sum = 0.f;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      uint32_t packed[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float p0 = fast_exp2(fmaf(s[c * 8 + 2 * e], scale_log2, -mu));
-        const float p1 = fast_exp2(fmaf(s[c * 8 + 2 * e + 1], scale_log2, -mu));
-        sum += p0 + p1;
-        packed[e] = pack2<kBF16>(p0, p1);
-      }
-      *reinterpret_cast<uint4*>(&p_tile[row * 128 + ((c ^ (row & 7)) << 4)]) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    }
-    l = l * alpha + sum;
-    fence_async_proxy();       // P (generic writes) before the MMA's reads
-    tcgen05_before_sync();     // this thread's TMEM reads and writes before the MMAs that follow the barrier
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      tcgen05_after_sync();
-      const int stage = jt % kUmmaStages;
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {   // O += P V over the 64 keys in four K = 16 steps
-        const uint64_t da = umma_desc(smem_u32(&sm.k[stage][0][0]) + ks * 32, 16, 1024);
-        const uint64_t db = umma_desc(smem_u32(&sm.v[stage][0][0]) + ks * 2048, 8192, 1024);
-        umma_issue(tmem + 64, da, db, kIdescPV, (jt > 0 || ks > 0) ? 1u : 0u);
-      }
-      if (jt + 1 < kv_tiles) {           // the next stage's scores run behind it
-        if (mbar_wait(smem_u32(&sm.full[(jt + 1) % kUmmaStages]), ((jt + 1) / kUmmaStages) & 1)) {
-          tcgen05_after_sync();
-          issue_qk(jt + 1);
+        if (kv_tiles > 0) {
+          tmem_load32(tmem_row + kTmemOut + c * 32, r);
+          tmem_load_wait();
         } else {
-          failed = true;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-      } else {
-        umma_commit(smem_u32(&sm.o_ready));   // the last product: the output tile is complete
+        if (row < tile.count) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const float* f = reinterpret_cast<const float*>(&r[q4 * 8]);
+            dst[c * 4 + q4] = make_uint4(pack2<kBF16>(f[0] * inv, f[1] * inv), pack2<kBF16>(f[2] * inv, f[3] * inv),
+                                         pack2<kBF16>(f[4] * inv, f[5] * inv), pack2<kBF16>(f[6] * inv, f[7] * inv));
+          }
+        }
       }
     }
   }
-  if (!failed && kv_tiles > 0 && !mbar_wait(smem_u32(&sm.o_ready), 0)) failed = true;
-  tcgen05_after_sync();
-  failed = __any_sync(0xffffffffu, failed);
   if (failed && lane == 0) atomicOr(error, 1u);
-  if (!failed) {
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
-    uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(a.out) + q_offset);
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r[32];
-      if (kv_tiles > 0) {
-        tmem_load32(tmem_row + 64 + c * 32, r);
-        tmem_load_wait();
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = 0u;
-      }
-      if (row < tile.count) {
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const float* f = reinterpret_cast<const float*>(&r[q4 * 8]);
-          dst[c * 4 + q4] = make_uint4(pack2<kBF16>(f[0] * inv, f[1] * inv), pack2<kBF16>(f[2] * inv, f[3] * inv),
-                                       pack2<kBF16>(f[4] * inv, f[5] * inv), pack2<kBF16>(f[6] * inv, f[7] * inv));
-        }
-      }
-    }
-  }
   tcgen05_before_sync();
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
+  if (issuer) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
 }
 
 size_t tile_capacity(int rows, int seqs) { return static_cast<size_t>(rows) / kTileRows + static_cast<size_t>(seqs) + 1; }
@@ -620,11 +653,11 @@ int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspa
     if (a.dtype == RLT_BF16) {
       auto kernel = prefill_umma_kernel<true>;
       RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-      kernel<<<grid, kUmmaRows, smem, stream>>>(k_map, v_map, a, header, tiles, &header->error, scale_log2);
+      kernel<<<grid, kUmmaThreads, smem, stream>>>(k_map, v_map, a, header, tiles, &header->error, scale_log2);
     } else {
       auto kernel = prefill_umma_kernel<false>;
       RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-      kernel<<<grid, kUmmaRows, smem, stream>>>(k_map, v_map, a, header, tiles, &header->error, scale_log2);
+      kernel<<<grid, kUmmaThreads, smem, stream>>>(k_map, v_map, a, header, tiles, &header->error, scale_log2);
     }
     return launch_status("prefill_umma_kernel");
   }
