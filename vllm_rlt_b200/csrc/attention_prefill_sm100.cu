@@ -615,6 +615,271 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   if (issuer) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
 }
 
+// ---- two query tiles per CTA: K / V stages shared, Q in tensor memory -------------------------
+// 256 query tokens of one query head per CTA (one CTA per SM, all 512 TMEM columns), ten warps:
+//   warps 0..3 / 4..7  the softmax rows of query tile 0 / 1 (row = TMEM lane),
+//   warp 8             one thread issues every MMA,
+//   warp 9             the TMA copies, kPairStages stages of 64 keys ahead.
+// Q never sits in shared memory: each thread stores its row (64 packed columns) with tcgen05.st,
+// and both MMAs of a tile take their A operand from tensor memory — S = Q K^T from the Q columns,
+// O += P V from P, stored over S.  Shared memory is then read only for K and V, once per query tile,
+// and every copied stage serves both tiles.  The tiles alternate: while the rows of one are in the
+// softmax, the tensor cores run the other's P V and next Q K^T.
+// TMEM columns: Q 0..63 | 64..127, S / P 128..191 | 192..255, O 256..383 | 384..511.
+constexpr int kPairRows = 2 * kUmmaRows;
+constexpr int kPairThreads = 320;
+constexpr int kPairStages = 5;
+constexpr uint32_t kPairTmemColumns = 512;
+
+struct __align__(1024) PairShared {
+  unsigned char k[kPairStages][2][kUmmaKeys * 128];      // [half][key][64 dims], 128-byte swizzle
+  unsigned char v[kPairStages][2][kUmmaKeys * 128];
+  unsigned long long full_k[kPairStages], full_v[kPairStages], free_k[kPairStages], free_v[kPairStages];
+  unsigned long long s_ready[2], p_ready[2], o_ready[2];
+  uint32_t tmem_base;
+};
+
+template <bool kBF16>
+__global__ void __launch_bounds__(kPairThreads, 1)
+prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                    AttentionArgs a, const PrefillHeader* header, const PrefillTile* tiles, unsigned* error,
+                    float scale_log2) {
+  using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
+  if (blockIdx.x >= header->tiles) return;
+  extern __shared__ unsigned char smem_raw[];
+  PairShared& sm = *reinterpret_cast<PairShared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const PrefillTile tile = tiles[blockIdx.x];
+  const int q_head = blockIdx.y, kv_head = q_head / (a.q_heads / a.kv_heads);
+  const int seq_first = a.cu_seqlens_q[tile.seq];
+  const int n_new = a.cu_seqlens_q[tile.seq + 1] - seq_first;
+  const int base_len = a.context_lengths[tile.seq] - n_new + 1;
+  // key stages of the two query tiles: tile 1 (the later rows) sees every stage tile 0 does
+  int stages[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int count = min(max(tile.count - t * kUmmaRows, 0), kUmmaRows);
+    const int kv_end = count > 0 ? max(base_len + tile.first + t * kUmmaRows + count - 1, 0) : 0;
+    stages[t] = (kv_end + kUmmaKeys - 1) / kUmmaKeys;
+  }
+  const int all_stages = max(stages[0], stages[1]);
+  const int total_pages = (max(base_len + tile.first + tile.count - 1, 0) + kPage - 1) / kPage;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(smem_u32(&sm.full_k[s]), 1);
+      mbar_init(smem_u32(&sm.full_v[s]), 1);
+      mbar_init(smem_u32(&sm.free_k[s]), 1);
+      mbar_init(smem_u32(&sm.free_v[s]), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&sm.s_ready[t]), 1);
+      mbar_init(smem_u32(&sm.p_ready[t]), kUmmaRows);
+      mbar_init(smem_u32(&sm.o_ready[t]), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 8) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kPairTmemColumns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  {  // V stages zeroed: a partial last stage multiplies P = 0 with what lies behind its last page
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    uint4* vz = reinterpret_cast<uint4*>(&sm.v[0][0][0]);
+    for (int i = threadIdx.x; i < static_cast<int>(sizeof(sm.v) / 16); i += kPairThreads) vz[i] = zero;
+  }
+  fence_async_proxy();
+  tcgen05_before_sync();
+  __syncthreads();
+  tcgen05_after_sync();
+  const uint32_t tmem = sm.tmem_base;
+  constexpr uint32_t kFormat = kBF16 ? 1u : 0u;
+  constexpr uint32_t kIdesc = (1u << 4) | (kFormat << 7) | (kFormat << 10) | (static_cast<uint32_t>(kUmmaRows >> 4) << 24);
+  constexpr uint32_t kIdescQK = kIdesc | (static_cast<uint32_t>(kUmmaKeys >> 3) << 17);            // N = 64 keys
+  constexpr uint32_t kIdescPV = kIdesc | (static_cast<uint32_t>(kHeadDim >> 3) << 17) | (1u << 16);  // N = 128 dims, B MN-major
+  constexpr uint32_t kColQ = 0, kColS = 128, kColO = 256;
+  bool failed = false;
+
+  if (warp == 9) {
+    // ---- copies: stage j takes key tile j once both of its operands' readers have committed ----
+    const uint64_t policy = policy_evict_first();
+    const int32_t* table = a.block_tables + static_cast<int64_t>(tile.seq) * a.table_width;
+    for (int j = 0; j < all_stages && !failed; ++j) {
+      const int stage = j % kPairStages, use = j / kPairStages;
+      const int pages = min(4, total_pages - j * 4);
+      const int page = (lane & 7) >> 1, half = lane & 1;
+      const int block = (lane < 8 && page < pages) ? table[j * 4 + page] : 0;
+#pragma unroll
+      for (int operand = 0; operand < 2; ++operand) {
+        bool ok = true;
+        if (lane == 0 && use > 0) ok = mbar_wait(smem_u32(operand == 0 ? &sm.free_k[stage] : &sm.free_v[stage]), (use - 1) & 1);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { failed = true; break; }
+        const uint32_t bar = smem_u32(operand == 0 ? &sm.full_k[stage] : &sm.full_v[stage]);
+        if (lane == 0) mbar_expect_tx(bar, pages * kTileBytes);
+        __syncwarp();
+        if (lane < 8 && page < pages) {
+          unsigned char* dst = (operand == 0 ? &sm.k[stage][half][0] : &sm.v[stage][half][0]) + page * 2048;
+          tma_load_page_half(smem_u32(dst), operand == 0 ? &k_map : &v_map, kv_head * kHeadDim + half * 64, block, bar, policy);
+        }
+      }
+    }
+  } else if (warp == 8) {
+    // ---- MMA issue: every softmax warp has stored its Q rows once p_ready completes phase 0 ... the
+    // first arrival on p_ready[t] announces Q, later ones P ----
+    if (lane == 0) {
+      auto issue_qk = [&](int t, int j) {   // S_t(j) = Q_t K(j)^T, eight K = 16 steps
+        const int stage = j % kPairStages;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t db = umma_desc(smem_u32(&sm.k[stage][ks >> 2][0]) + (ks & 3) * 32, 16, 1024);
+          umma_issue_ts(tmem + kColS + t * kUmmaKeys, tmem + kColQ + t * 64 + ks * 8, db, kIdescQK, ks > 0);
+        }
+        umma_commit(smem_u32(&sm.s_ready[t]));
+        if (t == (j < stages[1] ? 1 : 0)) umma_commit(smem_u32(&sm.free_k[stage]));   // the stage's last reader
+      };
+      for (int t = 0; t < 2 && !failed; ++t) {
+        if (stages[t] == 0) continue;
+        if (!mbar_wait(smem_u32(&sm.p_ready[t]), 0) || !mbar_wait(smem_u32(&sm.full_k[0]), 0)) { failed = true; break; }
+        tcgen05_after_sync();
+        issue_qk(t, 0);
+      }
+      for (int j = 0; j < all_stages && !failed; ++j) {
+        const int stage = j % kPairStages, use = j / kPairStages;
+        for (int t = 0; t < 2; ++t) {
+          if (j >= stages[t]) continue;
+          if (!mbar_wait(smem_u32(&sm.p_ready[t]), (j + 1) & 1) || !mbar_wait(smem_u32(&sm.full_v[stage]), use & 1)) { failed = true; break; }
+          tcgen05_after_sync();
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {   // O_t += P_t V over the 64 keys in four K = 16 steps
+            const uint64_t db = umma_desc(smem_u32(&sm.v[stage][0][0]) + ks * 2048, 8192, 1024);
+            umma_issue_ts(tmem + kColO + t * kHeadDim, tmem + kColS + t * kUmmaKeys + ks * 8, db, kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
+          }
+          if (t == (j < stages[1] ? 1 : 0)) umma_commit(smem_u32(&sm.free_v[stage]));
+          if (j + 1 < stages[t]) {
+            if (!mbar_wait(smem_u32(&sm.full_k[(j + 1) % kPairStages]), ((j + 1) / kPairStages) & 1)) { failed = true; break; }
+            tcgen05_after_sync();
+            issue_qk(t, j + 1);
+          } else {
+            umma_commit(smem_u32(&sm.o_ready[t]));
+          }
+        }
+      }
+    }
+    failed = __shfl_sync(0xffffffffu, failed, 0);
+  } else {
+    // ---- softmax rows ----
+    const int t = warp >> 2, row = threadIdx.x & (kUmmaRows - 1);
+    const int count = min(max(tile.count - t * kUmmaRows, 0), kUmmaRows);
+    const int len = row < count ? max(base_len + tile.first + t * kUmmaRows + row, 0) : 0;
+    const int my_stages = stages[t];
+    const int64_t q_offset = ((static_cast<int64_t>(seq_first) + tile.first + t * kUmmaRows + row) * a.q_heads + q_head) * kHeadDim;
+    const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    if (my_stages > 0) {   // this row of Q into tensor memory: 128 16-bit values, two per column
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(a.q) + q_offset);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 value = len > 0 ? __ldg(src + h * 8 + c) : make_uint4(0u, 0u, 0u, 0u);
+          r[c * 4] = value.x; r[c * 4 + 1] = value.y; r[c * 4 + 2] = value.z; r[c * 4 + 3] = value.w;
+        }
+        tmem_store32(tmem_row + kColQ + t * 64 + h * 32, r);
+      }
+      tmem_store_wait();
+      tcgen05_before_sync();
+      mbar_arrive(smem_u32(&sm.p_ready[t]));
+    }
+    constexpr float kRaise = 8.0f;
+    float m = -INFINITY, l = 0.f;
+    const uint32_t s_col = tmem_row + kColS + t * kUmmaKeys, o_col = tmem_row + kColO + t * kHeadDim;
+    for (int j = 0; j < my_stages; ++j) {
+      if (!mbar_wait(smem_u32(&sm.s_ready[t]), j & 1)) { failed = true; break; }
+      tcgen05_after_sync();
+      float s[kUmmaKeys];
+      {
+        uint32_t r0[32], r1[32];
+        tmem_load32(s_col, r0);
+        tmem_load32(s_col + 32, r1);
+        tmem_load_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r0[i]); s[32 + i] = __uint_as_float(r1[i]); }
+      }
+      const int first_key = j * kUmmaKeys;
+      if (first_key + kUmmaKeys > len) {
+#pragma unroll
+        for (int i = 0; i < kUmmaKeys; ++i)
+          if (first_key + i >= len) s[i] = -INFINITY;
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < kUmmaKeys; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
+      const float candidate = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      const bool raise = candidate > m + kRaise || (m == -INFINITY && candidate > -INFINITY);
+      const float alpha = (raise && m != -INFINITY) ? fast_exp2(m - candidate) : 1.0f;
+      if (raise) m = candidate;
+      const float mu = m == -INFINITY ? 0.f : m;
+      // S_t(j) complete means every earlier MMA is: the output tile is at rest until P(j) is announced
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_load32(o_col + c * 32, r);
+          tmem_load_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_store32(o_col + c * 32, r);
+        }
+      }
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[32];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const float p0 = fast_exp2(fmaf(s[2 * e], scale_log2, -mu));
+        const float p1 = fast_exp2(fmaf(s[2 * e + 1], scale_log2, -mu));
+        sum4[e & 3] += p0 + p1;
+        packed[e] = pack2<kBF16>(p0, p1);
+      }
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      tmem_store32(s_col, packed);   // P_t(j) over the first half of S_t(j)
+      tmem_store_wait();
+      tcgen05_before_sync();
+      mbar_arrive(smem_u32(&sm.p_ready[t]));
+    }
+    if (!failed && my_stages > 0 && !mbar_wait(smem_u32(&sm.o_ready[t]), 0)) failed = true;
+    tcgen05_after_sync();
+    failed = __any_sync(0xffffffffu, failed);
+    if (!failed && count > 0) {
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(a.out) + q_offset);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        if (my_stages > 0) {
+          tmem_load32(o_col + c * 32, r);
+          tmem_load_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (row < count) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const float* f = reinterpret_cast<const float*>(&r[q4 * 8]);
+            dst[c * 4 + q4] = make_uint4(pack2<kBF16>(f[0] * inv, f[1] * inv), pack2<kBF16>(f[2] * inv, f[3] * inv),
+                                         pack2<kBF16>(f[4] * inv, f[5] * inv), pack2<kBF16>(f[6] * inv, f[7] * inv));
+          }
+        }
+      }
+    }
+  }
+  if (failed && lane == 0) atomicOr(error, 1u);
+  tcgen05_before_sync();
+  __syncthreads();
+  if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kPairTmemColumns) : "memory");
+}
+
 size_t tile_capacity(int rows, int seqs) { return static_cast<size_t>(rows) / kTileRows + static_cast<size_t>(seqs) + 1; }
 
 }  // namespace
@@ -636,14 +901,33 @@ int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspa
     set_last_error_text("prefill_attention: workspace missing, misaligned or too small");
     return RLT_ERR_WORKSPACE;
   }
-  static const bool use_mma_sync = [] {
+  static const char kernel_choice = [] {
     const char* e = getenv("RLT_PREFILL_KERNEL");
-    return e != nullptr && e[0] == 'm';
+    return e != nullptr ? e[0] : 'p';
   }();
+  const bool use_mma_sync = kernel_choice == 'm';
   PrefillHeader* header = static_cast<PrefillHeader*>(workspace);
   PrefillTile* tiles = reinterpret_cast<PrefillTile*>(static_cast<unsigned char*>(workspace) + 256);
   const float scale_log2 = static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(kHeadDim)));
   CUtensorMap k_map, v_map;
+  if (kernel_choice == 'p' && make_page_map(&k_map, a.key_cache, a) == RLT_OK && make_page_map(&v_map, a.value_cache, a) == RLT_OK) {
+    prefill_plan_kernel<<<1, kPrefillPlanThreads, 0, stream>>>(a.cu_seqlens_q, a.table_rows, kPairRows, header, tiles);
+    int status = launch_status("prefill_plan_kernel");
+    if (status != RLT_OK) return status;
+    const size_t smem = sizeof(PairShared) + 1024;
+    const dim3 grid(static_cast<unsigned>(static_cast<size_t>(a.rows) / kPairRows + static_cast<size_t>(a.table_rows) + 1),
+                    static_cast<unsigned>(a.q_heads));
+    if (a.dtype == RLT_BF16) {
+      auto kernel = prefill_pair_kernel<true>;
+      RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      kernel<<<grid, kPairThreads, smem, stream>>>(k_map, v_map, a, header, tiles, &header->error, scale_log2);
+    } else {
+      auto kernel = prefill_pair_kernel<false>;
+      RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      kernel<<<grid, kPairThreads, smem, stream>>>(k_map, v_map, a, header, tiles, &header->error, scale_log2);
+    }
+    return launch_status("prefill_pair_kernel");
+  }
   if (!use_mma_sync && make_page_map(&k_map, a.key_cache, a) == RLT_OK && make_page_map(&v_map, a.value_cache, a) == RLT_OK) {
     prefill_plan_kernel<<<1, kPrefillPlanThreads, 0, stream>>>(a.cu_seqlens_q, a.table_rows, kUmmaRows, header, tiles);
     int status = launch_status("prefill_plan_kernel");
