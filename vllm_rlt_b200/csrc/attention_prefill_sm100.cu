@@ -615,27 +615,37 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   if (issuer) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
 }
 
-// ---- two query tiles per CTA: K / V stages shared, Q in tensor memory -------------------------
+// Non-blocking probe of a barrier phase (try_wait may suspend the thread for a while).
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+// ---- two query tiles per CTA: K / V stages shared, A operands in tensor memory -----------------
 // 256 query tokens of one query head per CTA (one CTA per SM, all 512 TMEM columns), ten warps:
 //   warps 0..3 / 4..7  the softmax rows of query tile 0 / 1 (row = TMEM lane),
-//   warp 8             one thread issues every MMA,
-//   warp 9             the TMA copies, kPairStages stages of 64 keys ahead.
-// Q never sits in shared memory: each thread stores its row (64 packed columns) with tcgen05.st,
-// and both MMAs of a tile take their A operand from tensor memory — S = Q K^T from the Q columns,
-// O += P V from P, stored over S.  Shared memory is then read only for K and V, once per query tile,
-// and every copied stage serves both tiles.  The tiles alternate: while the rows of one are in the
-// softmax, the tensor cores run the other's P V and next Q K^T.
-// TMEM columns: Q 0..63 | 64..127, S / P 128..191 | 192..255, O 256..383 | 384..511.
+//   warps 8, 9         one thread each issues the MMAs of tile 0 / 1, whichever is ready next,
+//   warp 10            the TMA copies, kPairStages stages of 64 keys ahead.
+// Per tile the scores S (64 columns) and the probabilities P (32 columns of packed 16-bit pairs)
+// have separate TMEM columns, so S(j + 1) = Q K(j + 1)^T is issued as soon as the rows have read
+// S(j) into registers, runs under their softmax, and O += P(j) V(j) follows when P(j) is stored:
+// in steady state neither the rows nor the tensor cores wait for each other.  P is always a TMEM
+// operand; Q of tile 0 is one too (each thread stores its row with tcgen05.st), Q of tile 1 sits in
+// shared memory (the 512 columns are used up).  Every copied stage serves both tiles.
+// TMEM columns: Q0 0..63 | S0 64..127, P0 128..159 | S1 160..223, P1 224..255 | O0 256..383 | O1 384..511.
 constexpr int kPairRows = 2 * kUmmaRows;
-constexpr int kPairThreads = 320;
+constexpr int kPairThreads = 352;
 constexpr int kPairStages = 5;
 constexpr uint32_t kPairTmemColumns = 512;
 
 struct __align__(1024) PairShared {
-  unsigned char k[kPairStages][2][kUmmaKeys * 128];      // [half][key][64 dims], 128-byte swizzle
+  unsigned char q[2][kUmmaRows * 128];                   // tile 1: [half][row][64 dims], 128-byte swizzle
+  unsigned char k[kPairStages][2][kUmmaKeys * 128];      // [half][key][64 dims]
   unsigned char v[kPairStages][2][kUmmaKeys * 128];
   unsigned long long full_k[kPairStages], full_v[kPairStages], free_k[kPairStages], free_v[kPairStages];
-  unsigned long long s_ready[2], p_ready[2], o_ready[2];
+  unsigned long long s_ready[2], s_free[2], p_ready[2], pv_done[2];
   uint32_t tmem_base;
 };
 
@@ -655,27 +665,24 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   const int n_new = a.cu_seqlens_q[tile.seq + 1] - seq_first;
   const int base_len = a.context_lengths[tile.seq] - n_new + 1;
   // key stages of the two query tiles: tile 1 (the later rows) sees every stage tile 0 does
-  int stages[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int count = min(max(tile.count - t * kUmmaRows, 0), kUmmaRows);
-    const int kv_end = count > 0 ? max(base_len + tile.first + t * kUmmaRows + count - 1, 0) : 0;
-    stages[t] = (kv_end + kUmmaKeys - 1) / kUmmaKeys;
-  }
-  const int all_stages = max(stages[0], stages[1]);
+  const int count0 = min(tile.count, kUmmaRows), count1 = max(tile.count - kUmmaRows, 0);
+  const int stages0 = (max(base_len + tile.first + count0 - 1, 0) + kUmmaKeys - 1) / kUmmaKeys;
+  const int stages1 = count1 > 0 ? (max(base_len + tile.first + kUmmaRows + count1 - 1, 0) + kUmmaKeys - 1) / kUmmaKeys : 0;
+  const int all_stages = max(stages0, stages1);
   const int total_pages = (max(base_len + tile.first + tile.count - 1, 0) + kPage - 1) / kPage;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
       mbar_init(smem_u32(&sm.full_k[s]), 1);
       mbar_init(smem_u32(&sm.full_v[s]), 1);
-      mbar_init(smem_u32(&sm.free_k[s]), 1);
-      mbar_init(smem_u32(&sm.free_v[s]), 1);
+      mbar_init(smem_u32(&sm.free_k[s]), 2);   // one arrival per query tile
+      mbar_init(smem_u32(&sm.free_v[s]), 2);
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(smem_u32(&sm.s_ready[t]), 1);
+      mbar_init(smem_u32(&sm.s_free[t]), kUmmaRows);
       mbar_init(smem_u32(&sm.p_ready[t]), kUmmaRows);
-      mbar_init(smem_u32(&sm.o_ready[t]), 1);
+      mbar_init(smem_u32(&sm.pv_done[t]), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -697,10 +704,10 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   constexpr uint32_t kIdesc = (1u << 4) | (kFormat << 7) | (kFormat << 10) | (static_cast<uint32_t>(kUmmaRows >> 4) << 24);
   constexpr uint32_t kIdescQK = kIdesc | (static_cast<uint32_t>(kUmmaKeys >> 3) << 17);            // N = 64 keys
   constexpr uint32_t kIdescPV = kIdesc | (static_cast<uint32_t>(kHeadDim >> 3) << 17) | (1u << 16);  // N = 128 dims, B MN-major
-  constexpr uint32_t kColQ = 0, kColS = 128, kColO = 256;
+  constexpr uint32_t kColQ = 0, kColS = 64, kTileCols = 96, kColP = 64, kColO = 256;   // P: offset inside a tile's S / P block
   bool failed = false;
 
-  if (warp == 9) {
+  if (warp == 10) {
     // ---- copies: stage j takes key tile j once both of its operands' readers have committed ----
     const uint64_t policy = policy_evict_first();
     const int32_t* table = a.block_tables + static_cast<int64_t>(tile.seq) * a.table_width;
@@ -724,45 +731,64 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         }
       }
     }
-  } else if (warp == 8) {
-    // ---- MMA issue: every softmax warp has stored its Q rows once p_ready completes phase 0 ... the
-    // first arrival on p_ready[t] announces Q, later ones P ----
+  } else if (warp >= 8) {
+    // ---- MMA issue, one thread per query tile (warp 8: tile 0, warp 9: tile 1).  Two streams of
+    // work, each gated by the rows' barrier and a copy:
+    //   S(j):  Q announced (first phase of p_ready) for j = 0, else S(j - 1) read (s_free) — and K(j)
+    //   O(j):  P(j) stored (p_ready) — and V(j)
+    // The thread polls the gates and issues what is ready.  A stage is released to the copy warp
+    // by the commits of both tiles' threads; for a tile that does not read the stage the other
+    // tile's thread arrives by hand. ----
     if (lane == 0) {
-      auto issue_qk = [&](int t, int j) {   // S_t(j) = Q_t K(j)^T, eight K = 16 steps
-        const int stage = j % kPairStages;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t db = umma_desc(smem_u32(&sm.k[stage][ks >> 2][0]) + (ks & 3) * 32, 16, 1024);
-          umma_issue_ts(tmem + kColS + t * kUmmaKeys, tmem + kColQ + t * 64 + ks * 8, db, kIdescQK, ks > 0);
-        }
-        umma_commit(smem_u32(&sm.s_ready[t]));
-        if (t == (j < stages[1] ? 1 : 0)) umma_commit(smem_u32(&sm.free_k[stage]));   // the stage's last reader
-      };
-      for (int t = 0; t < 2 && !failed; ++t) {
-        if (stages[t] == 0) continue;
-        if (!mbar_wait(smem_u32(&sm.p_ready[t]), 0) || !mbar_wait(smem_u32(&sm.full_k[0]), 0)) { failed = true; break; }
-        tcgen05_after_sync();
-        issue_qk(t, 0);
-      }
-      for (int j = 0; j < all_stages && !failed; ++j) {
-        const int stage = j % kPairStages, use = j / kPairStages;
-        for (int t = 0; t < 2; ++t) {
-          if (j >= stages[t]) continue;
-          if (!mbar_wait(smem_u32(&sm.p_ready[t]), (j + 1) & 1) || !mbar_wait(smem_u32(&sm.full_v[stage]), use & 1)) { failed = true; break; }
-          tcgen05_after_sync();
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {   // O_t += P_t V over the 64 keys in four K = 16 steps
-            const uint64_t db = umma_desc(smem_u32(&sm.v[stage][0][0]) + ks * 2048, 8192, 1024);
-            umma_issue_ts(tmem + kColO + t * kHeadDim, tmem + kColS + t * kUmmaKeys + ks * 8, db, kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
-          }
-          if (t == (j < stages[1] ? 1 : 0)) umma_commit(smem_u32(&sm.free_v[stage]));
-          if (j + 1 < stages[t]) {
-            if (!mbar_wait(smem_u32(&sm.full_k[(j + 1) % kPairStages]), ((j + 1) / kPairStages) & 1)) { failed = true; break; }
+      const int t = warp - 8;
+      const int mine = t == 0 ? stages0 : stages1, other = t == 0 ? stages1 : stages0;
+      const uint32_t s_col = tmem + kColS + t * kTileCols, o_col = tmem + kColO + t * kHeadDim;
+      int qk_next = 0, pv_next = 0;
+      long long last_progress = clock64();
+      while (pv_next < mine) {
+        bool progressed = false;
+        if (qk_next < mine) {
+          const int j = qk_next, stage = j % kPairStages;
+          const bool gate = j == 0 ? mbar_test(smem_u32(&sm.p_ready[t]), 0) : mbar_test(smem_u32(&sm.s_free[t]), (j - 1) & 1);
+          if (gate && mbar_test(smem_u32(&sm.full_k[stage]), (j / kPairStages) & 1)) {
             tcgen05_after_sync();
-            issue_qk(t, j + 1);
-          } else {
-            umma_commit(smem_u32(&sm.o_ready[t]));
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {   // S_t(j) = Q_t K(j)^T over the 128 dims
+              const uint64_t db = umma_desc(smem_u32(&sm.k[stage][ks >> 2][0]) + (ks & 3) * 32, 16, 1024);
+              if (t == 0) {
+                umma_issue_ts(s_col, tmem + kColQ + ks * 8, db, kIdescQK, ks > 0);
+              } else {
+                const uint64_t da = umma_desc(smem_u32(&sm.q[ks >> 2][0]) + (ks & 3) * 32, 16, 1024);
+                umma_issue(s_col, da, db, kIdescQK, ks > 0);
+              }
+            }
+            umma_commit(smem_u32(&sm.s_ready[t]));
+            umma_commit(smem_u32(&sm.free_k[stage]));
+            if (j >= other) mbar_arrive(smem_u32(&sm.free_k[stage]));
+            ++qk_next; progressed = true;
           }
+        }
+        // only behind its own S(j): a barrier none has arrived on yet reads as "previous phase complete"
+        if (pv_next < qk_next) {
+          const int j = pv_next, stage = j % kPairStages;
+          if (mbar_test(smem_u32(&sm.p_ready[t]), (j + 1) & 1) && mbar_test(smem_u32(&sm.full_v[stage]), (j / kPairStages) & 1)) {
+            tcgen05_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {   // O_t += P_t(j) V(j) over the 64 keys
+              const uint64_t db = umma_desc(smem_u32(&sm.v[stage][0][0]) + ks * 2048, 8192, 1024);
+              umma_issue_ts(o_col, s_col + kColP + ks * 8, db, kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
+            }
+            umma_commit(smem_u32(&sm.pv_done[t]));
+            umma_commit(smem_u32(&sm.free_v[stage]));
+            if (j >= other) mbar_arrive(smem_u32(&sm.free_v[stage]));
+            ++pv_next; progressed = true;
+          }
+        }
+        if (progressed) {
+          last_progress = clock64();
+        } else if (clock64() - last_progress > kWaitCycles) {
+          failed = true;
+          break;
         }
       }
     }
@@ -770,30 +796,40 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   } else {
     // ---- softmax rows ----
     const int t = warp >> 2, row = threadIdx.x & (kUmmaRows - 1);
-    const int count = min(max(tile.count - t * kUmmaRows, 0), kUmmaRows);
+    const int count = t == 0 ? count0 : count1;
     const int len = row < count ? max(base_len + tile.first + t * kUmmaRows + row, 0) : 0;
-    const int my_stages = stages[t];
+    const int my_stages = t == 0 ? stages0 : stages1;
     const int64_t q_offset = ((static_cast<int64_t>(seq_first) + tile.first + t * kUmmaRows + row) * a.q_heads + q_head) * kHeadDim;
     const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    if (my_stages > 0) {   // this row of Q into tensor memory: 128 16-bit values, two per column
+    if (my_stages > 0) {   // this row of Q: tile 0 into tensor memory (two 16-bit values per column), tile 1 into shared memory
       const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(a.q) + q_offset);
+      const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+      if (t == 0) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t r[32];
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 value = len > 0 ? __ldg(src + h * 8 + c) : make_uint4(0u, 0u, 0u, 0u);
-          r[c * 4] = value.x; r[c * 4 + 1] = value.y; r[c * 4 + 2] = value.z; r[c * 4 + 3] = value.w;
+          for (int c = 0; c < 8; ++c) {
+            const uint4 value = len > 0 ? __ldg(src + h * 8 + c) : zero;
+            r[c * 4] = value.x; r[c * 4 + 1] = value.y; r[c * 4 + 2] = value.z; r[c * 4 + 3] = value.w;
+          }
+          tmem_store32(tmem_row + kColQ + h * 32, r);
         }
-        tmem_store32(tmem_row + kColQ + t * 64 + h * 32, r);
+        tmem_store_wait();
+      } else {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const uint4 value = len > 0 ? __ldg(src + c) : zero;
+          *reinterpret_cast<uint4*>(&sm.q[c >> 3][row * 128 + (((c & 7) ^ (row & 7)) << 4)]) = value;
+        }
+        fence_async_proxy();
       }
-      tmem_store_wait();
       tcgen05_before_sync();
       mbar_arrive(smem_u32(&sm.p_ready[t]));
     }
     constexpr float kRaise = 8.0f;
     float m = -INFINITY, l = 0.f;
-    const uint32_t s_col = tmem_row + kColS + t * kUmmaKeys, o_col = tmem_row + kColO + t * kHeadDim;
+    const uint32_t s_col = tmem_row + kColS + t * kTileCols, p_col = s_col + kColP, o_col = tmem_row + kColO + t * kHeadDim;
     for (int j = 0; j < my_stages; ++j) {
       if (!mbar_wait(smem_u32(&sm.s_ready[t]), j & 1)) { failed = true; break; }
       tcgen05_after_sync();
@@ -806,6 +842,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 #pragma unroll
         for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r0[i]); s[32 + i] = __uint_as_float(r1[i]); }
       }
+      tcgen05_before_sync();
+      mbar_arrive(smem_u32(&sm.s_free[t]));   // the scores are in registers: the next stage's may be written
       const int first_key = j * kUmmaKeys;
       if (first_key + kUmmaKeys > len) {
 #pragma unroll
@@ -820,18 +858,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       const float alpha = (raise && m != -INFINITY) ? fast_exp2(m - candidate) : 1.0f;
       if (raise) m = candidate;
       const float mu = m == -INFINITY ? 0.f : m;
-      // S_t(j) complete means every earlier MMA is: the output tile is at rest until P(j) is announced
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_load32(o_col + c * 32, r);
-          tmem_load_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_store32(o_col + c * 32, r);
-        }
-      }
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[32];
 #pragma unroll
@@ -842,12 +868,27 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         packed[e] = pack2<kBF16>(p0, p1);
       }
       l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-      tmem_store32(s_col, packed);   // P_t(j) over the first half of S_t(j)
+      if (j > 0) {   // P(j - 1) has been read and the output tile is at rest once the previous product is complete
+        if (!mbar_wait(smem_u32(&sm.pv_done[t]), (j - 1) & 1)) { failed = true; break; }
+        tcgen05_after_sync();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {   // rescale this warp's 32 output rows in place
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_load32(o_col + c * 32, r);
+            tmem_load_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_store32(o_col + c * 32, r);
+          }
+        }
+      }
+      tmem_store32(p_col, packed);
       tmem_store_wait();
       tcgen05_before_sync();
       mbar_arrive(smem_u32(&sm.p_ready[t]));
     }
-    if (!failed && my_stages > 0 && !mbar_wait(smem_u32(&sm.o_ready[t]), 0)) failed = true;
+    if (!failed && my_stages > 0 && !mbar_wait(smem_u32(&sm.pv_done[t]), (my_stages - 1) & 1)) failed = true;
     tcgen05_after_sync();
     failed = __any_sync(0xffffffffu, failed);
     if (!failed && count > 0) {
