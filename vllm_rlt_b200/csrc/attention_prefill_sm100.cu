@@ -626,8 +626,9 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // ---- two query tiles per CTA: K / V stages shared, A operands in tensor memory -----------------
 // 256 query tokens of one query head per CTA (one CTA per SM, all 512 TMEM columns), ten warps:
 //   warps 0..3 / 4..7  the softmax rows of query tile 0 / 1 (row = TMEM lane),
-//   warps 8, 9         one thread each issues the MMAs of tile 0 / 1, whichever is ready next,
-//   warp 10            the TMA copies, kPairStages stages of 64 keys ahead.
+//   warps 8, 9         one thread each issues the Q K^T MMAs of tile 0 / 1,
+//   warps 10, 11       one thread each issues the P V MMAs of tile 0 / 1,
+//   warp 12            the TMA copies, kPairStages stages of 64 keys ahead.
 // Per tile the scores S (64 columns) and the probabilities P (32 columns of packed 16-bit pairs)
 // have separate TMEM columns, so S(j + 1) = Q K(j + 1)^T is issued as soon as the rows have read
 // S(j) into registers, runs under their softmax, and O += P(j) V(j) follows when P(j) is stored:
@@ -636,7 +637,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // shared memory (the 512 columns are used up).  Every copied stage serves both tiles.
 // TMEM columns: Q0 0..63 | S0 64..127, P0 128..159 | S1 160..223, P1 224..255 | O0 256..383 | O1 384..511.
 constexpr int kPairRows = 2 * kUmmaRows;
-constexpr int kPairThreads = 352;
+constexpr int kPairThreads = 416;
 constexpr int kPairStages = 5;
 constexpr uint32_t kPairTmemColumns = 512;
 
@@ -707,7 +708,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   constexpr uint32_t kColQ = 0, kColS = 64, kTileCols = 96, kColP = 64, kColO = 256;   // P: offset inside a tile's S / P block
   bool failed = false;
 
-  if (warp == 10) {
+  if (warp == 12) {
     // ---- copies: stage j takes key tile j once both of its operands' readers have committed ----
     const uint64_t policy = policy_evict_first();
     const int32_t* table = a.block_tables + static_cast<int64_t>(tile.seq) * a.table_width;
@@ -732,24 +733,25 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
     }
   } else if (warp >= 8) {
-    // ---- MMA issue, one thread per query tile (warp 8: tile 0, warp 9: tile 1).  Two streams of
-    // work, each gated by the rows' barrier and a copy:
+    // ---- MMA issue, one thread per query tile and product, each gated by the rows' barrier and a copy:
     //   S(j):  Q announced (first phase of p_ready) for j = 0, else S(j - 1) read (s_free) — and K(j)
     //   O(j):  P(j) stored (p_ready) — and V(j)
-    // The thread polls the gates and issues what is ready.  A stage is released to the copy warp
-    // by the commits of both tiles' threads; for a tile that does not read the stage the other
-    // tile's thread arrives by hand. ----
+    // The two products of a tile touch different TMEM columns, so their threads need no order
+    // between them.  A stage is released to the copy warp by the commits of both tiles' threads;
+    // for a tile that does not read the stage the other tile's thread arrives by hand. ----
     if (lane == 0) {
-      const int t = warp - 8;
+      const int t = (warp - 8) & 1;
+      const bool scores = warp < 10;
       const int mine = t == 0 ? stages0 : stages1, other = t == 0 ? stages1 : stages0;
       const uint32_t s_col = tmem + kColS + t * kTileCols, o_col = tmem + kColO + t * kHeadDim;
-      int qk_next = 0, pv_next = 0;
+      // Q announced: from here on p_ready has completed its first phase, so a parity probe of it is unambiguous
+      if (mine > 0 && !mbar_wait(smem_u32(&sm.p_ready[t]), 0)) failed = true;
       long long last_progress = clock64();
-      while (pv_next < mine) {
+      for (int j = 0; j < mine && !failed;) {
+        const int stage = j % kPairStages;
         bool progressed = false;
-        if (qk_next < mine) {
-          const int j = qk_next, stage = j % kPairStages;
-          const bool gate = j == 0 ? mbar_test(smem_u32(&sm.p_ready[t]), 0) : mbar_test(smem_u32(&sm.s_free[t]), (j - 1) & 1);
+        if (scores) {
+          const bool gate = j == 0 || mbar_test(smem_u32(&sm.s_free[t]), (j - 1) & 1);
           if (gate && mbar_test(smem_u32(&sm.full_k[stage]), (j / kPairStages) & 1)) {
             tcgen05_after_sync();
 #pragma unroll
@@ -765,30 +767,25 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
             umma_commit(smem_u32(&sm.s_ready[t]));
             umma_commit(smem_u32(&sm.free_k[stage]));
             if (j >= other) mbar_arrive(smem_u32(&sm.free_k[stage]));
-            ++qk_next; progressed = true;
+            progressed = true;
           }
-        }
-        // only behind its own S(j): a barrier none has arrived on yet reads as "previous phase complete"
-        if (pv_next < qk_next) {
-          const int j = pv_next, stage = j % kPairStages;
-          if (mbar_test(smem_u32(&sm.p_ready[t]), (j + 1) & 1) && mbar_test(smem_u32(&sm.full_v[stage]), (j / kPairStages) & 1)) {
-            tcgen05_after_sync();
+        } else if (mbar_test(smem_u32(&sm.p_ready[t]), (j + 1) & 1) && mbar_test(smem_u32(&sm.full_v[stage]), (j / kPairStages) & 1)) {
+          tcgen05_after_sync();
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {   // O_t += P_t(j) V(j) over the 64 keys
-              const uint64_t db = umma_desc(smem_u32(&sm.v[stage][0][0]) + ks * 2048, 8192, 1024);
-              umma_issue_ts(o_col, s_col + kColP + ks * 8, db, kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
-            }
-            umma_commit(smem_u32(&sm.pv_done[t]));
-            umma_commit(smem_u32(&sm.free_v[stage]));
-            if (j >= other) mbar_arrive(smem_u32(&sm.free_v[stage]));
-            ++pv_next; progressed = true;
+          for (int ks = 0; ks < 4; ++ks) {   // O_t += P_t(j) V(j) over the 64 keys
+            const uint64_t db = umma_desc(smem_u32(&sm.v[stage][0][0]) + ks * 2048, 8192, 1024);
+            umma_issue_ts(o_col, s_col + kColP + ks * 8, db, kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
           }
+          umma_commit(smem_u32(&sm.pv_done[t]));
+          umma_commit(smem_u32(&sm.free_v[stage]));
+          if (j >= other) mbar_arrive(smem_u32(&sm.free_v[stage]));
+          progressed = true;
         }
         if (progressed) {
+          ++j;
           last_progress = clock64();
         } else if (clock64() - last_progress > kWaitCycles) {
           failed = true;
-          break;
         }
       }
     }
