@@ -681,8 +681,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(smem_u32(&sm.s_ready[t]), 1);
-      mbar_init(smem_u32(&sm.s_free[t]), kUmmaRows);
-      mbar_init(smem_u32(&sm.p_ready[t]), kUmmaRows);
+      mbar_init(smem_u32(&sm.s_free[t]), kUmmaRows / 32);    // one arrival per softmax warp
+      mbar_init(smem_u32(&sm.p_ready[t]), kUmmaRows / 32);
       mbar_init(smem_u32(&sm.pv_done[t]), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -822,13 +822,14 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         fence_async_proxy();
       }
       tcgen05_before_sync();
-      mbar_arrive(smem_u32(&sm.p_ready[t]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready[t]));
     }
     constexpr float kRaise = 8.0f;
     float m = -INFINITY, l = 0.f;
     const uint32_t s_col = tmem_row + kColS + t * kTileCols, p_col = s_col + kColP, o_col = tmem_row + kColO + t * kHeadDim;
     for (int j = 0; j < my_stages; ++j) {
-      if (!mbar_wait(smem_u32(&sm.s_ready[t]), j & 1)) { failed = true; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sm.s_ready[t]), j & 1))) { failed = true; break; }   // warp-uniform exit
       tcgen05_after_sync();
       float s[kUmmaKeys];
       {
@@ -840,7 +841,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r0[i]); s[32 + i] = __uint_as_float(r1[i]); }
       }
       tcgen05_before_sync();
-      mbar_arrive(smem_u32(&sm.s_free[t]));   // the scores are in registers: the next stage's may be written
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sm.s_free[t]));   // the scores are in registers: the next stage's may be written
       const int first_key = j * kUmmaKeys;
       if (first_key + kUmmaKeys > len) {
 #pragma unroll
@@ -866,7 +868,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
       l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       if (j > 0) {   // P(j - 1) has been read and the output tile is at rest once the previous product is complete
-        if (!mbar_wait(smem_u32(&sm.pv_done[t]), (j - 1) & 1)) { failed = true; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sm.pv_done[t]), (j - 1) & 1))) { failed = true; break; }
         tcgen05_after_sync();
         if (__any_sync(0xffffffffu, alpha != 1.0f)) {   // rescale this warp's 32 output rows in place
 #pragma unroll
@@ -883,7 +885,8 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       tmem_store32(p_col, packed);
       tmem_store_wait();
       tcgen05_before_sync();
-      mbar_arrive(smem_u32(&sm.p_ready[t]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready[t]));
     }
     if (!failed && my_stages > 0 && !mbar_wait(smem_u32(&sm.pv_done[t]), (my_stages - 1) & 1)) failed = true;
     tcgen05_after_sync();
