@@ -53,6 +53,25 @@ def test_prefill_of_the_reference(golden):
     check(out, case["out"], torch.bfloat16)
 
 
+@pytest.fixture(params=["pair", "umma", "mma"])
+def forced_kernel(request, monkeypatch):
+    """Each of the three prefill kernels in turn (the library reads the variable at every call)."""
+    monkeypatch.setenv("RLT_PREFILL_KERNEL", request.param)
+    return request.param
+
+
+def test_each_prefill_kernel_on_tile_edges_and_long_contexts(forced_kernel):
+    # 128 / 256-row tile edges, a second tile with one row, contexts that wrap the stage ring
+    new = [1, 127, 128, 129, 255, 256, 257, 700, 33, 5]
+    context = [1, 127, 128, 129, 255, 256, 900, 700, 2000, 1234]
+    for dtype in (torch.bfloat16, torch.float16):
+        case = make_case(new, context, q_heads=4, kv_heads=2, dtype=dtype, seed=11, layers=2, layer=1)
+        got = run_prefill(rlt.B200PagedAttention(), case, max(new))
+        want = oracle.paged_attention(case["q"], case["key"], case["value"], case["tables"].clamp_min(0),
+                                      case["lengths"], case["cu"])
+        check(got, want, dtype)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("q_heads,kv_heads", [(4, 4), (4, 2), (8, 1)])
 @pytest.mark.parametrize("value_first", [False, True])

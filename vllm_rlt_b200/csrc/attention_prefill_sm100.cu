@@ -933,7 +933,7 @@ size_t prefill_sm100_workspace_bytes(int rows, int seqs) {
   return 256 + sizeof(PrefillTile) * tile_capacity(rows, seqs);
 }
 
-// The tcgen05 kernel by default; RLT_PREFILL_KERNEL=mma selects the mma.sync kernel.
+// The tcgen05 kernels by default; RLT_PREFILL_KERNEL=pair|umma|mma forces one of the three.
 // RLT_ERR_UNSUPPORTED when no tiled prefill kernel can address the caches (the caller then scores
 // the rows with the verify kernel).
 int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
@@ -942,10 +942,12 @@ int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspa
     set_last_error_text("prefill_attention: workspace missing, misaligned or too small");
     return RLT_ERR_WORKSPACE;
   }
-  static const char kernel_choice = [] {
-    const char* e = getenv("RLT_PREFILL_KERNEL");
-    return e != nullptr ? e[0] : 'p';
-  }();
+  // 'p'air, 'u'mma (one tile per CTA) or 'm'ma.sync; unset: the pair kernel when the sequences average
+  // more than one 128-row tile of new tokens (its second tile would idle otherwise), else one tile per CTA.
+  const char* forced = getenv("RLT_PREFILL_KERNEL");
+  const char kernel_choice = forced != nullptr && forced[0] != 0
+                                 ? forced[0]
+                                 : (static_cast<int64_t>(a.rows) > static_cast<int64_t>(kUmmaRows) * a.table_rows ? 'p' : 'u');
   const bool use_mma_sync = kernel_choice == 'm';
   PrefillHeader* header = static_cast<PrefillHeader*>(workspace);
   PrefillTile* tiles = reinterpret_cast<PrefillTile*>(static_cast<unsigned char*>(workspace) + 256);
