@@ -22,7 +22,8 @@ region).  One process per GPU; every rank runs an independent replica on its own
 the maximum over ranks.
 
 Other entry points (each prints its own JSON line; none is the contract line above):
-    --workload decode [--requests R --output-tokens T --temperature X --eager]
+    --workload decode [--requests R --output-tokens T --temperature X --eager --prompt-min A --prompt-max B
+                       --shared-prefix P --prefix-caching]
                       whole-model self-speculative decoding of a random-init Ouro-1.4B-shaped model
                       (BASELINE configs[2]) with its HBM roofline
     --only attention  [--requests --layers --tokens --depths --kv-heads --context-min --context-max --shared-plan]
@@ -572,9 +573,12 @@ def run_decode_workload(args):
     config = rlt.LoopedLMConfig()
     model = rlt.LoopedLM(config, rlt.seeded_state_dict(config, 3, device=device), device, torch.bfloat16)
     g = torch.Generator().manual_seed(11)
-    lengths = torch.randint(128, 1025, (args.requests,), generator=g).tolist()
+    lengths = torch.randint(args.prompt_min, args.prompt_max + 1, (args.requests,), generator=g).tolist()
     prompts = [torch.randint(1, config.vocab_size, (n,), generator=g).tolist() for n in lengths]
-    decoder = rlt.SelfSpeculativeDecoder(model, cuda_graphs=not args.eager)
+    if args.shared_prefix > 0:   # every second request starts with one common prefix (BASELINE configs[4]'s mix)
+        common = torch.randint(1, config.vocab_size, (args.shared_prefix,), generator=g).tolist()
+        prompts = [common[:len(p) - 1] + p[len(common[:len(p) - 1]):] if i % 2 else p for i, p in enumerate(prompts)]
+    decoder = rlt.SelfSpeculativeDecoder(model, cuda_graphs=not args.eager, prefix_caching=args.prefix_caching)
     clock = {}
 
     def start_clock():
@@ -602,9 +606,13 @@ def run_decode_workload(args):
     roofline_s = (weight_bytes + kv_bytes + head_bytes) / (peak * 1e9)
     print(json.dumps({
         "workload": "decode: Ouro-1.4B-shaped random-init bf16, self-spec k=4 from depth 2, "
-                    f"{args.requests} requests, prompts U[128,1024], {args.output_tokens} output tokens, T={args.temperature}, "
+                    f"{args.requests} requests, prompts U[{args.prompt_min},{args.prompt_max}]"
+                    + (f" (every second one behind a common {args.shared_prefix}-token prefix, prefix reuse "
+                       f"{'on' if args.prefix_caching else 'off'})" if args.shared_prefix else "")
+                    + f", {args.output_tokens} output tokens, T={args.temperature}, "
                     + ("eager launches" if args.eager else "recurrent loops replayed from CUDA graphs"),
         "prefill_and_capture_seconds": clock["start"] - clock["begin"], "prompt_tokens": sum(lengths),
+        "prompt_tokens_computed": stats.prompt_tokens_computed, "prefix_hit_tokens": stats.prefix_hit_tokens,
         "decode_seconds": seconds, "committed_tokens": stats.committed_tokens, "accepted_tokens": stats.accepted_tokens,
         "drafted_tokens": stats.drafted_tokens, "request_rounds": stats.rounds,
         "committed_tokens_per_s": stats.committed_tokens / seconds,
@@ -712,6 +720,11 @@ def main():
                         help="step: the verify-step microbench (the bench line); decode: whole-model decoding (secondary)")
     parser.add_argument("--output-tokens", type=int, default=32)
     parser.add_argument("--eager", action="store_true", help="decode workload: launch every kernel from the host")
+    parser.add_argument("--prompt-min", type=int, default=128, help="decode workload: shortest prompt")
+    parser.add_argument("--prompt-max", type=int, default=1024, help="decode workload: longest prompt")
+    parser.add_argument("--shared-prefix", type=int, default=0,
+                        help="decode workload: every second prompt starts with one common prefix of this many tokens")
+    parser.add_argument("--prefix-caching", action="store_true", help="decode workload: map shared prompt pages instead of recomputing them")
     parser.add_argument("--temperature", type=float, default=0.8)
     parser.add_argument("--requests", type=int, default=REQUESTS)
     parser.add_argument("--layers", type=int, default=LAYERS)

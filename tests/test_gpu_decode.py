@@ -203,3 +203,25 @@ def test_pipeline_mode_decoding_gives_the_reference_tokens(golden, name):
     stats = decoder.stats
     assert stats.committed_tokens == sum(len(t) - 1 for t in tokens)
     assert 0 <= stats.accepted_tokens <= stats.committed_tokens and stats.drafted_tokens >= stats.accepted_tokens
+
+
+def test_prefix_reuse_matches_cold_generation(golden):
+    # the reference's own check (tests/test_prefix_growth.py:27-45 there): a request that maps an
+    # earlier request's complete prompt pages generates what it generates when it computes them
+    case = golden("decode.pt")["config1"]
+    model = build(case)
+    g = torch.Generator().manual_seed(9)
+    vocab = case["config"]["vocab_size"]
+    base = torch.randint(1, vocab, (50,), generator=g).tolist()
+    other = torch.randint(1, vocab, (20,), generator=g).tolist()
+    prompts = [base, base[:35] + other[:5], list(base), base[:20] + other[5:15], other]
+    cold = rlt.SelfSpeculativeDecoder(model, block=16)
+    want = cold.generate(prompts, 24, num_speculative_tokens=4)
+    assert cold.stats.prefix_hit_tokens == 0
+    warm = rlt.SelfSpeculativeDecoder(model, block=16, prefix_caching=True)
+    got = warm.generate(prompts, 24, num_speculative_tokens=4)
+    assert got == want
+    assert warm.stats.prefix_hit_tokens == 32 + 48 + 16
+    assert warm.stats.prompt_tokens_computed == sum(len(p) for p in prompts) - 96
+    assert rlt.SelfSpeculativeDecoder(model, block=16, prefix_caching=True).generate_native(prompts, 24) == want
+    torch.cuda.synchronize()

@@ -12,6 +12,7 @@ from .activation import register_torch_op, silu_and_mul
 from .attention import (B200_CAPABILITIES, AttentionBackend, B200PagedAttention, BackendCapabilities,
                         create_backend)
 from .decoder import DecodeStats, GraphedLoops, PagedKV, SelfSpeculativeDecoder
+from .prefix_cache import PrefixIndex
 from .kv_cache import RollbackResult, finalize_tokens, kv_write, rollback
 from .layers import rope_kv_write, sandwich_norm
 from .looped_lm import LoopedLM, LoopedLMConfig, seeded_state_dict
@@ -19,7 +20,7 @@ from .speculative import (PipelineState, SpeculativeResult, accept_greedy, accep
                           decode_result, pipeline_shift, probabilities, raise_for_status, sample_rows)
 
 __all__ = [
-    "AttentionBackend", "B200PagedAttention", "DecodeStats", "GraphedLoops", "LoopedLM", "LoopedLMConfig", "PagedKV",
+    "AttentionBackend", "B200PagedAttention", "DecodeStats", "GraphedLoops", "LoopedLM", "LoopedLMConfig", "PagedKV", "PrefixIndex",
     "SelfSpeculativeDecoder", "seeded_state_dict", "B200_CAPABILITIES", "BackendCapabilities",
     "NativeLibraryMissing", "RollbackResult", "SpeculativeResult", "accept_greedy", "accept_rejection",
     "argmax_rows", "PipelineState", "create_backend", "decode_result", "finalize_tokens", "pipeline_shift", "kv_write", "load_library", "probabilities", "raise_for_status",

@@ -21,6 +21,7 @@ import torch
 
 from .kv_cache import rollback
 from .looped_lm import LoopedLM
+from .prefix_cache import PrefixIndex
 from .speculative import (PipelineState, accept_greedy, accept_rejection, argmax_rows, pipeline_shift,
                           raise_for_status, sample_rows)
 
@@ -38,6 +39,8 @@ class DecodeStats:
     # context tokens whose K/V those passes had to read (once per request and pass), LM-head rows
     loop_passes: int = 0
     context_tokens_read: int = 0
+    prefix_hit_tokens: int = 0          # prompt tokens mapped from the prefix index (KVCacheManager.prefix_hits)
+    prompt_tokens_computed: int = 0
     coda_rows: int = 0
 
 
@@ -50,26 +53,48 @@ class PagedKV:
     value: torch.Tensor
     tables: torch.Tensor
     block: int
+    shared_tokens: list | None = None   # per request: leading prompt tokens mapped from the prefix index
+    prefix_index: PrefixIndex | None = None
 
     @classmethod
-    def allocate(cls, model: LoopedLM, capacities, block: int, *, permute_seed: int | None = 0):
+    def allocate(cls, model: LoopedLM, capacities, block: int, *, permute_seed: int | None = 0, prompts=None):
+        """Pages for `capacities[i]` tokens of every request on every depth plane.  With `prompts`
+        (prefix reuse), request i maps the indexed complete pages of `prompts[i][:-1]` into its
+        tables instead of taking fresh ones (`KVCacheManager.allocate(..., prefix=...)`,
+        core/kv_cache_manager.py:277-319) and then offers its own complete prompt pages to the
+        requests after it; `shared_tokens[i]` is how many leading prompt tokens it does not compute."""
         c = model.config
         planes = c.total_ut_steps
         pages = [-(-n // block) for n in capacities]
         width = max(pages)
-        total = sum(pages) * planes
-        order = torch.arange(total, dtype=torch.int32)
-        if permute_seed is not None:  # physical pages deliberately out of order
-            order = order[torch.randperm(total, generator=torch.Generator().manual_seed(permute_seed))]
-        tables = torch.full((len(capacities), planes, width), -1, dtype=torch.int32)
+        index = PrefixIndex(block) if prompts is not None else None
+        logical = torch.full((len(capacities), planes, width), -1, dtype=torch.int64)
+        shared_tokens = []
         cursor = 0
         for i, n in enumerate(pages):
+            prefix = index.lookup(prompts[i]) if index is not None else ()
+            hit = len(prefix)
+            shared_tokens.append(hit * block)
             for plane in range(planes):
-                tables[i, plane, :n] = order[cursor:cursor + n]
-                cursor += n
+                for j in range(hit):
+                    logical[i, plane, j] = prefix[j][plane]
+                logical[i, plane, hit:n] = torch.arange(cursor, cursor + n - hit)
+                cursor += n - hit
+            if index is not None:
+                index.claim(prefix)
+                index.own(logical[i, :, hit:n].reshape(-1).tolist())
+                index.publish(prompts[i], len(prompts[i]), logical[i].tolist())
+        total = cursor
+        order = torch.arange(total, dtype=torch.int64)
+        if permute_seed is not None:  # physical pages deliberately out of order
+            order = order[torch.randperm(total, generator=torch.Generator().manual_seed(permute_seed))]
+        tables = torch.where(logical >= 0, order[logical.clamp_min(0)], logical).to(torch.int32)
+        if index is not None:
+            index.remap(order.tolist())
         shape = (total, c.num_hidden_layers, block, c.num_key_value_heads, c.head_dim)
         return cls(torch.zeros(shape, device=model.device, dtype=model.dtype),
-                   torch.zeros(shape, device=model.device, dtype=model.dtype), tables.to(model.device), block)
+                   torch.zeros(shape, device=model.device, dtype=model.dtype), tables.to(model.device), block,
+                   shared_tokens, index)
 
     def addressing(self, requests: torch.Tensor, positions: torch.Tensor, plane: int):
         """Write addresses, per-row block tables and context lengths of rows (request, position)."""
@@ -147,10 +172,11 @@ class GraphedLoops:
 
 
 class SelfSpeculativeDecoder:
-    def __init__(self, model: LoopedLM, *, block: int = 16, cuda_graphs: bool = False):
+    def __init__(self, model: LoopedLM, *, block: int = 16, cuda_graphs: bool = False, prefix_caching: bool = False):
         self.model = model
         self.block = block
         self.cuda_graphs = cuda_graphs
+        self.prefix_caching = prefix_caching   # CacheConfig.enable_prefix_caching of the reference
         self.stats = DecodeStats()
         self._graphs = None
 
@@ -172,30 +198,40 @@ class SelfSpeculativeDecoder:
             return self._graphs(hidden, positions, blocks, offsets, tables, lengths)
         return self.model.recurrent(hidden, positions, kv.key, kv.value, blocks, offsets, tables, lengths)
 
+    def _allocate(self, prompts, capacities):
+        return PagedKV.allocate(self.model, capacities, self.block, prompts=prompts if self.prefix_caching else None)
+
     def _prefill(self, kv: PagedKV, prompts):
         """All prompt positions through every loop, packed (one table row per prompt, causal inside
-        it); returns the first generated token of each request."""
+        it); returns the first generated token of each request.  Leading tokens whose pages a request
+        shares with an earlier one are not computed: its rows start behind them and attend to the
+        shared pages, which the earlier request's rows write in the same pass (within a layer every
+        K/V row is written before any row attends)."""
         device = self.model.device
+        skips = kv.shared_tokens if kv.shared_tokens is not None else [0] * len(prompts)
         lengths = [len(p) for p in prompts]
-        requests = torch.tensor([i for i, p in enumerate(prompts) for _ in p], device=device)
-        positions = torch.tensor([j for p in prompts for j in range(len(p))], device=device)
-        tokens = torch.tensor([t for p in prompts for t in p], device=device)
-        cu = torch.tensor([0] + torch.tensor(lengths).cumsum(0).tolist(), dtype=torch.int32, device=device)
+        new = [n - s for n, s in zip(lengths, skips)]
+        self.stats.prefix_hit_tokens += sum(skips)
+        self.stats.prompt_tokens_computed += sum(new)
+        requests = torch.tensor([i for i, n in enumerate(new) for _ in range(n)], device=device)
+        positions = torch.tensor([j for n, s in zip(lengths, skips) for j in range(s, n)], device=device)
+        tokens = torch.tensor([t for p, s in zip(prompts, skips) for t in p[s:]], device=device)
+        cu = torch.tensor([0] + torch.tensor(new).cumsum(0).tolist(), dtype=torch.int32, device=device)
         context = torch.tensor(lengths, dtype=torch.int32, device=device)
         hidden = self.model.prelude(tokens)
         for depth in range(self.model.config.total_ut_steps):
             tables = kv.tables[:, depth]
             blocks = tables[requests].gather(1, (positions // self.block)[:, None]).squeeze(1).long()
             hidden = self.model.recurrent(hidden, positions, kv.key, kv.value, blocks, positions % self.block,
-                                          tables.contiguous(), context, packed=(cu, max(lengths)))
-        last = torch.tensor([sum(len(p) for p in prompts[:i + 1]) - 1 for i in range(len(prompts))], device=device)
+                                          tables.contiguous(), context, packed=(cu, max(new)))
+        last = (cu[1:] - 1).long()
         return argmax_rows(self.model.coda(hidden[last]).float().contiguous()).tolist()
 
     # ---- native decoding -----------------------------------------------------------------
     @torch.no_grad()
     def generate_native(self, prompts, max_tokens: int):
         device = self.model.device
-        kv = PagedKV.allocate(self.model, [len(p) + max_tokens for p in prompts], self.block)
+        kv = self._allocate(prompts, [len(p) + max_tokens for p in prompts])
         generated = [[t] for t in self._prefill(kv, prompts)]
         while any(len(g) < max_tokens for g in generated):
             active = [i for i, g in enumerate(generated) if len(g) < max_tokens]
@@ -228,7 +264,7 @@ class SelfSpeculativeDecoder:
             raise ValueError("target_loops must be a positive multiple of draft_loops")
         width = min(num_speculative_tokens + 1, target_loops // draft_loops)
         n = len(prompts)
-        kv = PagedKV.allocate(model, [len(p) + max_tokens + width + 1 for p in prompts], self.block)
+        kv = self._allocate(prompts, [len(p) + max_tokens + width + 1 for p in prompts])
         first = self._prefill(kv, prompts)
         generated = [[t] for t in first]
         token = torch.tensor(first, device=device)
@@ -302,7 +338,7 @@ class SelfSpeculativeDecoder:
         if not 0 < draft_loops < target_loops <= model.config.total_ut_steps:
             raise ValueError("draft_loops must be smaller than target_loops")
         k = num_speculative_tokens
-        kv = PagedKV.allocate(model, [len(p) + max_tokens + k + 1 for p in prompts], self.block)
+        kv = self._allocate(prompts, [len(p) + max_tokens + k + 1 for p in prompts])
         generated = [[t] for t in self._prefill(kv, prompts)]  # the first token is the prefill's argmax
         if self.cuda_graphs:
             self._graphs = GraphedLoops(model, kv)
