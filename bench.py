@@ -227,6 +227,33 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(self.samples)}
 
 
+def bind_to_gpu_numa_node(local: int):
+    """Runs this process on the cores of the NUMA node its GPU hangs off (sysfs; a process
+    setting, nothing of the GPU's changes), so that the pinned staging buffers of the host-driven
+    step are first touched — and therefore placed — in that node's memory.  With several replicas
+    per machine the uploads otherwise share one node's memory channels and the socket link.
+    Returns the node, or None when the topology cannot be read."""
+    try:
+        bus = torch.cuda.get_device_properties(local).pci_bus_id
+        domain = torch.cuda.get_device_properties(local).pci_domain_id
+        device_id = torch.cuda.get_device_properties(local).pci_device_id
+        path = f"/sys/bus/pci/devices/{domain:04x}:{bus:02x}:{device_id:02x}.0/numa_node"
+        node = int(open(path).read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
 def run_gpu(args):
     import torch.distributed as dist
 
@@ -237,6 +264,7 @@ def run_gpu(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    numa = bind_to_gpu_numa_node(local) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
@@ -398,6 +426,7 @@ def run_gpu(args):
                 "kv_pool_gb": round(2 * key_pool.numel() * 2 / 1e9, 2),
                 "l2_policy": "inputs larger than L2 (KV pool streamed once per step)",
                 "parallelism": f"{world} independent replicas, no collective",
+                "host_numa_node_rank0": numa,
             },
             "committed_tokens_per_s": job["committed_tokens_per_s"],
             "acceptance_rate": accepted_total / (world * work.requests * (TOKENS - 1)),
