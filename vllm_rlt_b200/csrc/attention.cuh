@@ -64,7 +64,8 @@ int run_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspac
 // launch_attention_sm100 on the library's built-in 32 MiB scratch block (no allocation anywhere).
 size_t attention_sm100_builtin_scratch_bytes();
 int launch_attention_sm100_builtin(const AttentionArgs& a, cudaStream_t stream);
-// attention_prefill_sm100.cu: packed causal prefill, 64 query tokens per CTA, the same shapes.
+// attention_prefill_sm100.cu: packed causal prefill (tcgen05 kernels with 256 / 128 query tokens
+// per CTA, an mma.sync one with 64), the same shapes.
 bool prefill_sm100_supported(const AttentionArgs& a);
 size_t prefill_sm100_workspace_bytes(int rows, int seqs);
 int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspace_bytes, cudaStream_t stream);

@@ -1,18 +1,22 @@
 // Packed causal prefill over the paged KV cache for sm_100a: head_dim 128, 16-token pages,
 // fp16 / bf16.  The verify kernel scores at most 16 query rows per pass over a context, which
 // is right for verification rows and wrong for a prompt: a prompt of n tokens would read its
-// K/V n / 16 times.  Here a CTA owns 64 consecutive query tokens of one sequence and one query
-// head and walks that sequence's pages once, 64 tokens (four pages) per shared-memory stage.
+// K/V n / 16 times.  Here a CTA owns a tile of consecutive query tokens of one sequence and one
+// query head and walks that sequence's pages once, 64 keys (four pages) per shared-memory stage.
 //
-//   plan kernel   one CTA turns cu_seqlens_q into a list of (sequence, first query, count)
-//                 tiles, the last tile of a sequence first (it sees the longest context).
-//   main kernel   four warps of 16 query rows each.  Thread 0 copies the next four pages with
-//                 TMA (one copy per page through the 5-D map over both caches, 128-byte
-//                 swizzle) into a two-stage ring guarded by full / empty mbarriers; every warp
-//                 scores a stage (up to 64 keys) with 64 + 64 m16n8k16 tensor-core instructions
-//                 around one fp32 online-softmax step in the log2 domain, skipping pages that lie
-//                 entirely in its rows' causal future and masking only the stages its diagonal
-//                 crosses.
+//   plan kernel     one CTA turns cu_seqlens_q into a list of (sequence, first query, count)
+//                   tiles, the last tile of a sequence first (it sees the longest context).
+//   pair kernel     tcgen05 / TMEM, two 128-row query tiles per CTA that share every K / V stage;
+//                   Q and P are TMEM operands of the MMAs, separate warps copy, issue and do the
+//                   softmax (see the comment above prefill_pair_kernel).  Default for prompts.
+//   one-tile kernel tcgen05 / TMEM, one 128-row tile per CTA and two CTAs per SM (above
+//                   prefill_umma_kernel).  Default when the sequences average at most 128 new tokens.
+//   mma.sync kernel 64-row tiles, four warps of 16 query rows each.  Thread 0 copies the next four
+//                   pages with TMA (one copy per page through the 5-D map over both caches, 128-byte
+//                   swizzle) into a two-stage ring guarded by full / empty mbarriers; every warp
+//                   scores a stage with 64 + 64 m16n8k16 tensor-core instructions around one fp32
+//                   online-softmax step in the log2 domain, skipping pages that lie entirely in
+//                   its rows' causal future and masking only the stages its diagonal crosses.
 //
 // Causality is bottom-right aligned (`vllm_rlt/kernels/triton_attention.py:205-366` of the
 // reference): query i of the n_s new tokens of sequence s sees positions 0 .. len_s - n_s + i.
@@ -28,7 +32,7 @@
 namespace rlt {
 namespace {
 
-constexpr int kTileRows = 64;                  // query tokens per CTA
+constexpr int kTileRows = 64;                  // query tokens per CTA of the mma.sync kernel
 constexpr int kTilePages = 4;                  // pages per stage (64 keys)
 #ifndef RLT_PREFILL_STAGES
 #define RLT_PREFILL_STAGES 2
