@@ -55,6 +55,7 @@ class PagedKV:
     block: int
     shared_tokens: list | None = None   # per request: leading prompt tokens mapped from the prefix index
     prefix_index: PrefixIndex | None = None
+    refcounts: torch.Tensor | None = None   # int32 [blocks], holders of every page (prefix reuse only)
 
     @classmethod
     def allocate(cls, model: LoopedLM, capacities, block: int, *, permute_seed: int | None = 0, prompts=None):
@@ -91,10 +92,16 @@ class PagedKV:
         tables = torch.where(logical >= 0, order[logical.clamp_min(0)], logical).to(torch.int32)
         if index is not None:
             index.remap(order.tolist())
+        refcounts = None
+        if index is not None:
+            refcounts = torch.zeros(total, dtype=torch.int32)
+            for b, holders in index.refs.items():
+                refcounts[b] = holders
+            refcounts = refcounts.to(model.device)
         shape = (total, c.num_hidden_layers, block, c.num_key_value_heads, c.head_dim)
         return cls(torch.zeros(shape, device=model.device, dtype=model.dtype),
                    torch.zeros(shape, device=model.device, dtype=model.dtype), tables.to(model.device), block,
-                   shared_tokens, index)
+                   shared_tokens, index, refcounts)
 
     def addressing(self, requests: torch.Tensor, positions: torch.Tensor, plane: int):
         """Write addresses, per-row block tables and context lengths of rows (request, position)."""
@@ -428,8 +435,13 @@ class SelfSpeculativeDecoder:
                 result = accept_greedy(logits, cu_rows, tokens.contiguous(), start_tensor, slots,
                                        slot_values[:n].contiguous())
             accepted = result[rows_total:rows_total + n]
-            rolled = rollback(start_tensor, accepted + 1, kv.tables[active_t].contiguous(), self.block)
-            values = torch.cat([result, rolled.frontier, status.long()]).tolist()  # the round's one host read
+            # with prefix reuse the page reference counts go along: a frontier inside a shared page is refused
+            rolled = rollback(start_tensor, accepted + 1, kv.tables[active_t].contiguous(), self.block,
+                              refcounts=kv.refcounts)
+            values = torch.cat([result, rolled.frontier, status.long(), rolled.status.long()]).tolist()  # the round's one host read
+            if kv.refcounts is not None and 4 in values[len(values) - n:]:
+                raise RuntimeError("rollback refused: the frontier of a request lies in a shared page")
+            values = values[:len(values) - n]
             raise_for_status(values[rows_total + 3 * n:])
             for j, i in enumerate(active):
                 a = values[rows_total + j]
