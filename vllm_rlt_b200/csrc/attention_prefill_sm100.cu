@@ -619,6 +619,33 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   if (issuer) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
 }
 
+// Packed fp32 pairs and the three-input maximum of sm_100: half the instructions for the scaling,
+// the sums and the row maximum of the softmax, whose warps are bound by issue slots and latency.
+__device__ __forceinline__ float2 fma_pair(float2 a, float2 b, float2 c) {
+  unsigned long long ra, rb, rc, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float2 add_pair(float2 a, float2 b) {
+  unsigned long long ra, rb, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // Non-blocking probe of a barrier phase (try_wait may suspend the thread for a while).
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -855,22 +882,27 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < kUmmaKeys; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
+      for (int i = 0; i < kUmmaKeys; i += 8) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) mx4[c] = max3(mx4[c], s[i + 2 * c], s[i + 2 * c + 1]);
+      }
       const float candidate = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       const bool raise = candidate > m + kRaise || (m == -INFINITY && candidate > -INFINITY);
       const float alpha = (raise && m != -INFINITY) ? fast_exp2(m - candidate) : 1.0f;
       if (raise) m = candidate;
       const float mu = m == -INFINITY ? 0.f : m;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      float2 sum4[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
       uint32_t packed[32];
+      const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-mu, -mu);
 #pragma unroll
       for (int e = 0; e < 32; ++e) {
-        const float p0 = fast_exp2(fmaf(s[2 * e], scale_log2, -mu));
-        const float p1 = fast_exp2(fmaf(s[2 * e + 1], scale_log2, -mu));
-        sum4[e & 3] += p0 + p1;
-        packed[e] = pack2<kBF16>(p0, p1);
+        const float2 x = fma_pair(make_float2(s[2 * e], s[2 * e + 1]), scale2, shift2);
+        const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+        sum4[e & 3] = add_pair(sum4[e & 3], p);
+        packed[e] = pack2<kBF16>(p.x, p.y);
       }
-      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      const float2 sum2 = add_pair(add_pair(sum4[0], sum4[1]), add_pair(sum4[2], sum4[3]));
+      l = l * alpha + (sum2.x + sum2.y);
       if (j > 0) {   // P(j - 1) has been read and the output tile is at rest once the previous product is complete
         if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sm.pv_done[t]), (j - 1) & 1))) { failed = true; break; }
         tcgen05_after_sync();
