@@ -722,10 +722,17 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kPairTmemColumns) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  {  // V stages zeroed: a partial last stage multiplies P = 0 with what lies behind its last page
+  // A partial last stage multiplies P = 0 with what lies behind its last page of V: that has to be
+  // finite.  Once the ring has wrapped it is an earlier stage's data; before that it is whatever
+  // the shared memory held, so the tail of that one stage is zeroed.
+  if (all_stages > 0 && all_stages <= kPairStages) {
+    const int pages_last = total_pages - (all_stages - 1) * 4;   // 1 .. 4
+    const int tail = (4 - pages_last) * 2048 / 16;               // 16-byte words per half
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    uint4* vz = reinterpret_cast<uint4*>(&sm.v[0][0][0]);
-    for (int i = threadIdx.x; i < static_cast<int>(sizeof(sm.v) / 16); i += kPairThreads) vz[i] = zero;
+    for (int i = threadIdx.x; i < 2 * tail; i += kPairThreads) {
+      const int half = i / tail, word = i - half * tail;
+      reinterpret_cast<uint4*>(&sm.v[all_stages - 1][half][pages_last * 2048])[word] = zero;
+    }
   }
   fence_async_proxy();
   tcgen05_before_sync();
