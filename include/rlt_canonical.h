@@ -145,4 +145,44 @@ RLT_HD int rlt_in_support(uint32_t order_key, int v, uint32_t cut_key, int cut_l
   return order_key > cut_key || (order_key == cut_key && v <= cut_limit);
 }
 
+/*
+ * Uniforms of a speculative round.  The reference draws them from one torch.Generator per
+ * request (vllm_rlt/worker/sampler.py:84-119), on the host, in the order: the round's draft
+ * draws, then per verified row the accept test, then the final residual / bonus draw
+ * (vllm_rlt/worker/speculative.py:439-444, 483-510).  A device-resident round cannot consult host
+ * generators, so the same three streams are defined as a counter-based generator: Philox4x32-10
+ * (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11) keyed by the request's
+ * seed, with the counter (index, stream, round).  A request's uniforms therefore depend on its
+ * seed and on how many rounds it has run, never on the batch it shares a round with.
+ */
+#define RLT_STREAM_DRAFT 0u
+#define RLT_STREAM_ACCEPT 1u
+#define RLT_STREAM_FINAL 2u
+
+RLT_HD void rlt_philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1) {
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c[0];
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c[2];
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0;
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1;
+    c[0] = n0;
+    c[1] = (uint32_t)p1;
+    c[2] = n2;
+    c[3] = (uint32_t)p0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+}
+
+/* U[0, 1) with 24 random bits: exact in fp32, never 1. */
+RLT_HD float rlt_uniform(uint64_t seed, uint64_t round, uint32_t stream, uint32_t index) {
+  uint32_t c[4];
+  c[0] = index;
+  c[1] = stream;
+  c[2] = (uint32_t)round;
+  c[3] = (uint32_t)(round >> 32);
+  rlt_philox4x32_10(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+  return RLT_MUL((float)(c[0] >> 8), 5.9604644775390625e-08f); /* 2^-24 */
+}
+
 #endif /* RLT_CANONICAL_H_ */

@@ -8,10 +8,13 @@
  * pointer arguments for the lifetime of the work on that stream, and returns
  * an int status: RLT_OK or a negative RLT_ERR_* code.  No exception crosses
  * this boundary.  The library keeps no mutable global state besides a
- * per-device cache of immutable properties (SM count, driver entry points).
+ * per-device cache of immutable properties (SM count, driver entry points)
+ * and the fixed scratch block of rlt_verify_attention_noalloc, which is the one
+ * piece of device memory the library owns (see that entry point).
  *
  * Each declaration cites the reference interface (vllm-rlt v0.2.0, paths
- * relative to that project) it stands in for.
+ * relative to that project) it stands in for; the few entry points without a
+ * counterpart there say so.
  *
  * Element type codes (`dtype` arguments): see rlt_dtype.
  */
@@ -107,7 +110,13 @@ RLT_API int rlt_kv_write(void* key_cache, void* value_cache, int64_t block_strid
  * own query, length and K/V only (bit-identical alone, in any batch and in
  * any group).  len_r == 0 gives a zero row and never dereferences its table.
  * Table entries at or beyond ceil(len_r / block_size) are never read as page ids
- * for that row.
+ * for that row.  The lengths are device data the host may never have seen (graph
+ * replays), so a length beyond table_width * block_size is clamped to that capacity
+ * instead of indexing past the table: the row is scored over the tokens its table
+ * can address, and the tiled kernel records the event in the error word that
+ * rlt_verify_attention_status reports (bit 1).  The reference's Torch path raises
+ * IndexError for such a row; here the run stays in bounds and the host learns of it
+ * afterwards.
  * Replaces: TritonPagedAttention.__call__ / paged_attention
  *   (vllm_rlt/kernels/paged_attention.py:119-120, vllm_rlt/kernels/triton_attention.py:150-202,
  *    kernels :20-147); oracle torch_paged_attention (vllm_rlt/kernels/paged_attention.py:12-36);
@@ -180,7 +189,11 @@ RLT_API int rlt_verify_attention_run(const void* q, void* out, const void* key_c
  *     Anything larger is refused with RLT_ERR_WORKSPACE and a message in rlt_last_error();
  *     nothing is launched.
  *   - The first call on each device looks up the block's device address (with that device
- *     current).  Make that first call outside any stream capture.
+ *     current); under CUDA's lazy module loading that is also when the 32 MiB are taken from
+ *     the device.  A call with rows == 0 is a valid warm-up: it does this set-up and launches
+ *     nothing.  Make it once per device at start-up, BEFORE the host gives its remaining
+ *     device memory away (afterwards the set-up itself would fail with RLT_ERR_CUDA, out of
+ *     memory) and outside any stream capture.
  *   - All calls on a device share the one block, and it keeps whatever the previous call
  *     left; each call re-initialises the words that must start at zero.  Two calls whose
  *     work can overlap on the GPU (different streams, no ordering between them) race on
@@ -256,10 +269,15 @@ RLT_API int rlt_argmax_rows(const void* logits, int64_t row_stride, int rows, in
  *   AsyncSpeculativeRunner._accept_and_update_state
  *   (vllm_rlt/worker/async_speculative.py:417-447; wire layout :62-77).
  * tokens: int64 [n, tokens_width].  slot_values: int64 [*, 2].
+ * row_counts: NULL, or int32 [n] for rounds of a fixed shape (one CUDA graph per batch size):
+ *   every request then owns the same span of rows, cu_rows[i] .. cu_rows[i+1]-1, of which only
+ *   the first row_counts[i] are real; the padding rows are never compared and get -1 in
+ *   `result`.  A request with no rows (row_counts[i] <= 0, or an empty span) is left alone:
+ *   accepted 0, next_position = starts[i], no slot update.
  * ---------------------------------------------------------------------- */
 RLT_API int rlt_accept_greedy(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
-                      const int32_t* cu_rows, int n, const int64_t* tokens, int tokens_width,
-                      const int64_t* starts, const int64_t* slots, int64_t* slot_values,
+                      const int32_t* cu_rows, int n, const int32_t* row_counts, const int64_t* tokens,
+                      int tokens_width, const int64_t* starts, const int64_t* slots, int64_t* slot_values,
                       int64_t* result, rlt_stream_t stream);
 
 /* ------------------------------------------------------------------------
@@ -306,7 +324,9 @@ RLT_API int rlt_sample_rows(const void* logits, int64_t row_stride, int rows, in
  * Outputs as rlt_accept_greedy, except result[row] holds the EMITTED tokens of each
  * request at cu_rows[i] .. cu_rows[i]+accepted[i] (later rows of the request: -1),
  * and status[i] is an RLT_ROW_* code (on error accepted/next_* describe the prefix
- * emitted before the failing draft).
+ * emitted before the failing draft, and the request's slot keeps its old value, so a
+ * device-driven next round does not start from an invalid token).  row_counts as in
+ * rlt_accept_greedy.
  *
  * Arithmetic (identical in the CPU oracle, so results are bit-exact):
  *   t = x / T (IEEE);  m = max t;  e = rlt_expf(t - m);  Zfix = sum (u64)(e * 2^40);
@@ -326,11 +346,25 @@ RLT_API size_t rlt_accept_rejection_workspace_bytes(int rows);
 
 RLT_API int rlt_accept_rejection(const void* target_logits, const void* draft_logits, int64_t row_stride,
                          int rows, int vocab, int dtype, const int32_t* cu_rows, int n,
-                         const int64_t* tokens, int tokens_width, const int64_t* starts,
-                         const float* temperature, const int32_t* top_k, const float* top_p,
+                         const int32_t* row_counts, const int64_t* tokens, int tokens_width,
+                         const int64_t* starts, const float* temperature, const int32_t* top_k, const float* top_p,
                          const float* u_accept, const float* u_final, const int64_t* slots,
                          int64_t* slot_values, int64_t* result, int32_t* status, void* workspace,
                          size_t workspace_bytes, rlt_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Uniforms of one speculative round for n requests: u_draft[i, o] (the draw of draft o+1),
+ * u_accept[i, j] (the accept test of verification row j) and u_final[i] (the residual or bonus
+ * draw), each in [0, 1) with 24 random bits, from the counter-based generator of
+ * include/rlt_canonical.h (Philox4x32-10 keyed by seeds[i], counter = (index, stream, rounds[i])).
+ * A request's uniforms depend on its seed and round number only, not on its batch.
+ * Replaces: the per-request torch.Generator of RngRegistry (vllm_rlt/worker/sampler.py:84-119) as
+ *   SpeculativeRunner consumes it (vllm_rlt/worker/speculative.py:439-444, 483-510); the
+ *   reference's device-resident runner has no sampling at all (engine/stage_engine.py:327-332).
+ * seeds, rounds: int64 [n].  u_draft, u_accept: float32 [n, width].  u_final: float32 [n].
+ * ---------------------------------------------------------------------- */
+RLT_API int rlt_round_uniforms(const int64_t* seeds, const int64_t* rounds, int n, int width, float* u_draft,
+                       float* u_accept, float* u_final, rlt_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Device rollback of rejected positions.  For request i with round start
@@ -340,6 +374,9 @@ RLT_API int rlt_accept_rejection(const void* target_logits, const void* draft_lo
  *   context_lengths[i]      = frontier[i] + 1
  *   write_offsets[i]        = frontier[i] % block_size
  *   write_blocks[i,p]       = tables[i, p, frontier[i] / block_size]
+ *                             (-1 when frontier[i] == table_width * block_size: the allocation is
+ *                             full, the rollback itself is valid)
+ * A frontier below 0 or beyond table_width * block_size gives RLT_ROW_BAD_POSITION.
  * Block tables and physical pages are not modified (the reservation is kept).
  * If refcounts != NULL and any page of request i at or after frontier[i] / block_size
  * (within pages_used[i]) has refcounts[page] > 1 the request is left untouched and

@@ -106,11 +106,11 @@ def argmax_rows(logits):
     return targets
 
 
-def accept_greedy(logits, cu_rows, tokens, starts, slots=None, slot_values=None):
+def accept_greedy(logits, cu_rows, tokens, starts, slots=None, slot_values=None, row_counts=None):
     rows, n = logits.shape[0], cu_rows.numel() - 1
     result = torch.empty(rows + 2 * n, dtype=torch.int64)
     lib().orc_accept_greedy(_p(logits), _i64(logits.stride(0)), rows, logits.shape[1],
-                            _DTYPES[logits.dtype], _p(cu_rows), n, _p(tokens), tokens.shape[1],
+                            _DTYPES[logits.dtype], _p(cu_rows), n, _p(row_counts), _p(tokens), tokens.shape[1],
                             _p(starts), _p(slots), _p(slot_values), _p(result))
     return result
 
@@ -134,17 +134,36 @@ def sample_rows(logits, temperature, uniforms, top_k=None, top_p=None):
 
 
 def accept_rejection(target_logits, draft_logits, cu_rows, tokens, starts, temperature, u_accept,
-                     u_final, slots=None, slot_values=None, top_k=None, top_p=None):
+                     u_final, slots=None, slot_values=None, top_k=None, top_p=None, row_counts=None):
     rows, n = target_logits.shape[0], cu_rows.numel() - 1
     assert target_logits.stride() == draft_logits.stride()
     result = torch.empty(rows + 2 * n, dtype=torch.int64)
     status = torch.empty(n, dtype=torch.int32)
     lib().orc_accept_rejection(_p(target_logits), _p(draft_logits), _i64(target_logits.stride(0)),
                                rows, target_logits.shape[1], _DTYPES[target_logits.dtype],
-                               _p(cu_rows), n, _p(tokens), tokens.shape[1], _p(starts),
+                               _p(cu_rows), n, _p(row_counts), _p(tokens), tokens.shape[1], _p(starts),
                                _p(temperature), _p(top_k), _p(top_p), _p(u_accept), _p(u_final), _p(slots),
                                _p(slot_values), _p(result), _p(status))
     return result, status
+
+
+def round_uniforms(seeds, rounds, width):
+    """(u_draft [n, width], u_accept [n, width], u_final [n]) of a round, float32."""
+    n = seeds.numel()
+    u_draft, u_accept = torch.empty(n, width), torch.empty(n, width)
+    u_final = torch.empty(n)
+    lib().orc_round_uniforms(_p(seeds.contiguous()), _p(rounds.contiguous()), n, width, _p(u_draft), _p(u_accept),
+                             _p(u_final))
+    return u_draft, u_accept, u_final
+
+
+def philox4x32_10(counter, key):
+    """One Philox4x32-10 block (four 32-bit words) for a 4-word counter and a 2-word key."""
+    c = (ctypes.c_uint32 * 4)(*counter)
+    k = (ctypes.c_uint32 * 2)(*key)
+    out = (ctypes.c_uint32 * 4)()
+    lib().orc_philox4x32_10(c, k, out)
+    return list(out)
 
 
 def finalize_tokens(key_pool, value_pool, tables, slots, depths, positions):

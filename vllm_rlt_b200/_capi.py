@@ -38,12 +38,13 @@ SIGNATURES = {
                                    _P, _Z, _P]),
     "rlt_verify_attention_status": (_I, [_P, _P, _P]),
     "rlt_argmax_rows": (_I, [_P, _L, _I, _I, _I, _P, _P]),
-    "rlt_accept_greedy": (_I, [_P, _L, _I, _I, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P]),
+    "rlt_accept_greedy": (_I, [_P, _L, _I, _I, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _P]),
+    "rlt_round_uniforms": (_I, [_P, _P, _I, _I, _P, _P, _P, _P]),
     "rlt_probabilities": (_I, [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "rlt_sample_rows": (_I, [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
     "rlt_accept_rejection_workspace_bytes": (_Z, [_I]),
-    "rlt_accept_rejection": (_I, [_P, _P, _L, _I, _I, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
-                                  _P, _Z, _P]),
+    "rlt_accept_rejection": (_I, [_P, _P, _L, _I, _I, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                                  _P, _P, _Z, _P]),
     "rlt_finalize_tokens": (_I, [_P, _P, _L, _L, _L, _L, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P]),
     "rlt_pipeline_shift": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P]),
     "rlt_rope_kv_write": (_I, [_P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P,

@@ -127,14 +127,34 @@ argmax_rows_kernel(const T* __restrict__ logits, int64_t row_stride, int vocab, 
   if (threadIdx.x == 0) targets[blockIdx.x] = index;
 }
 
+// Rows of request i: the span cu_rows[i] .. cu_rows[i+1]-1, of which only the first
+// row_counts[i] are real when row_counts is given (a fixed-shape round pads every request to the
+// same span).  Zero rows: the request is left alone (accepted 0, next position = its start, no
+// slot update).
+__device__ __forceinline__ int request_rows(const int32_t* __restrict__ cu_rows, const int32_t* __restrict__ row_counts,
+                                            int i, int* first, int* span) {
+  *first = cu_rows[i];
+  *span = cu_rows[i + 1] - cu_rows[i];
+  const int c = row_counts != nullptr ? min(row_counts[i], *span) : *span;
+  return c > 0 ? c : 0;
+}
+
 // One thread per request: matching prefix, next token / position, slot update, wire buffer.
 __global__ void greedy_finish_kernel(const int32_t* __restrict__ cu_rows, int n, int rows,
+                                     const int32_t* __restrict__ row_counts,
                                      const int64_t* __restrict__ tokens, int tokens_width,
                                      const int64_t* __restrict__ starts, const int64_t* __restrict__ slots,
                                      int64_t* __restrict__ slot_values, int64_t* __restrict__ result) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const int a = cu_rows[i], c = cu_rows[i + 1] - a;
+  int a, span;
+  const int c = request_rows(cu_rows, row_counts, i, &a, &span);
+  for (int j = c; j < span; ++j) result[a + j] = -1;  // padding rows carry no target
+  if (c == 0) {
+    result[rows + i] = 0;
+    result[rows + n + i] = starts[i];
+    return;
+  }
   const int64_t* tok = tokens + static_cast<int64_t>(i) * tokens_width;
   int accepted = 0;
   while (accepted < c - 1 && tok[accepted + 1] == result[a + accepted]) ++accepted;
@@ -573,14 +593,17 @@ __device__ __forceinline__ int request_of_row(const int32_t* cu_rows, int n, int
 template <typename T, int kThreads, bool kStaged>
 __global__ void __launch_bounds__(kThreads)
 row_stats_kernel(const T* __restrict__ target_logits, const T* __restrict__ draft_logits, int64_t row_stride,
-                 int vocab, const int32_t* __restrict__ cu_rows, int n, const int64_t* __restrict__ tokens,
-                 int tokens_width, const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
-                 const float* __restrict__ top_p, RowStats* __restrict__ stats) {
+                 int vocab, const int32_t* __restrict__ cu_rows, int n, const int32_t* __restrict__ row_counts,
+                 const int64_t* __restrict__ tokens, int tokens_width, const float* __restrict__ temperature,
+                 const int32_t* __restrict__ top_k, const float* __restrict__ top_p, RowStats* __restrict__ stats) {
   __shared__ unsigned long long scratch[32];
   __shared__ SelectScratch select;
   const int row = blockIdx.x, side = blockIdx.y;  // side 0: target, 1: draft
   const int i = request_of_row(cu_rows, n, row);
-  const int first = cu_rows[i], count = cu_rows[i + 1] - first, j = row - first;
+  int first, span;
+  const int count = request_rows(cu_rows, row_counts, i, &first, &span);
+  const int j = row - first;
+  if (j >= count) return;  // a padding row: nothing reads its statistics
   const float temp = temperature[i];
   RowStats out = {0.0f, 0.0f, 0.0f, 0, whole_row()};
   if (temp == 0.0f) {
@@ -611,18 +634,28 @@ row_stats_kernel(const T* __restrict__ target_logits, const T* __restrict__ draf
 template <typename T>
 __global__ void __launch_bounds__(kSampleThreads)
 decide_kernel(const T* __restrict__ target_logits, const T* __restrict__ draft_logits, int64_t row_stride, int rows,
-              int vocab, const int32_t* __restrict__ cu_rows, int n, const int64_t* __restrict__ tokens,
-              int tokens_width, const int64_t* __restrict__ starts, const float* __restrict__ temperature,
-              const float* __restrict__ u_accept, const float* __restrict__ u_final,
-              const int64_t* __restrict__ slots, int64_t* __restrict__ slot_values,
-              const RowStats* __restrict__ stats, int64_t* __restrict__ result, int32_t* __restrict__ status) {
+              int vocab, const int32_t* __restrict__ cu_rows, int n, const int32_t* __restrict__ row_counts,
+              const int64_t* __restrict__ tokens, int tokens_width, const int64_t* __restrict__ starts,
+              const float* __restrict__ temperature, const float* __restrict__ u_accept,
+              const float* __restrict__ u_final, const int64_t* __restrict__ slots,
+              int64_t* __restrict__ slot_values, const RowStats* __restrict__ stats,
+              int64_t* __restrict__ result, int32_t* __restrict__ status) {
   __shared__ unsigned long long scratch[32];
   __shared__ int token_slot;
   const int i = blockIdx.x;
-  const int a = cu_rows[i], c = cu_rows[i + 1] - a;
+  int a, span;
+  const int c = request_rows(cu_rows, row_counts, i, &a, &span);
   const int64_t* tok = tokens + static_cast<int64_t>(i) * tokens_width;
   const float temp = temperature[i];
-  for (int j = threadIdx.x; j < c; j += kSampleThreads) result[a + j] = -1;
+  for (int j = threadIdx.x; j < span; j += kSampleThreads) result[a + j] = -1;
+  if (c == 0) {  // no rows: the request is left alone
+    if (threadIdx.x == 0) {
+      result[rows + i] = 0;
+      result[rows + n + i] = starts[i];
+      status[i] = RLT_ROW_OK;
+    }
+    return;
+  }
   __syncthreads();
 
   int accepted = 0, st = RLT_ROW_OK;
@@ -673,7 +706,8 @@ decide_kernel(const T* __restrict__ target_logits, const T* __restrict__ draft_l
     result[rows + i] = accepted;
     result[rows + n + i] = next_pos;
     status[i] = st;
-    if (slots != nullptr && slot_values != nullptr) {
+    // A failed request keeps its slot: the next round must not start from token -1.
+    if (st == RLT_ROW_OK && slots != nullptr && slot_values != nullptr) {
       slot_values[2 * slots[i]] = final_token;
       slot_values[2 * slots[i] + 1] = next_pos;
     }
@@ -708,9 +742,9 @@ extern "C" RLT_API int rlt_argmax_rows(const void* logits, int64_t row_stride, i
 }
 
 extern "C" RLT_API int rlt_accept_greedy(const void* logits, int64_t row_stride, int rows, int vocab, int dtype,
-                                 const int32_t* cu_rows, int n, const int64_t* tokens, int tokens_width,
-                                 const int64_t* starts, const int64_t* slots, int64_t* slot_values,
-                                 int64_t* result, rlt_stream_t stream) {
+                                 const int32_t* cu_rows, int n, const int32_t* row_counts, const int64_t* tokens,
+                                 int tokens_width, const int64_t* starts, const int64_t* slots,
+                                 int64_t* slot_values, int64_t* result, rlt_stream_t stream) {
   using namespace rlt;
   int status = check_logits(logits, row_stride, rows, vocab, dtype);
   if (status != RLT_OK) return status;
@@ -725,8 +759,8 @@ extern "C" RLT_API int rlt_accept_greedy(const void* logits, int64_t row_stride,
     if (status != RLT_OK) return status;
   }
   if (n > 0) {
-    greedy_finish_kernel<<<(n + 127) / 128, 128, 0, s>>>(cu_rows, n, rows, tokens, tokens_width, starts, slots,
-                                                         slot_values, result);
+    greedy_finish_kernel<<<(n + 127) / 128, 128, 0, s>>>(cu_rows, n, rows, row_counts, tokens, tokens_width, starts,
+                                                         slots, slot_values, result);
     status = launch_status("greedy_finish_kernel");
   }
   return status;
@@ -780,13 +814,42 @@ extern "C" RLT_API int rlt_probabilities(const void* logits, int64_t row_stride,
   return launch_status("probabilities_kernel");
 }
 
+namespace rlt {
+namespace {
+__global__ void round_uniforms_kernel(const int64_t* __restrict__ seeds, const int64_t* __restrict__ rounds, int n,
+                                      int width, float* __restrict__ u_draft, float* __restrict__ u_accept,
+                                      float* __restrict__ u_final) {
+  const int x = blockIdx.x * blockDim.x + threadIdx.x;
+  if (x >= n * (2 * width + 1)) return;
+  const int i = x / (2 * width + 1), j = x % (2 * width + 1);
+  const uint64_t seed = static_cast<uint64_t>(seeds[i]), round = static_cast<uint64_t>(rounds[i]);
+  if (j < width) u_draft[i * width + j] = rlt_uniform(seed, round, RLT_STREAM_DRAFT, j);
+  else if (j < 2 * width) u_accept[i * width + j - width] = rlt_uniform(seed, round, RLT_STREAM_ACCEPT, j - width);
+  else u_final[i] = rlt_uniform(seed, round, RLT_STREAM_FINAL, 0);
+}
+}  // namespace
+}  // namespace rlt
+
+extern "C" RLT_API int rlt_round_uniforms(const int64_t* seeds, const int64_t* rounds, int n, int width,
+                                          float* u_draft, float* u_accept, float* u_final, rlt_stream_t stream) {
+  using namespace rlt;
+  RLT_REQUIRE(n >= 0 && width >= 1 && width <= 4096, "round_uniforms: invalid request count or width");
+  if (n == 0) return RLT_OK;
+  RLT_REQUIRE(seeds && rounds && u_draft && u_accept && u_final, "round_uniforms: null pointer");
+  const int total = n * (2 * width + 1);
+  round_uniforms_kernel<<<(total + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      seeds, rounds, n, width, u_draft, u_accept, u_final);
+  return launch_status("round_uniforms_kernel");
+}
+
 extern "C" RLT_API size_t rlt_accept_rejection_workspace_bytes(int rows) {
   return rows > 0 ? static_cast<size_t>(rows) * 2 * sizeof(rlt::RowStats) : 32;
 }
 
 extern "C" RLT_API int rlt_accept_rejection(const void* target_logits, const void* draft_logits, int64_t row_stride,
                                             int rows, int vocab, int dtype, const int32_t* cu_rows, int n,
-                                            const int64_t* tokens, int tokens_width, const int64_t* starts,
+                                            const int32_t* row_counts, const int64_t* tokens, int tokens_width,
+                                            const int64_t* starts,
                                             const float* temperature, const int32_t* top_k, const float* top_p,
                                             const float* u_accept, const float* u_final, const int64_t* slots,
                                             int64_t* slot_values, int64_t* result, int32_t* status_out,
@@ -814,19 +877,20 @@ extern "C" RLT_API int rlt_accept_rejection(const void* target_logits, const voi
       RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
       kernel<<<dim3(rows, 2), kSampleThreads, smem, s>>>(static_cast<const T*>(target_logits),
                                                          static_cast<const T*>(draft_logits), row_stride, vocab, cu_rows,
-                                                         n, tokens, tokens_width, temperature, top_k, top_p, stats);
+                                                         n, row_counts, tokens, tokens_width, temperature, top_k, top_p,
+                                                         stats);
     });
   } else {
     RLT_DISPATCH_DTYPE(dtype, T, (row_stats_kernel<T, kStatsThreads, false><<<dim3(rows, 2), kStatsThreads, 0, s>>>(
                                      static_cast<const T*>(target_logits), static_cast<const T*>(draft_logits),
-                                     row_stride, vocab, cu_rows, n, tokens, tokens_width, temperature, top_k, top_p,
-                                     stats)));
+                                     row_stride, vocab, cu_rows, n, row_counts, tokens, tokens_width, temperature,
+                                     top_k, top_p, stats)));
   }
   status = launch_status("row_stats_kernel");
   if (status != RLT_OK) return status;
   RLT_DISPATCH_DTYPE(dtype, T, (decide_kernel<T><<<n, kSampleThreads, 0, s>>>(
                                    static_cast<const T*>(target_logits), static_cast<const T*>(draft_logits),
-                                   row_stride, rows, vocab, cu_rows, n, tokens, tokens_width, starts, temperature,
-                                   u_accept, u_final, slots, slot_values, stats, result, status_out)));
+                                   row_stride, rows, vocab, cu_rows, n, row_counts, tokens, tokens_width, starts,
+                                   temperature, u_accept, u_final, slots, slot_values, stats, result, status_out)));
   return launch_status("decide_kernel");
 }

@@ -29,20 +29,32 @@ struct AttentionArgs {
 // Table row and number of visible keys of query row `row`.
 // Unpacked: its own table row and context length.  Packed: the sequence s that contains
 // the row, and context_lengths[s] - n_s + i + 1 for its i-th of n_s rows.
-__device__ __forceinline__ void resolve_row(const AttentionArgs& a, int row, int* table_row, int* len) {
+// The lengths live on the device (graph replays change them without the host seeing them), so
+// a length beyond what the row's table can address (table_width * block_size tokens) is
+// clamped here: no kernel ever indexes a table row past its width.  `*clamped` (optional) is
+// set when that happened, so that the caller can report it.
+__device__ __forceinline__ void resolve_row(const AttentionArgs& a, int row, int* table_row, int* len,
+                                            bool* clamped = nullptr) {
+  const int64_t capacity64 = static_cast<int64_t>(a.table_width) * a.block_size;
+  const int capacity = capacity64 > 0x7fffffff ? 0x7fffffff : static_cast<int>(capacity64);
+  int n;
   if (a.cu_seqlens_q == nullptr) {
     *table_row = row;
-    *len = a.context_lengths[row];
-    return;
+    n = a.context_lengths[row];
+  } else {
+    int lo = 0, hi = a.table_rows - 1;  // last s with cu[s] <= row
+    while (lo < hi) {
+      int mid = (lo + hi + 1) >> 1;
+      if (a.cu_seqlens_q[mid] <= row) lo = mid; else hi = mid - 1;
+    }
+    const int first = a.cu_seqlens_q[lo], count = a.cu_seqlens_q[lo + 1] - first;
+    *table_row = lo;
+    n = a.context_lengths[lo] - count + (row - first) + 1;
   }
-  int lo = 0, hi = a.table_rows - 1;  // last s with cu[s] <= row
-  while (lo < hi) {
-    int mid = (lo + hi + 1) >> 1;
-    if (a.cu_seqlens_q[mid] <= row) lo = mid; else hi = mid - 1;
+  if (n > capacity) {
+    n = capacity;
+    if (clamped != nullptr) *clamped = true;
   }
-  const int first = a.cu_seqlens_q[lo], count = a.cu_seqlens_q[lo + 1] - first;
-  *table_row = lo;
-  const int n = a.context_lengths[lo] - count + (row - first) + 1;
   *len = n > 0 ? n : 0;
 }
 
@@ -64,6 +76,7 @@ int run_attention_sm100(const AttentionArgs& a, void* workspace, size_t workspac
 // launch_attention_sm100 on the library's built-in 32 MiB scratch block (no allocation anywhere).
 size_t attention_sm100_builtin_scratch_bytes();
 int launch_attention_sm100_builtin(const AttentionArgs& a, cudaStream_t stream);
+int attention_sm100_builtin_warmup();
 // attention_prefill_sm100.cu: packed causal prefill (tcgen05 kernels with 256 / 128 query tokens
 // per CTA, an mma.sync one with 64), the same shapes.
 bool prefill_sm100_supported(const AttentionArgs& a);

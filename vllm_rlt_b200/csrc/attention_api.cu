@@ -131,7 +131,10 @@ extern "C" RLT_API int rlt_verify_attention_noalloc(const void* q, void* out, co
   a.dtype = dtype; a.block_tables = block_tables; a.table_rows = table_rows; a.table_width = table_width;
   a.context_lengths = context_lengths; a.cu_seqlens_q = cu_seqlens_q; a.rows = rows;
   int status = check_args(a);
-  if (status != RLT_OK || rows == 0) return status;
+  if (status != RLT_OK) return status;
+  // A call without rows is the warm-up: it loads the library's device image (and with it the
+  // built-in block) and resolves the block's address for the current device, and launches nothing.
+  if (rows == 0) return attention_sm100_builtin_warmup();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (attention_sm100_supported(a)) return launch_attention_sm100_builtin(a, s);
   return launch_attention_generic(a, s);  // shapes outside the tiled kernel use no scratch at all

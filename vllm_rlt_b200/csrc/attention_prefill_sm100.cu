@@ -114,7 +114,7 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap kv_map, AttentionAr
   const int q_head = blockIdx.y, kv_head = q_head / (a.q_heads / a.kv_heads);
   const int seq_first = a.cu_seqlens_q[tile.seq];
   const int n_new = a.cu_seqlens_q[tile.seq + 1] - seq_first;
-  const int base_len = a.context_lengths[tile.seq] - n_new + 1;   // keys visible to the sequence's first new token
+  const int base_len = min(a.context_lengths[tile.seq], a.table_width * kPage) - n_new + 1;   // keys visible to the sequence's first new token
   // visible keys of fragment rows g and g + 8 of this warp (0 for rows beyond the tile)
   const int row0 = warp * 16 + g, row1 = row0 + 8;
   const int len0 = row0 < tile.count ? max(base_len + tile.first + row0, 0) : 0;
@@ -409,7 +409,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   const int q_head = blockIdx.y, kv_head = q_head / (a.q_heads / a.kv_heads);
   const int seq_first = a.cu_seqlens_q[tile.seq];
   const int n_new = a.cu_seqlens_q[tile.seq + 1] - seq_first;
-  const int base_len = a.context_lengths[tile.seq] - n_new + 1;
+  const int base_len = min(a.context_lengths[tile.seq], a.table_width * kPage) - n_new + 1;
   const int len = (!issuer && row < tile.count) ? max(base_len + tile.first + row, 0) : 0;   // keys this thread's row sees
   const int kv_end = max(base_len + tile.first + tile.count - 1, 0);
   const int total_pages = (kv_end + kPage - 1) / kPage;
@@ -695,7 +695,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   const int q_head = blockIdx.y, kv_head = q_head / (a.q_heads / a.kv_heads);
   const int seq_first = a.cu_seqlens_q[tile.seq];
   const int n_new = a.cu_seqlens_q[tile.seq + 1] - seq_first;
-  const int base_len = a.context_lengths[tile.seq] - n_new + 1;
+  const int base_len = min(a.context_lengths[tile.seq], a.table_width * kPage) - n_new + 1;
   // key stages of the two query tiles: tile 1 (the later rows) sees every stage tile 0 does
   const int count0 = min(tile.count, kUmmaRows), count1 = max(tile.count - kUmmaRows, 0);
   const int stages0 = (max(base_len + tile.first + count0 - 1, 0) + kUmmaKeys - 1) / kUmmaKeys;

@@ -47,6 +47,7 @@ namespace {
 constexpr int kPartialStride = 132;               // floats per stored partial: O[128], m, l, pad
 constexpr int kPlanThreads = 1024;
 constexpr int kMaxGroupRows = 16;
+constexpr unsigned kErrorWaitGaveUp = 1u, kErrorLengthClamped = 2u;
 constexpr int kSizeClasses = 64;                  // list B is bucketed by pages in the last chunk (64 or more share a class)
 
 // ---- context chunks -------------------------------------------------------------------
@@ -83,7 +84,7 @@ struct Header {
   unsigned full_items;   // items of list A (full-size chunks)
   unsigned last_items;   // items of list B (last chunk of every group)
   unsigned next_item;    // claim counter of the main kernel
-  unsigned error;        // nonzero: a bounded wait gave up
+  unsigned error;        // bit 0: a bounded wait gave up; bit 1: a context length exceeded its table and was clamped
   unsigned plan_done;    // CTAs of the plan kernel that finished phase 1
   unsigned zero_rows;    // rows of length 0 (their output is zero-filled by every run)
   unsigned exited;       // warps of the running main kernel that have finished
@@ -174,7 +175,9 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
   const int row = blockIdx.x * (kPlanThreads / 32) + warp;
   if (row < a.rows) {
     int table_row, len;
-    resolve_row(a, row, &table_row, &len);
+    bool clamped = false;
+    resolve_row(a, row, &table_row, &len, &clamped);
+    if (clamped && lane == 0) atomicOr(&ws.header->error, kErrorLengthClamped);
     int link = 0;
     if (len > 0 && row > 0) {
       int prev_table, prev_len;
@@ -313,8 +316,7 @@ plan_kernel(AttentionArgs a, Workspace ws, int cap) {
   if (threadIdx.x == 0) {
     ws.header->full_items = s_base_full;
     ws.header->last_items = s_base_last;
-    ws.header->next_item = 0;
-    ws.header->error = 0;
+    ws.header->next_item = 0;   // `error` keeps what phase 1 recorded (the header is zeroed before every plan)
     ws.header->plan_done = 0;
     ws.header->exited = 0;
   }
@@ -703,7 +705,7 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
   }
 
   if (failed) {
-    if (lane == 0) atomicOr(&ws.header->error, 1u);
+    if (lane == 0) atomicOr(&ws.header->error, kErrorWaitGaveUp);
     // let copies already in flight land before the shared memory is released
     for (unsigned n = consumed + 1; n < issued; ++n) mbar_wait(bar_base + (n % kStages) * 8, (n / kStages) & 1);
   }
@@ -887,6 +889,13 @@ int builtin_scratch_address(void** address) {
 }  // namespace
 
 size_t attention_sm100_builtin_scratch_bytes() { return kBuiltinScratchBytes; }
+
+// Looks the block up for the current device without launching anything: the one-time set-up a
+// host performs before it hands its remaining device memory to something else.
+int attention_sm100_builtin_warmup() {
+  void* scratch = nullptr;
+  return builtin_scratch_address(&scratch);
+}
 
 int launch_attention_sm100_builtin(const AttentionArgs& a, cudaStream_t stream) {
   const size_t need = make_layout(a.rows, a.q_heads, a.kv_heads, a.block_size, a.table_width).total;

@@ -25,7 +25,11 @@ rollback_kernel(const int64_t* __restrict__ starts, const int64_t* __restrict__ 
   const int64_t f = starts[i] + emitted[i];
   const int64_t page = f / block_size;
   if (lane == 0) frontier[i] = f;
-  if (f < 0 || page >= table_width) {
+  // truncate_suffix accepts 0 <= frontier <= max_tokens: a request that filled its allocation to
+  // the last token of its last page is rolled back like any other; only the page of its NEXT
+  // token does not exist (write_blocks = -1).
+  const bool full = f == static_cast<int64_t>(table_width) * block_size;
+  if (f < 0 || (page >= table_width && !full)) {
     if (lane == 0) status[i] = RLT_ROW_BAD_POSITION;
     return;
   }
@@ -50,7 +54,7 @@ rollback_kernel(const int64_t* __restrict__ starts, const int64_t* __restrict__ 
       if (w[x] > f) w[x] = f;
   }
   for (int p = lane; p < planes; p += 32)
-    write_blocks[static_cast<int64_t>(i) * planes + p] = mine[static_cast<int64_t>(p) * table_width + page];
+    write_blocks[static_cast<int64_t>(i) * planes + p] = full ? -1 : mine[static_cast<int64_t>(p) * table_width + page];
   if (lane == 0) {
     context_lengths[i] = static_cast<int32_t>(f + 1);
     write_offsets[i] = f % block_size;

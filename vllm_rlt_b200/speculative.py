@@ -35,10 +35,15 @@ def _check_logits(logits):
         raise ValueError("logits must be [rows, vocab] float32/float16/bfloat16 with unit inner stride")
 
 
-def _check_round(rows, cu_rows, tokens, starts, slots, slot_values):
+def _check_round(rows, cu_rows, tokens, starts, slots, slot_values, row_counts=None, result=None):
     n = cu_rows.numel() - 1
     if cu_rows.dtype != torch.int32 or cu_rows.dim() != 1 or n < 0:
         raise ValueError("cu_rows must be int32 [requests + 1]")
+    if row_counts is not None and (row_counts.dtype != torch.int32 or row_counts.shape != (n,)):
+        raise ValueError("row_counts must be int32 [requests]")
+    if result is not None and (result.dtype != torch.int64 or result.dim() != 1 or result.numel() < rows + 2 * n
+                               or not result.is_contiguous()):
+        raise ValueError("result must be contiguous int64 with at least rows + 2 * requests elements")
     if tokens.dtype != torch.int64 or tokens.dim() != 2 or tokens.shape[0] != n or not tokens.is_contiguous():
         raise ValueError("tokens must be contiguous int64 [requests, width]")
     if starts.dtype != torch.int64 or starts.shape != (n,):
@@ -69,27 +74,31 @@ def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
     return targets
 
 
-def accept_greedy(logits, cu_rows, tokens, starts, slots=None, slot_values=None, result=None):
+def accept_greedy(logits, cu_rows, tokens, starts, slots=None, slot_values=None, result=None, row_counts=None):
     """Greedy acceptance of a whole round on the device; returns the int64 wire buffer.
 
     ``result[:rows]`` are the target ids of every verification row, ``result[rows:rows+n]``
     the accepted counts, ``result[rows+n:]`` the next positions; ``slot_values[slots[i]]``
-    receives ``(next_token, next_position)``.  No generator is touched.
+    receives ``(next_token, next_position)``.  No generator is touched.  ``row_counts`` (int32
+    ``[n]``) marks how many rows of each request's span are real in a round of fixed shape; the
+    padding rows get -1 and a request without rows is left alone.
     """
-    _capi.require_cuda(logits, cu_rows, tokens, starts, slots, slot_values, result)
+    _capi.require_cuda(logits, cu_rows, tokens, starts, slots, slot_values, result, row_counts)
     _check_logits(logits)
     rows = logits.shape[0]
-    n = _check_round(rows, cu_rows, tokens, starts, slots, slot_values)
+    n = _check_round(rows, cu_rows, tokens, starts, slots, slot_values, row_counts, result)
     if result is None:
         result = torch.empty(rows + 2 * n, dtype=torch.int64, device=logits.device)
-    elif result.dtype != torch.int64 or result.numel() < rows + 2 * n or not result.is_contiguous():
-        raise ValueError("result must be contiguous int64 with at least rows + 2 * requests elements")
     if n == 0:
         return result
+    # contiguous copies are bound to names so that they outlive the launch
+    cu_rows, starts = cu_rows.contiguous(), starts.contiguous()
+    row_counts = None if row_counts is None else row_counts.contiguous()
+    slots = None if slots is None else slots.contiguous()
     with torch.cuda.device(logits.device):
         status = _capi.load().rlt_accept_greedy(
             _capi.ptr(logits), logits.stride(0), rows, logits.shape[1], _capi.DTYPE_CODES[logits.dtype],
-            _capi.ptr(cu_rows.contiguous()), n, _capi.ptr(tokens), tokens.shape[1], _capi.ptr(starts.contiguous()),
+            _capi.ptr(cu_rows), n, _capi.ptr(row_counts), _capi.ptr(tokens), tokens.shape[1], _capi.ptr(starts),
             _capi.ptr(slots), _capi.ptr(slot_values), _capi.ptr(result), _capi.stream_of(logits))
     _capi.check(status, "accept_greedy")
     return result
@@ -159,7 +168,8 @@ def sample_rows(logits, temperature, uniforms, top_k=None, top_p=None):
 
 
 def accept_rejection(target_logits, draft_logits, cu_rows, tokens, starts, temperature, u_accept, u_final,
-                     slots=None, slot_values=None, result=None, top_k=None, top_p=None):
+                     slots=None, slot_values=None, result=None, top_k=None, top_p=None, row_counts=None,
+                     status=None, workspace=None):
     """Rejection-sampling acceptance of a whole round; returns ``(result, status)``.
 
     ``result[cu_rows[i] : cu_rows[i] + accepted_i + 1]`` are request i's emitted tokens (its
@@ -168,39 +178,79 @@ def accept_rejection(target_logits, draft_logits, cu_rows, tokens, starts, tempe
     Use ``raise_for_status`` to turn them into those exceptions after the one host read of a
     round.  ``temperature[i] == 0`` takes the greedy branch for that request.  ``top_k`` /
     ``top_p`` are per request and filter both the target and the proposal distribution, as the
-    reference builds both with the request's ``SamplingParams``.
+    reference builds both with the request's ``SamplingParams``.  ``row_counts`` as in
+    ``accept_greedy``.  ``status`` (int32 ``[n]``) and ``workspace`` (uint8, at least
+    ``rlt_accept_rejection_workspace_bytes(rows)``) may be passed by a caller that owns its buffers.
     """
     _capi.require_cuda(target_logits, draft_logits, cu_rows, tokens, starts, temperature, u_accept, u_final,
-                       slots, slot_values, result, top_k, top_p)
+                       slots, slot_values, result, top_k, top_p, row_counts, status, workspace)
     _check_logits(target_logits)
     _check_logits(draft_logits)
     if target_logits.shape != draft_logits.shape or target_logits.stride() != draft_logits.stride() \
             or target_logits.dtype != draft_logits.dtype:
         raise ValueError("target and draft logits must share shape, strides and dtype")
     rows = target_logits.shape[0]
-    n = _check_round(rows, cu_rows, tokens, starts, slots, slot_values)
+    n = _check_round(rows, cu_rows, tokens, starts, slots, slot_values, row_counts, result)
     for name, t, count in (("temperature", temperature, n), ("u_accept", u_accept, rows), ("u_final", u_final, n)):
         if t.dtype != torch.float32 or t.shape != (count,):
             raise ValueError(f"{name} must be float32 [{count}]")
     top_k, top_p = _check_filters(top_k, top_p, n, "requests")
     if result is None:
         result = torch.empty(rows + 2 * n, dtype=torch.int64, device=target_logits.device)
-    status = torch.zeros(n, dtype=torch.int32, device=target_logits.device)
+    if status is None:
+        status = torch.zeros(n, dtype=torch.int32, device=target_logits.device)
+    elif status.dtype != torch.int32 or status.shape != (n,) or not status.is_contiguous():
+        raise ValueError("status must be contiguous int32 [requests]")
     if n == 0:
         return result, status
     lib = _capi.load()
-    workspace = torch.empty(lib.rlt_accept_rejection_workspace_bytes(rows), dtype=torch.uint8,
-                            device=target_logits.device)
+    need = lib.rlt_accept_rejection_workspace_bytes(rows)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=target_logits.device)
+    elif workspace.dtype != torch.uint8 or workspace.numel() < need or not workspace.is_contiguous():
+        raise ValueError(f"workspace must be contiguous uint8 with at least {need} bytes")
+    cu_rows, starts, temperature = cu_rows.contiguous(), starts.contiguous(), temperature.contiguous()
+    u_accept, u_final = u_accept.contiguous(), u_final.contiguous()
+    row_counts = None if row_counts is None else row_counts.contiguous()
+    slots = None if slots is None else slots.contiguous()
     with torch.cuda.device(target_logits.device):
         code = lib.rlt_accept_rejection(
             _capi.ptr(target_logits), _capi.ptr(draft_logits), target_logits.stride(0), rows,
-            target_logits.shape[1], _capi.DTYPE_CODES[target_logits.dtype], _capi.ptr(cu_rows.contiguous()), n,
-            _capi.ptr(tokens), tokens.shape[1], _capi.ptr(starts.contiguous()),
-            _capi.ptr(temperature.contiguous()), _capi.ptr(top_k), _capi.ptr(top_p),
-            _capi.ptr(u_accept.contiguous()), _capi.ptr(u_final.contiguous()), _capi.ptr(slots), _capi.ptr(slot_values), _capi.ptr(result),
-            _capi.ptr(status), _capi.ptr(workspace), workspace.numel(), _capi.stream_of(target_logits))
+            target_logits.shape[1], _capi.DTYPE_CODES[target_logits.dtype], _capi.ptr(cu_rows), n,
+            _capi.ptr(row_counts), _capi.ptr(tokens), tokens.shape[1], _capi.ptr(starts), _capi.ptr(temperature),
+            _capi.ptr(top_k), _capi.ptr(top_p), _capi.ptr(u_accept), _capi.ptr(u_final), _capi.ptr(slots),
+            _capi.ptr(slot_values), _capi.ptr(result), _capi.ptr(status), _capi.ptr(workspace), workspace.numel(),
+            _capi.stream_of(target_logits))
     _capi.check(code, "accept_rejection")
     return result, status
+
+
+def round_uniforms(seeds, rounds, width: int):
+    """Uniforms of one round: ``(u_draft [n, width], u_accept [n, width], u_final [n])``, float32.
+
+    The device counterpart of the per-request generators of the reference's ``RngRegistry``
+    (``vllm_rlt/worker/sampler.py:84-119``): a counter-based generator keyed by the request's
+    seed and its round number, so no host generator has to be consulted between rounds and a
+    request's draws do not depend on the batch it runs in.  ``seeds``, ``rounds``: int64 ``[n]``.
+    """
+    device = _capi.require_cuda(seeds, rounds)
+    n = seeds.numel()
+    for name, t in (("seeds", seeds), ("rounds", rounds)):
+        if t.dtype != torch.int64 or t.shape != (n,):
+            raise ValueError(f"{name} must be int64 [requests]")
+    if not 1 <= width <= 4096:
+        raise ValueError("width must be in [1, 4096]")
+    u_draft = torch.empty(n, width, dtype=torch.float32, device=device)
+    u_accept = torch.empty(n, width, dtype=torch.float32, device=device)
+    u_final = torch.empty(n, dtype=torch.float32, device=device)
+    if n == 0:
+        return u_draft, u_accept, u_final
+    seeds, rounds = seeds.contiguous(), rounds.contiguous()
+    with torch.cuda.device(device):
+        code = _capi.load().rlt_round_uniforms(_capi.ptr(seeds), _capi.ptr(rounds), n, width, _capi.ptr(u_draft),
+                                               _capi.ptr(u_accept), _capi.ptr(u_final), _capi.stream_of(seeds))
+    _capi.check(code, "round_uniforms")
+    return u_draft, u_accept, u_final
 
 
 @dataclass
