@@ -2,30 +2,36 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-One *step* is one pass of the verify hot path over one batch of synthetic input at the
-kernel-microbench shape of BASELINE.json (configs[1]) extended over the 24 layers of the
-Ouro-1.4B shape:
+The contract line measures two things in one process per GPU.
 
-    for each of 24 layers:  KV write of the new tokens -> grouped paged verify attention
-                            (64 requests, 16 heads x 128, 16-token pages, contexts U[512, 4096],
-                             16 rows per request = 4 tokens x 4 loop depths, shared depth plane)
-                         -> SiLU-and-Mul on [1024, 5632]
-    then                    greedy acceptance and rejection-sampling acceptance (T = 0.8) on
-                            64 x 4 rows of 49152 fp32 logits, and the device rollback.
+1. Self-speculative decoding of an Ouro-1.4B-shaped model (24 layers, hidden 2048, 16 x 128 MHA,
+   SwiGLU 5632, vocab 49152, 4 recurrent loops, random-init bf16): 128 concurrent requests with
+   prompts of uniform-random tokens, lengths U[128, 1024], k = 4 drafts from loop depth 2 verified at
+   depth 4, rejection sampling at temperature 0.8, through `SelfSpeculativeDecoder` /
+   `B200SpeculativeRunner`.  A *step* is one speculative round of the whole batch (5 draft passes of
+   128 rows through 2 loops, 2 verify passes of 640 rows, LM head, acceptance, rollback — one CUDA
+   graph).  After the prompts are in the cache and the graph exists, W warm-up rounds run, then K
+   rounds are timed with CUDA events (`value` = accepted tokens per second; committed tokens per
+   second and the acceptance rate beside it), then K more rounds are timed on the host clock from
+   `runner.submit(batch)` (Python request objects in) to `ticket.collect()` (Python token lists out):
+   `e2e`.  The GEMMs of the model are cuBLAS call sites; every other kernel is this library's.
+2. The verify attention alone at the kernel-microbench shape (64 requests, contexts U[512, 4096],
+   16 rows per request = 4 tokens x 4 loop depths on a shared plane, 24-layer pool): its CUDA-event
+   time per layer call against its algorithmic bytes is the `roofline` block, and its output for a
+   few requests is compared with the CPU oracle (`parity`).
 
-The model GEMMs / norms / RoPE between these calls are not part of the path and are not run.
-`value` is accepted tokens per second (device-resident inputs); committed tokens (accepted + 1
-per request) are reported beside it.  `e2e` is the same step driven from pinned host buffers
-through the public Python API (H2D of every input and D2H of the result inside the timed
-region).  One process per GPU; every rank runs an independent replica on its own requests
-(no collective on the path), the timed region is bracketed by a barrier, and the step time is
-the maximum over ranks.
+With N GPUs every rank is an independent engine replica that decodes the same 128 seeded requests
+(no collective on the path); the timed regions are bracketed by a barrier, the step time is the
+maximum over ranks and the tokens are summed, so the aggregate depends on step times only.
 
 Other entry points (each prints its own JSON line; none is the contract line above):
-    --workload decode [--requests R --output-tokens T --temperature X --eager --prompt-min A --prompt-max B
-                       --shared-prefix P --prefix-caching]
-                      whole-model self-speculative decoding of a random-init Ouro-1.4B-shaped model
-                      (BASELINE configs[2]) with its HBM roofline
+    --workload decode [--requests R --output-tokens T --temperature X --k K --eager --prompt-min A --prompt-max B
+                       --shared-prefix P --prefix-caching --in-flight F]
+                      one complete generation (prompt pass included in `total_seconds`)
+    --workload sharded [--total-requests R ...]
+                      R requests in total (default 1024, prompts U[256, 2048], 512 output tokens, k = 6),
+                      length-balanced over the ranks and decoded to completion in waves that fit the KV
+                      pool: whole-job strong scaling
     --only attention  [--requests --layers --tokens --depths --kv-heads --context-min --context-max --shared-plan]
     --only prefill    [--requests --tokens --kv-heads --eager]   packed causal prefill, TFLOP/s
     --only accept | --only silu                                  the small kernels at the step's shapes
@@ -34,6 +40,7 @@ Other entry points (each prints its own JSON line; none is the contract line abo
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -51,10 +58,12 @@ if str(ROOT) not in sys.path:
 LAYERS, HEADS, HEAD_DIM, BLOCK, FFN, VOCAB = 24, 16, 128, 16, 5632, 49152
 REQUESTS, TOKENS, DEPTHS = 64, 4, 4
 TEMPERATURE = 0.8
+DECODE_REQUESTS, DECODE_PROMPTS, DECODE_K, DECODE_OUTPUT = 128, (128, 1024), 4, 256
+DRAFT_LOOPS, TARGET_LOOPS = 2, 4
 METRIC = "accepted tokens/s/GPU, Ouro-1.4B self-spec decode; verify-attn % HBM peak"
-# DRAM bytes (read + write) per algorithmic byte of verify_attention_kernel, from the ncu capture
-# summarised in profiles/verify_attention_kernel_config2.md (32-request case; traffic grows in
-# proportion to the K/V read, so the ratio carries over to a full launch).
+# DRAM bytes (read + write) per algorithmic byte of verify_attention_kernel, from an ncu capture of a
+# 32-request launch of the same kernel (654.4 + 7.9 MB moved for 653.9 MB algorithmic); traffic grows
+# in proportion to the K/V read, so the ratio carries over to a full launch.
 ATTENTION_TRAFFIC_RATIO = 1.0128
 
 
@@ -148,7 +157,10 @@ def combine_ranks(stats, world: int, steps: int, gather=None):
     Replicas are independent, so the job's step time is the slowest rank's (max over ranks) and its
     tokens are the sum over ranks.  `gather(tensor) -> [world, 4]` collects the rows
     (torch.distributed all_gather in a multi-rank run)."""
-    table = stats[None] if gather is None or world == 1 else gather(stats)
+    if stats.dim() == 2:
+        table = stats                                      # already one row per rank
+    else:
+        table = stats[None] if gather is None or world == 1 else gather(stats)
     max_ms, max_e2e_ms = float(table[:, 0].max()), float(table[:, 1].max())
     accepted, committed = float(table[:, 2].sum()), float(table[:, 3].sum())
     ms_per_step = max_ms / steps
@@ -227,31 +239,134 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(self.samples)}
 
 
-def bind_to_gpu_numa_node(local: int):
-    """Runs this process on the cores of the NUMA node its GPU hangs off (sysfs; a process
-    setting, nothing of the GPU's changes), so that the pinned staging buffers of the host-driven
-    step are first touched — and therefore placed — in that node's memory.  With several replicas
-    per machine the uploads otherwise share one node's memory channels and the socket link.
-    Returns the node, or None when the topology cannot be read."""
-    try:
-        bus = torch.cuda.get_device_properties(local).pci_bus_id
-        domain = torch.cuda.get_device_properties(local).pci_domain_id
-        device_id = torch.cuda.get_device_properties(local).pci_device_id
-        path = f"/sys/bus/pci/devices/{domain:04x}:{bus:02x}:{device_id:02x}.0/numa_node"
-        node = int(open(path).read())
-        if node < 0:
-            return None
-        cpus = set()
-        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
-            lo, _, hi = part.partition("-")
-            cpus.update(range(int(lo), int(hi or lo) + 1))
-        allowed = cpus & os.sched_getaffinity(0)
-        if not allowed:
-            return None
-        os.sched_setaffinity(0, allowed)
-        return node
-    except (OSError, ValueError, AttributeError):
-        return None
+def decode_prompts(requests: int, prompt_range, vocab: int, seed: int = 11):
+    """Uniform-random token prompts with lengths U[prompt_range] (the same list for a given seed)."""
+    g = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(prompt_range[0], prompt_range[1] + 1, (requests,), generator=g).tolist()
+    return [torch.randint(1, vocab, (n,), generator=g).tolist() for n in lengths]
+
+
+def decode_round_bytes(config, stats_before, stats_after, rounds: int, k: int):
+    """Algorithmic HBM bytes of `rounds` speculative rounds: every recurrent pass streams the layer
+    weights once and, per layer, the K/V of every context it attends to once per request; every LM-head
+    call streams lm_head once (k draft calls and one verify call per round).  Activations and logits are
+    left out (a few percent)."""
+    c = config
+    layer_params = (c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim
+                    + c.num_attention_heads * c.head_dim * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
+    passes = stats_after.loop_passes - stats_before.loop_passes
+    context_tokens = stats_after.context_tokens_read - stats_before.context_tokens_read
+    weight_bytes = 2.0 * c.num_hidden_layers * layer_params * passes
+    kv_bytes = 2.0 * 2 * c.num_key_value_heads * c.head_dim * c.num_hidden_layers * context_tokens
+    head_bytes = 2.0 * c.vocab_size * c.hidden_size * (k + 1) * rounds
+    return {"weight_bytes": weight_bytes, "kv_bytes": kv_bytes, "lm_head_bytes": head_bytes,
+            "total": weight_bytes + kv_bytes + head_bytes}
+
+
+def launches_per_round(config, k: int, draft_loops: int, target_loops: int, sampled: bool) -> int:
+    """Kernels of this library in one round's graph (the cuBLAS GEMMs and the small index kernels of
+    the host layer are not counted): per recurrent pass one attention plan, one opening norm and per
+    layer rope_kv_write, attention + merge, SiLU-and-Mul and two sandwich norms; per draft offset one
+    proposal kernel; acceptance (two launches), the round's uniforms when sampling, rollback."""
+    passes = draft_loops * (k + 1) + target_loops - draft_loops
+    per_pass = 2 + 6 * config.num_hidden_layers
+    return passes * per_pass + k + 2 + (1 if sampled else 0) + 1
+
+
+def copy_stats(stats):
+    import copy
+
+    return copy.copy(stats)
+
+
+def attention_roofline(device, steps: int, warmup: int, parity_requests: int):
+    """The verify attention at the kernel-microbench shape inside a 24-layer pass (KV write ->
+    attention -> SiLU-and-Mul per layer, one plan per pass): CUDA-event time per attention call, its
+    algorithmic bytes, and a comparison of layer 0's output for `parity_requests` requests with the
+    CPU oracle.  Returns (roofline dict, parity dict, launches)."""
+    import vllm_rlt_b200 as rlt
+
+    work = Workload(seed=1234)
+    g = torch.Generator(device=device).manual_seed(99)
+    pool_shape = (work.total_pages, LAYERS, BLOCK, HEADS, HEAD_DIM)
+    key_pool = torch.empty(pool_shape, dtype=torch.bfloat16, device=device)
+    value_pool = torch.empty(pool_shape, dtype=torch.bfloat16, device=device)
+    for pool in (key_pool, value_pool):  # N(0,1) * 0.5, generated in slabs to bound temporaries
+        flat = pool.view(-1)
+        slab = 1 << 28
+        for start in range(0, flat.numel(), slab):
+            n = min(slab, flat.numel() - start)
+            flat[start:start + n] = (torch.randn(n, device=device, generator=g) * 0.5).to(torch.bfloat16)
+
+    def mk(*shape, scale=1.0):
+        return (torch.randn(*shape, device=device, generator=g) * scale).to(torch.bfloat16)
+
+    q = mk(LAYERS, work.rows, HEADS, HEAD_DIM, scale=0.5)
+    k_new = mk(LAYERS, work.kv_rows, HEADS, HEAD_DIM, scale=0.5)
+    v_new = mk(LAYERS, work.kv_rows, HEADS, HEAD_DIM, scale=0.5)
+    gate, up = mk(work.rows, FFN, scale=3.0), mk(work.rows, FFN)
+    tables, lengths = work.tables.to(device), work.lengths.to(device)
+    write_blocks, write_offsets = work.write_blocks.to(device), work.write_offsets.to(device)
+    backend = rlt.create_backend(device, torch.bfloat16, HEAD_DIM, BLOCK)
+    events, launches, first_out = [], 0, None
+    for step in range(warmup + steps):
+        with backend.kernel.shared_plan():
+            for layer in range(LAYERS):
+                kc, vc = key_pool[:, layer], value_pool[:, layer]
+                rlt.kv_write(kc, vc, k_new[layer], v_new[layer], write_blocks, write_offsets)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                out = backend(q[layer], kc, vc, tables, lengths)
+                b.record()
+                rlt.silu_and_mul(gate, up)
+                if step >= warmup:
+                    events.append((a, b))
+                    launches += 4
+                if step == 0 and layer == 0:
+                    first_out = out
+        launches += 1 if step >= warmup else 0
+    torch.cuda.synchronize()
+    attention_ms = statistics.mean(a.elapsed_time(b) for a, b in events)
+    status = backend.kernel.last_status(device)
+    peak, peak_kind = measured_peaks()
+    algorithmic = work.algorithmic_attention_bytes()
+    achieved = algorithmic / (attention_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "verify_attention_kernel + merge_kernel, per layer call of a 24-layer pass "
+                                          "(64 requests, ctx U[512,4096], 16 rows per request on a shared plane; "
+                                          "inputs larger than L2: 34 GB pool streamed once per pass)",
+                "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": ATTENTION_TRAFFIC_RATIO * algorithmic,
+                "traffic_source": "ncu dram bytes of a 32-request launch scaled by algorithmic bytes",
+                "algorithmic_bytes": algorithmic, "avg_launch_ms": attention_ms, "timed_calls": len(events),
+                "attention_status": status}
+    parity = attention_parity(work, first_out, q[0], key_pool, value_pool, parity_requests)
+    return roofline, parity, launches
+
+
+def attention_parity(work, gpu_out, q0, key_pool, value_pool, requests: int):
+    """Layer 0 of the full-size microbench against the CPU oracle for the first `requests` requests:
+    their pages are copied to the host (with the new tokens' K/V already written), renumbered, and the
+    oracle scores the same 16 rows per request.  Tolerance: 2e-2 absolute + 2e-2 relative (bf16)."""
+    from oracle import oracle
+
+    rows_per_request = TOKENS * DEPTHS
+    pages = ((work.contexts + BLOCK - 1) // BLOCK)[:requests]
+    ids = torch.cat([work.request_tables[i, : int(n)] for i, n in enumerate(pages.tolist())]).long()
+    kc = key_pool[ids.to(key_pool.device), 0].cpu()
+    vc = value_pool[ids.to(key_pool.device), 0].cpu()
+    tables = torch.zeros(requests * rows_per_request, int(pages.max()), dtype=torch.int32)
+    offset = 0
+    for i, n in enumerate(pages.tolist()):
+        tables[i * rows_per_request:(i + 1) * rows_per_request, :n] = torch.arange(offset, offset + n, dtype=torch.int32)
+        offset += n
+    rows = requests * rows_per_request
+    want = oracle.paged_attention(q0[:rows].cpu(), kc, vc, tables, work.lengths[:rows]).float()
+    got = gpu_out[:rows].float().cpu()
+    diff = (got - want).abs()
+    bound = 2e-2 + 2e-2 * want.abs()
+    return {"against": "CPU oracle", "requests": requests, "rows": rows, "max_abs": float(diff.max()),
+            "max_rel_of_bound": float((diff / bound).max()), "tolerance": "2e-2 abs + 2e-2 rel (bf16)",
+            "ok": bool((diff <= bound).all())}
 
 
 def run_gpu(args):
@@ -264,7 +379,6 @@ def run_gpu(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    numa = bind_to_gpu_numa_node(local) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
@@ -273,178 +387,126 @@ def run_gpu(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    work = Workload(seed=replica_seed(rank))
-    host = work.host_inputs(pin=True)
-    dev = {name: t.to(device) for name, t in host.items()}
-    g = torch.Generator(device=device).manual_seed(99 + rank)
-    pool_shape = (work.total_pages, LAYERS, BLOCK, HEADS, HEAD_DIM)
-    key_pool = torch.empty(pool_shape, dtype=torch.bfloat16, device=device)
-    value_pool = torch.empty(pool_shape, dtype=torch.bfloat16, device=device)
-    for pool in (key_pool, value_pool):  # N(0,1) * 0.5, generated in slabs to bound temporaries
-        flat = pool.view(-1)
-        step = 1 << 28
-        for start in range(0, flat.numel(), step):
-            n = min(step, flat.numel() - start)
-            flat[start:start + n] = (torch.randn(n, device=device, generator=g) * 0.5).to(torch.bfloat16)
-    backend = rlt.create_backend(device, torch.bfloat16, HEAD_DIM, BLOCK)
-    slot_values = torch.zeros(2 * work.requests, 2, dtype=torch.int64, device=device)
-    per_row_t = dev["temperature"].repeat_interleave(TOKENS)
-    launches = 0
-    attn_events = []
+    # ---- 1. the verify attention alone (roofline + parity), rank 0 ---------------------------
+    roofline = parity = None
+    attention_launches = 0
+    if rank == 0:
+        roofline, parity, attention_launches = attention_roofline(device, steps=min(args.steps, 10), warmup=2,
+                                                                  parity_requests=4)
+        gc.collect()
+        torch.cuda.empty_cache()
 
-    def hot_path(x, timed_attention, before_layer=None, before_accept=None):
-        """One verify pass on device tensors `x`; returns (result buffer, rollback state).
-        The two hooks let a host-driven caller wait for that layer's / the logits' upload."""
-        nonlocal launches
-        # all layers of the pass share the block tables and lengths: plan once, run per layer
-        with backend.kernel.shared_plan():
-            for layer in range(LAYERS):
-                if before_layer is not None:
-                    before_layer(layer)
-                kc, vc = key_pool[:, layer], value_pool[:, layer]
-                rlt.kv_write(kc, vc, x["k"][layer], x["v"][layer], x["write_blocks"], x["write_offsets"])
-                if timed_attention:
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record()
-                backend(x["q"][layer], kc, vc, x["tables"], x["lengths"])
-                if timed_attention:
-                    b.record()
-                    attn_events.append((a, b))
-                rlt.silu_and_mul(x["gate"][layer], x["up"][layer])
-                launches += 3  # kv_write, attention, silu_and_mul
-        launches += 1  # the pass's one attention plan
-        if before_accept is not None:
-            before_accept()
-        # drafts proposed from q with the explicit-uniform rule, then both acceptance modes
-        drafts, _ = rlt.sample_rows(x["draft"], per_row_t, x["u_draft"])
-        tokens = torch.zeros(work.requests, TOKENS, dtype=torch.int64, device=device)
-        tokens[:, 1:] = drafts.view(work.requests, TOKENS)[:, :-1]
-        rlt.accept_greedy(x["target"], x["cu_rows"], tokens, x["starts"], x["slots"], slot_values)
-        result, _ = rlt.accept_rejection(x["target"], x["draft"], x["cu_rows"], tokens, x["starts"],
-                                         x["temperature"], x["u_accept"], x["u_final"], x["slots"], slot_values)
-        accepted = result[work.accept_rows:work.accept_rows + work.requests]
-        rolled = rlt.rollback(x["starts"], accepted + 1, x["request_tables"], BLOCK)
-        launches += 6  # sample_rows, argmax + greedy finish, row stats + decide (rejection), rollback
-        return result, rolled
+    # ---- 2. self-speculative decoding: K rounds on the device clock, K on the host clock ------
+    steps, warmup = args.steps, args.warmup
+    k = DECODE_K
+    e2e_warmup = min(warmup, 3)
+    rounds_needed = warmup + steps + e2e_warmup + steps + 2
+    max_tokens = max(DECODE_OUTPUT, rounds_needed * (k + 1))
+    config = rlt.LoopedLMConfig()
+    model = rlt.LoopedLM(config, rlt.seeded_state_dict(config, 3, device=device), device, torch.bfloat16)
+    prompts = decode_prompts(DECODE_REQUESTS, DECODE_PROMPTS, config.vocab_size)
+    decoder = rlt.SelfSpeculativeDecoder(model, cuda_graphs=True, capture_sizes=[DECODE_REQUESTS])
+    torch.cuda.synchronize()
+    t_open = time.perf_counter()
+    session = decoder.open(prompts, max_tokens, num_speculative_tokens=k, draft_loops=DRAFT_LOOPS,
+                           target_loops=TARGET_LOOPS, temperature=TEMPERATURE, seed=1, in_flight=2)
+    torch.cuda.synchronize()
+    open_seconds = time.perf_counter() - t_open
+    stats = decoder.stats
 
-    # ---- device-resident timing ----
-    for _ in range(args.warmup):
-        hot_path(dev, False)
+    def run_rounds(count):
+        """`count` rounds, two in flight, every one collected before this returns."""
+        submitted = collected = 0
+        while collected < count:
+            while submitted < count and session.submit_round():
+                submitted += 1
+            if not session.collect_round():
+                raise RuntimeError("the requests ran out of output budget inside the timed region")
+            collected += 1
+
+    run_rounds(warmup)
     barrier()
-    launches = 0
     clocks = ClockSampler(local)
-    clocks.__enter__()  # samples until the end of the second (host-driven) timed region
+    clocks.__enter__()
+    before = copy_stats(stats)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(args.steps):
-        result, _ = hot_path(dev, True)
+    run_rounds(steps)
     stop.record()
     barrier()
-    elapsed_ms = start.elapsed_time(stop)
-    launches_per_step = launches // args.steps
-    attention_ms = statistics.mean(a.elapsed_time(b) for a, b in attn_events)
-    accepted_per_step = int(result[work.accept_rows:work.accept_rows + work.requests].sum())
-    committed_per_step = accepted_per_step + work.requests
+    device_ms = start.elapsed_time(stop)
+    after = copy_stats(stats)
+    accepted = after.accepted_tokens - before.accepted_tokens
+    committed = after.committed_tokens - before.committed_tokens
+    drafted = after.drafted_tokens - before.drafted_tokens
+    round_bytes = decode_round_bytes(config, before, after, steps, k)
 
-    # ---- end to end from pinned host buffers through the public API ----
-    # Every step uploads all of its inputs from pinned host memory and reads its result back.
-    # Uploads run on a copy stream, layer by layer, into one of two staging sets, so the copy of
-    # layer l+1 (and of the next step) overlaps the kernels of layer l; the compute stream waits
-    # for exactly the tensors it is about to read.
-    per_layer = ("q", "k", "v", "gate", "up")
-    last = ("target", "draft")
-    first = [name for name in host if name not in per_layer + last]
-    sets = [{name: torch.empty_like(t, device=device) for name, t in host.items()} for _ in range(2)]
-    copy_stream = torch.cuda.Stream(device=device)
-    compute_stream = torch.cuda.current_stream(device)
-    set_free = [None, None]  # event: the compute that used this staging set has finished
-    result_host = torch.empty(work.accept_rows + 2 * work.requests, dtype=torch.int64).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host.values())
-    d2h = result_host.numel() * 8
-    e2e_counter = 0
-
-    def e2e_step():
-        nonlocal e2e_counter
-        which = e2e_counter % 2
-        e2e_counter += 1
-        staged = sets[which]
-        layer_ready = [torch.cuda.Event() for _ in range(LAYERS)]
-        first_ready, last_ready = torch.cuda.Event(), torch.cuda.Event()
-        with torch.cuda.stream(copy_stream):
-            if set_free[which] is not None:
-                copy_stream.wait_event(set_free[which])
-            for name in first:
-                staged[name].copy_(host[name], non_blocking=True)
-            first_ready.record(copy_stream)
-            for layer in range(LAYERS):
-                for name in per_layer:
-                    staged[name][layer].copy_(host[name][layer], non_blocking=True)
-                layer_ready[layer].record(copy_stream)
-            for name in last:
-                staged[name].copy_(host[name], non_blocking=True)
-            last_ready.record(copy_stream)
-        compute_stream.wait_event(first_ready)
-        result, _ = hot_path(staged, False, before_layer=lambda layer: compute_stream.wait_event(layer_ready[layer]),
-                             before_accept=lambda: compute_stream.wait_event(last_ready))
-        result_host.copy_(result, non_blocking=True)
-        done = torch.cuda.Event()
-        done.record(compute_stream)
-        set_free[which] = done
-
-    for _ in range(min(args.warmup, 3)):
-        e2e_step()
+    run_rounds(e2e_warmup)
     barrier()
-    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e_start.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e_stop.record()
+    before_e2e = copy_stats(stats)
+    t0 = time.perf_counter()
+    run_rounds(steps)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
     barrier()
     clocks.__exit__(None, None, None)
-    e2e_ms = e_start.elapsed_time(e_stop)
-    status = backend.kernel.last_status(device)
+    after_e2e = copy_stats(stats)
+    e2e_accepted = after_e2e.accepted_tokens - before_e2e.accepted_tokens
+    runner = decoder.runner
+    nb, w = runner.bucket_of(DECODE_REQUESTS), runner.width
+    h2d, d2h = 3 * nb * 8, (nb * w + 4 * nb) * 8
+    decode_status = model.attention.last_status(device)
+    tokens_host = sum(len(r.generated_token_ids) for r in session.requests)
 
-    times = torch.tensor([elapsed_ms, e2e_ms, float(accepted_per_step), float(committed_per_step)],
+    times = torch.tensor([device_ms, e2e_ms, float(accepted), float(committed), float(e2e_accepted), float(drafted)],
                          dtype=torch.float64, device=device)
-    job = combine_ranks(times if world > 1 else times.cpu(), world, args.steps, all_gather_rows)
+    table = times[None].cpu() if world == 1 else all_gather_rows(times)
     if rank == 0:
-        ms_per_step, value = job["ms_per_step"], job["accepted_tokens_per_s"]
-        accepted_total, committed_total = job["accepted_per_step"], job["committed_per_step"]
+        job = combine_ranks(table[:, :4], world, steps)
+        max_ms, mean_ms = float(table[:, 0].max()), float(table[:, 0].mean())
+        e2e_value = float(table[:, 4].sum()) / (float(table[:, 1].max()) / 1e3)
         peak, peak_kind = measured_peaks()
-        algorithmic = work.algorithmic_attention_bytes()
-        achieved = algorithmic / (attention_ms * 1e-3) / 1e9
+        seconds = device_ms / 1e3
+        per_round = launches_per_round(config, k, DRAFT_LOOPS, TARGET_LOOPS, True)
         line = {
-            "metric": METRIC, "value": value, "unit": "accepted tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "metric": METRIC, "value": job["accepted_tokens_per_s"], "unit": "accepted tokens/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": job["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {
-                "workload": "configs[1] verify-step microbench x 24 layers: 64 requests/GPU, 16x128 MHA, "
-                            "block 16, ctx U[512,4096], 4 tokens x 4 depths shared plane, bf16; sampler 256 rows x "
-                            "49152 fp32 (greedy + rejection T=0.8, draft = target + N(0,0.5)); rollback",
-                "requests_per_gpu": work.requests, "layers": LAYERS, "attention_rows": work.rows,
-                "kv_pool_gb": round(2 * key_pool.numel() * 2 / 1e9, 2),
-                "l2_policy": "inputs larger than L2 (KV pool streamed once per step)",
-                "parallelism": f"{world} independent replicas, no collective",
-                "host_numa_node_rank0": numa,
+                "workload": "configs[2]: Ouro-1.4B-shaped random-init bf16 model (24 layers, hidden 2048, 16x128 MHA, "
+                            "FFN 5632, vocab 49152, 4 loops), 128 concurrent requests per GPU, prompts U[128,1024] of "
+                            "uniform-random tokens, self-speculation k=4 from depth 2 verified at depth 4, rejection "
+                            "sampling T=0.8; step = one speculative round of the whole batch (one CUDA graph), timed "
+                            "in steady state after the prompt pass; roofline block: configs[1] verify attention",
+                "requests_per_gpu": DECODE_REQUESTS, "k": k, "draft_loops": DRAFT_LOOPS, "target_loops": TARGET_LOOPS,
+                "temperature": TEMPERATURE, "output_budget_tokens": max_tokens, "rounds_in_flight": 2,
+                "kv_pool_gb": round(2 * session.runner.cache.key.numel() * 2 / 1e9, 2),
+                "l2_policy": "inputs larger than L2 (every pass streams the active contexts' K/V and the layer weights)",
+                "parallelism": f"{world} independent replicas decoding the same seeded requests, no collective",
+                "prompt_pass_and_graph_capture_seconds": open_seconds,
             },
             "committed_tokens_per_s": job["committed_tokens_per_s"],
-            "acceptance_rate": accepted_total / (world * work.requests * (TOKENS - 1)),
-            "e2e": {"value": job["e2e_accepted_tokens_per_s"], "unit": "accepted tokens/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": job["e2e_ms_per_step"]},
-            "gpu_launches": launches_per_step * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "verify_attention_kernel (per layer call; one plan per 24-layer pass amortised in)",
-                         "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": ATTENTION_TRAFFIC_RATIO * algorithmic,
-                         "traffic_source": "ncu dram bytes of a 32-request launch scaled by algorithmic bytes",
-                         "algorithmic_bytes": algorithmic,
-                         "avg_launch_ms": attention_ms},
+            "acceptance_rate": float(table[:, 2].sum()) / max(float(table[:, 5].sum()), 1.0),
+            "accepted_per_step": job["accepted_per_step"], "committed_per_step": job["committed_per_step"],
+            "rank_time_imbalance_max_over_mean": max_ms / mean_ms,
+            "e2e": {"value": e2e_value, "unit": "accepted tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": float(table[:, 1].max()) / steps,
+                    "path": "runner.submit(Python requests) -> graph replay -> ticket.collect() -> Python token lists, "
+                            "host clock", "tokens_on_host": tokens_host},
+            "gpu_launches": per_round * steps,
+            "hbm_roofline_decode": {**round_bytes, "peak_gbs": peak, "peak_kind": peak_kind,
+                                    "seconds_at_peak": round_bytes["total"] / (peak * 1e9),
+                                    "frac": round_bytes["total"] / (peak * 1e9) / seconds},
+            "roofline": roofline, "parity": parity,
             "clocks": clocks.summary(),
-            "attention_status": status,
+            "attention_status": decode_status,
         }
         if not args.no_cpu_baseline and world == 1:
-            line["cpu_baseline"] = cpu_baseline(threads=os.cpu_count() or 1, budget_s=12.0)
+            del session, decoder, model, runner
+            gc.collect()
+            torch.cuda.empty_cache()
+            line["cpu_baseline"] = cpu_baseline(threads=os.cpu_count() or 1, rounds=2)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -607,7 +669,9 @@ def run_decode_workload(args):
     if args.shared_prefix > 0:   # every second request starts with one common prefix (BASELINE configs[4]'s mix)
         common = torch.randint(1, config.vocab_size, (args.shared_prefix,), generator=g).tolist()
         prompts = [common[:len(p) - 1] + p[len(common[:len(p) - 1]):] if i % 2 else p for i, p in enumerate(prompts)]
-    decoder = rlt.SelfSpeculativeDecoder(model, cuda_graphs=not args.eager, prefix_caching=args.prefix_caching)
+    decoder = rlt.SelfSpeculativeDecoder(model, cuda_graphs=not args.eager, prefix_caching=args.prefix_caching,
+                                         capture_sizes=sorted({args.requests, max(args.requests // 2, 1),
+                                                               max(args.requests // 4, 1)}))
     clock = {}
 
     def start_clock():
@@ -616,8 +680,9 @@ def run_decode_workload(args):
 
     torch.cuda.synchronize()
     clock["begin"] = time.perf_counter()
-    tokens = decoder.generate(prompts, args.output_tokens, num_speculative_tokens=4, draft_loops=2, target_loops=4,
-                              temperature=args.temperature, seed=1, after_prefill=start_clock)
+    tokens = decoder.generate(prompts, args.output_tokens, num_speculative_tokens=args.k, draft_loops=DRAFT_LOOPS,
+                              target_loops=TARGET_LOOPS, temperature=args.temperature, seed=1, after_prefill=start_clock,
+                              in_flight=args.in_flight)
     torch.cuda.synchronize()
     seconds = time.perf_counter() - clock["start"]
     stats = decoder.stats
@@ -629,17 +694,18 @@ def run_decode_workload(args):
                     + c.num_attention_heads * c.head_dim * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
     weight_bytes = 2.0 * c.num_hidden_layers * layer_params * stats.loop_passes
     kv_bytes = 2.0 * 2 * c.num_key_value_heads * c.head_dim * c.num_hidden_layers * stats.context_tokens_read
-    head_calls = stats.rounds / max(args.requests, 1) * 5          # upper bound: k draft calls + 1 verify call per round
+    head_calls = stats.rounds / max(args.requests, 1) * (args.k + 1)   # upper bound: k draft calls + 1 verify call per round
     head_bytes = 2.0 * c.vocab_size * c.hidden_size * head_calls
     peak, peak_kind = measured_peaks()
     roofline_s = (weight_bytes + kv_bytes + head_bytes) / (peak * 1e9)
     print(json.dumps({
-        "workload": "decode: Ouro-1.4B-shaped random-init bf16, self-spec k=4 from depth 2, "
+        "workload": f"decode: Ouro-1.4B-shaped random-init bf16, self-spec k={args.k} from depth 2, "
                     f"{args.requests} requests, prompts U[{args.prompt_min},{args.prompt_max}]"
                     + (f" (every second one behind a common {args.shared_prefix}-token prefix, prefix reuse "
                        f"{'on' if args.prefix_caching else 'off'})" if args.shared_prefix else "")
                     + f", {args.output_tokens} output tokens, T={args.temperature}, "
-                    + ("eager launches" if args.eager else "recurrent loops replayed from CUDA graphs"),
+                    + ("eager launches" if args.eager else "every round one CUDA graph") + f", {args.in_flight} round(s) in flight",
+        "total_seconds": time.perf_counter() - clock["begin"],
         "prefill_and_capture_seconds": clock["start"] - clock["begin"], "prompt_tokens": sum(lengths),
         "prompt_tokens_computed": stats.prompt_tokens_computed, "prefix_hit_tokens": stats.prefix_hit_tokens,
         "decode_seconds": seconds, "committed_tokens": stats.committed_tokens, "accepted_tokens": stats.accepted_tokens,
@@ -654,82 +720,267 @@ def run_decode_workload(args):
         "tokens_out": sum(len(t) for t in tokens), "attention_status": model.attention.last_status(device)}))
 
 
-def cpu_step_seconds(threads: int, budget_s: float):
-    """Times the CPU oracle on a bounded sample of the same workload and extrapolates linearly
-    to one full step.  Returns (estimated seconds per step, accepted tokens per step, sample text)."""
-    from oracle import oracle
+def balanced_shards(lengths, world: int):
+    """Longest-first greedy assignment of requests to ranks by prompt length: returns one list of request
+    indices per rank whose total lengths differ by at most one request's length."""
+    order = sorted(range(len(lengths)), key=lambda i: -lengths[i])
+    loads, shards = [0] * world, [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda x: (loads[x], len(shards[x])))
+        shards[r].append(i)
+        loads[r] += lengths[i]
+    return shards
 
-    torch.set_num_threads(threads)
-    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
-    sample_requests = 32
-    work = Workload(seed=1234, requests=sample_requests, layers=1)
-    x = work.host_inputs(pin=False)
-    g = torch.Generator().manual_seed(5)
-    pool_shape = (work.total_pages, 1, BLOCK, HEADS, HEAD_DIM)
-    key_pool = (torch.randn(pool_shape, generator=g) * 0.5).bfloat16()
-    value_pool = (torch.randn(pool_shape, generator=g) * 0.5).bfloat16()
-    kc, vc = key_pool[:, 0], value_pool[:, 0]
 
-    def one_layer():
+def waves_under_budget(indices, lengths, tokens_extra: int, bytes_per_token: int, budget_bytes: float, max_wave: int):
+    """Consecutive groups of a rank's requests whose reserved KV (prompt + output + drafts, every depth
+    plane) fits the budget, at most `max_wave` requests each."""
+    waves, current, used = [], [], 0.0
+    for i in indices:
+        need = (lengths[i] + tokens_extra) * bytes_per_token
+        if current and (used + need > budget_bytes or len(current) >= max_wave):
+            waves.append(current)
+            current, used = [], 0.0
+        current.append(i)
+        used += need
+    if current:
+        waves.append(current)
+    return waves
+
+
+def run_sharded_workload(args):
+    """`--workload sharded`: a fixed set of requests (default 1024, prompts U[256, 2048], 512 output tokens,
+    k = 6, greedy) shared out over the ranks by prompt length and decoded to completion by every rank's own
+    engine in waves that fit its KV pool — whole-job strong scaling, prompt passes and graph captures
+    included.  One rank per GPU, no collective on the path; the job's time is the slowest rank's."""
+    import torch.distributed as dist
+
+    import vllm_rlt_b200 as rlt
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    config = rlt.LoopedLMConfig()
+    model = rlt.LoopedLM(config, rlt.seeded_state_dict(config, 3, device=device), device, torch.bfloat16)
+    prompts = decode_prompts(args.total_requests, (args.prompt_min, args.prompt_max), config.vocab_size, seed=23)
+    lengths = [len(p) for p in prompts]
+    mine = balanced_shards(lengths, world)[rank]
+    bytes_per_token = (config.total_ut_steps * config.num_hidden_layers * 2 * config.num_key_value_heads
+                       * config.head_dim * 2)
+    waves = waves_under_budget(mine, lengths, args.output_tokens + args.k + 1 + BLOCK, bytes_per_token,
+                               args.kv_budget_gb * 1e9, args.max_wave)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    accepted = committed = drafted = rounds = 0
+    for wave in waves:
+        decoder = rlt.SelfSpeculativeDecoder(model, cuda_graphs=not args.eager,
+                                             capture_sizes=sorted({len(wave), max(len(wave) // 2, 1), max(len(wave) // 4, 1)}))
+        decoder.generate([prompts[i] for i in wave], args.output_tokens, num_speculative_tokens=args.k,
+                         draft_loops=DRAFT_LOOPS, target_loops=TARGET_LOOPS, temperature=args.temperature, seed=1,
+                         in_flight=args.in_flight)
+        s = decoder.stats
+        accepted, committed, drafted = accepted + s.accepted_tokens, committed + s.committed_tokens, drafted + s.drafted_tokens
+        rounds += s.loop_passes
+        decoder.runner = None
+        del decoder
+        gc.collect()
+        torch.cuda.empty_cache()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    row = torch.tensor([seconds, float(accepted), float(committed), float(drafted), float(len(mine)),
+                        float(sum(lengths[i] for i in mine)), float(len(waves))], dtype=torch.float64, device=device)
+    table = row[None].cpu() if world == 1 else all_gather_rows(row)
+    if rank == 0:
+        slowest, mean = float(table[:, 0].max()), float(table[:, 0].mean())
+        print(json.dumps({
+            "workload": f"sharded: {args.total_requests} requests in total, prompts U[{args.prompt_min},{args.prompt_max}], "
+                        f"{args.output_tokens} output tokens, k={args.k}, T={args.temperature}, LAST_EXITED planes, every "
+                        f"request verified at depth {TARGET_LOOPS}; length-balanced over {world} rank(s), waves of at most "
+                        f"{args.max_wave} requests within {args.kv_budget_gb} GB of KV",
+            "n_gpus": world, "scaling": "strong", "job_seconds": slowest,
+            "rank_time_imbalance_max_over_mean": slowest / mean,
+            "accepted_tokens_per_s": float(table[:, 1].sum()) / slowest,
+            "committed_tokens_per_s": float(table[:, 2].sum()) / slowest,
+            "acceptance_rate": float(table[:, 1].sum()) / max(float(table[:, 3].sum()), 1.0),
+            "requests_per_rank": table[:, 4].tolist(), "prompt_tokens_per_rank": table[:, 5].tolist(),
+            "waves_per_rank": table[:, 6].tolist(), "seconds_per_rank": table[:, 0].tolist()}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+class CpuDecodeSample:
+    """The decode round of the bench on the host cores: the reference's Torch path for a speculative
+    round (worker/speculative.py:418-511 of the reference) restated over the CPU oracle's kernels
+    (paged attention, KV write, SiLU-and-Mul, sampler, rejection acceptance) and torch CPU GEMMs, bf16.
+
+    A bounded sample: `sample` of the 128 requests carry real contexts (attention, KV write, sampling
+    and acceptance run for them and are scaled by 128 / sample); the GEMMs, whose cost on a CPU is set
+    by the weights they stream rather than by a handful of rows, run at the FULL batch's row counts (128
+    rows per draft pass, 640 per verify pass, zero rows as filler) and are not scaled.  The prompts are
+    not run on the CPU (minutes): the sampled requests' pages hold seeded random K/V of the contexts'
+    lengths, which costs the same to attend to."""
+
+    def __init__(self, threads: int, sample: int = 8):
+        from oracle import oracle
+        from vllm_rlt_b200.looped_lm import LoopedLMConfig, rms_norm, rotate_half, seeded_state_dict
+
+        torch.set_num_threads(threads)
+        os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+        self.oracle, self.rms_norm, self.rotate_half = oracle, rms_norm, rotate_half
+        self.config = c = LoopedLMConfig()
+        self.sample, self.k = sample, DECODE_K
+        self.w = {n: t.to(torch.bfloat16) for n, t in seeded_state_dict(c, 3).items()}
+        g = torch.Generator().manual_seed(11)
+        prompts = torch.randint(DECODE_PROMPTS[0], DECODE_PROMPTS[1] + 1, (DECODE_REQUESTS,), generator=g)[:sample]
+        self.starts = prompts + DECODE_OUTPUT // 2                      # mid-generation positions
+        width = self.k + 1
+        pages = (self.starts + width + BLOCK) // BLOCK
+        planes = c.total_ut_steps
+        total = int(pages.sum()) * planes
+        order = torch.randperm(total, generator=g).int()
+        self.tables = torch.zeros(sample, planes, int(pages.max()), dtype=torch.int32)
+        cursor = 0
+        for i, n in enumerate(pages.tolist()):
+            for p in range(planes):
+                self.tables[i, p, :n] = order[cursor:cursor + n]
+                cursor += n
+        shape = (total, c.num_hidden_layers, BLOCK, c.num_key_value_heads, c.head_dim)
+        seed_block = (torch.randn(1 << 24, generator=g) * 0.5).to(torch.bfloat16)
+        self.key, self.value = torch.empty(shape, dtype=torch.bfloat16), torch.empty(shape, dtype=torch.bfloat16)
+        for pool, shift in ((self.key, 0), (self.value, 7919)):
+            flat = pool.view(-1)
+            for start in range(0, flat.numel(), seed_block.numel()):
+                n = min(seed_block.numel(), flat.numel() - start)
+                flat[start:start + n] = seed_block.roll(shift)[:n]
+        self.tokens0 = torch.randint(1, c.vocab_size, (sample,), generator=g)
+        self.inv_freq = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2, dtype=torch.float32) / c.head_dim))
+        self.generator = g
+        self.gemm_s = self.other_s = 0.0
+
+    def linear(self, x, weight, full_rows):
+        padded = torch.zeros(full_rows, x.shape[1], dtype=x.dtype)
+        padded[: x.shape[0]] = x
         t = time.perf_counter()
-        oracle.kv_write(kc, vc, x["k"][0], x["v"][0], x["write_blocks"], x["write_offsets"])
-        oracle.paged_attention(x["q"][0], kc, vc, x["tables"], x["lengths"])
-        oracle.silu_and_mul(x["gate"][0], x["up"][0])
-        return time.perf_counter() - t
+        y = torch.nn.functional.linear(padded, weight)
+        self.gemm_s += time.perf_counter() - t
+        return y[: x.shape[0]]
 
-    # The layers differ only in their data: time as many passes of one layer as fit the budget.
-    times = [one_layer()]
-    sample_layers = max(1, min(LAYERS, int(budget_s / max(times[0], 1e-3))))
-    times += [one_layer() for _ in range(sample_layers - 1)]
-    layer_s = statistics.mean(times)
-    t1 = time.perf_counter()
-    per_row_t = x["temperature"].repeat_interleave(TOKENS)
-    drafts, _ = oracle.sample_rows(x["draft"], per_row_t, x["u_draft"])
-    tokens = torch.zeros(sample_requests, TOKENS, dtype=torch.int64)
-    tokens[:, 1:] = drafts.view(sample_requests, TOKENS)[:, :-1]
-    oracle.accept_greedy(x["target"], x["cu_rows"], tokens, x["starts"])
-    result, _ = oracle.accept_rejection(x["target"], x["draft"], x["cu_rows"], tokens, x["starts"],
-                                        x["temperature"], x["u_accept"], x["u_final"])
-    accepted = result[work.accept_rows:work.accept_rows + sample_requests]
-    oracle.rollback(x["starts"], accepted + 1, x["request_tables"], BLOCK)
-    accept_s = time.perf_counter() - t1
-    scale = REQUESTS / sample_requests
-    step_s = scale * (LAYERS * layer_s + accept_s)
-    acceptance = float(accepted.sum()) / (sample_requests * (TOKENS - 1))
-    sample = (f"{sample_requests} of {REQUESTS} requests, {sample_layers} of {LAYERS} layers "
-              f"(kv_write + attention + silu) + acceptance on {work.accept_rows} rows; "
-              f"{sum(times) + accept_s:.1f} s measured, scaled x{scale:.0f} requests, layers x{LAYERS}")
-    return step_s, acceptance * REQUESTS * (TOKENS - 1), sample, oracle.num_threads()
+    def loop(self, hidden, positions, request_of_row, plane, full_rows):
+        """One recurrent loop over all layers (models/ouro.py:171-221, 283-291 of the reference)."""
+        c, w, o = self.config, self.w, self.oracle
+        rows = hidden.shape[0]
+        angles = positions.float().unsqueeze(-1) * self.inv_freq
+        angles = torch.cat((angles, angles), -1)
+        cos, sin = angles.cos().to(torch.bfloat16).unsqueeze(1), angles.sin().to(torch.bfloat16).unsqueeze(1)
+        tables = self.tables[request_of_row, plane].contiguous()
+        blocks = tables.gather(1, (positions // BLOCK)[:, None]).squeeze(1).long()
+        offsets, lengths = positions % BLOCK, (positions + 1).int()
+        for layer in range(c.num_hidden_layers):
+            p = f"model.layers.{layer}."
+            x = self.rms_norm(hidden, w[p + "input_layernorm.weight"], c.rms_norm_eps)
+            q = self.linear(x, w[p + "self_attn.q_proj.weight"], full_rows).view(rows, -1, c.head_dim)
+            k = self.linear(x, w[p + "self_attn.k_proj.weight"], full_rows).view(rows, -1, c.head_dim)
+            v = self.linear(x, w[p + "self_attn.v_proj.weight"], full_rows).view(rows, -1, c.head_dim)
+            q = q * cos + self.rotate_half(q) * sin
+            k = k * cos + self.rotate_half(k) * sin
+            kc, vc = self.key[:, layer], self.value[:, layer]
+            o.kv_write(kc, vc, k.contiguous(), v.contiguous(), blocks, offsets)
+            attended = o.paged_attention(q.contiguous(), kc, vc, tables, lengths).reshape(rows, -1)
+            attended = self.linear(attended, w[p + "self_attn.o_proj.weight"], full_rows)
+            hidden = hidden + self.rms_norm(attended, w[p + "input_layernorm_2.weight"], c.rms_norm_eps)
+            x = self.rms_norm(hidden, w[p + "post_attention_layernorm.weight"], c.rms_norm_eps)
+            gate = self.linear(x, w[p + "mlp.gate_proj.weight"], full_rows)
+            up = self.linear(x, w[p + "mlp.up_proj.weight"], full_rows)
+            mlp = self.linear(o.silu_and_mul(gate.contiguous(), up.contiguous()), w[p + "mlp.down_proj.weight"], full_rows)
+            hidden = hidden + self.rms_norm(mlp, w[p + "post_attention_layernorm_2.weight"], c.rms_norm_eps)
+        return self.rms_norm(hidden, w["model.norm.weight"], c.rms_norm_eps)
+
+    def round(self):
+        """One speculative round of the sampled requests; returns accepted tokens of the sample."""
+        c, o, n, width = self.config, self.oracle, self.sample, self.k + 1
+        g = self.generator
+        begin, gemm_before = time.perf_counter(), self.gemm_s
+        temperature = torch.full((n,), TEMPERATURE)
+        tokens = torch.zeros(n, width, dtype=torch.int64)
+        tokens[:, 0] = self.tokens0
+        requests = torch.arange(n)
+        retained, draft_logits = [], torch.zeros(n * width, c.vocab_size, dtype=torch.bfloat16)
+        for offset in range(width):
+            hidden = torch.nn.functional.embedding(tokens[:, offset], self.w["model.embed_tokens.weight"])
+            for depth in range(DRAFT_LOOPS):
+                hidden = self.loop(hidden, self.starts + offset, requests, depth, DECODE_REQUESTS)
+            retained.append(hidden)
+            if offset + 1 == width:
+                break
+            logits = self.linear(hidden, self.w["lm_head.weight"], DECODE_REQUESTS)
+            draft_logits.view(n, width, -1)[:, offset] = logits
+            proposed, _ = o.sample_rows(logits.contiguous(), temperature, torch.rand(n, generator=g))
+            tokens[:, offset + 1] = proposed.clamp_min(0)
+        hidden = torch.stack(retained, 1).reshape(n * width, -1)
+        row_request = requests.repeat_interleave(width)
+        positions = (self.starts[:, None] + torch.arange(width)[None, :]).reshape(-1)
+        for depth in range(DRAFT_LOOPS, TARGET_LOOPS):
+            hidden = self.loop(hidden, positions, row_request, depth, DECODE_REQUESTS * width)
+        logits = self.linear(hidden, self.w["lm_head.weight"], DECODE_REQUESTS * width).contiguous()
+        cu = (torch.arange(n + 1) * width).int()
+        result, _ = o.accept_rejection(logits, draft_logits, cu, tokens, self.starts.clone(), temperature,
+                                       torch.rand(n * width, generator=g), torch.rand(n, generator=g))
+        accepted = result[n * width: n * width + n]
+        o.rollback(self.starts.clone(), accepted + 1, self.tables, BLOCK)
+        total = time.perf_counter() - begin
+        self.other_s += total - (self.gemm_s - gemm_before)
+        return int(accepted.sum())
 
 
-def cpu_baseline(threads: int, budget_s: float):
-    step_s, accepted, sample, used = cpu_step_seconds(threads, budget_s)
-    return {"value": accepted / step_s, "unit": "accepted tokens/s", "cores": used, "kind": "port",
-            "sample": sample, "estimated_s_per_step": step_s}
+def cpu_decode_rounds(threads: int, rounds: int, warmup: int = 1, sample: int = 8):
+    """Times `rounds` CPU rounds of the bounded sample; returns the estimate for the full batch."""
+    cpu = CpuDecodeSample(threads, sample)
+    for _ in range(warmup):
+        cpu.round()
+    cpu.gemm_s = cpu.other_s = 0.0
+    accepted = sum(cpu.round() for _ in range(rounds))
+    scale = DECODE_REQUESTS / sample
+    round_s = (cpu.gemm_s + scale * cpu.other_s) / rounds
+    accepted_per_round = scale * accepted / rounds
+    text = (f"{sample} of {DECODE_REQUESTS} requests x {rounds} rounds (k={DECODE_K}, T={TEMPERATURE}): attention, KV write, "
+            f"sampler and acceptance for the sampled requests {cpu.other_s:.1f} s, scaled x{scale:.0f}; GEMMs at the full "
+            f"batch's row counts {cpu.gemm_s:.1f} s, not scaled; prompts not run on the CPU (seeded random K/V)")
+    return {"round_s": round_s, "accepted_per_round": accepted_per_round, "sample": text,
+            "cores": cpu.oracle.num_threads(), "measured_s": cpu.gemm_s + cpu.other_s}
+
+
+def cpu_baseline(threads: int, rounds: int):
+    r = cpu_decode_rounds(threads, rounds)
+    return {"value": r["accepted_per_round"] / r["round_s"], "unit": "accepted tokens/s", "cores": r["cores"],
+            "kind": "port", "sample": r["sample"], "estimated_s_per_step": r["round_s"]}
 
 
 def run_reference(args):
-    """The reference arm: the CPU restatement of the reference's Torch path for this step (the
-    reference package itself is Python over PyTorch and is not present on the GPU box), timed on
-    all host cores; each step is the same bounded sample, scaled to a full step."""
+    """The reference arm: the CPU restatement of the reference's Torch path for the same speculative
+    rounds (the reference package is Python over PyTorch and is not present where the bench runs),
+    timed on all host cores; each step is the bounded sample described in `CpuDecodeSample`."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    for _ in range(min(args.warmup, 1)):
-        cpu_step_seconds(threads, 8.0)
-    steps = max(1, min(args.steps, 3))
-    results = [cpu_step_seconds(threads, 8.0) for _ in range(steps)]
-    step_s = statistics.mean(r[0] for r in results)
-    accepted, sample, used = results[0][1], results[0][2], results[0][3]
-    value = accepted / step_s
+    steps, warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
+    r = cpu_decode_rounds(threads, steps, warmup)
+    value = r["accepted_per_round"] / r["round_s"]
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "accepted tokens/s",
-        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps, "warmup": min(args.warmup, 1),
-        "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps, "warmup": warmup,
+        "ms_per_step": r["round_s"] * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "configs[1] verify-step microbench x 24 layers (CPU, bounded sample scaled to a full step)"},
-        "cpu_baseline": {"value": value, "unit": "accepted tokens/s", "cores": used, "kind": "port", "sample": sample},
+        "config": {"workload": "configs[2] speculative rounds on the host cores (CPU port of the reference's Torch path, "
+                               "bounded sample scaled to the full batch of 128 requests)"},
+        "cpu_baseline": {"value": value, "unit": "accepted tokens/s", "cores": r["cores"], "kind": "port",
+                         "sample": r["sample"]},
         "e2e": {"value": value, "unit": "accepted tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -745,16 +996,24 @@ def main():
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--only", default=None, choices=["attention", "accept", "silu", "prefill"],
                         help="profiling aid: run only this kernel family (not a bench line)")
-    parser.add_argument("--workload", default="step", choices=["step", "decode"],
-                        help="step: the verify-step microbench (the bench line); decode: whole-model decoding (secondary)")
-    parser.add_argument("--output-tokens", type=int, default=32)
+    parser.add_argument("--workload", default="rounds", choices=["rounds", "decode", "sharded"],
+                        help="rounds: timed speculative rounds (the bench line); decode: one complete generation; "
+                             "sharded: a fixed request set shared out over the ranks, decoded to completion")
+    parser.add_argument("--k", type=int, default=None, help="decode / sharded workloads: drafts per round")
+    parser.add_argument("--in-flight", type=int, default=2, help="decode / sharded workloads: rounds in flight (1 or 2)")
+    parser.add_argument("--total-requests", type=int, default=1024, help="sharded workload: requests over all ranks")
+    parser.add_argument("--kv-budget-gb", type=float, default=110.0, help="sharded workload: KV bytes a wave may reserve")
+    parser.add_argument("--max-wave", type=int, default=128, help="sharded workload: most requests decoded together")
+    parser.add_argument("--output-tokens", type=int, default=None,
+                        help="decode workload: tokens per request (default 32); sharded workload: default 512")
     parser.add_argument("--eager", action="store_true", help="decode workload: launch every kernel from the host")
-    parser.add_argument("--prompt-min", type=int, default=128, help="decode workload: shortest prompt")
-    parser.add_argument("--prompt-max", type=int, default=1024, help="decode workload: longest prompt")
+    parser.add_argument("--prompt-min", type=int, default=None, help="shortest prompt (decode: 128, sharded: 256)")
+    parser.add_argument("--prompt-max", type=int, default=None, help="longest prompt (decode: 1024, sharded: 2048)")
     parser.add_argument("--shared-prefix", type=int, default=0,
                         help="decode workload: every second prompt starts with one common prefix of this many tokens")
     parser.add_argument("--prefix-caching", action="store_true", help="decode workload: map shared prompt pages instead of recomputing them")
-    parser.add_argument("--temperature", type=float, default=0.8)
+    parser.add_argument("--temperature", type=float, default=None,
+                        help="sampling temperature (decode: 0.8, sharded: 0 = greedy)")
     parser.add_argument("--requests", type=int, default=REQUESTS)
     parser.add_argument("--layers", type=int, default=LAYERS)
     parser.add_argument("--tokens", type=int, default=TOKENS, help="with --only attention: new tokens per request")
@@ -770,6 +1029,14 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the verify-step kernels have no CPU fallback")
+    sharded = args.workload == "sharded"
+    for name, decode_default, sharded_default in (("k", DECODE_K, 6), ("output_tokens", 32, 512), ("prompt_min", 128, 256),
+                                                  ("prompt_max", 1024, 2048), ("temperature", TEMPERATURE, 0.0)):
+        if getattr(args, name) is None:
+            setattr(args, name, sharded_default if sharded else decode_default)
+    if sharded:
+        run_sharded_workload(args)
+        return
     if args.workload == "decode":
         run_decode_workload(args)
         return

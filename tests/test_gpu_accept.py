@@ -322,3 +322,107 @@ def test_pipeline_shift_matches_every_reference_step(golden):
             for key in ("tokens", "depths", "candidates", "active", "token", "position"):
                 assert torch.equal(getattr(state, key).cpu(), after[key]), key
             assert torch.equal(state.hidden.cpu(), after["hidden"].to(dtype))
+
+
+def _padded_round(n, k, vocab, seed):
+    """A round in the fixed shape a graph needs: every request owns k + 1 rows, of which only its
+    first counts[i] are real (some requests have none); the rest hold garbage that must never be read."""
+    g = torch.Generator().manual_seed(seed)
+    width = k + 1
+    counts = torch.randint(0, width + 1, (n,), generator=g).int()
+    counts[0], counts[1] = 0, width
+    cu = (torch.arange(n + 1) * width).int()
+    target = torch.randn(n * width, vocab, generator=g) * 3
+    draft = target + torch.randn(n * width, vocab, generator=g) * 0.5
+    tokens = torch.randint(0, vocab, (n, width), generator=g)
+    targets = target.argmax(-1).view(n, width)
+    tokens[:, 1:] = torch.where(torch.rand(n, k, generator=g) < 0.6, targets[:, :-1], tokens[:, 1:])
+    real = torch.arange(width)[None, :] < counts[:, None]
+    target[~real.reshape(-1)] = float("nan")                     # padding rows: poison
+    draft[~real.reshape(-1)] = float("nan")
+    starts = torch.randint(1, 3000, (n,), generator=g)
+    slots = torch.randperm(2 * n, generator=g)[:n]
+    return dict(counts=counts, cu=cu, target=target, draft=draft, tokens=tokens, starts=starts, slots=slots, g=g,
+                width=width)
+
+
+def test_fixed_shape_greedy_round_with_padding_rows_matches_the_compact_round():
+    n, k, vocab = 23, 4, 2048
+    r = _padded_round(n, k, vocab, 5)
+    want_slots = torch.full((2 * n, 2), -9, dtype=torch.int64)
+    want = oracle.accept_greedy(r["target"], r["cu"], r["tokens"], r["starts"], r["slots"], want_slots, r["counts"])
+    got_slots = torch.full((2 * n, 2), -9, dtype=torch.int64).cuda()
+    got = rlt.accept_greedy(r["target"].cuda(), r["cu"].cuda(), r["tokens"].cuda(), r["starts"].cuda(), r["slots"].cuda(),
+                            got_slots, row_counts=r["counts"].cuda()).cpu()
+    assert torch.equal(got, want) and torch.equal(got_slots.cpu(), want_slots)
+    # the same requests as a compact round (the reference's layout): same decisions, padding rows are -1
+    rows, width = n * r["width"], r["width"]
+    keep = (torch.arange(width)[None, :] < r["counts"][:, None]).reshape(-1)
+    cu = torch.zeros(n + 1, dtype=torch.int32)
+    cu[1:] = r["counts"].cumsum(0)
+    live = r["counts"] > 0
+    compact = oracle.accept_greedy(r["target"][keep], cu, r["tokens"], r["starts"])
+    total = int(cu[-1])
+    assert torch.equal(got[:rows][keep], compact[:total]) and bool((got[:rows][~keep] == -1).all())
+    assert torch.equal(got[rows:rows + n][live], compact[total:total + n][live])
+    assert torch.equal(got[rows + n:][live], compact[total + n:][live])
+    # a request without rows is left alone: nothing accepted, position unchanged, slot untouched
+    idle = ~live
+    assert bool((got[rows:rows + n][idle] == 0).all()) and torch.equal(got[rows + n:][idle], r["starts"][idle])
+    assert bool((got_slots.cpu()[r["slots"][idle]] == -9).all())
+
+
+def test_fixed_shape_rejection_round_with_padding_rows_matches_the_oracle():
+    n, k, vocab = 19, 3, 4096
+    r = _padded_round(n, k, vocab, 8)
+    g, width = r["g"], r["width"]
+    temperature = torch.full((n,), 0.8)
+    temperature[::5] = 0.0
+    u_accept, u_final = torch.rand(n * width, generator=g), torch.rand(n, generator=g)
+    top_k = torch.full((n,), -1, dtype=torch.int32)       # filters off (their arrays still travel the padded path)
+    top_p = torch.ones(n)
+    want_slots = torch.full((2 * n, 2), -9, dtype=torch.int64)
+    want, want_status = oracle.accept_rejection(r["target"], r["draft"], r["cu"], r["tokens"], r["starts"], temperature,
+                                                u_accept, u_final, r["slots"], want_slots, top_k, top_p, r["counts"])
+    got_slots = torch.full((2 * n, 2), -9, dtype=torch.int64).cuda()
+    status = torch.full((n,), 7, dtype=torch.int32).cuda()
+    workspace = torch.empty(rlt.load_library().rlt_accept_rejection_workspace_bytes(n * width), dtype=torch.uint8).cuda()
+    got, got_status = rlt.accept_rejection(
+        r["target"].cuda(), r["draft"].cuda(), r["cu"].cuda(), r["tokens"].cuda(), r["starts"].cuda(), temperature.cuda(),
+        u_accept.cuda(), u_final.cuda(), r["slots"].cuda(), got_slots, None, top_k.cuda(), top_p.cuda(),
+        row_counts=r["counts"].cuda(), status=status, workspace=workspace)
+    assert got_status is status
+    assert torch.equal(got_status.cpu(), want_status) and int(want_status.abs().sum()) == 0   # NaN padding never read
+    assert torch.equal(got.cpu(), want) and torch.equal(got_slots.cpu(), want_slots)
+
+
+def test_a_failed_request_keeps_its_slot_and_misuse_of_result_is_refused():
+    vocab = 8
+    target, draft = torch.zeros(2, vocab), torch.zeros(2, vocab)
+    draft[0, 3] = -2000.0                                          # zero proposal probability for the draft
+    slot_values = torch.tensor([[11, 12], [13, 14]]).cuda()
+    args = [torch.tensor([0, 2], dtype=torch.int32), torch.tensor([[0, 3]]), torch.tensor([5]),
+            torch.tensor([1.0]), torch.tensor([0.5, 0.0]), torch.tensor([0.5])]
+    _, status = rlt.accept_rejection(target.cuda(), draft.cuda(), *[a.cuda() for a in args], torch.tensor([1]).cuda(),
+                                     slot_values)
+    assert status.tolist() == [1] and slot_values.tolist() == [[11, 12], [13, 14]]
+    cuda_args = [a.cuda() for a in args]
+    for bad in (torch.zeros(3, dtype=torch.int64).cuda(), torch.zeros(8, dtype=torch.int32).cuda()):
+        with pytest.raises(ValueError, match="result"):
+            rlt.accept_rejection(target.cuda(), draft.cuda(), *cuda_args, result=bad)
+        with pytest.raises(ValueError, match="result"):
+            rlt.accept_greedy(target.cuda(), cuda_args[0], cuda_args[1], cuda_args[2], result=bad)
+
+
+def test_round_uniforms_match_the_oracle_and_are_per_request_streams():
+    seeds = torch.tensor([0, 1, 2 ** 62 + 5, 1, 77])
+    rounds = torch.tensor([0, 3, 9, 4, 2 ** 40])
+    got = rlt.round_uniforms(seeds.cuda(), rounds.cuda(), 7)
+    want = oracle.round_uniforms(seeds, rounds, 7)
+    for a, b in zip(got, want):
+        assert torch.equal(a.cpu(), b)
+        assert float(b.min()) >= 0.0 and float(b.max()) < 1.0
+    # the same (seed, round) gives the same uniforms whatever else is in the batch
+    alone = rlt.round_uniforms(seeds[3:4].cuda(), rounds[3:4].cuda(), 7)
+    assert torch.equal(alone[0][0], got[0][3]) and torch.equal(alone[1][0], got[1][3]) and alone[2][0] == got[2][3]
+    assert not torch.equal(got[0][1], got[0][3])                  # another round of the same request differs

@@ -331,3 +331,76 @@ def test_random_batches_match_oracle_and_replay_identically(kernel, seed):
         one = slice(row, row + 1)
         alone = kernel(args[0][one], args[1], args[2], args[3][one], args[4][one])
         assert torch.equal(alone[0], first[row]), row
+
+
+@pytest.mark.parametrize("dtype,dim", [(torch.bfloat16, 128), (torch.float32, 64)])
+def test_a_length_beyond_the_table_is_clamped_and_reported(kernel, dtype, dim):
+    # device-side lengths are never seen by the host: a length the row's table cannot address must not
+    # index past the table (tiled and generic kernels), and the tiled kernel reports it
+    pool = make_pool([64, 300, 48], kv_heads=2, head_dim=dim, block=16, dtype=dtype, seed=12,
+                     row_lengths=[[62, 63, 64], [300], [48]])
+    width = pool["tables"].shape[1]
+    capacity = width * 16
+    tables = pool["tables"].clone()
+    tables[tables < 0] = tables[0, 0]                 # a full-width table for every row (any valid page)
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(tables.shape[0], 4, dim, generator=g).to(dtype)
+    lengths = pool["lengths"].clone()
+    over = lengths.clone()
+    over[1], over[4] = capacity + 1, 2 ** 31 - 1
+    clamped = lengths.clone()
+    clamped[1] = clamped[4] = capacity
+    got = run_gpu(kernel, q, pool["key_pool"], pool["value_pool"], 0, tables, over)
+    want = run_gpu(kernel, q, pool["key_pool"], pool["value_pool"], 0, tables, clamped)
+    assert torch.equal(got, want)
+    check(got, oracle.paged_attention(q, pool["key"], pool["value"], tables, clamped), dtype)
+    if dtype == torch.bfloat16:
+        kernel(q.cuda(), pool["key_pool"].cuda()[:, 0], pool["value_pool"].cuda()[:, 0], tables.cuda(), over.cuda())
+        assert kernel.last_status()["error"] == 2     # bit 1: a length was clamped; bit 0 (a wait gave up) is clear
+        kernel(q.cuda(), pool["key_pool"].cuda()[:, 0], pool["value_pool"].cuda()[:, 0], tables.cuda(), clamped.cuda())
+        assert kernel.last_status()["error"] == 0
+
+
+def test_shared_plan_notices_metadata_rewritten_in_place(kernel):
+    # inside shared_plan() a plan is reused only while the metadata tensors are unmodified
+    dtype = torch.bfloat16
+    pool = make_pool([700, 90], kv_heads=2, head_dim=128, block=16, dtype=dtype, seed=4, rows_per_group=3)
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(pool["tables"].shape[0], 4, 128, generator=g).to(dtype).cuda()
+    kp, vp = pool["key_pool"].cuda(), pool["value_pool"].cuda()
+    tables, lengths = pool["tables"].clamp_min(0).cuda(), pool["lengths"].cuda()
+    shorter = (pool["lengths"] - 40).cuda()
+    want_long = kernel(q, kp[:, 0], vp[:, 0], tables, lengths)
+    want_short = kernel(q, kp[:, 0], vp[:, 0], tables, shorter)
+    assert not torch.equal(want_long, want_short)
+    with kernel.shared_plan():
+        assert torch.equal(kernel(q, kp[:, 0], vp[:, 0], tables, lengths), want_long)
+        lengths.copy_(shorter)                        # same storage, new contents
+        assert torch.equal(kernel(q, kp[:, 0], vp[:, 0], tables, lengths), want_short)
+
+
+def test_full_size_microbench_shape_matches_the_oracle_over_a_layer_strided_pool(kernel):
+    # 64 requests, contexts U[512, 4096], 16 rows per request on a shared plane, layer 5 of a 24-layer pool
+    # (34 GB): the oracle scores the rows of four requests from a host copy of their pages
+    import bench
+
+    work = bench.Workload(seed=1234)
+    device = torch.device("cuda")
+    g = torch.Generator(device=device).manual_seed(7)
+    shape = (work.total_pages, bench.LAYERS, bench.BLOCK, bench.HEADS, bench.HEAD_DIM)
+    key_pool = torch.empty(shape, dtype=torch.bfloat16, device=device)
+    value_pool = torch.empty(shape, dtype=torch.bfloat16, device=device)
+    layer = 5
+    for pool in (key_pool, value_pool):               # only the layer under test needs values
+        pool[:, layer] = (torch.randn(shape[0], *shape[2:], device=device, generator=g) * 0.5).to(torch.bfloat16)
+    q = (torch.randn(work.rows, bench.HEADS, bench.HEAD_DIM, device=device, generator=g) * 0.5).to(torch.bfloat16)
+    out = kernel(q, key_pool[:, layer], value_pool[:, layer], work.tables.to(device), work.lengths.to(device))
+    status = kernel.last_status()
+    assert status["error"] == 0 and status["zero_rows"] == 0
+    chunks = sum(chunk_count(int(c)) for c in work.contexts)
+    assert status["items"] == chunks * bench.HEADS                   # one group per request: K/V read once per request
+    moved = [key_pool[:, layer:layer + 1], value_pool[:, layer:layer + 1]]
+    parity = bench.attention_parity(work, out, q, moved[0], moved[1], requests=4)
+    assert parity["ok"] and parity["rows"] == 64, parity
+    del key_pool, value_pool
+    torch.cuda.empty_cache()

@@ -121,3 +121,22 @@ def test_finalize_tokens_match_the_reference_and_the_oracle(golden):
     assert torch.equal(got_k.cpu().view(torch.int16), want_k.view(torch.int16))
     assert torch.equal(got_v.cpu().view(torch.int16), want_v.view(torch.int16))
     assert not torch.equal(want_k, key)
+
+
+def test_rollback_to_the_last_token_of_a_full_allocation_is_valid():
+    # truncate_suffix accepts 0 <= frontier <= max_tokens (core/kv_cache_manager.py:340-342 of the reference):
+    # a request that filled its pages exactly is rolled back like any other, only its next page does not exist
+    planes, width, block, layers = 2, 3, 16, 2
+    tables = torch.arange(2 * planes * width, dtype=torch.int32).view(2, planes, width)
+    starts, emitted = torch.tensor([width * block - 3, width * block - 3]), torch.tensor([3, 4])
+    prefix = torch.full((2, planes, layers), width * block + 5)
+    want_prefix = prefix.clone()
+    want = oracle.rollback(starts, emitted, tables, block, None, None, want_prefix)
+    got_prefix = prefix.clone().cuda()
+    got = rlt.rollback(starts.cuda(), emitted.cuda(), tables.cuda(), block, written_prefix=got_prefix)
+    assert got.status.tolist() == want[4].tolist() == [0, 5]       # exactly full is fine, one beyond is refused
+    assert got.frontier.tolist() == [width * block, width * block + 1]
+    assert got.context_lengths.tolist()[0] == width * block + 1 and got.write_blocks.tolist()[0] == [-1, -1]
+    assert torch.equal(got.write_blocks.cpu()[0], want[2][0])
+    assert torch.equal(got_prefix.cpu(), want_prefix) and int(got_prefix[0].max()) == width * block
+    assert int(got_prefix[1].max()) == width * block + 5             # the refused request is untouched

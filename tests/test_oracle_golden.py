@@ -367,3 +367,66 @@ def test_packed_prefill_matches_the_reference_rows(golden):
                                  case["cu_seqlens_q"])
     torch.testing.assert_close(out.float(), case["out"].float(), rtol=2e-2, atol=2e-2)
     assert float((out == case["out"]).float().mean()) > 0.95   # both round an fp32 result to bf16 once
+
+
+def test_philox_known_answers_and_round_uniform_streams():
+    # the published known-answer vectors of Philox4x32-10 (Random123 kat_vectors)
+    assert oracle.philox4x32_10([0, 0, 0, 0], [0, 0]) == [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]
+    assert oracle.philox4x32_10([0xffffffff] * 4, [0xffffffff] * 2) == [0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd]
+    assert oracle.philox4x32_10([0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344], [0xa4093822, 0x299f31d0]) == \
+        [0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1]
+    seeds, rounds = torch.tensor([5, 5, 6]), torch.tensor([0, 1, 0])
+    draft, accept, final = oracle.round_uniforms(seeds, rounds, 64)
+    everything = torch.cat([draft.reshape(-1), accept.reshape(-1), final])
+    assert float(everything.min()) >= 0.0 and float(everything.max()) < 1.0
+    assert everything.unique().numel() > 0.99 * everything.numel()          # streams do not repeat each other
+    assert abs(float(everything.mean()) - 0.5) < 0.05
+    again = oracle.round_uniforms(seeds[:1], rounds[:1], 64)
+    assert torch.equal(again[0][0], draft[0]) and torch.equal(again[1][0], accept[0])
+
+
+def test_padded_rounds_decide_like_compact_rounds():
+    # a round of fixed shape (every request owns k + 1 rows, row_counts says how many are real) gives the
+    # decisions of the reference's compact layout; requests without rows are left alone
+    g = torch.Generator().manual_seed(3)
+    n, width, vocab = 9, 4, 97
+    counts = torch.tensor([0, 4, 1, 3, 0, 2, 4, 1, 3], dtype=torch.int32)
+    cu_padded = (torch.arange(n + 1) * width).int()
+    cu = torch.zeros(n + 1, dtype=torch.int32)
+    cu[1:] = counts.cumsum(0)
+    keep = (torch.arange(width)[None, :] < counts[:, None]).reshape(-1)
+    target = torch.randn(n * width, vocab, generator=g) * 3
+    draft = target + torch.randn(n * width, vocab, generator=g)
+    tokens = torch.randint(0, vocab, (n, width), generator=g)
+    tokens[:, 1:] = torch.where(torch.rand(n, width - 1, generator=g) < 0.7, target.argmax(-1).view(n, width)[:, :-1],
+                                tokens[:, 1:])
+    starts = torch.randint(5, 500, (n,), generator=g)
+    temperature = torch.tensor([0.8, 0.8, 0.0, 0.8, 0.0, 0.8, 0.8, 0.8, 0.0])
+    u_accept, u_final = torch.rand(n * width, generator=g), torch.rand(n, generator=g)
+    rows, total = n * width, int(cu[-1])
+    live = counts > 0
+    for greedy in (True, False):
+        slots = torch.arange(n)
+        padded_slots, compact_slots = torch.full((n, 2), -3), torch.full((n, 2), -3)
+        if greedy:
+            padded = oracle.accept_greedy(target, cu_padded, tokens, starts, slots, padded_slots, counts)
+            compact = oracle.accept_greedy(target[keep], cu, tokens, starts, slots, compact_slots)
+        else:
+            padded, status = oracle.accept_rejection(target, draft, cu_padded, tokens, starts, temperature, u_accept,
+                                                     u_final, slots, padded_slots, row_counts=counts)
+            compact, _ = oracle.accept_rejection(target[keep], draft[keep], cu, tokens, starts, temperature,
+                                                 u_accept[keep], u_final, slots, compact_slots)
+            assert status.tolist() == [0] * n
+        assert torch.equal(padded[:rows][keep], compact[:total]) and bool((padded[:rows][~keep] == -1).all())
+        assert torch.equal(padded[rows:rows + n][live], compact[total:total + n][live])
+        assert torch.equal(padded[rows + n:][live], compact[total + n:][live])
+        assert torch.equal(padded[rows + n:][~live], starts[~live]) and bool((padded[rows:rows + n][~live] == 0).all())
+        assert torch.equal(padded_slots[live], compact_slots[live]) and bool((padded_slots[~live] == -3).all())
+
+
+def test_rollback_accepts_a_frontier_at_the_end_of_the_allocation():
+    tables = torch.arange(8, dtype=torch.int32).view(1, 2, 4)
+    frontier, lengths, blocks, offsets, status = oracle.rollback(torch.tensor([60]), torch.tensor([4]), tables, 16)
+    assert status.tolist() == [0] and frontier.tolist() == [64] and lengths.tolist() == [65]
+    assert blocks.tolist() == [[-1, -1]] and offsets.tolist() == [0]
+    assert oracle.rollback(torch.tensor([60]), torch.tensor([5]), tables, 16)[4].tolist() == [5]

@@ -16,8 +16,11 @@ from .prefix_cache import PrefixIndex
 from .kv_cache import RollbackResult, finalize_tokens, kv_write, rollback
 from .layers import rope_kv_write, sandwich_norm
 from .looped_lm import LoopedLM, LoopedLMConfig, seeded_state_dict
+from .runner import (B200SpeculativeRunner, ModelRunnerOutput, Request, SamplingParams, ScheduledRequest,
+                     SchedulerOutput, SpeculativeConfig, SpeculativeRoundTicket, SpeculativeStats)
 from .speculative import (PipelineState, SpeculativeResult, accept_greedy, accept_rejection, argmax_rows,
-                          decode_result, pipeline_shift, probabilities, raise_for_status, sample_rows)
+                          decode_result, pipeline_shift, probabilities, raise_for_status, round_uniforms,
+                          sample_rows)
 
 __all__ = [
     "AttentionBackend", "B200PagedAttention", "DecodeStats", "GraphedLoops", "LoopedLM", "LoopedLMConfig", "PagedKV", "PrefixIndex",
@@ -25,4 +28,6 @@ __all__ = [
     "NativeLibraryMissing", "RollbackResult", "SpeculativeResult", "accept_greedy", "accept_rejection",
     "argmax_rows", "PipelineState", "create_backend", "decode_result", "finalize_tokens", "pipeline_shift", "kv_write", "load_library", "probabilities", "raise_for_status",
     "register_torch_op", "rollback", "rope_kv_write", "sample_rows", "sandwich_norm", "silu_and_mul",
+    "B200SpeculativeRunner", "ModelRunnerOutput", "Request", "SamplingParams", "ScheduledRequest", "SchedulerOutput",
+    "SpeculativeConfig", "SpeculativeRoundTicket", "SpeculativeStats", "round_uniforms",
 ]

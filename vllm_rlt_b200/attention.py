@@ -89,10 +89,13 @@ class B200PagedAttention:
         """Reuse the row grouping / work list across the layers of one depth pass.
 
         Inside this context, consecutive calls on one stream that pass the *same* block-table,
-        length (and ``cu_seqlens_q``) tensors plan once and then only run.  The caller promises
-        what the reference's model loop already guarantees (``models/ouro.py:283-291``: one
-        metadata object for all 24 layers): those tensors are not modified while the context is
-        active.  Outside the context every call plans for itself.
+        length (and ``cu_seqlens_q``) tensors plan once and then only run, as the reference's
+        model loop hands one metadata object to all 24 layers (``models/ouro.py:283-291``).
+        "The same" means the same storage AND the same contents: a tensor that was rewritten in
+        place since the plan was built (its version counter moved) is planned again, so a stale
+        plan is never reused.  Tensors that carry no version counter (created under
+        ``torch.inference_mode``) are planned on every call.  Outside the context every call
+        plans for itself.
         """
         self._sharing += 1
         try:
@@ -113,6 +116,14 @@ class B200PagedAttention:
             self._workspaces[key] = buffer
             self._planned.pop(key, None)
         return buffer
+
+    @staticmethod
+    def _versions(*tensors):
+        """In-place modification counters of the metadata tensors, or None if one has none."""
+        try:
+            return tuple(-1 if t is None else t._version for t in tensors)
+        except RuntimeError:
+            return None
 
     @staticmethod
     def _check_cache(q, key_cache, value_cache):
@@ -170,10 +181,11 @@ class B200PagedAttention:
                 _capi.ptr(context_lengths), _capi.ptr(cu_seqlens_q), rows, _capi.ptr(workspace),
                 workspace.numel(), stream)
             status = _capi.ERR_UNSUPPORTED
-            if self._sharing:
+            versions = self._versions(block_tables, context_lengths, cu_seqlens_q) if self._sharing else None
+            if versions is not None:
                 plan_key = (block_tables.data_ptr(), table_rows, width, context_lengths.data_ptr(),
                             0 if cu_seqlens_q is None else cu_seqlens_q.data_ptr(), rows, q.shape[1], kv_heads,
-                            head_dim, block_size, dtype)
+                            head_dim, block_size, dtype, versions)
                 if self._planned.get(ws_key) != plan_key:
                     status = lib.rlt_verify_attention_plan(
                         _capi.ptr(block_tables), table_rows, width, _capi.ptr(context_lengths),

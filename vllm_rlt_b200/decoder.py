@@ -1,13 +1,13 @@
-"""Greedy self-speculative decoding of a looped LM on the B200 kernels (block mode).
+"""Self-speculative decoding of a looped LM on the B200 kernels: the engine loop around the runner.
 
-The loop of `SpeculativeRunner._submit_round` / `_collect_round`
-(`vllm_rlt/worker/speculative.py:418-511` of the reference) with the reference's round geometry
-(a round of request i processes `c_i = min(K+1, max_tokens - generated_i)` input
-positions starting at the last committed token; draft offset o runs loops `0..d-1` and proposes
-token o+1 from `coda(hidden_d).argmax`; the retained depth-d states of all c_i rows then run
-loops `d..D-1` and every row's argmax is a target), on a LAST_EXITED paged KV cache (one plane
-per loop depth).  Acceptance, the next token / position and the rollback frontier are computed
-on the device by `accept_greedy` / `rollback`; the host reads one small buffer per round.
+`SelfSpeculativeDecoder` plays the part of the reference's engine for this path
+(`StageEngine._step_async_speculative`, `vllm_rlt/engine/stage_engine.py:732-793`, with the span
+rule of `Scheduler._make_scheduled_request`, `vllm_rlt/core/scheduler.py:603-608`): it reserves the
+pages, runs the prompts, schedules spans `(request, token_start, token_count = min(K + 1, remaining))`
+on a LAST_EXITED paged KV cache (one plane per loop depth), submits them to
+`B200SpeculativeRunner`, keeps up to two rounds in flight, and applies the collected results
+(tokens, frontier check) the way `Scheduler.update_from_output` does (`:1360-1397`).  All of the
+round itself — draft and verify passes, acceptance, device state, rollback — is the runner's.
 
 `native` decoding (one token per step through all loops) is provided for the token-identity
 check the reference applies to its own runner (tests/test_speculative.py:71-87 there).
@@ -19,11 +19,13 @@ from dataclasses import dataclass
 
 import torch
 
-from .kv_cache import rollback
+from collections import deque
+
 from .looped_lm import LoopedLM
 from .prefix_cache import PrefixIndex
-from .speculative import (PipelineState, accept_greedy, accept_rejection, argmax_rows, pipeline_shift,
-                          raise_for_status, sample_rows)
+from .runner import (B200SpeculativeRunner, Request, SamplingParams, ScheduledRequest, SchedulerOutput,
+                     SpeculativeConfig)
+from .speculative import argmax_rows
 
 
 @dataclass
@@ -103,6 +105,14 @@ class PagedKV:
                    torch.zeros(shape, device=model.device, dtype=model.dtype), tables.to(model.device), block,
                    shared_tokens, index, refcounts)
 
+    @property
+    def max_pages(self) -> int:
+        return self.tables.shape[2]
+
+    def device_tables(self, request_id) -> torch.Tensor:
+        """int32 [planes, pages] of one request (requests are named by their row, as a string or int)."""
+        return self.tables[int(request_id)]
+
     def addressing(self, requests: torch.Tensor, positions: torch.Tensor, plane: int):
         """Write addresses, per-row block tables and context lengths of rows (request, position)."""
         tables = self.tables[requests, plane]
@@ -179,26 +189,18 @@ class GraphedLoops:
 
 
 class SelfSpeculativeDecoder:
-    def __init__(self, model: LoopedLM, *, block: int = 16, cuda_graphs: bool = False, prefix_caching: bool = False):
+    def __init__(self, model: LoopedLM, *, block: int = 16, cuda_graphs: bool = False, prefix_caching: bool = False,
+                 capture_sizes=None):
         self.model = model
         self.block = block
         self.cuda_graphs = cuda_graphs
+        self.capture_sizes = capture_sizes         # batch sizes with a round graph (None: the runner's default)
+        self.runner = None
         self.prefix_caching = prefix_caching   # CacheConfig.enable_prefix_caching of the reference
         self.stats = DecodeStats()
         self._graphs = None
 
     # ---- shared pieces -------------------------------------------------------------------
-    def _upload(self, host_tensors):
-        """int64 CPU tensors -> device tensors through one pinned staging buffer and one
-        asynchronous copy.  The buffer is reused by the next call, which the decoder makes only
-        after it has read a round's results back (so the copy has completed)."""
-        sizes = [t.numel() for t in host_tensors]
-        total = sum(sizes)
-        if getattr(self, "_staging", None) is None or self._staging.numel() < total:
-            self._staging = torch.empty(max(total, 4096) * 2, dtype=torch.int64, pin_memory=True)
-        torch.cat([t.reshape(-1).long() for t in host_tensors], out=self._staging[:total])
-        return self._staging[:total].to(self.model.device, non_blocking=True).split(sizes)
-
     def _loop(self, kv: PagedKV, hidden, requests, positions, depth):
         blocks, offsets, tables, lengths = kv.addressing(requests, positions, depth)
         if self._graphs is not None and self._graphs.kv is kv:
@@ -251,10 +253,69 @@ class SelfSpeculativeDecoder:
                 generated[i].append(token)
         return generated
 
-    # ---- pipeline self-speculation --------------------------------------------------------
+    # ---- self-speculation through the runner ---------------------------------------------
+    def _requests(self, prompts, first_tokens, max_tokens, temperature, top_k, top_p, seed):
+        return [Request(str(i), list(p), SamplingParams(max_tokens=max_tokens, temperature=temperature, top_k=top_k,
+                                                        top_p=top_p, seed=(seed * 1000003 + i) % (2 ** 63)),
+                        generated_token_ids=[t])
+                for i, (p, t) in enumerate(zip(prompts, first_tokens))]
+
+    def _schedule(self, requests, k: int, pipeline: bool):
+        """The speculative spans of one submission (core/scheduler.py:603-608, 734-739 of the reference): at
+        most two rounds of a request in flight, `token_count = min(K + 1, remaining)` with the tokens of
+        uncollected rounds counted as placeholders, `token_start` the position those placeholders imply."""
+        spans = []
+        for request in requests:
+            if request.finished or request.num_speculative_rounds >= 2:
+                continue
+            remaining = request.sampling_params.max_tokens - request.num_scheduled_outputs
+            if remaining <= 0:
+                continue
+            spans.append(ScheduledRequest(request, request.position, min(k + 1, remaining)))
+        return SchedulerOutput("speculative", spans) if spans else None
+
+    @staticmethod
+    def _after_submission(batch, pipeline: bool):
+        """`Scheduler.update_after_submission` (core/scheduler.py:1400-1420): the submitted span's tokens
+        become placeholders.  Only now, because the runner's first sight of a request reads its committed
+        position."""
+        for span in batch.requests:
+            span.request.num_output_placeholders += 1 if pipeline else span.token_count
+            span.request.num_speculative_rounds += 1
+
+    def _apply(self, ticket, output, pipeline: bool, config):
+        """`Scheduler.update_from_output` for a speculative round (core/scheduler.py:1360-1397): release
+        the placeholders, check the device's frontier against the committed prefix, record the tokens."""
+        d, target = config.draft_loops, config.target_loops
+        for span, result, frontier in zip(ticket.batch.requests, output.speculative, output.frontiers):
+            request = span.request
+            request.num_output_placeholders -= 1 if pipeline else span.token_count
+            request.num_speculative_rounds -= 1
+            if request.finished:
+                continue                                     # a round that was in flight when the request ended
+            expected = len(request.prompt_token_ids) + len(request.generated_token_ids) - 1
+            if frontier != expected + len(result.token_ids):
+                raise RuntimeError("speculative GPU frontier disagrees with committed prefix")
+            if not pipeline:                                 # work accounting of the round, from the true start
+                start, count = expected, span.token_count
+                self.stats.context_tokens_read += d * sum(start + o + 1 for o in range(count)) \
+                    + (target - d) * (start + count)
+            room = request.sampling_params.max_tokens - len(request.generated_token_ids)
+            emitted = result.token_ids[:room]
+            request.generated_token_ids.extend(emitted)
+            self.stats.committed_tokens += len(emitted)
+            self.stats.accepted_tokens += min(result.accepted_count, len(emitted))
+            if len(request.generated_token_ids) >= request.sampling_params.max_tokens:
+                request.finished = True
+
+    def _drive(self, runner, requests, k: int, in_flight: int):
+        session = DecodeSession(self, runner, requests, k, in_flight)
+        session.run()
+        session.close()
+
     @torch.no_grad()
     def generate_pipeline(self, prompts, max_tokens: int, *, num_speculative_tokens: int, draft_loops: int = 2,
-                          target_loops: int | None = None):
+                          target_loops: int | None = None, in_flight: int = 1):
         """Pipeline-mode self-speculation, greedy (`AsyncSpeculativeRunner._pipeline_step`,
         worker/async_speculative.py:502-584 of the reference).
 
@@ -265,192 +326,121 @@ class SelfSpeculativeDecoder:
         the head slot that reached depth D is emitted and checked against the candidate it was
         drafted from; a mismatch drops its descendants and restarts from the corrected token.  The
         host reads six integers per request and step."""
-        model, device = self.model, self.model.device
+        model = self.model
         target_loops = target_loops or model.config.total_ut_steps
-        if not 0 < draft_loops <= target_loops <= model.config.total_ut_steps or target_loops % draft_loops:
-            raise ValueError("target_loops must be a positive multiple of draft_loops")
+        if not 0 < draft_loops < target_loops <= model.config.total_ut_steps or target_loops % draft_loops:
+            raise ValueError("target_loops must be a multiple of draft_loops and larger than it")
+        config = SpeculativeConfig(num_speculative_tokens, draft_loops, target_loops, mode="pipeline")
         width = min(num_speculative_tokens + 1, target_loops // draft_loops)
-        n = len(prompts)
         kv = self._allocate(prompts, [len(p) + max_tokens + width + 1 for p in prompts])
-        first = self._prefill(kv, prompts)
-        generated = [[t] for t in first]
-        token = torch.tensor(first, device=device)
-        state = PipelineState(
-            tokens=token[:, None].repeat(1, width).contiguous(),
-            depths=torch.zeros(n, width, dtype=torch.int64, device=device),
-            candidates=torch.zeros(n, width, dtype=torch.int64, device=device),
-            active=(torch.arange(width, device=device) == 0)[None, :].repeat(n, 1).contiguous(),
-            hidden=torch.zeros(n, width, model.config.hidden_size, dtype=model.dtype, device=device),
-            token=token.clone(),
-            position=torch.tensor([len(p) for p in prompts], device=device))
-        limits = torch.tensor([len(p) + max_tokens - 1 for p in prompts], device=device)
-        widths = torch.full((n,), width, dtype=torch.int32, device=device)
-        row_starts = (torch.arange(n, device=device) * width).int()
-        request_of_row = torch.arange(n, device=device).repeat_interleave(width)
-        slot_of_row = torch.arange(width, device=device).repeat(n)
-        for _ in range(max_tokens * (target_loops // draft_loops) + 8):      # each step emits or advances
-            if all(len(g) >= max_tokens for g in generated):
-                break
-            active = state.active.view(-1)
-            depths = state.depths.view(-1)
-            positions = torch.where(active, state.position[request_of_row] + slot_of_row, 0)
-            hidden = torch.where((depths == 0)[:, None], model.prelude(state.tokens.view(-1)),
-                                 state.hidden.view(n * width, -1))
-            lengths = torch.where(active, positions + 1, 0).int()
-            for offset in range(draft_loops):
-                plane = torch.where(active, depths + offset, 0)
-                tables = kv.tables[request_of_row, plane].contiguous()
-                blocks = tables.gather(1, (positions // self.block)[:, None]).squeeze(1).long()
-                hidden = model.recurrent(hidden, positions, kv.key, kv.value, blocks, positions % self.block, tables,
-                                         lengths, write_mask=active)
-            self.stats.loop_passes += draft_loops
-            choices = argmax_rows(model.coda(hidden).float().contiguous())
-            wire = pipeline_shift(state, widths, row_starts, choices, hidden.contiguous(), limits,
-                                  draft_loops=draft_loops, target_loops=target_loops)
-            for i, (prediction, accepted, emitted, _, drafted, verified) in enumerate(wire.tolist()):  # the step's one host read
-                if emitted and len(generated[i]) < max_tokens:
-                    generated[i].append(prediction)
-                    self.stats.committed_tokens += 1
-                    self.stats.accepted_tokens += accepted
-                self.stats.drafted_tokens += drafted
-                self.stats.verified_rows += verified
-            self.stats.rounds += n
-        return [g[:max_tokens] for g in generated]
+        requests = self._requests(prompts, self._prefill(kv, prompts), max_tokens, 0.0, -1, 1.0, 0)
+        runner = B200SpeculativeRunner(model, kv, config, max_num_seqs=len(prompts), cuda_graphs=False)
+        self._drive(runner, requests, num_speculative_tokens, in_flight)
+        return [r.generated_token_ids[:max_tokens] for r in requests]
 
-    # ---- block self-speculation ----------------------------------------------------------
     @torch.no_grad()
-    def generate(self, prompts, max_tokens: int, *, num_speculative_tokens: int, draft_loops: int = 2,
-                 target_loops: int | None = None, temperature: float = 0.0, top_k: int = -1, top_p: float = 1.0,
-                 seed: int = 0, after_prefill=None):
-        """Block self-speculation.  `temperature == 0` is greedy acceptance; otherwise drafts are
-        sampled from the draft distribution (softmax(draft logits / T) after top-k / top-p, as
-        Sampler.probabilities builds it) and verified by rejection sampling with residual
-        resampling (worker/speculative.py:47-63, 483-510 of the reference), with every uniform
-        drawn from one seeded device generator in the reference's order per round: the draft
-        draws, then the accept tests, then the final (residual or bonus) draw.  `after_prefill`, if
-        given, is called once the prompts are in the cache (benchmarks start their clock there)."""
-        model, device = self.model, self.model.device
-        sampled = temperature > 0
-        generator = torch.Generator(device=device).manual_seed(seed) if sampled else None
+    def open(self, prompts, max_tokens: int, *, num_speculative_tokens: int, draft_loops: int = 2,
+             target_loops: int | None = None, temperature: float = 0.0, top_k: int = -1, top_p: float = 1.0,
+             seed: int = 0, in_flight: int = 1) -> "DecodeSession":
+        """Everything `generate` does before its first round — pages reserved, prompts run, requests
+        created, runner built and (with CUDA graphs) its round graphs captured — as a `DecodeSession`."""
+        model = self.model
         if not 0 < top_p <= 1 or (top_k != -1 and top_k < 1):
             raise ValueError("top_p must be in (0, 1] and top_k must be -1 or positive")
-        filtered = sampled and (top_k > 0 or top_p < 1)
-
-        def filters(count):
-            if not filtered:
-                return None, None
-            return (torch.full((count,), top_k, dtype=torch.int32, device=device),
-                    torch.full((count,), top_p, dtype=torch.float32, device=device))
         target_loops = target_loops or model.config.total_ut_steps
         if not 0 < draft_loops < target_loops <= model.config.total_ut_steps:
             raise ValueError("draft_loops must be smaller than target_loops")
         k = num_speculative_tokens
+        config = SpeculativeConfig(k, draft_loops, target_loops)
         kv = self._allocate(prompts, [len(p) + max_tokens + k + 1 for p in prompts])
-        generated = [[t] for t in self._prefill(kv, prompts)]  # the first token is the prefill's argmax
+        requests = self._requests(prompts, self._prefill(kv, prompts), max_tokens, temperature, top_k, top_p, seed)
+        runner = B200SpeculativeRunner(model, kv, config, max_num_seqs=len(prompts), cuda_graphs=self.cuda_graphs,
+                                       capture_sizes=self.capture_sizes)
+        self.runner = runner
         if self.cuda_graphs:
-            self._graphs = GraphedLoops(model, kv)
-            self._graphs.prepare(len(prompts) * (k + 1))
+            runner.prepare(sampled=temperature > 0)
+        return DecodeSession(self, runner, requests, k, in_flight)
+
+    @torch.no_grad()
+    def generate(self, prompts, max_tokens: int, *, num_speculative_tokens: int, draft_loops: int = 2,
+                 target_loops: int | None = None, temperature: float = 0.0, top_k: int = -1, top_p: float = 1.0,
+                 seed: int = 0, after_prefill=None, in_flight: int = 1):
+        """Block self-speculation.  `temperature == 0` is greedy acceptance; otherwise drafts are
+        sampled from the draft distribution (softmax(draft logits / T) after top-k / top-p, as
+        Sampler.probabilities builds it) and verified by rejection sampling with residual
+        resampling (worker/speculative.py:47-63, 483-510 of the reference); request i draws from its
+        own stream, seeded `seed * 1000003 + i`.  `in_flight = 1` collects a round before the next is
+        submitted (the schedule of the reference's synchronous runner, so its counters are
+        reproduced); `in_flight = 2` submits the next round first, as the reference's asynchronous
+        engine does — the tokens are the same, rounds near a request's output limit are scheduled
+        more cautiously.  `after_prefill`, if given, is called once the prompts are in the cache and
+        the round graphs exist (benchmarks start their clock there)."""
+        session = self.open(prompts, max_tokens, num_speculative_tokens=num_speculative_tokens, draft_loops=draft_loops,
+                            target_loops=target_loops, temperature=temperature, top_k=top_k, top_p=top_p, seed=seed,
+                            in_flight=in_flight)
         if after_prefill is not None:
             after_prefill()
-        slot_values = torch.zeros(len(prompts), 2, dtype=torch.int64, device=device)
-        while any(len(g) < max_tokens for g in generated):
-            active = [i for i, g in enumerate(generated) if len(g) < max_tokens]
-            counts = [min(k + 1, max_tokens - len(generated[i])) for i in active]
-            starts = [len(prompts[i]) + len(generated[i]) - 1 for i in active]
-            n, width = len(active), max(counts)
-            rows_total = sum(counts)
-            counts_t = torch.tensor(counts)
-            # which (request, offset) cells exist, and where each lands among the retained rows
-            present = counts_t[:, None] > torch.arange(width)[None, :]                 # [n, width]
-            per_offset = present.sum(0)                                                # rows of draft pass o
-            rank = present.long().cumsum(0) - 1                                        # row of request j in pass o
-            base = torch.cat([torch.zeros(1, dtype=torch.long), per_offset.cumsum(0)[:-1]])
-            firsts = [0] + counts_t.cumsum(0).tolist()[:-1]
-            in_pass_host = [present[:, o].nonzero().flatten() for o in range(width)]
-            drafting_host = [present[present[:, o], o + 1].nonzero().flatten() if o + 1 < width
-                             else torch.zeros(0, dtype=torch.long) for o in range(width)]
-            row_request = torch.repeat_interleave(torch.arange(n), counts_t)
-            row_offset = torch.cat([torch.arange(c) for c in counts])
-            # every index tensor of the round goes to the device in one pinned, asynchronous copy:
-            # a pageable upload in the middle of a round would wait for the GPU and stall the launches
-            (active_t, starts_t, last_t, gather, first_row, row_request_t, row_offset_t, cu_rows64, *per_pass) = \
-                self._upload([torch.tensor(active), torch.tensor(starts),
-                              torch.tensor([generated[i][-1] for i in active]), (base[None, :] + rank)[present],
-                              torch.tensor(firsts), row_request, row_offset,
-                              torch.tensor([0] + counts_t.cumsum(0).tolist()), *in_pass_host, *drafting_host])
-            in_pass_dev, drafting_dev = per_pass[:width], per_pass[width:]
-            tokens = torch.zeros(n, width, dtype=torch.int64, device=device)
-            tokens[:, 0] = last_t
-            draft_logits = None
-            if sampled:  # row j of a request keeps the logits its draft j+1 was sampled from
-                draft_logits = torch.zeros(rows_total, model.config.vocab_size, dtype=torch.float32, device=device)
-                u_draft = torch.rand(n, width, generator=generator, device=device)
-            retained = []
-            # draft: one new position per request and offset, loops 0 .. d-1
-            for offset in range(width):
-                in_pass = in_pass_dev[offset]                                           # requests with c > offset
-                hidden = model.prelude(tokens[in_pass, offset])
-                for depth in range(draft_loops):
-                    hidden = self._loop(kv, hidden, active_t[in_pass], starts_t[in_pass] + offset, depth)
-                self.stats.loop_passes += draft_loops
-                self.stats.context_tokens_read += draft_loops * sum(s + offset + 1 for s, c in zip(starts, counts) if c > offset)
-                retained.append(hidden)
-                if offset + 1 >= width:
-                    break
-                drafting = drafting_dev[offset]                                         # rows of this pass that draft on
-                if drafting.numel() == 0:
-                    break
-                drafting_requests = in_pass[drafting]
-                logits = model.coda(hidden[drafting]).float().contiguous()
-                if sampled:
-                    draft_logits[first_row[drafting_requests] + offset] = logits
-                    proposed, _ = sample_rows(logits, torch.full((logits.shape[0],), temperature, device=device),
-                                              u_draft[drafting_requests, offset].contiguous(), *filters(logits.shape[0]))
-                else:
-                    proposed = argmax_rows(logits)
-                tokens[drafting_requests, offset + 1] = proposed
-                self.stats.drafted_tokens += int(logits.shape[0])
-                self.stats.coda_rows += int(logits.shape[0])
-            # verify: the retained depth-d states of all rows, request-major, loops d .. D-1
-            hidden = torch.cat(retained)[gather]
-            requests = active_t[row_request_t]
-            positions = starts_t[row_request_t] + row_offset_t
-            for depth in range(draft_loops, target_loops):
-                hidden = self._loop(kv, hidden, requests, positions, depth)
-            self.stats.loop_passes += target_loops - draft_loops
-            self.stats.context_tokens_read += (target_loops - draft_loops) * sum(s + c for s, c in zip(starts, counts))
-            self.stats.coda_rows += rows_total
-            logits = model.coda(hidden).float().contiguous()
-            cu_rows = cu_rows64.int()
-            start_tensor = starts_t
-            slots = torch.arange(n, device=device)
-            if sampled:
-                result, status = accept_rejection(
-                    logits, draft_logits, cu_rows, tokens.contiguous(), start_tensor,
-                    torch.full((n,), temperature, device=device), torch.rand(rows_total, generator=generator, device=device),
-                    torch.rand(n, generator=generator, device=device), slots, slot_values[:n].contiguous(),
-                    None, *filters(n))
-            else:
-                status = torch.zeros(n, dtype=torch.int32, device=device)
-                result = accept_greedy(logits, cu_rows, tokens.contiguous(), start_tensor, slots,
-                                       slot_values[:n].contiguous())
-            accepted = result[rows_total:rows_total + n]
-            # with prefix reuse the page reference counts go along: a frontier inside a shared page is refused
-            rolled = rollback(start_tensor, accepted + 1, kv.tables[active_t].contiguous(), self.block,
-                              refcounts=kv.refcounts)
-            values = torch.cat([result, rolled.frontier, status.long(), rolled.status.long()]).tolist()  # the round's one host read
-            if kv.refcounts is not None and 4 in values[len(values) - n:]:
-                raise RuntimeError("rollback refused: the frontier of a request lies in a shared page")
-            values = values[:len(values) - n]
-            raise_for_status(values[rows_total + 3 * n:])
-            for j, i in enumerate(active):
-                a = values[rows_total + j]
-                emitted = values[firsts[j]:firsts[j] + a + 1]
-                generated[i].extend(emitted)
-                assert values[rows_total + n + j] == starts[j] + a + 1 == values[rows_total + 2 * n + j]
-                self.stats.accepted_tokens += a
-                self.stats.committed_tokens += len(emitted)
-            self.stats.rounds += n
-            self.stats.verified_rows += rows_total
-        self._graphs = None
-        return [g[:max_tokens] for g in generated]
+        session.run()
+        session.close()
+        return [r.generated_token_ids[:max_tokens] for r in session.requests]
+
+
+class DecodeSession:
+    """The engine loop over one set of requests, one submission or collection at a time (so that a
+    caller can time a window of rounds): `submit_round()` schedules and submits the next round if the
+    in-flight limit and the requests allow one, `collect_round()` waits for the oldest round and applies
+    its tokens, `run()` alternates them until every request has its tokens."""
+
+    def __init__(self, decoder: SelfSpeculativeDecoder, runner: B200SpeculativeRunner, requests, k: int,
+                 in_flight: int = 1):
+        if in_flight not in (1, 2):
+            raise ValueError("one or two rounds in flight")
+        self.decoder, self.runner, self.requests, self.k, self.in_flight = decoder, runner, requests, k, in_flight
+        self.pipeline = runner.config.mode == "pipeline"
+        self.pending = deque()
+
+    def submit_round(self) -> bool:
+        if len(self.pending) >= self.in_flight:
+            return False
+        batch = self.decoder._schedule(self.requests, self.k, self.pipeline)
+        if batch is None:
+            return False
+        self.pending.append(self.runner.submit(batch))
+        self.decoder._after_submission(batch, self.pipeline)
+        stats, config = self.decoder.stats, self.runner.config
+        if self.pipeline:
+            stats.loop_passes += config.draft_loops
+        else:
+            stats.loop_passes += config.draft_loops * max(s.token_count for s in batch.requests) \
+                + config.target_loops - config.draft_loops
+            stats.coda_rows += sum(2 * s.token_count - 1 for s in batch.requests)
+        return True
+
+    def collect_round(self) -> bool:
+        if not self.pending:
+            return False
+        ticket = self.pending.popleft()
+        self.decoder._apply(ticket, ticket.collect(), self.pipeline, self.runner.config)
+        self._sync_stats()
+        return True
+
+    def _sync_stats(self):
+        stats, source = self.decoder.stats, self.runner.stats
+        stats.rounds, stats.drafted_tokens, stats.verified_rows = source.rounds, source.drafted_tokens, source.verified_rows
+
+    def run(self):
+        while True:
+            while self.submit_round():
+                pass
+            if not self.collect_round():
+                break
+
+    def drain(self):
+        while self.collect_round():
+            pass
+
+    def close(self):
+        self.drain()
+        for request in self.requests:
+            self.runner.release(request)
+        self._sync_stats()
