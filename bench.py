@@ -462,7 +462,9 @@ def run_gpu(args):
                          dtype=torch.float64, device=device)
     table = times[None].cpu() if world == 1 else all_gather_rows(times)
     if rank == 0:
-        job = combine_ranks(table[:, :4], world, steps)
+        per_step = table[:, :4].clone()
+        per_step[:, 2:] /= steps                         # tokens of the timed window -> per step
+        job = combine_ranks(per_step, world, steps)
         max_ms, mean_ms = float(table[:, 0].max()), float(table[:, 0].mean())
         e2e_value = float(table[:, 4].sum()) / (float(table[:, 1].max()) / 1e3)
         peak, peak_kind = measured_peaks()

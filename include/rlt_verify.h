@@ -80,6 +80,17 @@ RLT_API const char* rlt_last_error(void);
 RLT_API int rlt_silu_and_mul(const void* gate, const void* up, void* out, int64_t n,
                      int dtype, rlt_stream_t stream);
 
+/* SiLU-and-Mul over the two column halves of one fused gate/up projection:
+ *   out[r, c] = T(silu_f32(f32(gate_up[r, c]))) * gate_up[r, cols + c]
+ * with the arithmetic of rlt_silu_and_mul (bit-identical results).  The reference's MLP runs gate_proj
+ * and up_proj as two GEMMs on the same input (vllm_rlt/models/ouro.py:196-197); running them as one
+ * GEMM over the concatenated weights leaves gate and up side by side in one [rows, 2 * cols] tensor,
+ * which this entry reads in place.  gate_up: `rows` rows of `row_stride` elements (row_stride >=
+ * 2 * cols); out: [rows, cols] contiguous.  No counterpart in the reference (its op takes two
+ * contiguous tensors). */
+RLT_API int rlt_silu_and_mul_packed(const void* gate_up, int64_t row_stride, void* out, int64_t rows,
+                            int64_t cols, int dtype, rlt_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * KV write.  For each active row r: cache[write_blocks[r], write_offsets[r], :, :] = k[r]
  * (and v).  A row is active iff r < *active_rows (when active_rows != NULL) and

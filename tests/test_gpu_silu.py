@@ -160,3 +160,21 @@ def test_torch_op_registration_dispatches_cuda_to_the_kernel():
     up = torch.randn_like(gate)
     out = torch.ops.vllm_rlt_b200_test.silu_and_mul(gate, up)
     assert torch.equal(out, torch_reference(gate, up))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,cols,pad", [(128, 5632, 0), (640, 5632, 0), (7, 40, 0), (5, 33, 0), (3, 24, 8), (1, 1, 0)])
+def test_packed_form_reads_the_two_halves_of_one_projection_in_place(dtype, rows, cols, pad):
+    # gate and up side by side in one [rows, 2 * cols] tensor (optionally a column slice of a wider one, so
+    # the row stride exceeds 2 * cols); bit-identical to the two-tensor op and to F.silu(gate) * up
+    g = torch.Generator().manual_seed(rows * 31 + cols)
+    wide = (torch.randn(rows, 2 * cols + pad, generator=g) * 3).to(dtype).cuda()
+    packed = wide[:, : 2 * cols]
+    gate, up = packed[:, :cols].contiguous(), packed[:, cols:].contiguous()
+    got = rlt.silu_and_mul_packed(packed)
+    assert got.shape == (rows, cols) and got.is_contiguous()
+    assert torch.equal(got, rlt.silu_and_mul(gate, up))
+    assert torch.equal(got, torch.nn.functional.silu(gate) * up)
+    with pytest.raises(ValueError):
+        rlt.silu_and_mul_packed(wide[:, :3] if cols != 1 else wide[:, :1])
+    assert rlt.silu_and_mul_packed(packed[:0]).shape == (0, cols)

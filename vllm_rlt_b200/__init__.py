@@ -8,7 +8,7 @@ raises if the CUDA library has not been built.
 """
 
 from ._capi import NativeLibraryMissing, load as load_library
-from .activation import register_torch_op, silu_and_mul
+from .activation import register_torch_op, silu_and_mul, silu_and_mul_packed
 from .attention import (B200_CAPABILITIES, AttentionBackend, B200PagedAttention, BackendCapabilities,
                         create_backend)
 from .decoder import DecodeStats, GraphedLoops, PagedKV, SelfSpeculativeDecoder
@@ -29,5 +29,5 @@ __all__ = [
     "argmax_rows", "PipelineState", "create_backend", "decode_result", "finalize_tokens", "pipeline_shift", "kv_write", "load_library", "probabilities", "raise_for_status",
     "register_torch_op", "rollback", "rope_kv_write", "sample_rows", "sandwich_norm", "silu_and_mul",
     "B200SpeculativeRunner", "ModelRunnerOutput", "Request", "SamplingParams", "ScheduledRequest", "SchedulerOutput",
-    "SpeculativeConfig", "SpeculativeRoundTicket", "SpeculativeStats", "round_uniforms",
+    "SpeculativeConfig", "SpeculativeRoundTicket", "SpeculativeStats", "round_uniforms", "silu_and_mul_packed",
 ]

@@ -25,6 +25,7 @@ SIGNATURES = {
     "rlt_version": (c_char_p, []),
     "rlt_last_error": (c_char_p, []),
     "rlt_silu_and_mul": (_I, [_P, _P, _P, _L, _I, _P]),
+    "rlt_silu_and_mul_packed": (_I, [_P, _L, _P, _L, _L, _I, _P]),
     "rlt_kv_write": (_I, [_P, _P, _L, _L, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P]),
     "rlt_verify_attention_workspace_bytes": (_Z, [_I, _I, _I, _I, _I, _I]),
     "rlt_verify_attention": (_I, [_P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _I,

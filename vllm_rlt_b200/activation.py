@@ -46,6 +46,28 @@ def silu_and_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def silu_and_mul_packed(gate_up: torch.Tensor) -> torch.Tensor:
+    """``F.silu(gate_up[:, :F]) * gate_up[:, F:]`` for the output ``[rows, 2 * F]`` of one GEMM over the
+    concatenated gate and up weights (the two projections of ``OuroMLP``, ``vllm_rlt/models/ouro.py:196-197``,
+    share their input).  Same arithmetic and bits as ``silu_and_mul`` on the two halves."""
+    _capi.require_cuda(gate_up)
+    if gate_up.dim() != 2 or gate_up.shape[1] % 2 or gate_up.stride(1) != 1:
+        raise ValueError("silu_and_mul_packed expects [rows, 2 * features] with unit inner stride")
+    if gate_up.dtype not in _capi.DTYPE_CODES:
+        raise TypeError("silu_and_mul supports float32, float16 and bfloat16")
+    if torch.is_grad_enabled() and gate_up.requires_grad:
+        raise RuntimeError("silu_and_mul is inference-only")
+    rows, cols = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty(rows, cols, dtype=gate_up.dtype, device=gate_up.device)
+    if out.numel() == 0:
+        return out
+    with torch.cuda.device(gate_up.device):
+        status = _capi.load().rlt_silu_and_mul_packed(_capi.ptr(gate_up), gate_up.stride(0), _capi.ptr(out), rows, cols,
+                                                      _capi.DTYPE_CODES[gate_up.dtype], _capi.stream_of(gate_up))
+    _capi.check(status, "silu_and_mul_packed")
+    return out
+
+
 def register_torch_op(namespace: str = "vllm_rlt") -> None:
     """Make ``torch.ops.<namespace>.silu_and_mul`` dispatch CUDA tensors to this kernel.
 

@@ -125,8 +125,76 @@ int launch(const void* gate, const void* up, void* out, int64_t n, cudaStream_t 
   return launch_status("silu_and_mul_kernel");
 }
 
+// Row-strided form: gate and up are [rows, cols] views with their own row strides (the two column
+// halves of one fused gate/up projection), out is contiguous.  Every thread handles kUnroll 16-byte
+// vectors of one row; rows whose three pointers are not 16-byte aligned go through the scalar loop.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+silu_and_mul_rows_kernel(const T* __restrict__ gate, int64_t gate_stride, const T* __restrict__ up, int64_t up_stride,
+                         T* __restrict__ out, int64_t rows, int64_t cols, int vector_ok) {
+  constexpr int kElems = 16 / sizeof(T);
+  const int64_t row = blockIdx.y;
+  const T* g = gate + row * gate_stride;
+  const T* u = up + row * up_stride;
+  T* o = out + row * cols;
+  const int64_t nvec = vector_ok ? cols / kElems : 0;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * kThreads;
+  const uint4* gv = reinterpret_cast<const uint4*>(g);
+  const uint4* uv = reinterpret_cast<const uint4*>(u);
+  uint4* ov = reinterpret_cast<uint4*>(o);
+  for (int64_t base = tid; base < nvec; base += nthreads * kUnroll) {
+    uint4 gr[kUnroll], ur[kUnroll];
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      const int64_t i = base + j * nthreads;
+      if (i < nvec) { gr[j] = __ldcs(gv + i); ur[j] = __ldcs(uv + i); }
+    }
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      const int64_t i = base + j * nthreads;
+      if (i < nvec) ov[i] = Pack<T>::apply(gr[j], ur[j]);
+    }
+  }
+  for (int64_t i = nvec * kElems + tid; i < cols; i += nthreads) o[i] = Pack<T>::scalar(g[i], u[i]);
+}
+
+template <typename T>
+int launch_rows(const void* gate, int64_t gate_stride, const void* up, int64_t up_stride, void* out, int64_t rows,
+                int64_t cols, cudaStream_t stream) {
+  constexpr int kElems = 16 / sizeof(T);
+  const bool vector_ok = aligned16(gate) && aligned16(up) && aligned16(out) && gate_stride % kElems == 0 &&
+                         up_stride % kElems == 0 && cols % kElems == 0;
+  const int64_t per_row = vector_ok ? (cols / kElems + kUnroll - 1) / kUnroll : cols;
+  int64_t blocks_x = (per_row + kThreads - 1) / kThreads;
+  if (blocks_x < 1) blocks_x = 1;
+  if (blocks_x > 64) blocks_x = 64;
+  if (rows > 65535) {
+    set_last_error_text("silu_and_mul_packed: more than 65535 rows");
+    return RLT_ERR_INVALID;
+  }
+  silu_and_mul_rows_kernel<T><<<dim3(static_cast<unsigned>(blocks_x), static_cast<unsigned>(rows)), kThreads, 0, stream>>>(
+      static_cast<const T*>(gate), gate_stride, static_cast<const T*>(up), up_stride, static_cast<T*>(out), rows, cols,
+      vector_ok ? 1 : 0);
+  return launch_status("silu_and_mul_rows_kernel");
+}
+
 }  // namespace
 }  // namespace rlt
+
+extern "C" RLT_API int rlt_silu_and_mul_packed(const void* gate_up, int64_t row_stride, void* out, int64_t rows,
+                                               int64_t cols, int dtype, rlt_stream_t stream) {
+  using namespace rlt;
+  RLT_REQUIRE(dtype_valid(dtype), "silu_and_mul_packed supports float32, float16 and bfloat16");
+  RLT_REQUIRE(rows >= 0 && cols >= 0 && row_stride >= 2 * cols, "silu_and_mul_packed: invalid shape");
+  if (rows == 0 || cols == 0) return RLT_OK;
+  RLT_REQUIRE(gate_up && out, "silu_and_mul_packed: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int status = RLT_OK;
+  RLT_DISPATCH_DTYPE(dtype, T, status = launch_rows<T>(gate_up, row_stride, static_cast<const T*>(gate_up) + cols,
+                                                       row_stride, out, rows, cols, s));
+  return status;
+}
 
 extern "C" RLT_API int rlt_silu_and_mul(const void* gate, const void* up, void* out, int64_t n, int dtype,
                                 rlt_stream_t stream) {

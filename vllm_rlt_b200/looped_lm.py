@@ -17,7 +17,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
-from .activation import silu_and_mul
+from .activation import silu_and_mul, silu_and_mul_packed
 from .attention import B200PagedAttention
 from .kv_cache import kv_write
 from .layers import rope_kv_write, sandwich_norm
@@ -106,6 +106,9 @@ class LoopedLM:
         # one projection for q, k and v: the rotary kernel reads its three column slices in place
         self.qkv = [torch.cat([self.w[f"model.layers.{layer}.self_attn.{n}_proj.weight"] for n in "qkv"])
                     for layer in range(config.num_hidden_layers)] if fused else None
+        # and one for gate and up: SiLU-and-Mul reads the two column halves of its output in place
+        self.gate_up = [torch.cat([self.w[f"model.layers.{layer}.mlp.{n}_proj.weight"] for n in ("gate", "up")])
+                        for layer in range(config.num_hidden_layers)] if fused else None
         self.inv_freq = 1.0 / (config.rope_theta ** (
             torch.arange(0, config.head_dim, 2, dtype=torch.float32, device=self.device) / config.head_dim))
 
@@ -165,9 +168,10 @@ class LoopedLM:
 
     def _recurrent_fused(self, hidden, positions, key_pool, value_pool, write_blocks, write_offsets, block_tables,
                          context_lengths, active_rows=None, packed=None, write_mask=None):
-        """The same loop with ten launches per layer: QKV GEMM, rope_kv_write, attention, O GEMM,
-        sandwich_norm (residual add + the MLP's input norm), gate and up GEMMs, silu_and_mul, down
-        GEMM, sandwich_norm (residual add + the next layer's input norm, or the final norm).
+        """The same loop with nine launches per layer (ten when the attention merges chunks): QKV GEMM,
+        rope_kv_write, attention, O GEMM, sandwich_norm (residual add + the MLP's input norm), one gate-and-up
+        GEMM, silu_and_mul_packed, down GEMM, sandwich_norm (residual add + the next layer's input norm, or the
+        final norm).
         `active_rows` (0-dim int32) marks padding rows of a captured graph: they write no K/V."""
         c, w = self.config, self.w
         cos, sin = self.rope(positions)
@@ -190,9 +194,7 @@ class LoopedLM:
                 stream, x = sandwich_norm(attended, w[p + "input_layernorm_2.weight"], c.rms_norm_eps,
                                           hidden if stream is None else stream,
                                           w[p + "post_attention_layernorm.weight"], in_place=stream is not None)
-                gate = F.linear(x, w[p + "mlp.gate_proj.weight"])
-                up = F.linear(x, w[p + "mlp.up_proj.weight"])
-                mlp = F.linear(silu_and_mul(gate, up), w[p + "mlp.down_proj.weight"])
+                mlp = F.linear(silu_and_mul_packed(F.linear(x, self.gate_up[layer])), w[p + "mlp.down_proj.weight"])
                 following = (w[f"model.layers.{layer + 1}.input_layernorm.weight"]
                              if layer + 1 < c.num_hidden_layers else w["model.norm.weight"])
                 stream, x = sandwich_norm(mlp, w[p + "post_attention_layernorm_2.weight"], c.rms_norm_eps, stream,
