@@ -592,6 +592,78 @@ def run_prefill_only(args):
                       "peak_kind": "measured" if peaks else "fallback", "frac": flops / ms / 1e9 / peak}))
 
 
+def silu_comparison(device, steps: int, warmup: int):
+    """SiLU-and-Mul at the path's shapes, this library's kernel beside the reference's own CUDA kernel when its
+    extension (`vllm_rlt._C`, built from the reference's unmodified csrc for sm_100) is present under
+    baseline/_ref: CUDA events, per call, L2-warm (the same tensors every call) and L2-cold (a ring of input
+    sets larger than L2, so every call reads from HBM), plus one case where gate, up and out each start at a
+    different 16-byte misalignment."""
+    import glob
+
+    import vllm_rlt_b200 as rlt
+
+    kernels = {"b200": rlt.silu_and_mul}
+    found = glob.glob(str(ROOT / "baseline" / "_ref" / "vllm_rlt" / "_C*.so"))
+    note = None
+    if found:
+        try:
+            torch.ops.load_library(found[0])
+            kernels["reference"] = torch.ops.vllm_rlt.silu_and_mul
+        except Exception as error:
+            note = f"the reference extension did not load: {error}"
+    else:
+        note = "no reference extension under baseline/_ref"
+    g = torch.Generator(device=device).manual_seed(3)
+    peak, _ = measured_peaks()
+
+    unroll = 32
+
+    def timed(fn, sets):
+        """Microseconds per call: a CUDA graph of `unroll` calls (as the reference's own benchmark of this
+        kernel does, benchmarks/kernels/silu_and_mul.py there), replayed `steps` times, so that the host's
+        per-call cost is not what is measured."""
+        for i in range(max(warmup, 1)):
+            fn(*sets[i % len(sets)])
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            kept = [fn(*sets[i % len(sets)]) for i in range(unroll)]
+        graph.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(max(steps, 1)):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        del kept
+        return a.elapsed_time(b) / (max(steps, 1) * unroll) * 1e3
+
+    table = []
+    for rows in (128, 640, 768, 1024):
+        nbytes = 3 * rows * FFN * 2
+        ring = max(2, int(400e6 // (2 * rows * FFN * 2)) + 1)            # inputs of the ring: > 3 x L2
+        sets = [((torch.randn(rows, FFN, device=device, generator=g) * 3).to(torch.bfloat16),
+                 torch.randn(rows, FFN, device=device, generator=g).to(torch.bfloat16)) for _ in range(ring)]
+        row = {"shape": [rows, FFN], "dtype": "bf16", "bytes": nbytes}
+        for name, fn in kernels.items():
+            warm, cold = timed(fn, sets[:1]), timed(fn, sets)
+            row[name] = {"warm_us": warm, "cold_us": cold, "cold_gbs": nbytes / cold / 1e3, "cold_frac": nbytes / cold / 1e3 / peak}
+        if "reference" in kernels:
+            assert torch.equal(kernels["b200"](*sets[0]), kernels["reference"](*sets[0]))
+        table.append(row)
+        del sets
+    # independent misalignments: gate +2, up +4, (out is allocated by the op) elements off a 16-byte boundary
+    rows = 640
+    base = [torch.randn(rows * FFN + 16, device=device, generator=g).to(torch.bfloat16) for _ in range(2)]
+    gate, up = base[0][1:1 + rows * FFN].view(rows, FFN), base[1][2:2 + rows * FFN].view(rows, FFN)
+    row = {"shape": [rows, FFN], "dtype": "bf16", "misaligned": "gate +2 bytes, up +4 bytes", "bytes": 3 * rows * FFN * 2}
+    for name, fn in kernels.items():
+        row[name] = {"warm_us": timed(fn, [(gate, up)])}
+    table.append(row)
+    return {"silu_and_mul": table, "reference_kernel": "vllm_rlt._C built from the reference's csrc for sm_100"
+            if "reference" in kernels else None, "note": note}
+
+
 def run_small_only(args):
     """Profiling aid: the acceptance kernels (`--only accept`) or SiLU-and-Mul (`--only silu`) at the
     step's shapes, a few hundred MB on the device, timed per call with CUDA events."""
@@ -614,12 +686,7 @@ def run_small_only(args):
         return a.elapsed_time(b) / args.steps
 
     if args.only == "silu":
-        g = torch.Generator(device=device).manual_seed(3)
-        gate = (torch.randn(work.rows, FFN, device=device, generator=g) * 3).to(torch.bfloat16)
-        up = torch.randn(work.rows, FFN, device=device, generator=g).to(torch.bfloat16)
-        ms = timed(lambda: rlt.silu_and_mul(gate, up))
-        nbytes = 3 * gate.numel() * 2
-        out.update(rows=work.rows, ms=ms, bytes=nbytes, gbs=nbytes / ms / 1e6)
+        out.update(silu_comparison(device, args.steps, args.warmup))
     else:
         x = {k: v.to(device) for k, v in work.host_inputs(pin=False).items() if k not in ("q", "k", "v", "gate", "up")}
         per_row_t = x["temperature"].repeat_interleave(TOKENS)

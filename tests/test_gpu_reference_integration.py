@@ -1,0 +1,142 @@
+"""The B200 kernels plugged into the vllm-rlt reference itself.
+
+Runs only where an UNMODIFIED copy of the reference package is importable from `baseline/_ref/`
+(`python -m pip install --no-deps --no-build-isolation --target baseline/_ref <reference checkout>`; the
+directory is not part of this repository).  The test then does what a maintainer of the reference would do
+to adopt the kernels: one more backend name in `validate_backend_name` / `_create_explicit`
+that wraps `B200PagedAttention` in the reference's OWN `AttentionBackend` / `BackendCapabilities` classes, and
+`register_torch_op("vllm_rlt")` so that `torch.ops.vllm_rlt.silu_and_mul` dispatches CUDA tensors to the B200
+kernel — and runs the reference's engine (its scheduler, KV-cache manager, speculative runner and model code,
+on the GPU) to the golden tokens of its CPU run (tests/golden/decode.pt).
+"""
+
+import dataclasses
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import vllm_rlt_b200 as rlt
+
+REFERENCE = Path(__file__).resolve().parents[1] / "baseline" / "_ref"
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not (REFERENCE / "vllm_rlt").is_dir(), reason="no reference package under baseline/_ref")]
+
+
+@pytest.fixture(scope="module")
+def reference():
+    """The reference package with its own native extension kept out, so that the only CUDA implementation
+    of `torch.ops.vllm_rlt.silu_and_mul` is the one this library registers."""
+    sys.modules.setdefault("vllm_rlt._C", None)          # `import vllm_rlt._C` now fails: the op is defined in Python
+    sys.path.insert(0, str(REFERENCE))
+    try:
+        import vllm_rlt
+        import vllm_rlt.kernels.activation  # defines the schema + the composite fallback
+    except Exception as error:  # missing optional dependency of the reference on this box
+        pytest.skip(f"the reference package does not import here: {error}")
+    rlt.register_torch_op("vllm_rlt")
+    return vllm_rlt
+
+
+@pytest.fixture
+def b200_backend(reference, monkeypatch):
+    """The two-line patch of the reference: a backend name and its constructor."""
+    from vllm_rlt.attention import backend as backend_module
+    from vllm_rlt.core import kv_cache_manager as cache_module
+
+    original = backend_module.validate_backend_name
+
+    def validate(name):
+        if name != "b200":
+            original(name)
+
+    def explicit(name, device, dtype, head_dim, block_size):
+        if name != "b200":
+            return create(name, device, dtype, head_dim, block_size)
+        ours = rlt.create_backend(device, dtype, head_dim, block_size)
+        capabilities = backend_module.BackendCapabilities(**dataclasses.asdict(ours.capabilities))
+        return backend_module.AttentionBackend(ours.kernel, capabilities, {"backend": "b200"})
+
+    create = backend_module._create_explicit
+    monkeypatch.setattr(backend_module, "validate_backend_name", validate)
+    monkeypatch.setattr(cache_module, "validate_backend_name", validate)
+    monkeypatch.setattr(backend_module, "_create_explicit", explicit)
+    return backend_module
+
+
+def reference_model(case, dtype=torch.float32):
+    from vllm_rlt.models import OuroConfig, OuroForCausalLM
+
+    config = OuroConfig(**case["config"], max_position_embeddings=256, bos_token_id=0, eos_token_id=0)
+    model = OuroForCausalLM(config)
+    state = rlt.seeded_state_dict(rlt.LoopedLMConfig(**case["config"]), case["seed"])
+    model.load_state_dict({name: state[name] for name in model.state_dict()}, strict=True)
+    return model.to(device="cuda", dtype=dtype)
+
+
+def run_engine(engine, prompts, params):
+    for i, prompt in enumerate(prompts):
+        engine.add_request(str(i), list(prompt), params)
+    finished = {}
+    while engine.has_unfinished_requests():
+        for output in engine.step():
+            if output.finished:
+                finished[output.request_id] = list(output.token_ids)
+    return [finished[str(i)] for i in range(len(prompts))]
+
+
+def test_torch_op_of_the_reference_dispatches_to_the_b200_kernel(reference):
+    from vllm_rlt.kernels.activation import silu_and_mul
+
+    g = torch.Generator().manual_seed(1)
+    gate, up = (torch.randn(37, 5632, generator=g) * 3).bfloat16().cuda(), torch.randn(37, 5632, generator=g).bfloat16().cuda()
+    assert torch.equal(silu_and_mul(gate, up), rlt.silu_and_mul(gate, up))
+    assert torch.equal(silu_and_mul(gate, up), torch.nn.functional.silu(gate) * up)
+    with pytest.raises(RuntimeError, match="contiguous"):          # the B200 entry is what ran: its own check fires
+        silu_and_mul(gate[:, ::2], up[:, ::2])
+
+
+@pytest.mark.parametrize("name", ["config1", "tiny_k3"])
+def test_reference_engine_decodes_the_golden_tokens_on_the_b200_backend(reference, b200_backend, golden, name):
+    from vllm_rlt import CacheConfig, SamplingParams, SpeculativeConfig
+    from vllm_rlt.engine.stage_engine import StageEngine
+
+    case = golden("decode.pt")[name]
+    model = reference_model(case)
+    params = SamplingParams(max_tokens=case["max_tokens"], ignore_eos=True)
+    native = StageEngine(model, cache_config=CacheConfig(256, case["block"]), attention_backend="b200")
+    cache = native.cache_manager
+    assert type(cache.attention).__module__.startswith("vllm_rlt.attention")       # the reference's adapter class ...
+    assert isinstance(cache.attention.kernel, rlt.B200PagedAttention)             # ... around the B200 kernel
+    assert cache.attention_info["selected_backend"] == "b200"
+    assert run_engine(native, case["prompts"], params) == case["tokens"]
+    speculative = StageEngine(model, cache_config=CacheConfig(256, case["block"]), attention_backend="b200",
+                              speculative_config=SpeculativeConfig(case["k"], draft_loops=case["draft_loops"],
+                                                                   target_loops=case["target_loops"]))
+    assert run_engine(speculative, case["prompts"], params) == case["tokens"]
+    stats, want = speculative.speculative_runner.stats, case["stats"]
+    assert (stats.rounds, stats.drafted_tokens, stats.verified_rows) == (want["rounds"], want["drafted"], want["verified_rows"])
+    torch.cuda.synchronize()
+
+
+def test_reference_engine_on_the_tiled_kernel_agrees_with_its_torch_backend(reference, b200_backend):
+    # bf16, 128-wide heads, 16-token pages: the reference's model and runner on the TMA / tensor-core kernel
+    # against the same engine on its own Torch attention; greedy tokens agree (bf16 rounding may flip a near-tie)
+    from vllm_rlt import CacheConfig, SamplingParams, SpeculativeConfig
+    from vllm_rlt.engine.stage_engine import StageEngine
+
+    case = dict(config=dict(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                            num_attention_heads=2, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
+                            rope_theta=10000.0, total_ut_steps=4, initializer_range=0.02), seed=21)
+    model = reference_model(case, torch.bfloat16)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(1, 512, (n,), generator=g).tolist() for n in (40, 3, 17)]
+    params = SamplingParams(max_tokens=12, ignore_eos=True)
+    outputs = {}
+    for backend in ("torch", "b200"):
+        engine = StageEngine(model, cache_config=CacheConfig(64, 16), attention_backend=backend,
+                             speculative_config=SpeculativeConfig(3))
+        outputs[backend] = run_engine(engine, prompts, params)
+    same = sum(a == b for x, y in zip(outputs["torch"], outputs["b200"]) for a, b in zip(x, y))
+    assert same >= 0.8 * 36, outputs
