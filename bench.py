@@ -625,9 +625,10 @@ def silu_comparison(device, steps: int, warmup: int):
         for i in range(max(warmup, 1)):
             fn(*sets[i % len(sets)])
         torch.cuda.synchronize()
+        calls = max(unroll, len(sets))                 # every set of a cold ring is visited once per replay
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            kept = [fn(*sets[i % len(sets)]) for i in range(unroll)]
+            kept = [fn(*sets[i % len(sets)]) for i in range(calls)]
         graph.replay()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
@@ -636,7 +637,7 @@ def silu_comparison(device, steps: int, warmup: int):
         b.record()
         torch.cuda.synchronize()
         del kept
-        return a.elapsed_time(b) / (max(steps, 1) * unroll) * 1e3
+        return a.elapsed_time(b) / (max(steps, 1) * calls) * 1e3
 
     table = []
     for rows in (128, 640, 768, 1024):
