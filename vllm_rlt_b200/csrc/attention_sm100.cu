@@ -345,24 +345,66 @@ struct __align__(1024) SharedStorage {
   unsigned long long full[kWarps][kStages];
 };
 
-__device__ __forceinline__ ItemCtx claim_item(const AttentionArgs& a, const Workspace& ws, int lane) {
-  ItemCtx c;
+// Claiming a work item is a chain of dependent global accesses (the atomic that hands out the index,
+// the item record, then the rows' lengths and the first page ids).  It is split into stages that the
+// main loop issues an item ahead of their use, each stage only after the previous one has had a page's
+// time to arrive, so that none of them is waited for:
+//   claim_index   the atomic; result first used one whole item later
+//   fetch_item    the 16-byte item record
+//   fetch_rows    lane-indexed: the group's row lengths and the chunk's first 32 page ids
+//   finish_item   warp reductions over what fetch_rows loaded
+struct Pending {
+  int valid;
+  Item it;
+  int len;
+  int page;
+};
+
+__device__ __forceinline__ unsigned claim_index(const Workspace& ws, int lane) {
   unsigned idx = 0;
   if (lane == 0) idx = atomicAdd(&ws.header->next_item, 1u);
-  idx = __shfl_sync(0xffffffffu, idx, 0);
+  return __shfl_sync(0xffffffffu, idx, 0);
+}
+
+__device__ __forceinline__ Pending fetch_item(const Workspace& ws, unsigned idx) {
+  Pending p;
   const unsigned full = ws.header->full_items, last = ws.header->last_items;
-  c.valid = idx < full + last;
-  c.row_start = c.table_row = c.nrows = c.kv_head = c.chunk = c.chunk_start = c.ntiles = 0;
-  c.len = 0;
+  p.valid = idx < full + last;
+  p.len = 0;
+  p.page = -1;
+  p.it.row_start = p.it.table_row = p.it.nrows_head = p.it.chunk = 0;
+  if (p.valid) {
+    const int4 raw = *reinterpret_cast<const int4*>(idx < full ? &ws.items_a[idx] : &ws.items_b[idx - full]);
+    p.it.row_start = raw.x; p.it.table_row = raw.y; p.it.nrows_head = raw.z; p.it.chunk = raw.w;
+  }
+  return p;
+}
+
+__device__ __forceinline__ void fetch_rows(const AttentionArgs& a, const Workspace& ws, Pending& p, int lane) {
+  if (!p.valid) return;
+  const int nrows = p.it.nrows_head & 0xffff;
+  p.len = lane < nrows ? ws.row_len[p.it.row_start + lane] : 0;
+  int cstart, cend;
+  chunk_range(p.it.chunk, &cstart, &cend);
+  // Page ids are fetched for every lane whose entry lies inside the table row: entries beyond the
+  // group's pages are padding, loaded but never used as addresses (finish_item discards them).
+  const int first = cstart / kPage;
+  const int32_t* table = a.block_tables + static_cast<int64_t>(p.it.table_row) * a.table_width;
+  p.page = first + lane < a.table_width ? table[first + lane] : -1;
+}
+
+__device__ __forceinline__ ItemCtx finish_item(const Pending& p, int lane) {
+  ItemCtx c;
+  c.valid = p.valid;
+  c.row_start = p.it.row_start;
+  c.table_row = p.it.table_row;
+  c.nrows = p.it.nrows_head & 0xffff;
+  c.kv_head = p.it.nrows_head >> 16;
+  c.chunk = p.it.chunk;
+  c.len = p.len;
+  c.chunk_start = c.ntiles = 0;
   c.page = -1;
   if (!c.valid) return c;
-  const Item it = idx < full ? ws.items_a[idx] : ws.items_b[idx - full];
-  c.row_start = it.row_start;
-  c.table_row = it.table_row;
-  c.nrows = it.nrows_head & 0xffff;
-  c.kv_head = it.nrows_head >> 16;
-  c.chunk = it.chunk;
-  c.len = lane < c.nrows ? ws.row_len[it.row_start + lane] : 0;
   int longest = c.len;
 #pragma unroll
   for (int x = 16; x > 0; x >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, x));
@@ -370,9 +412,14 @@ __device__ __forceinline__ ItemCtx claim_item(const AttentionArgs& a, const Work
   chunk_range(c.chunk, &c.chunk_start, &cend);
   const int visible = min(cend, longest) - c.chunk_start;
   c.ntiles = visible > 0 ? (visible + kPage - 1) / kPage : 0;
-  const int32_t* table = a.block_tables + static_cast<int64_t>(c.table_row) * a.table_width + c.chunk_start / kPage;
-  c.page = lane < c.ntiles ? table[lane] : -1;
+  c.page = lane < c.ntiles ? p.page : -1;
   return c;
+}
+
+__device__ __forceinline__ ItemCtx claim_item(const AttentionArgs& a, const Workspace& ws, int lane) {
+  Pending p = fetch_item(ws, claim_index(ws, lane));
+  fetch_rows(a, ws, p, lane);
+  return finish_item(p, lane);
 }
 
 // Merge of one row's per-chunk partials, one warp per (row, query head), lane l owning dims
@@ -489,14 +536,43 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 
   unsigned issued = 0, consumed = 0;  // tiles of this warp's ring
   bool failed = false;
+  // A warp holds two items: `cur` is being scored and `nxt` is the one it will score next (claiming
+  // further ahead costs more in the schedule's tail than it saves).  nxt is claimed when cur starts,
+  // one stage of the chain per page of cur, so it is complete — record, rows, Q fragments — after
+  // cur's third page and the issue side can run on into its pages as before.
   ItemCtx cur = claim_item(a, ws, lane);
-  ItemCtx nxt = cur.valid ? claim_item(a, ws, lane) : cur;
+  ItemCtx nxt = cur;
+  nxt.valid = 0;
+
+  // Q rows of an item as mma A-fragments (fragment rows g and g + 8 -> group row and query head).
+  auto load_q = [&](const ItemCtx& it, uint32_t (&q)[8][4]) {
+    const int rows = it.nrows * gqa;
+    const int r0 = g, r1 = g + 8;
+    const int l0 = __shfl_sync(0xffffffffu, it.len, (r0 < rows ? r0 : 0) / gqa);
+    const int l1 = __shfl_sync(0xffffffffu, it.len, (r1 < rows ? r1 : 0) / gqa);
+    const bool live0 = it.valid && r0 < rows && l0 > 0, live1 = it.valid && r1 < rows && l1 > 0;
+    const int64_t row0 = it.row_start + r0 / gqa, row1 = it.row_start + r1 / gqa;
+    const int head0 = it.kv_head * gqa + r0 % gqa, head1 = it.kv_head * gqa + r1 % gqa;
+    const int64_t e0 = (row0 * a.q_heads + head0) * kHeadDim, e1 = (row1 * a.q_heads + head1) * kHeadDim;
+    const uint32_t* qp = reinterpret_cast<const uint32_t*>(a.q);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int c = ks * 16 + 2 * t;
+      q[ks][0] = live0 ? __ldg(qp + ((e0 + c) >> 1)) : 0u;
+      q[ks][1] = live1 ? __ldg(qp + ((e1 + c) >> 1)) : 0u;
+      q[ks][2] = live0 ? __ldg(qp + ((e0 + c + 8) >> 1)) : 0u;
+      q[ks][3] = live1 ? __ldg(qp + ((e1 + c + 8) >> 1)) : 0u;
+    }
+  };
+  uint32_t qa[8][4];
+  load_q(cur, qa);
 
   // Issue side state, all in registers: the item whose pages are being requested.
   int iss_valid = cur.valid, iss_ntiles = cur.ntiles, iss_x0 = cur.kv_head * kHeadDim;
   int iss_page = cur.page, iss_page_base = 0, iss_tile = 0;
   const int32_t* iss_table = a.block_tables + static_cast<int64_t>(cur.table_row) * a.table_width + cur.chunk_start / kPage;
   bool iss_on_next = false;  // the issue side has moved on to `nxt`
+  bool nxt_ready = false;    // nxt's claim is complete (it may still be the invalid end marker)
 
   // Keep every stage that is not being scored in flight.  Called when all tiles below
   // `consumed` are finished, so tile n may go into stage n % kStages as long as
@@ -505,7 +581,7 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     while (issued - consumed < static_cast<unsigned>(kStages)) {
       if (!iss_valid) break;
       if (iss_tile >= iss_ntiles) {
-        if (iss_on_next) break;  // at most one item ahead of the one being scored
+        if (iss_on_next || !nxt_ready) break;  // at most one item ahead of the one being scored
         iss_on_next = true;
         iss_valid = nxt.valid; iss_ntiles = nxt.ntiles; iss_x0 = nxt.kv_head * kHeadDim;
         iss_page = nxt.page; iss_page_base = 0; iss_tile = 0;
@@ -550,21 +626,30 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 #pragma unroll
     for (int x = 16; x > 0; x >>= 1) shortest = min(shortest, __shfl_xor_sync(0xffffffffu, shortest, x));
     const bool padded_rows = mrows < 16;
+    nxt_ready = false;  // `nxt` still names this item until the new claim below completes
     top_up();
 
     const int64_t qrow0 = cur.row_start + r0 / gqa, qrow1 = cur.row_start + r1 / gqa;
     const int qhead0 = cur.kv_head * gqa + r0 % gqa, qhead1 = cur.kv_head * gqa + r1 % gqa;
     const int64_t q0 = (qrow0 * a.q_heads + qhead0) * kHeadDim, q1 = (qrow1 * a.q_heads + qhead1) * kHeadDim;
-    const uint32_t* qp = reinterpret_cast<const uint32_t*>(a.q);
-    uint32_t qa[8][4];
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      const int c = ks * 16 + 2 * t;
-      qa[ks][0] = len0 > 0 ? __ldg(qp + ((q0 + c) >> 1)) : 0u;
-      qa[ks][1] = len1 > 0 ? __ldg(qp + ((q1 + c) >> 1)) : 0u;
-      qa[ks][2] = len0 > 0 ? __ldg(qp + ((q0 + c + 8) >> 1)) : 0u;
-      qa[ks][3] = len1 > 0 ? __ldg(qp + ((q1 + c + 8) >> 1)) : 0u;
-    }
+    // nxt: the atomic now, its record after cur's first page, its rows after the second, the warp
+    // reductions and the Q fragments after the third (or at the end of a shorter item).
+    uint32_t qb[8][4];
+    const unsigned nxt_index = claim_index(ws, lane);
+    Pending pending;
+    int stage_done = 0;
+    auto advance_claim = [&]() {
+      if (stage_done == 0) {
+        pending = fetch_item(ws, nxt_index);
+      } else if (stage_done == 1) {
+        fetch_rows(a, ws, pending, lane);
+      } else if (stage_done == 2) {
+        nxt = finish_item(pending, lane);
+        load_q(nxt, qb);
+        nxt_ready = true;
+      }
+      ++stage_done;
+    };
 
     float o[16][4];
 #pragma unroll
@@ -649,6 +734,7 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         mma_16816<kBF16>(o[2 * jp + 1], pa, b[2], b[3]);
       }
       ++consumed;
+      if (j < 3) advance_claim();
       // The stage just read is free.  Every lane's ldmatrix results have been consumed by its
       // MMAs, so the reads are complete before lane 0 passes this barrier and issues the copy
       // that overwrites the stage (the consumer-release step of a TMA pipeline needs no
@@ -657,6 +743,7 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       top_up();
     }
     if (failed) break;
+    while (stage_done < 3) advance_claim();  // items of fewer than three pages
 
     // ---- epilogue: straight from registers ----
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -691,9 +778,10 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         if (t == 0) { part[kHeadDim] = m1; part[kHeadDim + 1] = l1; }
       }
     }
-    // ---- the warp that stores a group's last partial merges its chunks in chunk order ----
     // ---- next item ----
     cur = nxt;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) { qa[ks][0] = qb[ks][0]; qa[ks][1] = qb[ks][1]; qa[ks][2] = qb[ks][2]; qa[ks][3] = qb[ks][3]; }
     if (iss_on_next) {
       iss_on_next = false;  // the issue side is already inside the new `cur`
     } else {                // (re)start the issue side at the first page of the new item
@@ -701,7 +789,6 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       iss_page = cur.page; iss_page_base = 0; iss_tile = 0;
       iss_table = a.block_tables + static_cast<int64_t>(cur.table_row) * a.table_width + cur.chunk_start / kPage;
     }
-    nxt = cur.valid ? claim_item(a, ws, lane) : cur;
   }
 
   if (failed) {
