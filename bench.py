@@ -724,7 +724,7 @@ def run_small_only(args):
 def run_decode_workload(args):
     """Secondary workload (`--workload decode`): self-speculative decoding of a random-init
     Ouro-1.4B-shaped model (24 layers, hidden 2048, 16 x 128 MHA, FFN 5632, vocab 49152, 4 loops, bf16)
-    through `vllm_rlt_b200.SelfSpeculativeDecoder` — BASELINE configs[2] with the output length set by
+    through `vllm_rlt_b200.SelfSpeculativeDecoder` — the bench line's workload run to completion, with the output length set by
     `--output-tokens`.  The GEMMs are cuBLAS; every recurrent loop is replayed from a CUDA graph per
     row bucket unless `--eager` is given.  The prefill and the graph captures are outside the timed region."""
     import vllm_rlt_b200 as rlt
@@ -736,7 +736,7 @@ def run_decode_workload(args):
     g = torch.Generator().manual_seed(11)
     lengths = torch.randint(args.prompt_min, args.prompt_max + 1, (args.requests,), generator=g).tolist()
     prompts = [torch.randint(1, config.vocab_size, (n,), generator=g).tolist() for n in lengths]
-    if args.shared_prefix > 0:   # every second request starts with one common prefix (BASELINE configs[4]'s mix)
+    if args.shared_prefix > 0:   # every second request starts with one common prefix (a long-context mix with shared prefixes)
         common = torch.randint(1, config.vocab_size, (args.shared_prefix,), generator=g).tolist()
         prompts = [common[:len(p) - 1] + p[len(common[:len(p) - 1]):] if i % 2 else p for i, p in enumerate(prompts)]
     decoder = rlt.SelfSpeculativeDecoder(model, cuda_graphs=not args.eager, prefix_caching=args.prefix_caching,

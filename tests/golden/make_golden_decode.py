@@ -10,7 +10,7 @@ with `seeded_parameter(name, shape, seed)` below (a documented, order-independen
 `vllm_rlt_b200.looped_lm.seeded_state_dict` repeats), so the test rebuilds the same model.
 
 Cases: the reference's own tiny test architecture (GQA 4/2 heads of dim 8, block size 2) and
-BASELINE configs[0] (2 layers, hidden 256, 4 x 64 MHA, FFN 688, vocab 1024, 4 loops, 4 prompts x 32
+the small CPU-runnable configuration (2 layers, hidden 256, 4 x 64 MHA, FFN 688, vocab 1024, 4 loops, 4 prompts x 32
 tokens, 64 generated, k = 4 from depth 2 verified at depth 4, block size 16).
 """
 

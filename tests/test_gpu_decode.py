@@ -2,7 +2,7 @@
 
 The golden tokens and counters in tests/golden/decode.pt come from the reference's Torch
 execution on CPU (tests/golden/make_golden_decode.py): the reference's tiny test architecture
-and BASELINE configs[0] (2 layers, hidden 256, 4 x 64 MHA, FFN 688, vocab 1024, 4 loops, 4 prompts
+and a small CPU-runnable configuration (2 layers, hidden 256, 4 x 64 MHA, FFN 688, vocab 1024, 4 loops, 4 prompts
 of 32 tokens, 64 generated, k = 4 drafts from depth 2 verified at depth 4, greedy, block 16).
 The model here is rebuilt from the same seeded weights and decoded (a) natively and (b) with
 block self-speculation through kv_write / verify attention / SiLU-and-Mul / accept_greedy /

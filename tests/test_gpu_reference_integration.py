@@ -3,7 +3,7 @@
 Runs only where an UNMODIFIED copy of the reference package is importable from `baseline/_ref/`
 (`python -m pip install --no-deps --no-build-isolation --target baseline/_ref <reference checkout>`; the
 directory is not part of this repository).  The test then does what a maintainer of the reference would do
-to adopt the kernels (INTEGRATION.md): one more backend name in `validate_backend_name` / `_create_explicit`
+to adopt the kernels: one more backend name in `validate_backend_name` / `_create_explicit`
 that wraps `B200PagedAttention` in the reference's OWN `AttentionBackend` / `BackendCapabilities` classes, and
 `register_torch_op("vllm_rlt")` so that `torch.ops.vllm_rlt.silu_and_mul` dispatches CUDA tensors to the B200
 kernel — and runs the reference's engine (its scheduler, KV-cache manager, speculative runner and model code,

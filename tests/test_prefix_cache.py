@@ -67,3 +67,14 @@ def test_page_tables_share_the_indexed_prefix_on_every_plane():
     assert all(kv.prefix_index.refs[b] == 4 for b in shared)          # owner + index + two followers
     assert all(kv.prefix_index.refs[b] <= 2 for b in set(used.tolist()) - shared)
     assert kv.prefix_index.hit_tokens == 64
+
+
+def test_matching_an_entry_makes_it_the_most_recent():
+    index = PrefixIndex(2)
+    index.publish([1, 2, 3], 3, [[10, 11]])
+    index.publish([7, 8, 9], 3, [[20, 21]])
+    first, second = list(page_keys([1, 2], 2))[0], list(page_keys([7, 8], 2))[0]
+    assert index.least_recent() == first
+    index.lookup([1, 2, 5])
+    assert index.least_recent() == second
+    assert PrefixIndex(2).least_recent() is None

@@ -4,7 +4,7 @@
     python -m vllm_rlt_b200.build --force
 
 The library targets sm_100a only and links the CUDA runtime statically, so it has no
-dependency on PyTorch and can be bound from any host language.
+dependency on PyTorch and can be bound from any host language through `include/rlt_verify.h`.
 """
 
 from __future__ import annotations

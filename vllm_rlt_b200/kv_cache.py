@@ -45,13 +45,15 @@ def kv_write(key_cache, value_cache, k, v, write_blocks, write_offsets, write_ma
     if rows == 0:
         return
     k, v = k.contiguous(), v.contiguous()
+    write_blocks, write_offsets = write_blocks.contiguous(), write_offsets.contiguous()
+    write_mask = None if write_mask is None else write_mask.contiguous()
     with torch.cuda.device(key_cache.device):
         status = _capi.load().rlt_kv_write(
             _capi.ptr(key_cache), _capi.ptr(value_cache), key_cache.stride(0), key_cache.stride(1),
             key_cache.shape[0], key_cache.shape[1], key_cache.shape[2], key_cache.shape[3],
             _capi.DTYPE_CODES[key_cache.dtype], _capi.ptr(k), _capi.ptr(v),
-            _capi.ptr(write_blocks.contiguous()), _capi.ptr(write_offsets.contiguous()),
-            _capi.ptr(None if write_mask is None else write_mask.contiguous()),
+            _capi.ptr(write_blocks), _capi.ptr(write_offsets),
+            _capi.ptr(write_mask),
             _capi.ptr(active_rows), rows, _capi.stream_of(key_cache))
     _capi.check(status, "kv_write")
 
@@ -79,12 +81,13 @@ def finalize_tokens(key_pool, value_pool, tables, slots, depths, positions) -> N
     if rows == 0:
         return
     blocks, layers, block_size, kv_heads, head_dim = key_pool.shape
+    tables, slots, depths, positions = tables.contiguous(), slots.contiguous(), depths.contiguous(), positions.contiguous()
     with torch.cuda.device(key_pool.device):
         status = _capi.load().rlt_finalize_tokens(
             _capi.ptr(key_pool), _capi.ptr(value_pool), key_pool.stride(0), key_pool.stride(1), key_pool.stride(2),
             blocks, layers, block_size, kv_heads, head_dim, _capi.DTYPE_CODES[key_pool.dtype],
-            _capi.ptr(tables.contiguous()), tables.shape[1], tables.shape[2], _capi.ptr(slots.contiguous()),
-            _capi.ptr(depths.contiguous()), _capi.ptr(positions.contiguous()), rows, _capi.stream_of(key_pool))
+            _capi.ptr(tables), tables.shape[1], tables.shape[2], _capi.ptr(slots),
+            _capi.ptr(depths), _capi.ptr(positions), rows, _capi.stream_of(key_pool))
     _capi.check(status, "finalize_tokens")
 
 
@@ -129,10 +132,11 @@ def rollback(starts, emitted, tables, block_size, *, pages_used=None, refcounts=
     )
     if n == 0:
         return result
+    starts, emitted, tables = starts.contiguous(), emitted.contiguous(), tables.contiguous()
     with torch.cuda.device(device):
         status = _capi.load().rlt_rollback(
-            _capi.ptr(starts.contiguous()), _capi.ptr(emitted.contiguous()), n,
-            _capi.ptr(tables.contiguous()), planes, width, block_size, _capi.ptr(pages_used),
+            _capi.ptr(starts), _capi.ptr(emitted), n,
+            _capi.ptr(tables), planes, width, block_size, _capi.ptr(pages_used),
             _capi.ptr(refcounts), 0 if refcounts is None else refcounts.numel(),
             _capi.ptr(written_prefix), layers, _capi.ptr(result.frontier),
             _capi.ptr(result.context_lengths), _capi.ptr(result.write_blocks),

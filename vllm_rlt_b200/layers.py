@@ -58,13 +58,15 @@ def rope_kv_write(q, k, v, cos, sin, key_cache, value_cache, write_blocks, write
     q_out = torch.empty((rows, q_heads, head_dim), dtype=q.dtype, device=q.device)
     if rows == 0:
         return q_out
+    cos, sin = cos.contiguous(), sin.contiguous()
+    write_blocks, write_offsets = write_blocks.contiguous(), write_offsets.contiguous()
     with torch.cuda.device(q.device):
         code = _capi.load().rlt_rope_kv_write(
             _capi.ptr(q), q.stride(0), _capi.ptr(k), k.stride(0), _capi.ptr(v), v.stride(0),
-            _capi.ptr(cos.contiguous()), _capi.ptr(sin.contiguous()), _capi.ptr(q_out), _capi.ptr(key_cache),
+            _capi.ptr(cos), _capi.ptr(sin), _capi.ptr(q_out), _capi.ptr(key_cache),
             _capi.ptr(value_cache), key_cache.stride(0), key_cache.stride(1), key_cache.shape[0], key_cache.shape[1],
-            q_heads, kv_heads, head_dim, _capi.DTYPE_CODES[q.dtype], _capi.ptr(write_blocks.contiguous()),
-            _capi.ptr(write_offsets.contiguous()), _capi.ptr(mask), _capi.ptr(active_rows), rows, _capi.stream_of(q))
+            q_heads, kv_heads, head_dim, _capi.DTYPE_CODES[q.dtype], _capi.ptr(write_blocks),
+            _capi.ptr(write_offsets), _capi.ptr(mask), _capi.ptr(active_rows), rows, _capi.stream_of(q))
     _capi.check(code, "rope_kv_write")
     return q_out
 

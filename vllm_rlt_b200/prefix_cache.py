@@ -1,94 +1,113 @@
-"""Prefix reuse over paged KV: complete prompt pages are indexed by a hash chain of their tokens
-and mapped into later requests' block tables instead of being recomputed.
+"""Prefix reuse over paged KV: complete prompt pages are found again by the hash of everything up to
+and including them, and mapped into later requests' block tables instead of being recomputed.
 
-The rules are those of the reference's `KVCacheManager` (`vllm_rlt/core/kv_cache_manager.py:219-319`
-there):
+The rules are those of the reference's `KVCacheManager` (`vllm_rlt/core/kv_cache_manager.py:219-319`):
 
-* the key of page i is `sha256(key of page i - 1 || the page's tokens as little-endian int64)`,
-  so a hit on page i implies hits on pages 0..i-1 (`_prefix_keys`, `:219-224`);
-* only complete pages are indexed, and never the page holding the last prompt token: the index
-  keeps K/V, not the final hidden state the LM head needs, so at least one token is always
-  recomputed (`publish_prefix`, `:246-250`; `lookup_prefix` looks up `tokens[:-1]`, `:270`);
-* an entry holds one physical page per depth plane (`blocks = tuple(t[index] for t in
-  allocation.block_tables)`, `:259`), and every holder of a page counts in its reference count;
-* pages with more than one holder are never rolled back (`truncate_suffix` refuses them,
-  `:338-356`) — decoding only ever writes behind the prompt, so it never touches them.
+* the key of page i is `sha256(key of page i - 1 || the page's tokens as little-endian int64)`, so two
+  prompts share a key exactly when they agree on every token up to the end of that page, and the byte
+  format is the reference's (a prompt indexed there is found here);
+* only complete pages are indexed, and never the page that holds the last prompt token: the index keeps
+  K/V, not the hidden state the LM head needs, so the last token is always computed;
+* an entry names one physical page per depth plane, and everything that points at a page — the request
+  that wrote it, the index, every request that mapped it — counts as a holder;
+* a page with more than one holder is never rolled back (`truncate_suffix` refuses, `:338-356`); decoding
+  only ever writes behind the prompt, so it never needs to.
 """
 
 from __future__ import annotations
 
 import hashlib
-import struct
-from collections import OrderedDict
+from dataclasses import dataclass
 
 
 def page_keys(tokens, block: int):
-    """Chained digests of the complete pages of `tokens`."""
-    digest = b""
-    for start in range(0, len(tokens) // block * block, block):
-        values = tokens[start:start + block]
-        digest = hashlib.sha256(digest + struct.pack(f"<{len(values)}q", *values)).digest()
-        yield digest
+    """One digest per complete page of `tokens`, each chained to the digest before it."""
+    previous = b""
+    for page in range(len(tokens) // block):
+        body = b"".join(int(t).to_bytes(8, "little", signed=True) for t in tokens[page * block:(page + 1) * block])
+        previous = hashlib.sha256(previous + body).digest()
+        yield previous
+
+
+@dataclass
+class _Entry:
+    pages: tuple            # physical page of every depth plane
+    touched: int            # value of the index's clock when the entry was last matched or added
 
 
 class PrefixIndex:
-    """key -> one physical page per depth plane, in least-recently-used order."""
+    """digest of a prompt prefix -> the physical pages (one per depth plane) that hold its last page."""
 
     def __init__(self, block: int):
         self.block = block
-        self._entries: OrderedDict[bytes, tuple[int, ...]] = OrderedDict()
-        self.refs: dict[int, int] = {}
+        self._entries: dict[bytes, _Entry] = {}
+        self._clock = 0
+        self.refs: dict[int, int] = {}      # page -> holders
         self.queries = 0
         self.hit_tokens = 0
 
     def __len__(self):
         return len(self._entries)
 
+    def _tick(self) -> int:
+        self._clock += 1
+        return self._clock
+
+    def _hold(self, pages) -> None:
+        for page in pages:
+            page = int(page)
+            self.refs[page] = self.refs.get(page, 0) + 1
+
     def lookup(self, tokens) -> tuple[tuple[int, ...], ...]:
-        """Pages (one tuple per page, one id per plane) of the longest indexed prefix of
-        `tokens[:-1]`."""
-        found = []
-        for key in page_keys(tokens[:-1], self.block):
-            pages = self._entries.get(key)
-            if pages is None:
+        """The indexed pages a request with this prompt can map: as many leading pages as are both
+        complete without the prompt's last token and present in the index (page tuple per page)."""
+        reusable = (len(tokens) - 1) // self.block if tokens else 0
+        matched = []
+        for count, key in enumerate(page_keys(tokens, self.block)):
+            entry = self._entries.get(key) if count < reusable else None
+            if entry is None:
                 break
-            self._entries.move_to_end(key)
-            found.append(pages)
-        return tuple(found)
+            entry.touched = self._tick()
+            matched.append(entry.pages)
+        return tuple(matched)
 
     def claim(self, prefix) -> None:
-        """A request maps `prefix` (a `lookup` result) into its tables."""
-        for pages in prefix:
-            for b in pages:
-                self.refs[b] = self.refs.get(b, 0) + 1
+        """A request maps the pages of a `lookup` result into its tables and becomes one more holder."""
         self.queries += 1
-        self.hit_tokens += len(prefix) * self.block
+        self.hit_tokens += self.block * len(prefix)
+        for pages in prefix:
+            self._hold(pages)
 
-    def publish(self, tokens, length: int, tables) -> int:
-        """Index the complete pages of the first `min(length, len(tokens) - 1)` prompt tokens of a
-        request whose per-plane block tables are `tables`; returns how many entries were added."""
-        added = 0
-        publishable = min(length, len(tokens) - 1)
-        for index, key in enumerate(page_keys(tokens[:publishable], self.block)):
-            if key in self._entries:
-                continue
-            pages = tuple(int(t[index]) for t in tables)
-            for b in pages:
-                self.refs[b] = self.refs.get(b, 0) + 1
-            self._entries[key] = pages
-            added += 1
-        return added
+    def own(self, pages) -> None:
+        """A request takes fresh pages of its own: their first holder."""
+        self._hold(pages)
 
-    def own(self, blocks) -> None:
-        """A request takes fresh pages: it is their first holder."""
-        for b in blocks:
-            self.refs[int(b)] = self.refs.get(int(b), 0) + 1
+    def publish(self, tokens, computed: int, tables) -> int:
+        """Offers a request's prompt pages to later requests.  `computed` prompt tokens are in the cache
+        and `tables[plane][page]` are the request's pages; every complete page that lies before the last
+        prompt token and is not indexed yet gets an entry (and the index as a holder).  Returns how many."""
+        usable = min(computed, len(tokens) - 1) // self.block
+        fresh = 0
+        for page, key in enumerate(page_keys(tokens, self.block)):
+            if page >= usable:
+                break
+            if key not in self._entries:
+                pages = tuple(int(plane[page]) for plane in tables)
+                self._entries[key] = _Entry(pages, self._tick())
+                self._hold(pages)
+                fresh += 1
+        return fresh
 
     def remap(self, physical) -> None:
-        """Rename every page id b to `physical[b]` (ids are dealt in order first and permuted once
-        the pool size is known)."""
-        self._entries = OrderedDict((k, tuple(physical[b] for b in pages)) for k, pages in self._entries.items())
-        self.refs = {physical[b]: n for b, n in self.refs.items()}
+        """Renames every page id b to `physical[b]` (ids are dealt in order first and shuffled once the pool
+        size is known)."""
+        for entry in self._entries.values():
+            entry.pages = tuple(physical[b] for b in entry.pages)
+        self.refs = {physical[b]: holders for b, holders in self.refs.items()}
 
-    def shared(self, block_id: int) -> bool:
-        return self.refs.get(int(block_id), 0) > 1
+    def shared(self, page: int) -> bool:
+        return self.refs.get(int(page), 0) > 1
+
+    def least_recent(self):
+        """Digest of the entry matched longest ago (the one an eviction would drop first), or None."""
+        return min(self._entries, key=lambda key: self._entries[key].touched, default=None)

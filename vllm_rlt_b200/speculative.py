@@ -132,10 +132,11 @@ def probabilities(logits, temperature, top_k=None, top_p=None):
     status = torch.zeros(rows, dtype=torch.int32, device=logits.device)
     if rows == 0:
         return probs, status
+    temperature = temperature.contiguous()      # bound to a name: it must outlive the launch
     with torch.cuda.device(logits.device):
         code = _capi.load().rlt_probabilities(
             _capi.ptr(logits), logits.stride(0), rows, vocab, _capi.DTYPE_CODES[logits.dtype],
-            _capi.ptr(temperature.contiguous()), _capi.ptr(top_k), _capi.ptr(top_p), _capi.ptr(probs),
+            _capi.ptr(temperature), _capi.ptr(top_k), _capi.ptr(top_p), _capi.ptr(probs),
             _capi.ptr(status), _capi.stream_of(logits))
     _capi.check(code, "probabilities")
     return probs, status
@@ -158,11 +159,12 @@ def sample_rows(logits, temperature, uniforms, top_k=None, top_p=None):
     status = torch.zeros(rows, dtype=torch.int32, device=logits.device)
     if rows == 0:
         return tokens, status
+    temperature, uniforms = temperature.contiguous(), uniforms.contiguous()
     with torch.cuda.device(logits.device):
         code = _capi.load().rlt_sample_rows(
             _capi.ptr(logits), logits.stride(0), rows, logits.shape[1], _capi.DTYPE_CODES[logits.dtype],
-            _capi.ptr(temperature.contiguous()), _capi.ptr(top_k), _capi.ptr(top_p),
-            _capi.ptr(uniforms.contiguous()), _capi.ptr(tokens), _capi.ptr(status), _capi.stream_of(logits))
+            _capi.ptr(temperature), _capi.ptr(top_k), _capi.ptr(top_p),
+            _capi.ptr(uniforms), _capi.ptr(tokens), _capi.ptr(status), _capi.stream_of(logits))
     _capi.check(code, "sample_rows")
     return tokens, status
 
@@ -301,12 +303,14 @@ def pipeline_shift(state: PipelineState, widths, row_starts, choices, step_hidde
         result = torch.empty(6 * n, dtype=torch.int64, device=state.tokens.device)
     if n == 0:
         return result.view(0, 6)
+    widths, row_starts = widths.contiguous(), row_starts.contiguous()
+    choices, step_hidden = choices.contiguous(), step_hidden.contiguous()
     with torch.cuda.device(state.tokens.device):
         status = _capi.load().rlt_pipeline_shift(
             _capi.ptr(state.tokens), _capi.ptr(state.depths), _capi.ptr(state.candidates), _capi.ptr(state.active),
             _capi.ptr(state.hidden), _capi.ptr(state.token), _capi.ptr(state.position),
-            _capi.ptr(widths.contiguous()), _capi.ptr(row_starts.contiguous()), _capi.ptr(choices.contiguous()),
-            _capi.ptr(step_hidden.contiguous()), _capi.ptr(limits), n, width, state.hidden.shape[2],
+            _capi.ptr(widths), _capi.ptr(row_starts), _capi.ptr(choices),
+            _capi.ptr(step_hidden), _capi.ptr(limits), n, width, state.hidden.shape[2],
             _capi.DTYPE_CODES[state.hidden.dtype], draft_loops, target_loops, _capi.ptr(result),
             _capi.stream_of(state.tokens))
     _capi.check(status, "pipeline_shift")
