@@ -29,7 +29,7 @@ Other entry points (each prints its own JSON line; none is the contract line abo
                        --shared-prefix P --prefix-caching --in-flight F]
                       one complete generation (prompt pass included in `total_seconds`)
     --workload sharded [--total-requests R ...]
-                      R requests in total (default 1024, prompts U[256, 2048], 512 output tokens, k = 6),
+                      R requests in total (default 1024, prompts U[256, 2048], 512 output tokens, k = 6, T = 0.8),
                       length-balanced over the ranks and decoded to completion in waves that fit the KV
                       pool: whole-job strong scaling
     --only attention  [--requests --layers --tokens --depths --kv-heads --context-min --context-max --shared-plan]
@@ -820,7 +820,7 @@ def waves_under_budget(indices, lengths, tokens_extra: int, bytes_per_token: int
 
 def run_sharded_workload(args):
     """`--workload sharded`: a fixed set of requests (default 1024, prompts U[256, 2048], 512 output tokens,
-    k = 6, greedy) shared out over the ranks by prompt length and decoded to completion by every rank's own
+    k = 6, rejection sampling at T = 0.8) shared out over the ranks by prompt length and decoded to completion by every rank's own
     engine in waves that fit its KV pool — whole-job strong scaling, prompt passes and graph captures
     included.  One rank per GPU, no collective on the path; the job's time is the slowest rank's."""
     import torch.distributed as dist
@@ -1083,7 +1083,7 @@ def main():
                         help="decode workload: every second prompt starts with one common prefix of this many tokens")
     parser.add_argument("--prefix-caching", action="store_true", help="decode workload: map shared prompt pages instead of recomputing them")
     parser.add_argument("--temperature", type=float, default=None,
-                        help="sampling temperature (decode: 0.8, sharded: 0 = greedy)")
+                        help="sampling temperature (default 0.8; 0 = greedy)")
     parser.add_argument("--requests", type=int, default=REQUESTS)
     parser.add_argument("--layers", type=int, default=LAYERS)
     parser.add_argument("--tokens", type=int, default=TOKENS, help="with --only attention: new tokens per request")
@@ -1101,7 +1101,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the verify-step kernels have no CPU fallback")
     sharded = args.workload == "sharded"
     for name, decode_default, sharded_default in (("k", DECODE_K, 6), ("output_tokens", 32, 512), ("prompt_min", 128, 256),
-                                                  ("prompt_max", 1024, 2048), ("temperature", TEMPERATURE, 0.0)):
+                                                  ("prompt_max", 1024, 2048), ("temperature", TEMPERATURE, TEMPERATURE)):
         if getattr(args, name) is None:
             setattr(args, name, sharded_default if sharded else decode_default)
     if sharded:
