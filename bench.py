@@ -834,9 +834,12 @@ def run_sharded_workload(args):
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    config = rlt.LoopedLMConfig()
+    config = rlt.LoopedLMConfig(num_hidden_layers=args.model_layers)
     model = rlt.LoopedLM(config, rlt.seeded_state_dict(config, 3, device=device), device, torch.bfloat16)
     prompts = decode_prompts(args.total_requests, (args.prompt_min, args.prompt_max), config.vocab_size, seed=23)
+    if args.shared_prefix > 0:   # every second request starts with one common prefix
+        common = decode_prompts(1, (args.shared_prefix, args.shared_prefix), config.vocab_size, seed=29)[0]
+        prompts = [common[:len(p) - 1] + p[len(common[:len(p) - 1]):] if i % 2 else p for i, p in enumerate(prompts)]
     lengths = [len(p) for p in prompts]
     mine = balanced_shards(lengths, world)[rank]
     bytes_per_token = (config.total_ut_steps * config.num_hidden_layers * 2 * config.num_key_value_heads
@@ -847,9 +850,9 @@ def run_sharded_workload(args):
         dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    accepted = committed = drafted = rounds = 0
+    accepted = committed = drafted = rounds = prefix_hits = 0
     for wave in waves:
-        decoder = rlt.SelfSpeculativeDecoder(model, cuda_graphs=not args.eager,
+        decoder = rlt.SelfSpeculativeDecoder(model, cuda_graphs=not args.eager, prefix_caching=args.prefix_caching,
                                              capture_sizes=sorted({len(wave), max(len(wave) // 2, 1), max(len(wave) // 4, 1)}))
         decoder.generate([prompts[i] for i in wave], args.output_tokens, num_speculative_tokens=args.k,
                          draft_loops=DRAFT_LOOPS, target_loops=TARGET_LOOPS, temperature=args.temperature, seed=1,
@@ -857,6 +860,7 @@ def run_sharded_workload(args):
         s = decoder.stats
         accepted, committed, drafted = accepted + s.accepted_tokens, committed + s.committed_tokens, drafted + s.drafted_tokens
         rounds += s.loop_passes
+        prefix_hits += s.prefix_hit_tokens
         decoder.runner = None
         del decoder
         gc.collect()
@@ -864,7 +868,8 @@ def run_sharded_workload(args):
     torch.cuda.synchronize()
     seconds = time.perf_counter() - t0
     row = torch.tensor([seconds, float(accepted), float(committed), float(drafted), float(len(mine)),
-                        float(sum(lengths[i] for i in mine)), float(len(waves))], dtype=torch.float64, device=device)
+                        float(sum(lengths[i] for i in mine)), float(len(waves)), float(prefix_hits)],
+                       dtype=torch.float64, device=device)
     table = row[None].cpu() if world == 1 else all_gather_rows(row)
     if rank == 0:
         slowest, mean = float(table[:, 0].max()), float(table[:, 0].mean())
@@ -878,6 +883,8 @@ def run_sharded_workload(args):
             "accepted_tokens_per_s": float(table[:, 1].sum()) / slowest,
             "committed_tokens_per_s": float(table[:, 2].sum()) / slowest,
             "acceptance_rate": float(table[:, 1].sum()) / max(float(table[:, 3].sum()), 1.0),
+            "model_layers": args.model_layers, "shared_prefix_tokens": args.shared_prefix,
+            "prefix_caching": bool(args.prefix_caching), "prompt_tokens_mapped_from_the_prefix_index": float(table[:, 7].sum()),
             "requests_per_rank": table[:, 4].tolist(), "prompt_tokens_per_rank": table[:, 5].tolist(),
             "waves_per_rank": table[:, 6].tolist(), "seconds_per_rank": table[:, 0].tolist()}))
     if world > 1:
@@ -1074,14 +1081,15 @@ def main():
     parser.add_argument("--total-requests", type=int, default=1024, help="sharded workload: requests over all ranks")
     parser.add_argument("--kv-budget-gb", type=float, default=110.0, help="sharded workload: KV bytes a wave may reserve")
     parser.add_argument("--max-wave", type=int, default=128, help="sharded workload: most requests decoded together")
+    parser.add_argument("--model-layers", type=int, default=LAYERS, help="sharded workload: decoder layers of the model (24; 48 for the 2.6B shape)")
     parser.add_argument("--output-tokens", type=int, default=None,
                         help="decode workload: tokens per request (default 32); sharded workload: default 512")
     parser.add_argument("--eager", action="store_true", help="decode workload: launch every kernel from the host")
     parser.add_argument("--prompt-min", type=int, default=None, help="shortest prompt (decode: 128, sharded: 256)")
     parser.add_argument("--prompt-max", type=int, default=None, help="longest prompt (decode: 1024, sharded: 2048)")
     parser.add_argument("--shared-prefix", type=int, default=0,
-                        help="decode workload: every second prompt starts with one common prefix of this many tokens")
-    parser.add_argument("--prefix-caching", action="store_true", help="decode workload: map shared prompt pages instead of recomputing them")
+                        help="decode / sharded workloads: every second prompt starts with one common prefix of this many tokens")
+    parser.add_argument("--prefix-caching", action="store_true", help="decode / sharded workloads: map shared prompt pages instead of recomputing them")
     parser.add_argument("--temperature", type=float, default=None,
                         help="sampling temperature (default 0.8; 0 = greedy)")
     parser.add_argument("--requests", type=int, default=REQUESTS)

@@ -70,3 +70,26 @@ def test_workload_is_deterministic_per_seed_and_tables_are_disjoint():
     assert a.rows == 6 * bench.TOKENS * bench.DEPTHS
     assert int(a.lengths.max()) == int(a.contexts.max())
     assert a.algorithmic_attention_bytes() > int(a.contexts.sum()) * bench.HEADS * bench.HEAD_DIM * 4
+
+
+def test_requests_are_shared_out_by_length_and_cut_into_waves_that_fit():
+    sys.path.insert(0, str(ROOT))
+    import bench
+
+    g = torch.Generator().manual_seed(5)
+    lengths = torch.randint(256, 2049, (1024,), generator=g).tolist()
+    for world in (1, 2, 4, 8):
+        shards = bench.balanced_shards(lengths, world)
+        assert sorted(i for shard in shards for i in shard) == list(range(1024))      # every request exactly once
+        loads = [sum(lengths[i] for i in shard) for shard in shards]
+        assert max(loads) - min(loads) <= max(lengths)                                  # within one request's length
+        assert max(len(s) for s in shards) - min(len(s) for s in shards) <= 1
+    shard = bench.balanced_shards(lengths, 8)[3]
+    per_token, extra = 768 * 1024, 512 + 7 + 16
+    waves = bench.waves_under_budget(shard, lengths, extra, per_token, 110e9, 128)
+    assert [i for wave in waves for i in wave] == shard                                # order kept, nothing dropped
+    for wave in waves:
+        assert len(wave) <= 128 and sum((lengths[i] + extra) * per_token for i in wave) <= 110e9
+    assert len(waves) == 2                                                              # 128 requests of ~1.3 GB each
+    # a single request larger than the budget still gets a wave of its own
+    assert bench.waves_under_budget([0], [10 ** 6], 0, per_token, 1e9, 128) == [[0]]
