@@ -846,25 +846,34 @@ def run_sharded_workload(args):
                        * config.head_dim * 2)
     waves = waves_under_budget(mine, lengths, args.output_tokens + args.k + 1 + BLOCK, bytes_per_token,
                                args.kv_budget_gb * 1e9, args.max_wave)
+    # The engine's fixed resources, built once: a pool that holds the largest wave, one runner over it and
+    # the round graphs of three batch sizes.  A wave gets the pool's pages afresh; nothing is re-captured.
+    extra = args.output_tokens + args.k + 1
+    pages_of = lambda i: -(-(lengths[i] + extra) // BLOCK)
+    pool_pages = max(sum(pages_of(i) for i in wave) for wave in waves) * config.total_ut_steps
+    largest = max(len(wave) for wave in waves)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
+    kv = rlt.PagedKV.reserve(model, pool_pages, largest, max(pages_of(i) for i in mine), BLOCK)
+    runner = rlt.B200SpeculativeRunner(model, kv, rlt.SpeculativeConfig(args.k, DRAFT_LOOPS, TARGET_LOOPS),
+                                       max_num_seqs=largest, cuda_graphs=not args.eager,
+                                       capture_sizes=sorted({largest, max(largest // 2, 1), max(largest // 4, 1)}))
     accepted = committed = drafted = rounds = prefix_hits = 0
     for wave in waves:
-        decoder = rlt.SelfSpeculativeDecoder(model, cuda_graphs=not args.eager, prefix_caching=args.prefix_caching,
-                                             capture_sizes=sorted({len(wave), max(len(wave) // 2, 1), max(len(wave) // 4, 1)}))
-        decoder.generate([prompts[i] for i in wave], args.output_tokens, num_speculative_tokens=args.k,
-                         draft_loops=DRAFT_LOOPS, target_loops=TARGET_LOOPS, temperature=args.temperature, seed=1,
-                         in_flight=args.in_flight)
+        decoder = rlt.SelfSpeculativeDecoder(model, cuda_graphs=not args.eager, prefix_caching=args.prefix_caching)
+        session = decoder.open([prompts[i] for i in wave], args.output_tokens, num_speculative_tokens=args.k,
+                               draft_loops=DRAFT_LOOPS, target_loops=TARGET_LOOPS, temperature=args.temperature, seed=1,
+                               in_flight=args.in_flight, kv=kv, runner=runner)
+        before = (runner.stats.drafted_tokens, runner.stats.rounds)
+        session.run()
+        session.close()
         s = decoder.stats
-        accepted, committed, drafted = accepted + s.accepted_tokens, committed + s.committed_tokens, drafted + s.drafted_tokens
+        accepted, committed = accepted + s.accepted_tokens, committed + s.committed_tokens
+        drafted += runner.stats.drafted_tokens - before[0]
         rounds += s.loop_passes
         prefix_hits += s.prefix_hit_tokens
-        decoder.runner = None
-        del decoder
-        gc.collect()
-        torch.cuda.empty_cache()
     torch.cuda.synchronize()
     seconds = time.perf_counter() - t0
     row = torch.tensor([seconds, float(accepted), float(committed), float(drafted), float(len(mine)),

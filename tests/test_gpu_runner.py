@@ -239,3 +239,32 @@ def test_bf16_model_with_128_wide_heads_matches_the_reference_torch_execution(go
         torch.testing.assert_close(got, want, atol=0.08, rtol=0.04)
         worst = max(worst, float((got - want).abs().max()) / float(want.abs().max()))
     assert worst < 2e-2          # logits within 2e-2 relative (of the largest logit) for bf16
+
+
+def test_an_engine_reuses_its_pool_runner_and_graphs_for_the_next_requests(golden):
+    # one reserved pool, one runner, graphs captured once; two different sets of requests decoded one after the
+    # other give what a fresh engine gives for each (stale K/V of the first set is never read by the second)
+    case = golden("decode.pt")["config1"]
+    model = build(case)
+    k, block = case["k"], case["block"]
+    first, second = case["prompts"][:3], [p[:20] for p in case["prompts"][1:]] + [case["prompts"][0][5:]]
+    fresh = []
+    for prompts in (first, second):
+        fresh.append(rlt.SelfSpeculativeDecoder(model, block=block).generate(prompts, 40, num_speculative_tokens=k))
+    pages = -(-(32 + 40 + k + 1) // block)
+    kv = rlt.PagedKV.reserve(model, 4 * pages * 4, 4, pages, block)
+    runner = rlt.B200SpeculativeRunner(model, kv, rlt.SpeculativeConfig(k), max_num_seqs=4, cuda_graphs=True,
+                                       capture_sizes=[2, 4])
+    captured = None
+    for prompts, want in zip((first, second), fresh):
+        decoder = rlt.SelfSpeculativeDecoder(model, block=block, cuda_graphs=True)
+        session = decoder.open(prompts, 40, num_speculative_tokens=k, kv=kv, runner=runner, in_flight=2)
+        session.run()
+        session.close()
+        assert [r.generated_token_ids[:40] for r in session.requests] == want
+        assert not runner.states
+        graphs = {key: id(r.graph) for key, r in runner._rounds.items()}
+        assert captured is None or graphs == captured          # nothing was captured again
+        captured = graphs
+    with pytest.raises(ValueError):                            # more requests than the pool's tables hold
+        rlt.SelfSpeculativeDecoder(model, block=block).open(case["prompts"] * 2, 8, num_speculative_tokens=k, kv=kv, runner=runner)

@@ -59,15 +59,11 @@ class PagedKV:
     prefix_index: PrefixIndex | None = None
     refcounts: torch.Tensor | None = None   # int32 [blocks], holders of every page (prefix reuse only)
 
-    @classmethod
-    def allocate(cls, model: LoopedLM, capacities, block: int, *, permute_seed: int | None = 0, prompts=None):
-        """Pages for `capacities[i]` tokens of every request on every depth plane.  With `prompts`
-        (prefix reuse), request i maps the indexed complete pages of `prompts[i][:-1]` into its
-        tables instead of taking fresh ones (`KVCacheManager.allocate(..., prefix=...)`,
-        core/kv_cache_manager.py:277-319) and then offers its own complete prompt pages to the
-        requests after it; `shared_tokens[i]` is how many leading prompt tokens it does not compute."""
-        c = model.config
-        planes = c.total_ut_steps
+    @staticmethod
+    def _plan_tables(planes: int, capacities, block: int, permute_seed, prompts):
+        """Page ids for `capacities[i]` tokens of every request on every depth plane: int32 tables
+        `[requests, planes, pages]` (padding -1), the number of pages they name, and with `prompts`
+        (prefix reuse) the tokens every request maps instead of computing, the index and the holders."""
         pages = [-(-n // block) for n in capacities]
         width = max(pages)
         index = PrefixIndex(block) if prompts is not None else None
@@ -92,18 +88,58 @@ class PagedKV:
         if permute_seed is not None:  # physical pages deliberately out of order
             order = order[torch.randperm(total, generator=torch.Generator().manual_seed(permute_seed))]
         tables = torch.where(logical >= 0, order[logical.clamp_min(0)], logical).to(torch.int32)
+        holders = None
         if index is not None:
             index.remap(order.tolist())
-        refcounts = None
-        if index is not None:
-            refcounts = torch.zeros(total, dtype=torch.int32)
-            for b, holders in index.refs.items():
-                refcounts[b] = holders
-            refcounts = refcounts.to(model.device)
-        shape = (total, c.num_hidden_layers, block, c.num_key_value_heads, c.head_dim)
+            holders = index.refs
+        return tables, total, shared_tokens, index, holders
+
+    @classmethod
+    def allocate(cls, model: LoopedLM, capacities, block: int, *, permute_seed: int | None = 0, prompts=None):
+        """A pool of exactly the pages `capacities[i]` tokens of every request need on every depth plane.
+        With `prompts` (prefix reuse), request i maps the indexed complete pages of `prompts[i][:-1]` into
+        its tables instead of taking fresh ones (`KVCacheManager.allocate(..., prefix=...)`,
+        core/kv_cache_manager.py:277-319) and then offers its own complete prompt pages to the requests
+        after it; `shared_tokens[i]` is how many leading prompt tokens it does not compute."""
+        c = model.config
+        tables, total, shared_tokens, index, holders = cls._plan_tables(c.total_ut_steps, capacities, block,
+                                                                        permute_seed, prompts)
+        kv = cls.reserve(model, total, len(capacities), tables.shape[2], block)
+        kv._install(tables, total, shared_tokens, index, holders)
+        return kv
+
+    @classmethod
+    def reserve(cls, model: LoopedLM, pages: int, requests: int, width: int, block: int):
+        """An engine's fixed pool: `pages` physical pages, tables for up to `requests` requests of up to
+        `width` pages per plane.  `assign` hands the pages out to a set of requests; the pool, and therefore
+        every pointer a captured round graph holds, stays where it is from one set of requests to the next."""
+        c = model.config
+        shape = (pages, c.num_hidden_layers, block, c.num_key_value_heads, c.head_dim)
         return cls(torch.zeros(shape, device=model.device, dtype=model.dtype),
-                   torch.zeros(shape, device=model.device, dtype=model.dtype), tables.to(model.device), block,
-                   shared_tokens, index, refcounts)
+                   torch.zeros(shape, device=model.device, dtype=model.dtype),
+                   torch.full((requests, c.total_ut_steps, width), -1, dtype=torch.int32, device=model.device), block)
+
+    def assign(self, capacities, *, permute_seed: int | None = 0, prompts=None):
+        """Hands the pool's pages out afresh to requests of the given capacities (rows 0..n-1 of the tables).
+        What earlier requests left in the pages is never read: a request writes a position before any row
+        attends to it."""
+        tables, total, shared_tokens, index, holders = self._plan_tables(self.tables.shape[1], capacities, self.block,
+                                                                         permute_seed, prompts)
+        if len(capacities) > self.tables.shape[0] or tables.shape[2] > self.tables.shape[2] or total > self.key.shape[0]:
+            raise ValueError(f"{len(capacities)} requests / {tables.shape[2]} pages per plane / {total} pages do not fit "
+                             f"the reserved {tuple(self.tables.shape[::2])} tables and {self.key.shape[0]} pages")
+        self._install(tables, total, shared_tokens, index, holders)
+
+    def _install(self, tables, total, shared_tokens, index, holders):
+        self.tables.fill_(-1)
+        self.tables[: tables.shape[0], :, : tables.shape[2]] = tables.to(self.tables.device)
+        self.shared_tokens, self.prefix_index = shared_tokens, index
+        self.refcounts = None
+        if holders is not None:
+            refcounts = torch.zeros(self.key.shape[0], dtype=torch.int32)
+            for page, count in holders.items():
+                refcounts[page] = count
+            self.refcounts = refcounts.to(self.tables.device)
 
     @property
     def max_pages(self) -> int:
@@ -229,7 +265,7 @@ class SelfSpeculativeDecoder:
         context = torch.tensor(lengths, dtype=torch.int32, device=device)
         hidden = self.model.prelude(tokens)
         for depth in range(self.model.config.total_ut_steps):
-            tables = kv.tables[:, depth]
+            tables = kv.tables[: len(prompts), depth]       # a reserved pool may have more table rows than requests
             blocks = tables[requests].gather(1, (positions // self.block)[:, None]).squeeze(1).long()
             hidden = self.model.recurrent(hidden, positions, kv.key, kv.value, blocks, positions % self.block,
                                           tables.contiguous(), context, packed=(cu, max(new)))
@@ -341,9 +377,13 @@ class SelfSpeculativeDecoder:
     @torch.no_grad()
     def open(self, prompts, max_tokens: int, *, num_speculative_tokens: int, draft_loops: int = 2,
              target_loops: int | None = None, temperature: float = 0.0, top_k: int = -1, top_p: float = 1.0,
-             seed: int = 0, in_flight: int = 1) -> "DecodeSession":
+             seed: int = 0, in_flight: int = 1, kv: PagedKV | None = None,
+             runner: B200SpeculativeRunner | None = None) -> "DecodeSession":
         """Everything `generate` does before its first round — pages reserved, prompts run, requests
-        created, runner built and (with CUDA graphs) its round graphs captured — as a `DecodeSession`."""
+        created, runner built and (with CUDA graphs) its round graphs captured — as a `DecodeSession`.
+        An engine that serves one set of requests after another passes its reserved pool (`PagedKV.reserve`)
+        and the runner it built over that pool: the pages are handed out afresh, the runner and its graphs
+        are reused."""
         model = self.model
         if not 0 < top_p <= 1 or (top_k != -1 and top_k < 1):
             raise ValueError("top_p must be in (0, 1] and top_k must be -1 or positive")
@@ -352,12 +392,19 @@ class SelfSpeculativeDecoder:
             raise ValueError("draft_loops must be smaller than target_loops")
         k = num_speculative_tokens
         config = SpeculativeConfig(k, draft_loops, target_loops)
-        kv = self._allocate(prompts, [len(p) + max_tokens + k + 1 for p in prompts])
+        capacities = [len(p) + max_tokens + k + 1 for p in prompts]
+        if kv is None:
+            kv = self._allocate(prompts, capacities)
+        else:
+            kv.assign(capacities, prompts=prompts if self.prefix_caching else None)
         requests = self._requests(prompts, self._prefill(kv, prompts), max_tokens, temperature, top_k, top_p, seed)
-        runner = B200SpeculativeRunner(model, kv, config, max_num_seqs=len(prompts), cuda_graphs=self.cuda_graphs,
-                                       capture_sizes=self.capture_sizes)
+        if runner is None:
+            runner = B200SpeculativeRunner(model, kv, config, max_num_seqs=len(prompts), cuda_graphs=self.cuda_graphs,
+                                           capture_sizes=self.capture_sizes)
+        elif runner.cache is not kv or runner.config != config or runner.max_num_seqs < len(prompts) or runner.states:
+            raise ValueError("the runner was built for another pool or configuration, is too small, or still holds requests")
         self.runner = runner
-        if self.cuda_graphs:
+        if runner.cuda_graphs:
             runner.prepare(sampled=temperature > 0)
         return DecodeSession(self, runner, requests, k, in_flight)
 
