@@ -57,7 +57,8 @@ class PagedKV:
     block: int
     shared_tokens: list | None = None   # per request: leading prompt tokens mapped from the prefix index
     prefix_index: PrefixIndex | None = None
-    refcounts: torch.Tensor | None = None   # int32 [blocks], holders of every page (prefix reuse only)
+    refcounts: torch.Tensor | None = None   # int32 [blocks], holders of every page (prefix reuse; always present in a reserved pool)
+    reserved: bool = False                  # built by `reserve`: tables and holders are rewritten in place by `assign`
 
     @staticmethod
     def _plan_tables(planes: int, capacities, block: int, permute_seed, prompts):
@@ -105,6 +106,7 @@ class PagedKV:
         tables, total, shared_tokens, index, holders = cls._plan_tables(c.total_ut_steps, capacities, block,
                                                                         permute_seed, prompts)
         kv = cls.reserve(model, total, len(capacities), tables.shape[2], block)
+        kv.reserved, kv.refcounts = False, None
         kv._install(tables, total, shared_tokens, index, holders)
         return kv
 
@@ -117,7 +119,8 @@ class PagedKV:
         shape = (pages, c.num_hidden_layers, block, c.num_key_value_heads, c.head_dim)
         return cls(torch.zeros(shape, device=model.device, dtype=model.dtype),
                    torch.zeros(shape, device=model.device, dtype=model.dtype),
-                   torch.full((requests, c.total_ut_steps, width), -1, dtype=torch.int32, device=model.device), block)
+                   torch.full((requests, c.total_ut_steps, width), -1, dtype=torch.int32, device=model.device), block,
+                   refcounts=torch.zeros(pages, dtype=torch.int32, device=model.device), reserved=True)
 
     def assign(self, capacities, *, permute_seed: int | None = 0, prompts=None):
         """Hands the pool's pages out afresh to requests of the given capacities (rows 0..n-1 of the tables).
@@ -134,12 +137,16 @@ class PagedKV:
         self.tables.fill_(-1)
         self.tables[: tables.shape[0], :, : tables.shape[2]] = tables.to(self.tables.device)
         self.shared_tokens, self.prefix_index = shared_tokens, index
-        self.refcounts = None
-        if holders is not None:
-            refcounts = torch.zeros(self.key.shape[0], dtype=torch.int32)
-            for page, count in holders.items():
-                refcounts[page] = count
-            self.refcounts = refcounts.to(self.tables.device)
+        if holders is None and not self.reserved:
+            self.refcounts = None
+            return
+        counts = torch.zeros(self.key.shape[0], dtype=torch.int32)
+        for page, count in (holders or {}).items():
+            counts[page] = count
+        if self.refcounts is None:
+            self.refcounts = counts.to(self.tables.device)
+        else:
+            self.refcounts.copy_(counts)    # in place: a captured round graph holds this tensor's address
 
     @property
     def max_pages(self) -> int:
