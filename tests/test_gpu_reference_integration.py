@@ -7,7 +7,8 @@ to adopt the kernels: one more backend name in `validate_backend_name` / `_creat
 that wraps `B200PagedAttention` in the reference's OWN `AttentionBackend` / `BackendCapabilities` classes, and
 `register_torch_op("vllm_rlt")` so that `torch.ops.vllm_rlt.silu_and_mul` dispatches CUDA tensors to the B200
 kernel — and runs the reference's engine (its scheduler, KV-cache manager, speculative runner and model code,
-on the GPU) to the golden tokens of its CPU run (tests/golden/decode.pt).
+on the GPU) to the golden tokens of its CPU run (tests/golden/decode.pt).  A second step replaces the
+reference's speculative runner by `B200SpeculativeRunner` under the same unmodified engine.
 """
 
 import dataclasses
@@ -86,6 +87,36 @@ def run_engine(engine, prompts, params):
     return [finished[str(i)] for i in range(len(prompts))]
 
 
+class RoundControllerOnTheReferenceCache:
+    """What the reference's `Executor(speculation=...)` and `StageEngine.speculative_runner` get instead of
+    the reference's own `SpeculativeRunner`: `submit(batch) -> ticket`, `release(request)`, `stats`.  The
+    reference's KV-cache manager goes on owning the pools and the block tables; the B200 runner reads both
+    through `KVCacheManagerView` and is told to look at a request's tables again before each of its rounds."""
+
+    def __init__(self, engine, case, dtype, k, **config):
+        self.model = rlt.LoopedLM(rlt.LoopedLMConfig(**case["config"]), engine.model.state_dict(), "cuda", dtype)
+        manager = engine.cache_manager
+        view = rlt.KVCacheManagerView(manager, max_pages=-(-256 // manager.block_size))
+        self.runner = rlt.B200SpeculativeRunner(
+            self.model, view, rlt.SpeculativeConfig(k, **config), max_num_seqs=engine.scheduler.config.max_num_seqs,
+            cuda_graphs=False, report_frontiers=False)
+        self.stats = self.runner.stats
+        self.submitted = 0
+
+    def submit(self, batch):
+        for span in batch.requests:
+            self.runner.refresh_tables(span.request)
+        self.submitted += 1
+        return self.runner.submit(batch)
+
+    def release(self, request):
+        self.runner.release(request)
+
+    def install(self, engine):
+        engine.speculative_runner = engine.executor.speculation = self
+        return engine
+
+
 def test_torch_op_of_the_reference_dispatches_to_the_b200_kernel(reference):
     from vllm_rlt.kernels.activation import silu_and_mul
 
@@ -120,6 +151,29 @@ def test_reference_engine_decodes_the_golden_tokens_on_the_b200_backend(referenc
     torch.cuda.synchronize()
 
 
+@pytest.mark.parametrize("name", ["config1", "tiny_k3"])
+def test_reference_engine_drives_the_b200_round_controller_to_the_golden_tokens(reference, b200_backend, golden, name):
+    # the reference's scheduler, KV-cache manager, prompt path and token bookkeeping, unmodified, with the
+    # B200 runner in the place of its SpeculativeRunner: same tokens, same round statistics
+    from vllm_rlt import CacheConfig, SamplingParams, SpeculativeConfig
+    from vllm_rlt.engine.stage_engine import StageEngine
+
+    case = golden("decode.pt")[name]
+    model = reference_model(case)
+    params = SamplingParams(max_tokens=case["max_tokens"], ignore_eos=True)
+    loops = dict(draft_loops=case["draft_loops"], target_loops=case["target_loops"])
+    engine = StageEngine(model, cache_config=CacheConfig(256, case["block"]), attention_backend="b200",
+                         speculative_config=SpeculativeConfig(case["k"], **loops))
+    controller = RoundControllerOnTheReferenceCache(engine, case, torch.float32, case["k"], **loops)
+    controller.install(engine)
+    assert run_engine(engine, case["prompts"], params) == case["tokens"]
+    assert controller.submitted > 0 and not controller.runner.states            # every request was released
+    stats, want = controller.stats, case["stats"]
+    assert (stats.rounds, stats.drafted_tokens, stats.verified_rows) == (want["rounds"], want["drafted"], want["verified_rows"])
+    assert (stats.committed_tokens, stats.accepted_tokens) == (want["committed"], want["accepted"])
+    torch.cuda.synchronize()
+
+
 def test_reference_engine_on_the_tiled_kernel_agrees_with_its_torch_backend(reference, b200_backend):
     # bf16, 128-wide heads, 16-token pages: the reference's model and runner on the TMA / tensor-core kernel
     # against the same engine on its own Torch attention; greedy tokens agree (bf16 rounding may flip a near-tie)
@@ -138,5 +192,10 @@ def test_reference_engine_on_the_tiled_kernel_agrees_with_its_torch_backend(refe
         engine = StageEngine(model, cache_config=CacheConfig(64, 16), attention_backend=backend,
                              speculative_config=SpeculativeConfig(3))
         outputs[backend] = run_engine(engine, prompts, params)
-    same = sum(a == b for x, y in zip(outputs["torch"], outputs["b200"]) for a, b in zip(x, y))
-    assert same >= 0.8 * 36, outputs
+    engine = StageEngine(model, cache_config=CacheConfig(64, 16), attention_backend="b200",
+                         speculative_config=SpeculativeConfig(3))
+    RoundControllerOnTheReferenceCache(engine, case, torch.bfloat16, 3).install(engine)
+    outputs["b200 runner"] = run_engine(engine, prompts, params)
+    for name in ("b200", "b200 runner"):
+        same = sum(a == b for x, y in zip(outputs["torch"], outputs[name]) for a, b in zip(x, y))
+        assert same >= 0.8 * 36, outputs

@@ -170,3 +170,60 @@ def test_spans_follow_the_scheduler_rule(on_cpu):
     decoder._after_submission(batch, False)
     assert (fresh.num_output_placeholders, fresh.num_speculative_rounds, fresh.position) == (5, 1, 8)
     assert decoder._schedule([fresh], 4, False) is None          # its budget is reserved until the round is collected
+
+
+REFERENCE = __import__("pathlib").Path(__file__).resolve().parents[1] / "baseline" / "_ref"
+
+
+@pytest.mark.skipif(not (REFERENCE / "vllm_rlt").is_dir(), reason="no reference package under baseline/_ref")
+@pytest.mark.parametrize("name", ["tiny_k3", "tiny_k1_draft1"])
+def test_the_reference_engine_can_drive_the_runner_in_place_of_its_own(golden, on_cpu, name):
+    # the unmodified reference engine (scheduler, KV-cache manager, prompt path) with this runner as its
+    # round controller: `Executor(speculation=...)`, `engine.speculative_runner`; the manager's pools and block
+    # tables are read through KVCacheManagerView.  The GPU form of this test is in
+    # test_gpu_reference_integration.py; here the kernels are the oracle's.
+    import sys
+
+    sys.modules.setdefault("vllm_rlt._C", None)
+    sys.path.insert(0, str(REFERENCE))
+    try:
+        from vllm_rlt import CacheConfig, SamplingParams, SpeculativeConfig
+        from vllm_rlt.engine.stage_engine import StageEngine
+        from vllm_rlt.models import OuroConfig, OuroForCausalLM
+    except Exception as error:
+        pytest.skip(f"the reference package does not import here: {error}")
+    case = golden("decode.pt")[name]
+    theirs = OuroForCausalLM(OuroConfig(**case["config"], max_position_embeddings=256, bos_token_id=0, eos_token_id=0))
+    state = rlt.seeded_state_dict(rlt.LoopedLMConfig(**case["config"]), case["seed"])
+    theirs.load_state_dict({n: state[n] for n in theirs.state_dict()}, strict=True)
+    loops = dict(draft_loops=case["draft_loops"], target_loops=case["target_loops"])
+    engine = StageEngine(theirs, cache_config=CacheConfig(256, case["block"]), attention_backend="torch",
+                         speculative_config=SpeculativeConfig(case["k"], **loops))
+    view = rlt.KVCacheManagerView(engine.cache_manager, max_pages=-(-256 // case["block"]))
+    runner = rlt.B200SpeculativeRunner(build(case), view, rlt.SpeculativeConfig(case["k"], **loops), max_num_seqs=8,
+                                       cuda_graphs=False, report_frontiers=False)
+
+    class Controller:
+        stats = runner.stats
+        release = staticmethod(runner.release)
+
+        @staticmethod
+        def submit(batch):
+            for span in batch.requests:
+                runner.refresh_tables(span.request)
+            return runner.submit(batch)
+
+    engine.speculative_runner = engine.executor.speculation = Controller
+    params = SamplingParams(max_tokens=case["max_tokens"], ignore_eos=True)
+    for i, prompt in enumerate(case["prompts"]):
+        engine.add_request(str(i), list(prompt), params)
+    finished = {}
+    while engine.has_unfinished_requests():
+        for output in engine.step():
+            if output.finished:
+                finished[output.request_id] = list(output.token_ids)
+    assert [finished[str(i)] for i in range(len(case["prompts"]))] == case["tokens"]
+    stats, want = runner.stats, case["stats"]
+    assert (stats.rounds, stats.drafted_tokens, stats.accepted_tokens, stats.committed_tokens, stats.verified_rows) == \
+        (want["rounds"], want["drafted"], want["accepted"], want["committed"], want["verified_rows"])
+    assert not runner.states

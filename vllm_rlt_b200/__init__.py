@@ -16,7 +16,7 @@ from .prefix_cache import PrefixIndex
 from .kv_cache import RollbackResult, finalize_tokens, kv_write, rollback
 from .layers import rope_kv_write, sandwich_norm
 from .looped_lm import LoopedLM, LoopedLMConfig, seeded_state_dict
-from .runner import (B200SpeculativeRunner, ModelRunnerOutput, Request, SamplingParams, ScheduledRequest,
+from .runner import (B200SpeculativeRunner, KVCacheManagerView, ModelRunnerOutput, Request, SamplingParams, ScheduledRequest,
                      SchedulerOutput, SpeculativeConfig, SpeculativeRoundTicket, SpeculativeStats)
 from .speculative import (PipelineState, SpeculativeResult, accept_greedy, accept_rejection, argmax_rows,
                           decode_result, pipeline_shift, probabilities, raise_for_status, round_uniforms,
@@ -30,4 +30,5 @@ __all__ = [
     "register_torch_op", "rollback", "rope_kv_write", "sample_rows", "sandwich_norm", "silu_and_mul",
     "B200SpeculativeRunner", "ModelRunnerOutput", "Request", "SamplingParams", "ScheduledRequest", "SchedulerOutput",
     "SpeculativeConfig", "SpeculativeRoundTicket", "SpeculativeStats", "round_uniforms", "silu_and_mul_packed",
+    "KVCacheManagerView",
 ]

@@ -162,6 +162,32 @@ class SpeculativeRequestState:
     delivered: int = 0
 
 
+class KVCacheManagerView:
+    """The runner's view of a `vllm_rlt.core.kv_cache_manager.KVCacheManager` (or anything shaped like it):
+    the LAST_EXITED pools as they are (`key_cache` / `value_cache`, `[blocks, layers, block, kv_heads,
+    head_dim]`, core/kv_cache_manager.py:143-145) and a request's block tables, one per depth plane, from its
+    allocation (`_get_allocation(request_id).block_tables`, :54-59).  `max_pages` bounds the pages of one
+    request on one plane (its `max_tokens / block_size`).  The manager keeps allocating, growing and freeing;
+    call `runner.refresh_tables(request)` after it has grown a request's tables."""
+
+    def __init__(self, manager, max_pages: int):
+        self.manager = manager
+        self.key, self.value = manager.key_cache, manager.value_cache
+        self.block, self.max_pages = manager.block_size, max_pages
+        self.refcounts = None            # the manager refuses shared pages itself when the scheduler truncates
+
+    def device_tables(self, request_id) -> torch.Tensor:
+        tables = self.manager._get_allocation(request_id).block_tables
+        width = max(len(t) for t in tables)
+        if width > self.max_pages:
+            raise ValueError("the request's block tables are wider than max_pages")
+        host = torch.zeros(len(tables), width, dtype=torch.int32)
+        for plane, table in enumerate(tables):
+            host[plane, : len(table)] = torch.tensor(table, dtype=torch.int32)
+        self._staging = host.pin_memory()                      # kept until the next call's copy is queued behind it
+        return self._staging.to(self.key.device, non_blocking=True)
+
+
 class _HostBuffer:
     """Pinned staging of one in-flight round (the reference's SpeculativeRoundBuffer,
     async_speculative.py:55-82): the plan that goes up and the wire record that comes down."""
@@ -221,7 +247,9 @@ class SpeculativeRoundTicket:
             for i in range(n):
                 accepted = values[rows + i]
                 results.append(SpeculativeResult(values[i * w: i * w + accepted + 1], accepted))
-            self.cached = ModelRunnerOutput(speculative=results, frontiers=values[rows + nb: rows + nb + n])
+            frontiers = values[rows + nb: rows + nb + n]
+            self.cached = ModelRunnerOutput(speculative=results,
+                                            frontiers=frontiers if self.runner.report_frontiers else None)
         for state in self.states:
             state.delivered += 1
         self.retire()
@@ -272,7 +300,7 @@ class B200SpeculativeRunner:
     """
 
     def __init__(self, model, cache, config: SpeculativeConfig, *, max_num_seqs: int, cuda_graphs: bool = True,
-                 capture_sizes=None, compute_stream=None):
+                 capture_sizes=None, compute_stream=None, report_frontiers: bool = True):
         if config.target_loops > model.config.total_ut_steps:
             raise ValueError("target_loops exceeds the model's recurrent depth")
         self.model, self.cache, self.config = model, cache, config
@@ -284,6 +312,11 @@ class B200SpeculativeRunner:
         if self.cuda_graphs and not model.fused:
             raise ValueError("graph capture needs the fused layer path")
         self.compute_stream = compute_stream
+        # True: tickets carry the device's next positions (`ModelRunnerOutput.frontiers`), which is how the
+        # reference's scheduler recognises a round of its device-resident runner (it then releases the round's
+        # placeholders and does not truncate, core/scheduler.py:1362-1386).  False: `frontiers` is None, the
+        # form of its synchronous runner, after which the scheduler calls `truncate_suffix` itself (:1386-1394).
+        self.report_frontiers = report_frontiers
         self.stats = SpeculativeStats()
         self.states: dict[str, SpeculativeRequestState] = {}
         slots = 2 * max_num_seqs + 1                       # the last slot is the padding rows' dummy
