@@ -92,6 +92,31 @@ def test_prefill_matches_oracle_and_the_verify_kernel(dtype, q_heads, kv_heads, 
     assert not torch.equal(got, grouped)              # two kernels (no split-KV merge in the prefill one)
 
 
+def test_pair_kernel_on_more_ragged_tiles_than_sms(monkeypatch):
+    # several waves of CTAs (256-row tiles x heads), ragged: full pairs, lone first tiles, second tiles of a few
+    # rows, an empty sequence.  All rows against the mma.sync kernel, a sample of sequences against the oracle.
+    g = torch.Generator().manual_seed(23)
+    new = torch.randint(1, 700, (90,), generator=g).tolist()
+    new[3], new[4], new[5], new[40] = 0, 256, 257, 1
+    context = [n + int(torch.randint(0, 300, (1,), generator=g)) for n in new]
+    context = [max(c, 1) for c in context]
+    case = make_case(new, context, q_heads=4, kv_heads=2, dtype=torch.bfloat16, seed=29)
+    kernel = rlt.B200PagedAttention()
+    monkeypatch.setenv("RLT_PREFILL_KERNEL", "pair")
+    got = run_prefill(kernel, case, max(new))
+    again = run_prefill(kernel, case, max(new))
+    assert torch.equal(got, again)
+    monkeypatch.setenv("RLT_PREFILL_KERNEL", "mma")
+    check(got, run_prefill(kernel, case, max(new)), torch.bfloat16)
+    cu = case["cu"].tolist()
+    longest = max(range(len(new)), key=lambda s: context[s])
+    for s in (0, 4, 5, 40, 89, longest):
+        rows = slice(cu[s], cu[s + 1])
+        want = oracle.paged_attention(case["q"][rows], case["key"], case["value"], case["tables"][s:s + 1].clamp_min(0),
+                                      case["lengths"][s:s + 1], torch.tensor([0, new[s]], dtype=torch.int32))
+        check(got[rows], want, torch.bfloat16)
+
+
 def test_prefill_handles_many_sequences_and_empty_ones():
     g = torch.Generator().manual_seed(3)
     new = torch.randint(0, 90, (1500,), generator=g).tolist()      # more sequences than one plan pass covers

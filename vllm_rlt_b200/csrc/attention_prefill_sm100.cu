@@ -657,8 +657,8 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // ---- two query tiles per CTA: K / V stages shared, A operands in tensor memory -----------------
 // 256 query tokens of one query head per CTA (one CTA per SM, all 512 TMEM columns), ten warps:
 //   warps 0..3 / 4..7  the softmax rows of query tile 0 / 1 (row = TMEM lane),
-//   warps 8, 9         one thread each issues the Q K^T MMAs of tile 0 / 1,
-//   warps 10, 11       one thread each issues the P V MMAs of tile 0 / 1,
+//   warps 8, 9         issue the Q K^T MMAs of tile 0 / 1 (the warp runs the loop, an elected lane issues),
+//   warps 10, 11       issue the P V MMAs of tile 0 / 1,
 //   warp 12            the TMA copies, kPairStages stages of 64 keys ahead.
 // Per tile the scores S (64 columns) and the probabilities P (32 columns of packed 16-bit pairs)
 // have separate TMEM columns, so S(j + 1) = Q K(j + 1)^T is issued as soon as the rows have read
@@ -678,19 +678,89 @@ struct __align__(1024) PairShared {
   unsigned char v[kPairStages][2][kUmmaKeys * 128];
   unsigned long long full_k[kPairStages], full_v[kPairStages], free_k[kPairStages], free_v[kPairStages];
   unsigned long long s_ready[2], s_free[2], p_ready[2], pv_done[2];
+  unsigned long long turn[kUmmaRows / 32][2];            // [scheduler][tile]: the other tile's warp has left its exponentials
   uint32_t tmem_base;
 };
+
+__device__ __forceinline__ bool elect_one() {
+  uint32_t leader;
+  asm volatile("{\n.reg .pred e;\nelect.sync _|e, 0xffffffff;\nselp.u32 %0, 1, 0, e;\n}\n" : "=r"(leader));
+  return leader != 0;
+}
+
+constexpr uint32_t kColQ = 0, kColS = 64, kTileCols = 96, kColP = 64, kColO = 256;   // P: offset inside a tile's S / P block
+
+// The issue loop of one warp: the scores (kScores) or the output product of query tile kTile, `mine` stages
+// (`other`: the stages of the other tile).  The whole warp runs the loop, so that the barrier probes, the
+// stage arithmetic and the operand descriptors stay warp-uniform; one elected lane issues the MMAs and their
+// commits.
+//   S(j):  Q announced (first phase of p_ready) for j = 0, else S(j - 1) read (s_free) — and K(j)
+//   O(j):  P(j) stored (p_ready) — and V(j)
+// The two products of a tile touch different TMEM columns, so their warps need no order between
+// them.  A stage is released to the copy warp by the commits of both tiles' warps; for a tile that
+// does not read the stage the other tile's warp arrives by hand.  Returns true when a wait gave up.
+template <bool kScores, int kTile>
+__device__ __forceinline__ bool pair_issue(PairShared& sm, uint32_t tmem, int mine, int other, uint32_t idesc) {
+  const uint32_t s_col = tmem + kColS + kTile * kTileCols, o_col = tmem + kColO + kTile * kHeadDim;
+  // Q announced: from here on p_ready has completed its first phase, so a parity probe of it is unambiguous
+  if (mine > 0 && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&sm.p_ready[kTile]), 0))) return true;
+  const uint64_t q_desc = umma_desc(smem_u32(&sm.q[0][0]), 16, 1024);
+  long long last_progress = clock64();
+  unsigned probes = 0;
+  int stage = 0;
+  uint32_t ring_parity = 0;
+  for (int j = 0; j < mine;) {
+    bool go;
+    if (kScores) go = (j == 0 || mbar_test(smem_u32(&sm.s_free[kTile]), (j - 1) & 1)) && mbar_test(smem_u32(&sm.full_k[stage]), ring_parity);
+    else go = mbar_test(smem_u32(&sm.p_ready[kTile]), (j + 1) & 1) && mbar_test(smem_u32(&sm.full_v[stage]), ring_parity);
+    if (!__all_sync(0xffffffffu, go)) {
+      if ((++probes & 255u) == 0 && clock64() - last_progress > kWaitCycles) return true;
+      continue;
+    }
+    tcgen05_after_sync();
+    if (kScores) {   // S(j) = Q K(j)^T over the 128 dims
+      const uint64_t k_desc = umma_desc(smem_u32(&sm.k[stage][0][0]), 16, 1024);
+      if (elect_one()) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t step = static_cast<uint64_t>(((ks >> 2) * (kUmmaKeys * 128) + (ks & 3) * 32) >> 4);   // address field, 16-byte units
+          if (kTile == 0) umma_issue_ts(s_col, tmem + kColQ + ks * 8, k_desc + step, idesc, ks > 0);
+          else umma_issue(s_col, q_desc + static_cast<uint64_t>(((ks >> 2) * (kUmmaRows * 128) + (ks & 3) * 32) >> 4), k_desc + step, idesc, ks > 0);
+        }
+        umma_commit(smem_u32(&sm.s_ready[kTile]));
+        umma_commit(smem_u32(&sm.free_k[stage]));
+        if (j >= other) mbar_arrive(smem_u32(&sm.free_k[stage]));
+      }
+    } else {         // O += P(j) V(j) over the 64 keys
+      const uint64_t v_desc = umma_desc(smem_u32(&sm.v[stage][0][0]), 8192, 1024);
+      if (elect_one()) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_issue_ts(o_col, s_col + kColP + ks * 8, v_desc + static_cast<uint64_t>((ks * 2048) >> 4), idesc, (j > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(smem_u32(&sm.pv_done[kTile]));
+        umma_commit(smem_u32(&sm.free_v[stage]));
+        if (j >= other) mbar_arrive(smem_u32(&sm.free_v[stage]));
+      }
+    }
+    __syncwarp();
+    ++j;
+    if (++stage == kPairStages) { stage = 0; ring_parity ^= 1u; }
+    last_progress = clock64();
+    probes = 0;
+  }
+  return false;
+}
 
 template <bool kBF16>
 __global__ void __launch_bounds__(kPairThreads, 1)
 prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                     AttentionArgs a, const PrefillHeader* header, const PrefillTile* tiles, unsigned* error,
-                    float scale_log2) {
+                    float scale_log2, int take_turns) {
   using T = typename std::conditional<kBF16, __nv_bfloat16, __half>::type;
   if (blockIdx.x >= header->tiles) return;
   extern __shared__ unsigned char smem_raw[];
   PairShared& sm = *reinterpret_cast<PairShared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31, warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);   // warp-uniform for the compiler too
   const PrefillTile tile = tiles[blockIdx.x];
   const int q_head = blockIdx.y, kv_head = q_head / (a.q_heads / a.kv_heads);
   const int seq_first = a.cu_seqlens_q[tile.seq];
@@ -715,6 +785,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       mbar_init(smem_u32(&sm.s_free[t]), kUmmaRows / 32);    // one arrival per softmax warp
       mbar_init(smem_u32(&sm.p_ready[t]), kUmmaRows / 32);
       mbar_init(smem_u32(&sm.pv_done[t]), 1);
+      for (int w = 0; w < kUmmaRows / 32; ++w) mbar_init(smem_u32(&sm.turn[w][t]), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -743,7 +814,6 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   constexpr uint32_t kIdesc = (1u << 4) | (kFormat << 7) | (kFormat << 10) | (static_cast<uint32_t>(kUmmaRows >> 4) << 24);
   constexpr uint32_t kIdescQK = kIdesc | (static_cast<uint32_t>(kUmmaKeys >> 3) << 17);            // N = 64 keys
   constexpr uint32_t kIdescPV = kIdesc | (static_cast<uint32_t>(kHeadDim >> 3) << 17) | (1u << 16);  // N = 128 dims, B MN-major
-  constexpr uint32_t kColQ = 0, kColS = 64, kTileCols = 96, kColP = 64, kColO = 256;   // P: offset inside a tile's S / P block
   bool failed = false;
 
   if (warp == 12) {
@@ -771,63 +841,11 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
     }
   } else if (warp >= 8) {
-    // ---- MMA issue, one thread per query tile and product, each gated by the rows' barrier and a copy:
-    //   S(j):  Q announced (first phase of p_ready) for j = 0, else S(j - 1) read (s_free) — and K(j)
-    //   O(j):  P(j) stored (p_ready) — and V(j)
-    // The two products of a tile touch different TMEM columns, so their threads need no order
-    // between them.  A stage is released to the copy warp by the commits of both tiles' threads;
-    // for a tile that does not read the stage the other tile's thread arrives by hand. ----
-    if (lane == 0) {
-      const int t = (warp - 8) & 1;
-      const bool scores = warp < 10;
-      const int mine = t == 0 ? stages0 : stages1, other = t == 0 ? stages1 : stages0;
-      const uint32_t s_col = tmem + kColS + t * kTileCols, o_col = tmem + kColO + t * kHeadDim;
-      // Q announced: from here on p_ready has completed its first phase, so a parity probe of it is unambiguous
-      if (mine > 0 && !mbar_wait(smem_u32(&sm.p_ready[t]), 0)) failed = true;
-      long long last_progress = clock64();
-      for (int j = 0; j < mine && !failed;) {
-        const int stage = j % kPairStages;
-        bool progressed = false;
-        if (scores) {
-          const bool gate = j == 0 || mbar_test(smem_u32(&sm.s_free[t]), (j - 1) & 1);
-          if (gate && mbar_test(smem_u32(&sm.full_k[stage]), (j / kPairStages) & 1)) {
-            tcgen05_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {   // S_t(j) = Q_t K(j)^T over the 128 dims
-              const uint64_t db = umma_desc(smem_u32(&sm.k[stage][ks >> 2][0]) + (ks & 3) * 32, 16, 1024);
-              if (t == 0) {
-                umma_issue_ts(s_col, tmem + kColQ + ks * 8, db, kIdescQK, ks > 0);
-              } else {
-                const uint64_t da = umma_desc(smem_u32(&sm.q[ks >> 2][0]) + (ks & 3) * 32, 16, 1024);
-                umma_issue(s_col, da, db, kIdescQK, ks > 0);
-              }
-            }
-            umma_commit(smem_u32(&sm.s_ready[t]));
-            umma_commit(smem_u32(&sm.free_k[stage]));
-            if (j >= other) mbar_arrive(smem_u32(&sm.free_k[stage]));
-            progressed = true;
-          }
-        } else if (mbar_test(smem_u32(&sm.p_ready[t]), (j + 1) & 1) && mbar_test(smem_u32(&sm.full_v[stage]), (j / kPairStages) & 1)) {
-          tcgen05_after_sync();
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {   // O_t += P_t(j) V(j) over the 64 keys
-            const uint64_t db = umma_desc(smem_u32(&sm.v[stage][0][0]) + ks * 2048, 8192, 1024);
-            umma_issue_ts(o_col, s_col + kColP + ks * 8, db, kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
-          }
-          umma_commit(smem_u32(&sm.pv_done[t]));
-          umma_commit(smem_u32(&sm.free_v[stage]));
-          if (j >= other) mbar_arrive(smem_u32(&sm.free_v[stage]));
-          progressed = true;
-        }
-        if (progressed) {
-          ++j;
-          last_progress = clock64();
-        } else if (clock64() - last_progress > kWaitCycles) {
-          failed = true;
-        }
-      }
-    }
-    failed = __shfl_sync(0xffffffffu, failed, 0);
+    // ---- MMA issue: one warp per query tile and product ----
+    if (warp == 8) failed = pair_issue<true, 0>(sm, tmem, stages0, stages1, kIdescQK);
+    else if (warp == 9) failed = pair_issue<true, 1>(sm, tmem, stages1, stages0, kIdescQK);
+    else if (warp == 10) failed = pair_issue<false, 0>(sm, tmem, stages0, stages1, kIdescPV);
+    else failed = pair_issue<false, 1>(sm, tmem, stages1, stages0, kIdescPV);
   } else {
     // ---- softmax rows ----
     const int t = warp >> 2, row = threadIdx.x & (kUmmaRows - 1);
@@ -864,6 +882,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready[t]));
     }
     constexpr float kRaise = 8.0f;
+    const bool alternate = take_turns != 0 && stages0 > 0 && stages1 > 0;
     float m = -INFINITY, l = 0.f;
     const uint32_t s_col = tmem_row + kColS + t * kTileCols, p_col = s_col + kColP, o_col = tmem_row + kColO + t * kHeadDim;
     for (int j = 0; j < my_stages; ++j) {
@@ -901,12 +920,23 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       float2 sum4[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
       uint32_t packed[32];
       const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-mu, -mu);
+      // On long prompts the two tiles' warps of one scheduler take turns at its exponential unit (tile 0 first
+      // in every stage): left alone they fall into step, and one warp's loads, maxima and stores then no
+      // longer run under the other's exponentials.
+      if (alternate) {
+        const bool wait = t == 0 ? j > 0 : j < stages0;
+        if (wait && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&sm.turn[warp & 3][t]), (t == 0 ? j - 1 : j) & 1))) { failed = true; break; }
+      }
 #pragma unroll
       for (int e = 0; e < 32; ++e) {
         const float2 x = fma_pair(make_float2(s[2 * e], s[2 * e + 1]), scale2, shift2);
         const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
         sum4[e & 3] = add_pair(sum4[e & 3], p);
         packed[e] = pack2<kBF16>(p.x, p.y);
+      }
+      if (alternate) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm.turn[warp & 3][t ^ 1]));
       }
       const float2 sum2 = add_pair(add_pair(sum4[0], sum4[1]), add_pair(sum4[2], sum4[3]));
       l = l * alpha + (sum2.x + sum2.y);
@@ -1001,16 +1031,17 @@ int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspa
     int status = launch_status("prefill_plan_kernel");
     if (status != RLT_OK) return status;
     const size_t smem = sizeof(PairShared) + 1024;
+    const int take_turns = static_cast<int64_t>(a.rows) >= 2048ll * a.table_rows ? 1 : 0;   // prompts of 2048 tokens and more on average
     const dim3 grid(static_cast<unsigned>(static_cast<size_t>(a.rows) / kPairRows + static_cast<size_t>(a.table_rows) + 1),
                     static_cast<unsigned>(a.q_heads));
     if (a.dtype == RLT_BF16) {
       auto kernel = prefill_pair_kernel<true>;
       RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-      kernel<<<grid, kPairThreads, smem, stream>>>(k_map, v_map, a, header, tiles, &header->error, scale_log2);
+      kernel<<<grid, kPairThreads, smem, stream>>>(k_map, v_map, a, header, tiles, &header->error, scale_log2, take_turns);
     } else {
       auto kernel = prefill_pair_kernel<false>;
       RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-      kernel<<<grid, kPairThreads, smem, stream>>>(k_map, v_map, a, header, tiles, &header->error, scale_log2);
+      kernel<<<grid, kPairThreads, smem, stream>>>(k_map, v_map, a, header, tiles, &header->error, scale_log2, take_turns);
     }
     return launch_status("prefill_pair_kernel");
   }
