@@ -676,6 +676,7 @@ struct __align__(1024) PairShared {
   unsigned char q[2][kUmmaRows * 128];                   // tile 1: [half][row][64 dims], 128-byte swizzle
   unsigned char k[kPairStages][2][kUmmaKeys * 128];      // [half][key][64 dims]
   unsigned char v[kPairStages][2][kUmmaKeys * 128];
+  unsigned char rows[2 * kUmmaRows / 32][32 * 128];      // per softmax warp: its 32 rows, 64 columns of 16 bits, 16-byte pieces swizzled
   unsigned long long full_k[kPairStages], full_v[kPairStages], free_k[kPairStages], free_v[kPairStages];
   unsigned long long s_ready[2], s_free[2], p_ready[2], pv_done[2];
   unsigned long long turn[kUmmaRows / 32][2];            // [scheduler][tile]: the other tile's warp has left its exponentials
@@ -852,28 +853,51 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     const int count = t == 0 ? count0 : count1;
     const int len = row < count ? max(base_len + tile.first + t * kUmmaRows + row, 0) : 0;
     const int my_stages = t == 0 ? stages0 : stages1;
-    const int64_t q_offset = ((static_cast<int64_t>(seq_first) + tile.first + t * kUmmaRows + row) * a.q_heads + q_head) * kHeadDim;
     const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    if (my_stages > 0) {   // this row of Q: tile 0 into tensor memory (two 16-bit values per column), tile 1 into shared memory
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(a.q) + q_offset);
+    // This warp's 32 rows of the query and of the output are read and written as 128-byte pieces by eight lanes
+    // each (a thread that moved its own 256-byte row would touch 32 lines per instruction, and the eight warps
+    // together would keep the load / store unit busy for thousands of cycles); a thread's own row goes through the
+    // warp's staging rows in shared memory, whose 16-byte pieces are swizzled by the row.
+    const int warp_row = (warp & 3) * 32, warp_count = min(max(count - warp_row, 0), 32);
+    const int64_t row_stride = static_cast<int64_t>(a.q_heads) * kHeadDim;
+    const int64_t warp_offset = ((static_cast<int64_t>(seq_first) + tile.first + t * kUmmaRows + warp_row) * a.q_heads + q_head) * kHeadDim;
+    unsigned char* staging = &sm.rows[warp][0];
+    if (my_stages > 0) {   // Q: tile 0 into tensor memory (two 16-bit values per column, a thread stores its row), tile 1 into shared memory
+      const T* src = static_cast<const T*>(a.q) + warp_offset;
       const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
       if (t == 0) {
+        uint4 piece[2][8];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + (lane >> 3);
+            piece[h][i] = r < warp_count ? __ldg(reinterpret_cast<const uint4*>(src + r * row_stride + h * 64) + (lane & 7)) : zero;
+          }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          uint32_t r[32];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + (lane >> 3);
+            *reinterpret_cast<uint4*>(staging + r * 128 + (((lane & 7) ^ (r & 7)) << 4)) = piece[h][i];
+          }
+          __syncwarp();
+          uint32_t q[32];
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
-            const uint4 value = len > 0 ? __ldg(src + h * 8 + c) : zero;
-            r[c * 4] = value.x; r[c * 4 + 1] = value.y; r[c * 4 + 2] = value.z; r[c * 4 + 3] = value.w;
+            const uint4 value = *reinterpret_cast<const uint4*>(staging + lane * 128 + ((c ^ (lane & 7)) << 4));
+            q[c * 4] = value.x; q[c * 4 + 1] = value.y; q[c * 4 + 2] = value.z; q[c * 4 + 3] = value.w;
           }
-          tmem_store32(tmem_row + kColQ + h * 32, r);
+          tmem_store32(tmem_row + kColQ + h * 32, q);
+          __syncwarp();
         }
         tmem_store_wait();
       } else {
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const uint4 value = len > 0 ? __ldg(src + c) : zero;
-          *reinterpret_cast<uint4*>(&sm.q[c >> 3][row * 128 + (((c & 7) ^ (row & 7)) << 4)]) = value;
+        for (int i = 0; i < 16; ++i) {
+          const int r = 2 * i + (lane >> 4), c = lane & 15;
+          const uint4 value = r < warp_count ? __ldg(reinterpret_cast<const uint4*>(src + r * row_stride) + c) : zero;
+          *reinterpret_cast<uint4*>(&sm.q[c >> 3][(warp_row + r) * 128 + (((c & 7) ^ (r & 7)) << 4)]) = value;
         }
         fence_async_proxy();
       }
@@ -966,25 +990,34 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     failed = __any_sync(0xffffffffu, failed);
     if (!failed && count > 0) {
       const float inv = l > 0.f ? 1.0f / l : 0.f;
-      uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(a.out) + q_offset);
+      T* dst = static_cast<T*>(a.out) + warp_offset;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
+      for (int h = 0; h < 2; ++h) {   // 64 output columns at a time
+        uint32_t lo[32], hi[32];
         if (my_stages > 0) {
-          tmem_load32(o_col + c * 32, r);
+          tmem_load32(o_col + h * 64, lo);
+          tmem_load32(o_col + h * 64 + 32, hi);
           tmem_load_wait();
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
+          for (int i = 0; i < 32; ++i) lo[i] = hi[i] = 0u;
         }
-        if (row < count) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const float* f = reinterpret_cast<const float*>(&r[q4 * 8]);
-            dst[c * 4 + q4] = make_uint4(pack2<kBF16>(f[0] * inv, f[1] * inv), pack2<kBF16>(f[2] * inv, f[3] * inv),
-                                         pack2<kBF16>(f[4] * inv, f[5] * inv), pack2<kBF16>(f[6] * inv, f[7] * inv));
-          }
+        for (int c = 0; c < 8; ++c) {
+          const float* f = reinterpret_cast<const float*>(c < 4 ? &lo[c * 8] : &hi[(c - 4) * 8]);
+          *reinterpret_cast<uint4*>(staging + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+              make_uint4(pack2<kBF16>(f[0] * inv, f[1] * inv), pack2<kBF16>(f[2] * inv, f[3] * inv),
+                         pack2<kBF16>(f[4] * inv, f[5] * inv), pack2<kBF16>(f[6] * inv, f[7] * inv));
         }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = 4 * i + (lane >> 3);
+          if (r < warp_count)
+            reinterpret_cast<uint4*>(dst + r * row_stride + h * 64)[lane & 7] =
+                *reinterpret_cast<const uint4*>(staging + r * 128 + (((lane & 7) ^ (r & 7)) << 4));
+        }
+        __syncwarp();
       }
     }
   }
