@@ -219,6 +219,24 @@ RLT_API int rlt_verify_attention_noalloc(const void* q, void* out, const void* k
                                  int table_width, const int32_t* context_lengths,
                                  const int32_t* cu_seqlens_q, int rows, rlt_stream_t stream);
 
+/* ----------------------------------------------------------------------
+ * Sliding-window attention: query row r (one block-table row per query row, no packing) attends
+ * only its last `window` keys, positions max(0, context_lengths[r] - window) .. context_lengths[r] - 1,
+ * its own included; keys outside the window stay stored and are not read.  A row of length 0 is
+ * zeros.  Any head_dim <= 256, block size and GQA ratio, fp32 / fp16 / bf16; no workspace; safe
+ * under CUDA-graph capture.
+ * Replaces: AttentionBackend.windowed (vllm_rlt/attention/backend.py:44-50) as served by
+ *   TritonPagedAttention.windowed / torch_paged_attention_windowed
+ *   (vllm_rlt/kernels/paged_attention.py:39-70,122-125), called from
+ *   KVCacheManager._attend_windowed (vllm_rlt/core/kv_cache_manager.py:773-803).
+ * RLT_ERR_INVALID when window <= 0 (the reference raises ValueError).
+ * ---------------------------------------------------------------------- */
+RLT_API int rlt_windowed_attention(const void* q, void* out, const void* key_cache, const void* value_cache,
+                                   int64_t block_stride, int64_t token_stride, int64_t num_blocks,
+                                   int block_size, int q_heads, int kv_heads, int head_dim, int dtype,
+                                   const int32_t* block_tables, int table_width,
+                                   const int32_t* context_lengths, int rows, int window, rlt_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * Packed causal prefill: the same result as rlt_verify_attention with cu_seqlens_q (query i of
  * the n_s new tokens of sequence s sees keys 0 .. context_lengths[s] - n_s + i), computed for

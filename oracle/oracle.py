@@ -98,6 +98,19 @@ def paged_attention(q, key_cache, value_cache, block_tables, context_lengths, cu
     return out
 
 
+def paged_attention_windowed(q, key_cache, value_cache, block_tables, context_lengths, window):
+    bs, ts = _cache_geometry(key_cache)
+    assert _cache_geometry(value_cache) == (bs, ts) and type(window) is int and window > 0
+    q = q.contiguous()
+    out = torch.empty_like(q)
+    tables = block_tables.to(torch.int32).contiguous()
+    lens = context_lengths.to(torch.int32).contiguous()
+    lib().orc_paged_attention_windowed(_p(q), _p(out), _p(key_cache), _p(value_cache), _i64(bs), _i64(ts),
+                                       key_cache.shape[1], q.shape[1], key_cache.shape[2], q.shape[2],
+                                       _DTYPES[q.dtype], _p(tables), tables.shape[1], _p(lens), q.shape[0], window)
+    return out
+
+
 def argmax_rows(logits):
     assert logits.dim() == 2 and logits.stride(1) == 1
     targets = torch.empty(logits.shape[0], dtype=torch.int64)

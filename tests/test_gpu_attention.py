@@ -241,9 +241,9 @@ def test_backend_adapter_and_capabilities():
     assert backend.info["selected_backend"] == "b200" and backend.info["tiled_kernel"]
     caps = backend.capabilities
     assert caps.cuda_graphs and caps.async_scheduling and caps.device_context_lengths
-    assert caps.packed_prefill and caps.packed_matches_decode and not caps.sliding_window
-    with pytest.raises(NotImplementedError, match="sliding-window"):
-        backend.windowed()
+    assert caps.packed_prefill and caps.packed_matches_decode and caps.sliding_window
+    with pytest.raises(NotImplementedError, match="sliding-window"):       # an adapter around a kernel without the entry
+        rlt.attention.AttentionBackend(lambda *a: None, caps, {"selected_backend": "plain"}).windowed()
     with pytest.raises(ValueError, match="CUDA"):
         rlt.create_backend("cpu", torch.bfloat16, 128, 16)
 

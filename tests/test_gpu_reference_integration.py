@@ -199,3 +199,31 @@ def test_reference_engine_on_the_tiled_kernel_agrees_with_its_torch_backend(refe
     for name in ("b200", "b200 runner"):
         same = sum(a == b for x, y in zip(outputs["torch"], outputs[name]) for a, b in zip(x, y))
         assert same >= 0.8 * 36, outputs
+
+
+def test_reference_cache_manager_attends_through_the_b200_window_entry(reference, b200_backend):
+    # KVCacheManager.attend(..., window=) reaches `attention.windowed` only on a backend that advertises
+    # `sliding_window` (core/kv_cache_manager.py:773-803): the manager on the B200 backend against the same manager
+    # on its own Torch kernel, after identical writes (the scene of tests/test_dory.py:409-437, on the GPU)
+    from vllm_rlt.core.kv_cache_manager import KVCacheManager
+
+    def manager(backend):
+        return KVCacheManager(num_layers=2, num_kv_heads=2, head_dim=8, num_blocks=64, block_size=2, max_loops=2,
+                              device="cuda", dtype=torch.float32, backend=backend)
+
+    ours, theirs = manager("b200"), manager("torch")
+    assert ours.attention_capabilities.sliding_window and isinstance(ours.attention.kernel, rlt.B200PagedAttention)
+    g = torch.Generator().manual_seed(7)
+    for cache in (ours, theirs):
+        assert cache.allocate("request", 12)
+    for position in range(12):
+        k, v = torch.randn(1, 2, 8, generator=g).cuda(), torch.randn(1, 2, 8, generator=g).cuda()
+        for cache in (ours, theirs):
+            cache.write(1, ["request"], [0], [position], k, v)
+    query = torch.randn(1, 4, 8, generator=g).cuda()
+    for window in (1, 3, 12, 50):
+        got = ours.attend(1, ["request"], [0], [11], query, window=window)
+        want = theirs.attend(1, ["request"], [0], [11], query, window=window)
+        torch.testing.assert_close(got, want, atol=3e-6, rtol=1e-5)
+    assert not torch.allclose(ours.attend(1, ["request"], [0], [11], query, window=3),
+                              ours.attend(1, ["request"], [0], [11], query))

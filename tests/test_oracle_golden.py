@@ -59,6 +59,19 @@ def test_attention_matches_reference_outputs(golden):
             assert torch.count_nonzero(got[row]) == 0
 
 
+def test_windowed_attention_matches_reference_outputs(golden):
+    data = golden("windowed.pt")
+    for case in data["grid"]:
+        for (window, length), want in case["out"].items():
+            got = oracle.paged_attention_windowed(case["q"], case["key"], case["value"], case["tables"],
+                                                  torch.tensor([length], dtype=torch.int32), window)
+            torch.testing.assert_close(got, want, atol=2e-6, rtol=2e-5)     # the reference's own bounds for its Triton kernel
+    case = data["batched"]
+    for window, want in case["out"].items():
+        got = oracle.paged_attention_windowed(case["q"], case["key"], case["value"], case["tables"], case["lengths"], window)
+        torch.testing.assert_close(got.float(), want.float(), atol=8e-3, rtol=8e-3)   # one bf16 rounding of the output
+
+
 def test_attention_packed_rows_equal_per_row_expansion():
     g = torch.Generator().manual_seed(3)
     block, heads, dim = 4, 2, 16

@@ -34,6 +34,7 @@ SIGNATURES = {
     "rlt_verify_attention_run": (_I, [_P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _I,
                                       _P, _Z, _P]),
     "rlt_verify_attention_noalloc": (_I, [_P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _I, _P]),
+    "rlt_windowed_attention": (_I, [_P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P]),
     "rlt_prefill_attention_workspace_bytes": (_Z, [_I, _I, _I, _I, _I, _I, _I]),
     "rlt_prefill_attention": (_I, [_P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _I,
                                    _P, _Z, _P]),

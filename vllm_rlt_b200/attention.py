@@ -56,8 +56,11 @@ class AttentionBackend:
         return self.kernel.prefill(*args, **kwargs)
 
     def windowed(self, *args, **kwargs):
-        selected = self.info.get("selected_backend", "this attention backend")
-        raise NotImplementedError(f"{selected} does not implement sliding-window masking")
+        method = getattr(self.kernel, "windowed", None)
+        if method is None:
+            selected = self.info.get("selected_backend", "this attention backend")
+            raise NotImplementedError(f"{selected} does not implement sliding-window masking")
+        return method(*args, **kwargs)
 
     @property
     def generation(self):
@@ -72,7 +75,7 @@ B200_CAPABILITIES = BackendCapabilities(
     async_scheduling=True,
     packed_matches_decode=True,
     device_context_lengths=True,
-    sliding_window=False,
+    sliding_window=True,
 )
 
 
@@ -220,6 +223,34 @@ class B200PagedAttention:
 
     def __call__(self, q, key_cache, value_cache, block_tables, context_lengths):
         return self._run(q, key_cache, value_cache, block_tables, context_lengths, None)
+
+    def windowed(self, q, key_cache, value_cache, block_tables, context_lengths, window):
+        """Row r attends only its last ``window`` keys, its own position included; keys outside the
+        window stay stored (``torch_paged_attention_windowed``, kernels/paged_attention.py:39-70 of the
+        reference, reached through ``KVCacheManager._attend_windowed``, core/kv_cache_manager.py:773-803).
+        One block-table row per query row; ``ValueError`` for a window that is not a positive ``int``."""
+        if isinstance(window, bool) or not isinstance(window, int) or window <= 0:
+            raise ValueError("window must be a positive integer")
+        device = _capi.require_cuda(q, key_cache, value_cache, block_tables, context_lengths)
+        self._check_cache(q, key_cache, value_cache)
+        if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or not block_tables.is_contiguous():
+            raise ValueError("block tables must be contiguous int32 [rows, pages]")
+        rows = q.shape[0]
+        if context_lengths.dtype != torch.int32 or context_lengths.shape != (rows,) or block_tables.shape[0] != rows:
+            raise ValueError("one block-table row and one int32 context length per query row")
+        q = q.contiguous()
+        out = torch.empty_like(q)
+        if rows == 0:
+            return out
+        blocks, block_size, kv_heads, head_dim = key_cache.shape
+        with torch.cuda.device(device):
+            status = _capi.load().rlt_windowed_attention(
+                _capi.ptr(q), _capi.ptr(out), _capi.ptr(key_cache), _capi.ptr(value_cache), key_cache.stride(0),
+                key_cache.stride(1), blocks, block_size, q.shape[1], kv_heads, head_dim, _capi.DTYPE_CODES[q.dtype],
+                _capi.ptr(block_tables), block_tables.shape[1], _capi.ptr(context_lengths.contiguous()), rows,
+                min(window, 2**31 - 1), _capi.stream_of(q))
+        _capi.check(status, "windowed_attention")
+        return out
 
     def prefill(self, q, key_cache, value_cache, block_tables, context_lengths, cu_seqlens_q, max_seqlen_q):
         """Packed rows: one block-table row per sequence, bottom-right causal lengths.

@@ -59,7 +59,7 @@ __device__ __forceinline__ void resolve_row(const AttentionArgs& a, int row, int
 }
 
 // attention_generic.cu: any shape, one CTA per (row, head).
-int launch_attention_generic(const AttentionArgs& a, cudaStream_t stream);
+int launch_attention_generic(const AttentionArgs& a, cudaStream_t stream, int window = 0);   // window > 0: the row's last `window` keys only
 
 // attention_sm100.cu: head_dim 128, 16-token pages, fp16/bf16 — TMA page streaming,
 // request-grouped rows on tensor cores, split-KV with a deterministic merge.

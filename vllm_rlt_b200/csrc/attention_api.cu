@@ -68,6 +68,25 @@ extern "C" RLT_API int rlt_verify_attention(const void* q, void* out, const void
   return launch_attention_generic(a, s);
 }
 
+extern "C" RLT_API int rlt_windowed_attention(const void* q, void* out, const void* key_cache, const void* value_cache,
+                                              int64_t block_stride, int64_t token_stride, int64_t num_blocks,
+                                              int block_size, int q_heads, int kv_heads, int head_dim, int dtype,
+                                              const int32_t* block_tables, int table_width,
+                                              const int32_t* context_lengths, int rows, int window,
+                                              rlt_stream_t stream) {
+  using namespace rlt;
+  RLT_REQUIRE(window > 0, "windowed_attention: window must be a positive integer");
+  AttentionArgs a;
+  a.q = q; a.out = out; a.key_cache = key_cache; a.value_cache = value_cache;
+  a.block_stride = block_stride; a.token_stride = token_stride; a.num_blocks = num_blocks;
+  a.block_size = block_size; a.q_heads = q_heads; a.kv_heads = kv_heads; a.head_dim = head_dim;
+  a.dtype = dtype; a.block_tables = block_tables; a.table_rows = rows; a.table_width = table_width;
+  a.context_lengths = context_lengths; a.cu_seqlens_q = nullptr; a.rows = rows;
+  int status = check_args(a);
+  if (status != RLT_OK || rows == 0) return status;
+  return launch_attention_generic(a, static_cast<cudaStream_t>(stream), window);
+}
+
 extern "C" RLT_API int rlt_verify_attention_plan(const int32_t* block_tables, int table_rows, int table_width,
                                                  const int32_t* context_lengths, const int32_t* cu_seqlens_q,
                                                  int rows, int q_heads, int kv_heads, int head_dim, int block_size,

@@ -4,6 +4,7 @@
 // result depends on nothing but its own query, length and K/V.  This is the path for
 // shapes the tiled sm_100a kernel (attention_sm100.cu) does not cover — the fp32 tiny
 // model and the odd head sizes the reference's tests use; it reads K/V once per row.
+// With window > 0 a row attends only its last `window` keys (sliding-window layers).
 #include <math.h>
 
 #include "attention.cuh"
@@ -17,7 +18,7 @@ constexpr int kMaxPerLane = 8;  // head_dim <= 256
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-attention_generic_kernel(AttentionArgs a, float scale) {
+attention_generic_kernel(AttentionArgs a, float scale, int window) {
   const int row = blockIdx.x / a.q_heads;
   const int head = blockIdx.x % a.q_heads;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -44,7 +45,8 @@ attention_generic_kernel(AttentionArgs a, float scale) {
     o[j] = 0.0f;
   }
   float m = -INFINITY, l = 0.0f;
-  for (int t = warp; t < len; t += kWarps) {
+  const int first = window > 0 && len > window ? len - window : 0;
+  for (int t = first + warp; t < len; t += kWarps) {
     const int64_t page = table[t / a.block_size];
     if (page < 0 || page >= a.num_blocks) continue;  // corrupt table entry: never dereferenced
     const int64_t base = page * a.block_stride + static_cast<int64_t>(t % a.block_size) * a.token_stride +
@@ -94,7 +96,7 @@ attention_generic_kernel(AttentionArgs a, float scale) {
 
 }  // namespace
 
-int launch_attention_generic(const AttentionArgs& a, cudaStream_t stream) {
+int launch_attention_generic(const AttentionArgs& a, cudaStream_t stream, int window) {
   if (a.head_dim > 32 * kMaxPerLane) {
     set_last_error_text("verify_attention supports head_dim <= 256");
     return RLT_ERR_UNSUPPORTED;
@@ -106,7 +108,7 @@ int launch_attention_generic(const AttentionArgs& a, cudaStream_t stream) {
   }
   const float scale = static_cast<float>(1.0 / sqrt(static_cast<double>(a.head_dim)));
   RLT_DISPATCH_DTYPE(a.dtype, T,
-                     (attention_generic_kernel<T><<<static_cast<unsigned>(ctas), kThreads, 0, stream>>>(a, scale)));
+                     (attention_generic_kernel<T><<<static_cast<unsigned>(ctas), kThreads, 0, stream>>>(a, scale, window)));
   return launch_status("attention_generic_kernel");
 }
 
