@@ -27,8 +27,14 @@ def make_case(new, context, *, q_heads, kv_heads, dtype, seed, layers=1, layer=0
     order = torch.randperm(total, generator=g).tolist()
     width = max(pages)
     tables = torch.full((len(new), width), -1, dtype=torch.int32)
+    written = torch.zeros(total, block, dtype=torch.bool)
     for s, n in enumerate(pages):
-        tables[s, :n] = torch.tensor([order.pop() for _ in range(n)], dtype=torch.int32)
+        ids = [order.pop() for _ in range(n)]
+        tables[s, :n] = torch.tensor(ids, dtype=torch.int32)
+        for index, page in enumerate(ids):
+            written[page, : max(0, min(block, context[s] - index * block))] = True
+    # slots nobody stored a token in hold NaN, as a pool allocated with torch.empty may: no result may depend on them
+    both.masked_fill_(~written[None, :, None, :, None, None].expand_as(both), float("nan"))
     q = (torch.randn(sum(new), q_heads, dim, generator=g) * 0.5).to(dtype)
     cu = torch.tensor([0] + torch.tensor(new).cumsum(0).tolist(), dtype=torch.int32)
     return dict(q=q, both=both, value_first=value_first, layer=layer, tables=tables,

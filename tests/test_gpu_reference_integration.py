@@ -69,6 +69,11 @@ def b200_backend(reference, monkeypatch):
 def reference_model(case, dtype=torch.float32):
     from vllm_rlt.models import OuroConfig, OuroForCausalLM
 
+    # The reference allocates its KV pools with torch.empty (core/kv_cache_manager.py:143-145): whatever the caching
+    # allocator hands back is what lies behind every context's last token.  Leave it blocks of NaN to hand back.
+    for elements in (1 << 18, 1 << 20, 1 << 22, 1 << 24):
+        torch.full((elements,), float("nan"), dtype=torch.float32, device="cuda")
+
     config = OuroConfig(**case["config"], max_position_embeddings=256, bos_token_id=0, eos_token_id=0)
     model = OuroForCausalLM(config)
     state = rlt.seeded_state_dict(rlt.LoopedLMConfig(**case["config"]), case["seed"])
@@ -227,3 +232,42 @@ def test_reference_cache_manager_attends_through_the_b200_window_entry(reference
         torch.testing.assert_close(got, want, atol=3e-6, rtol=1e-5)
     assert not torch.allclose(ours.attend(1, ["request"], [0], [11], query, window=3),
                               ours.attend(1, ["request"], [0], [11], query))
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_reference_async_engine_drives_the_b200_runner_with_two_rounds_in_flight(reference, b200_backend, golden, graphs):
+    # `ExecutionConfig(async_scheduling=True)`: the reference's engine submits a round ahead of the one it collects,
+    # books placeholders at submission, checks every collected round against the device's frontier and counts
+    # deliveries itself (engine/stage_engine.py:732-793, core/scheduler.py:1362-1375).  Its AsyncSpeculativeRunner is
+    # replaced by B200SpeculativeRunner in its default, device-resident protocol; nothing else changes.
+    from vllm_rlt import CacheConfig, ExecutionConfig, SamplingParams, SpeculativeConfig
+    from vllm_rlt.engine.stage_engine import StageEngine
+
+    case = golden("decode.pt")["config1"]
+    model = reference_model(case)
+    loops = dict(draft_loops=case["draft_loops"], target_loops=case["target_loops"])
+    engine = StageEngine(model, cache_config=CacheConfig(256, case["block"]), attention_backend="b200",
+                         execution_config=ExecutionConfig(async_scheduling=True),
+                         speculative_config=SpeculativeConfig(case["k"], **loops))
+    assert engine.async_speculative
+    ours = rlt.LoopedLM(rlt.LoopedLMConfig(**case["config"]), model.state_dict(), "cuda", torch.float32)
+    view = rlt.KVCacheManagerView(engine.cache_manager, max_pages=-(-256 // case["block"]))
+    runner = rlt.B200SpeculativeRunner(ours, view, rlt.SpeculativeConfig(case["k"], **loops),
+                                       max_num_seqs=engine.scheduler.config.max_num_seqs, cuda_graphs=graphs,
+                                       compute_stream=engine.model_runner.core_stream)
+    engine.speculative_runner = engine.executor.speculation = runner
+    in_flight = []
+    submit = runner.submit
+
+    def counted(batch):
+        ticket = submit(batch)
+        in_flight.append(len(engine._pending_speculative) + 1)
+        return ticket
+
+    runner.submit = counted
+    params = SamplingParams(max_tokens=case["max_tokens"], ignore_eos=True)
+    assert run_engine(engine, case["prompts"], params) == case["tokens"]
+    assert max(in_flight) == 2 and not runner.states and not engine._pending_speculative
+    assert runner.stats.committed_tokens == case["stats"]["committed"]
+    assert all(not buffer.leased for buffer in runner.buffers)
+    torch.cuda.synchronize()

@@ -190,6 +190,12 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap kv_map, AttentionAr
     if (!mbar_wait(smem_u32(&sm.full[stage]), parity)) { failed = true; break; }
     const int pages = min(kTilePages, total_pages - jt * kTilePages);
     const int tile_start = jt * kTilePages * kPage;
+    if (jt == kv_tiles - 1 && kv_end < tile_start + pages * kPage) {
+      // slots of the last page behind the last key any row of the tile sees (every warp clears them before its own
+      // reads: the same zeros from each)
+      unsigned char* v_page = &sm.stages[stage][pages - 1][0] + (k_first ? kTileBytes : 0);
+      zero_rows_warp(v_page, v_page + 2048, kv_end - tile_start - (pages - 1) * kPage, kPage, lane);
+    }
     // pages of this stage that hold a key some row of this warp can see (the rest is its causal future)
     const int mine = min(pages, max(warp_max - tile_start + kPage - 1, 0) / kPage);
     if (mine > 0) {
@@ -385,7 +391,6 @@ __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // D[tmem] (+)= A[tmem] * B[smem]: A as packed 16-bit pairs, one row per lane.
 __device__ __forceinline__ void umma_issue_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
@@ -508,6 +513,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
       if (!warp_wait(&sm.p_ready[b], phase)) break;
       if (!warp_wait(&sm.full_v[b], phase)) break;
+      if (jt == kv_tiles - 1 && kv_end < jt * kUmmaKeys + min(4, total_pages - jt * 4) * kPage)   // slots behind the last visible key
+        zero_rows_warp(&sm.v[b][0][0], &sm.v[b][1][0], kv_end - jt * kUmmaKeys, min(4, total_pages - jt * 4) * kPage, lane);
       if (lane == 0) {
         tcgen05_after_sync();
 #pragma unroll
@@ -701,7 +708,8 @@ constexpr uint32_t kColQ = 0, kColS = 64, kTileCols = 96, kColP = 64, kColO = 25
 // them.  A stage is released to the copy warp by the commits of both tiles' warps; for a tile that
 // does not read the stage the other tile's warp arrives by hand.  Returns true when a wait gave up.
 template <bool kScores, int kTile>
-__device__ __forceinline__ bool pair_issue(PairShared& sm, uint32_t tmem, int mine, int other, uint32_t idesc) {
+__device__ __forceinline__ bool pair_issue(PairShared& sm, uint32_t tmem, int mine, int other, uint32_t idesc,
+                                           int kv_end, int total_pages, int lane) {
   const uint32_t s_col = tmem + kColS + kTile * kTileCols, o_col = tmem + kColO + kTile * kHeadDim;
   // Q announced: from here on p_ready has completed its first phase, so a parity probe of it is unambiguous
   if (mine > 0 && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&sm.p_ready[kTile]), 0))) return true;
@@ -733,6 +741,9 @@ __device__ __forceinline__ bool pair_issue(PairShared& sm, uint32_t tmem, int mi
         if (j >= other) mbar_arrive(smem_u32(&sm.free_k[stage]));
       }
     } else {         // O += P(j) V(j) over the 64 keys
+      const int rows = min(4, total_pages - j * 4) * kPage;
+      if (kv_end - j * kUmmaKeys < rows)   // the last stage: slots behind the last key any row sees (both tiles' warps may clear them)
+        zero_rows_warp(&sm.v[stage][0][0], &sm.v[stage][1][0], kv_end - j * kUmmaKeys, rows, lane);
       const uint64_t v_desc = umma_desc(smem_u32(&sm.v[stage][0][0]), 8192, 1024);
       if (elect_one()) {
 #pragma unroll
@@ -843,10 +854,11 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     }
   } else if (warp >= 8) {
     // ---- MMA issue: one warp per query tile and product ----
-    if (warp == 8) failed = pair_issue<true, 0>(sm, tmem, stages0, stages1, kIdescQK);
-    else if (warp == 9) failed = pair_issue<true, 1>(sm, tmem, stages1, stages0, kIdescQK);
-    else if (warp == 10) failed = pair_issue<false, 0>(sm, tmem, stages0, stages1, kIdescPV);
-    else failed = pair_issue<false, 1>(sm, tmem, stages1, stages0, kIdescPV);
+    const int kv_end = max(base_len + tile.first + tile.count - 1, 0);   // keys the pair's last row sees
+    if (warp == 8) failed = pair_issue<true, 0>(sm, tmem, stages0, stages1, kIdescQK, kv_end, total_pages, lane);
+    else if (warp == 9) failed = pair_issue<true, 1>(sm, tmem, stages1, stages0, kIdescQK, kv_end, total_pages, lane);
+    else if (warp == 10) failed = pair_issue<false, 0>(sm, tmem, stages0, stages1, kIdescPV, kv_end, total_pages, lane);
+    else failed = pair_issue<false, 1>(sm, tmem, stages1, stages0, kIdescPV, kv_end, total_pages, lane);
   } else {
     // ---- softmax rows ----
     const int t = warp >> 2, row = threadIdx.x & (kUmmaRows - 1);

@@ -661,6 +661,16 @@ verify_attention_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       const int stage = consumed % kStages;
       if (!mbar_wait(bar_base + stage * 8, (consumed / kStages) & 1)) { failed = true; break; }
       const uint32_t base = stage_base + stage * kStageBytes;
+      if (j == cur.ntiles - 1) {   // the page that may end behind the group's longest context: clear V of the slots nobody sees
+        int longest = cur.len;
+#pragma unroll
+        for (int x = 16; x > 0; x >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, x));
+        const int seen = longest - (cur.chunk_start + j * kPage);
+        if (seen < kPage) {
+          unsigned char* v_page = &sm.stages[warp][stage][0] + (k_first ? kTileBytes : 0);
+          zero_rows_warp(v_page, v_page + 2048, max(seen, 0), kPage, lane);
+        }
+      }
 
       // S = Q K^T for the 16 tokens of this page (two n8 tiles, two accumulator chains each)
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};

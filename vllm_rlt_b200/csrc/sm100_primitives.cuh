@@ -107,6 +107,25 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
 }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Zero token rows [first_row, end_row) of a K or V operand block in shared memory — two halves of 128-byte rows
+// (64 dims each), swizzled within the row, so a whole row can be cleared without knowing the swizzle.  Done by the
+// whole warp.  Cache slots behind a context's last token were never written: the caller's allocation may hold
+// anything there (NaN and Inf bit patterns included), the scores of such keys are masked by assignment, but in
+// P V a probability of zero times a NaN is a NaN, so those rows of V are cleared before they are multiplied.
+// Ends with the proxy fence the block's next asynchronous reader (an MMA) or writer (the next copy) needs.
+__device__ __forceinline__ void zero_rows_warp(unsigned char* half0, unsigned char* half1, int first_row, int end_row, int lane) {
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  const int pieces = (end_row - first_row) * 16;   // eight 16-byte pieces per row and half
+  for (int x = lane; x < pieces; x += 32) {
+    const int r = first_row + (x >> 4), piece = x & 15;
+    *reinterpret_cast<uint4*>(((piece & 8) ? half1 : half0) + r * 128 + ((piece & 7) << 4)) = zero;
+  }
+  fence_async_proxy();
+  __syncwarp();
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -474,7 +474,14 @@ class DecodeSession:
         if not self.pending:
             return False
         ticket = self.pending.popleft()
-        self.decoder._apply(ticket, ticket.collect(), self.pipeline, self.runner.config)
+        output = ticket.collect()
+        if self.runner.report_frontiers:          # the engine's share of the device-resident protocol
+            for state, round_id in zip(ticket.states, ticket.rounds):      # (engine/stage_engine.py:738-752)
+                if state.delivered != round_id:
+                    raise RuntimeError("out-of-order speculative round delivery")
+                state.delivered += 1
+        self.decoder._apply(ticket, output, self.pipeline, self.runner.config)
+        ticket.retire()
         self._sync_stats()
         return True
 

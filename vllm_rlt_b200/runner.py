@@ -160,6 +160,7 @@ class SpeculativeRequestState:
     slot: int
     submitted: int = 0
     delivered: int = 0
+    event: object = None       # completion of the last round submitted for the request
 
 
 class KVCacheManagerView:
@@ -250,8 +251,12 @@ class SpeculativeRoundTicket:
             frontiers = values[rows + nb: rows + nb + n]
             self.cached = ModelRunnerOutput(speculative=results,
                                             frontiers=frontiers if self.runner.report_frontiers else None)
-        for state in self.states:
-            state.delivered += 1
+        # Delivery is counted by whoever drives the runner in the device-resident protocol (the reference's
+        # engine checks `state.delivered == round` and increments it, engine/stage_engine.py:738-752); in the
+        # synchronous protocol nobody else would.  The staging buffer is free either way: its record is decoded.
+        if not self.runner.report_frontiers:
+            for state in self.states:
+                state.delivered += 1
         self.retire()
         return self.cached
 
@@ -312,12 +317,15 @@ class B200SpeculativeRunner:
         if self.cuda_graphs and not model.fused:
             raise ValueError("graph capture needs the fused layer path")
         self.compute_stream = compute_stream
-        # True: tickets carry the device's next positions (`ModelRunnerOutput.frontiers`), which is how the
-        # reference's scheduler recognises a round of its device-resident runner (it then releases the round's
-        # placeholders and does not truncate, core/scheduler.py:1362-1386).  False: `frontiers` is None, the
-        # form of its synchronous runner, after which the scheduler calls `truncate_suffix` itself (:1386-1394).
+        # True: the protocol of the reference's device-resident runner — tickets carry the device's next positions
+        # (`ModelRunnerOutput.frontiers`), from which its scheduler releases the round's placeholders without
+        # truncating (core/scheduler.py:1362-1386), and the engine counts deliveries and retires tickets.
+        # False: the protocol of its synchronous runner — `frontiers` is None, after which the scheduler calls
+        # `truncate_suffix` itself (:1386-1394), and a collected ticket has counted its own delivery.
         self.report_frontiers = report_frontiers
         self.stats = SpeculativeStats()
+        self.discarded_rounds = 0          # counters the reference's engine keeps on its runner
+        self.readback_waits = 0            # (engine/stage_engine.py:737,747)
         self.states: dict[str, SpeculativeRequestState] = {}
         slots = 2 * max_num_seqs + 1                       # the last slot is the padding rows' dummy
         self.dummy_slot = slots - 1
@@ -408,13 +416,34 @@ class B200SpeculativeRunner:
             tables = self.cache.device_tables(request.request_id)
             self.slot_tables[state.slot, :, : tables.shape[1]].copy_(tables)
 
-    def release(self, request) -> None:
-        """Discard this request generation's device state.  Work already queued for its slot runs
-        before anything a later owner of the slot queues (one compute stream), so no wait is needed."""
+    def request_ready(self, request) -> bool:
+        """Whether every round submitted for the request has run (async_speculative.py:663-665)."""
         state = self.states.get(request.request_id)
-        if state is not None and state.request is request:
-            del self.states[request.request_id]
-            self.free_slots.append(state.slot)
+        return state is None or state.event is None or state.event.query()
+
+    def release(self, request) -> None:
+        """Discard this request generation's device state, after its last submitted round has run: the
+        caller frees the request's pages next, and another stream may write them (async_speculative.py:667-676)."""
+        state = self.states.get(request.request_id)
+        if state is None:
+            return
+        if state.request is not request:
+            raise RuntimeError("releasing a different speculative request generation")
+        if state.event is not None:
+            state.event.synchronize()
+        del self.states[request.request_id]
+        self.free_slots.append(state.slot)
+
+    def synchronize(self) -> None:
+        """Drain the stream the rounds run on (async_speculative.py:689-691)."""
+        stream = self.compute_stream if self.compute_stream is not None else torch.cuda.current_stream(self.device)
+        stream.synchronize()
+
+    def discard_buffers(self) -> None:
+        """Take back every staging buffer after the streams have drained and all tickets are retired, a
+        failed submission's included (async_speculative.py:678-687)."""
+        for buffer in self.buffers:
+            buffer.leased = False
 
     def snapshot_pipeline(self, request, device):
         """The request's retained pipeline slots as tensors on `device` (speculative.py:280-287 of
@@ -577,6 +606,8 @@ class B200SpeculativeRunner:
                 ticket = self._submit_block(batch, buffer, states)
             buffer.done = torch.cuda.Event()
             buffer.done.record(torch.cuda.current_stream(self.device))
+        for state in states:
+            state.event = buffer.done
         buffer.leased = True
         ticket.keepalive, self._bootstrap_keepalive = self._bootstrap_keepalive, []
         self.stats.rounds += len(requests)
