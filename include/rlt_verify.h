@@ -128,6 +128,10 @@ RLT_API int rlt_kv_write(void* key_cache, void* value_cache, int64_t block_strid
  * rlt_verify_attention_status reports (bit 1).  The reference's Torch path raises
  * IndexError for such a row; here the run stays in bounds and the host learns of it
  * afterwards.
+ * Cache slots behind a context's last token (the rest of its last page, pages nobody owns)
+ * may hold anything, NaN and Inf bit patterns included — the reference allocates its pools
+ * uninitialised (vllm_rlt/core/kv_cache_manager.py:143-145): no result depends on them, here
+ * and in rlt_prefill_attention and rlt_windowed_attention.
  * Replaces: TritonPagedAttention.__call__ / paged_attention
  *   (vllm_rlt/kernels/paged_attention.py:119-120, vllm_rlt/kernels/triton_attention.py:150-202,
  *    kernels :20-147); oracle torch_paged_attention (vllm_rlt/kernels/paged_attention.py:12-36);
