@@ -28,6 +28,11 @@ Other entry points (each prints its own JSON line; none is the contract line abo
     --workload decode [--requests R --output-tokens T --temperature X --k K --eager --prompt-min A --prompt-max B
                        --shared-prefix P --prefix-caching --in-flight F]
                       one complete generation (prompt pass included in `total_seconds`)
+    --workload decode --engine reference [--sync]
+                      the same requests, weights and output budget through the UNMODIFIED reference engine on the
+                      GPU, when a copy of it is importable from baseline/_ref: its own scheduler, runner, Triton
+                      attention and CUDA graphs (`ExecutionConfig(async_scheduling=True, cuda_graphs=True)`; greedy
+                      only — `--sync` selects its synchronous runner, which also samples) — the same-box comparison
     --workload sharded [--total-requests R ...]
                       R requests in total (default 1024, prompts U[256, 2048], 512 output tokens, k = 6, T = 0.8),
                       length-balanced over the ranks and decoded to completion in waves that fit the KV
@@ -790,6 +795,74 @@ def run_decode_workload(args):
         "tokens_out": sum(len(t) for t in tokens), "attention_status": model.attention.last_status(device)}))
 
 
+def run_reference_engine_workload(args):
+    """`--workload decode --engine reference`: the decode workload's requests through the unmodified vllm-rlt
+    engine on the GPU (an installed copy under baseline/_ref; nothing of this library on the path): the model
+    class of the reference with the same seeded weights, its scheduler and speculative runner, its Triton paged
+    attention, its CUDA graphs.  Timing follows the reference's own benchmark: the decode clock starts when
+    every request has its first token and the device is idle, counts the tokens produced from then on and
+    stops after the device has finished."""
+    import vllm_rlt_b200 as rlt
+
+    reference_root = ROOT / "baseline" / "_ref"
+    if not (reference_root / "vllm_rlt").is_dir():
+        print(json.dumps({"engine": "reference", "unavailable": "no copy of the reference under baseline/_ref"}))
+        return
+    sys.path.insert(0, str(reference_root))
+    from vllm_rlt import CacheConfig, ExecutionConfig, SamplingParams, SpeculativeConfig
+    from vllm_rlt.config import SchedulerConfig
+    from vllm_rlt.engine.stage_engine import StageEngine
+    from vllm_rlt.models import OuroConfig, OuroForCausalLM
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    ours = rlt.LoopedLMConfig()
+    shape = {name: getattr(ours, name) for name in (
+        "vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
+        "num_key_value_heads", "head_dim", "rms_norm_eps", "rope_theta", "total_ut_steps")}
+    config = OuroConfig(**shape, max_position_embeddings=4096, bos_token_id=0, eos_token_id=0)
+    with torch.device(device):
+        model = OuroForCausalLM(config).to(torch.bfloat16)
+    state = rlt.seeded_state_dict(ours, 3, device=device)
+    model.load_state_dict({name: state[name] for name in model.state_dict()}, strict=True)
+    del state
+    prompts = decode_prompts(args.requests, (args.prompt_min, args.prompt_max), config.vocab_size)
+    pages = sum(-(-(len(p) + args.output_tokens + args.k + 2) // BLOCK) for p in prompts) * config.total_ut_steps + 64
+    engine = StageEngine(
+        model, cache_config=CacheConfig(pages, BLOCK), attention_backend="triton",
+        scheduler_config=SchedulerConfig(max_num_seqs=args.requests,
+                                         max_num_batched_tokens=max(2048, args.requests * (args.k + 1))),
+        execution_config=ExecutionConfig(async_scheduling=not args.sync, cuda_graphs=not args.eager),
+        speculative_config=SpeculativeConfig(args.k, draft_loops=DRAFT_LOOPS, target_loops=TARGET_LOOPS))
+    params = SamplingParams(max_tokens=args.output_tokens, ignore_eos=True, temperature=args.temperature, seed=1)
+    torch.cuda.synchronize()
+    begin = time.perf_counter()
+    for i, prompt in enumerate(prompts):
+        engine.add_request(str(i), prompt, params)
+    produced, finished, start, at_start = {}, 0, None, 0
+    while engine.has_unfinished_requests():
+        for output in engine.step():
+            produced[output.request_id] = len(output.token_ids)
+            finished += bool(output.finished)
+        if start is None and len(produced) == args.requests:
+            torch.cuda.synchronize()
+            start, at_start = time.perf_counter(), sum(produced.values())
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - start
+    stats = engine.speculative_runner.stats
+    print(json.dumps({
+        "engine": "vllm-rlt reference, unmodified, on the GPU", "attention_backend": "triton",
+        "async_scheduling": not args.sync, "cuda_graphs": not args.eager,
+        "workload": f"decode: Ouro-1.4B-shaped random-init bf16, self-spec k={args.k} from depth 2, {args.requests} requests, "
+                    f"prompts U[{args.prompt_min},{args.prompt_max}], {args.output_tokens} output tokens, T={args.temperature}",
+        "total_seconds": time.perf_counter() - begin, "prompt_pass_seconds": start - begin, "decode_seconds": seconds,
+        "decode_tokens": sum(produced.values()) - at_start,
+        "decode_tokens_per_s": (sum(produced.values()) - at_start) / seconds,
+        "accepted_tokens": stats.accepted_tokens, "drafted_tokens": stats.drafted_tokens, "request_rounds": stats.rounds,
+        "accepted_tokens_per_s_over_the_whole_run": stats.accepted_tokens / (time.perf_counter() - begin),
+        "finished_requests": finished}))
+
+
 def balanced_shards(lengths, world: int):
     """Longest-first greedy assignment of requests to ranks by prompt length: returns one list of request
     indices per rank whose total lengths differ by at most one request's length."""
@@ -1085,6 +1158,9 @@ def main():
     parser.add_argument("--workload", default="rounds", choices=["rounds", "decode", "sharded"],
                         help="rounds: timed speculative rounds (the bench line); decode: one complete generation; "
                              "sharded: a fixed request set shared out over the ranks, decoded to completion")
+    parser.add_argument("--engine", default="b200", choices=["b200", "reference"],
+                        help="decode workload: this library's decoder, or the unmodified reference engine on the GPU")
+    parser.add_argument("--sync", action="store_true", help="decode workload, reference engine: its synchronous runner")
     parser.add_argument("--k", type=int, default=None, help="decode / sharded workloads: drafts per round")
     parser.add_argument("--in-flight", type=int, default=2, help="decode / sharded workloads: rounds in flight (1 or 2)")
     parser.add_argument("--total-requests", type=int, default=1024, help="sharded workload: requests over all ranks")
@@ -1125,7 +1201,10 @@ def main():
         run_sharded_workload(args)
         return
     if args.workload == "decode":
-        run_decode_workload(args)
+        if args.engine == "reference":
+            run_reference_engine_workload(args)
+        else:
+            run_decode_workload(args)
         return
     if args.only == "attention":
         run_attention_only(args)
