@@ -32,7 +32,9 @@ Other entry points (each prints its own JSON line; none is the contract line abo
                       the same requests, weights and output budget through the UNMODIFIED reference engine on the
                       GPU, when a copy of it is importable from baseline/_ref: its own scheduler, runner, Triton
                       attention and CUDA graphs (`ExecutionConfig(async_scheduling=True, cuda_graphs=True)`; greedy
-                      only — `--sync` selects its synchronous runner, which also samples) — the same-box comparison
+                      only — `--sync` selects its synchronous runner, which also samples) — the same-box comparison;
+                      `--adopt attention|runner` plugs this library's attention backend (and speculative runner) into
+                      that engine (a backend name and a runner assignment on the reference's side)
     --workload sharded [--total-requests R ...]
                       R requests in total (default 1024, prompts U[256, 2048], 512 output tokens, k = 6, T = 0.8),
                       length-balanced over the ranks and decoded to completion in waves that fit the KV
@@ -828,12 +830,43 @@ def run_reference_engine_workload(args):
     del state
     prompts = decode_prompts(args.requests, (args.prompt_min, args.prompt_max), config.vocab_size)
     pages = sum(-(-(len(p) + args.output_tokens + args.k + 2) // BLOCK) for p in prompts) * config.total_ut_steps + 64
+    if args.adopt != "nothing":
+        # What a maintainer of the reference adds to adopt the kernels: one more backend name that wraps
+        # B200PagedAttention in the reference's own AttentionBackend / BackendCapabilities classes.
+        import dataclasses
+
+        from vllm_rlt.attention import backend as backend_module
+        from vllm_rlt.core import kv_cache_manager as cache_module
+
+        validate, create = backend_module.validate_backend_name, backend_module._create_explicit
+
+        def explicit(name, device_, dtype, head_dim, block_size):
+            if name != "b200":
+                return create(name, device_, dtype, head_dim, block_size)
+            native = rlt.create_backend(device_, dtype, head_dim, block_size)
+            capabilities = backend_module.BackendCapabilities(**dataclasses.asdict(native.capabilities))
+            return backend_module.AttentionBackend(native.kernel, capabilities, {"backend": "b200"})
+
+        backend_module.validate_backend_name = cache_module.validate_backend_name = \
+            lambda name: None if name == "b200" else validate(name)
+        backend_module._create_explicit = explicit
+        rlt.register_torch_op("vllm_rlt")
     engine = StageEngine(
-        model, cache_config=CacheConfig(pages, BLOCK), attention_backend="triton",
+        model, cache_config=CacheConfig(pages, BLOCK), attention_backend="triton" if args.adopt == "nothing" else "b200",
         scheduler_config=SchedulerConfig(max_num_seqs=args.requests,
                                          max_num_batched_tokens=max(2048, args.requests * (args.k + 1))),
         execution_config=ExecutionConfig(async_scheduling=not args.sync, cuda_graphs=not args.eager),
         speculative_config=SpeculativeConfig(args.k, draft_loops=DRAFT_LOOPS, target_loops=TARGET_LOOPS))
+    if args.adopt == "runner":
+        # ... and the runner: this library's looped LM over the reference's weights and KV-cache manager, in the place of
+        # the engine's own speculative runner (device-resident protocol under the async engine, synchronous otherwise).
+        native_model = rlt.LoopedLM(ours, model.state_dict(), device, torch.bfloat16)
+        view = rlt.KVCacheManagerView(engine.cache_manager, max_pages=-(-config.max_position_embeddings // BLOCK))
+        runner = rlt.B200SpeculativeRunner(
+            native_model, view, rlt.SpeculativeConfig(args.k, draft_loops=DRAFT_LOOPS, target_loops=TARGET_LOOPS),
+            max_num_seqs=args.requests, cuda_graphs=not args.eager, capture_sizes=[args.requests],
+            compute_stream=engine.model_runner.core_stream, report_frontiers=not args.sync)
+        engine.speculative_runner = engine.executor.speculation = runner
     params = SamplingParams(max_tokens=args.output_tokens, ignore_eos=True, temperature=args.temperature, seed=1)
     torch.cuda.synchronize()
     begin = time.perf_counter()
@@ -851,7 +884,9 @@ def run_reference_engine_workload(args):
     seconds = time.perf_counter() - start
     stats = engine.speculative_runner.stats
     print(json.dumps({
-        "engine": "vllm-rlt reference, unmodified, on the GPU", "attention_backend": "triton",
+        "engine": "vllm-rlt reference on the GPU, " + {"nothing": "unmodified", "attention": "with this library's attention "
+                  "backend and SiLU op", "runner": "with this library's attention backend and speculative runner"}[args.adopt],
+        "attention_backend": "triton" if args.adopt == "nothing" else "b200",
         "async_scheduling": not args.sync, "cuda_graphs": not args.eager,
         "workload": f"decode: Ouro-1.4B-shaped random-init bf16, self-spec k={args.k} from depth 2, {args.requests} requests, "
                     f"prompts U[{args.prompt_min},{args.prompt_max}], {args.output_tokens} output tokens, T={args.temperature}",
@@ -1161,6 +1196,10 @@ def main():
     parser.add_argument("--engine", default="b200", choices=["b200", "reference"],
                         help="decode workload: this library's decoder, or the unmodified reference engine on the GPU")
     parser.add_argument("--sync", action="store_true", help="decode workload, reference engine: its synchronous runner")
+    parser.add_argument("--adopt", default="nothing", choices=["nothing", "attention", "runner"],
+                        help="decode workload, reference engine: what of this library the engine adopts (nothing: the "
+                             "unmodified reference; attention: the b200 attention backend and SiLU op; runner: also the "
+                             "speculative runner)")
     parser.add_argument("--k", type=int, default=None, help="decode / sharded workloads: drafts per round")
     parser.add_argument("--in-flight", type=int, default=2, help="decode / sharded workloads: rounds in flight (1 or 2)")
     parser.add_argument("--total-requests", type=int, default=1024, help="sharded workload: requests over all ranks")

@@ -256,6 +256,11 @@ RLT_API int rlt_windowed_attention(const void* q, void* out, const void* key_cac
  * cache including the new tokens); cu_seqlens_q: int32 [sequences + 1].  workspace: device
  * scratch of rlt_prefill_attention_workspace_bytes(...) bytes, 256-byte aligned; its second
  * 32-bit word is nonzero after a run in which a bounded device-side wait gave up.
+ * For head_dim 128 with 16-token pages that is the prompt kernels' tile list (tens of bytes per
+ * 256 query tokens).  Where such a call has to fall back to the kernels behind rlt_verify_attention
+ * (a 32-bit dtype, or caches the tensor map cannot express) it needs their scratch instead, which
+ * grows with rows x heads x context chunks: the call then returns RLT_ERR_WORKSPACE if the workspace
+ * is smaller than rlt_verify_attention_workspace_bytes(rows, ...), and is to be repeated with that.
  * ---------------------------------------------------------------------- */
 RLT_API size_t rlt_prefill_attention_workspace_bytes(int rows, int sequences, int q_heads, int kv_heads,
                                              int head_dim, int block_size, int table_width);

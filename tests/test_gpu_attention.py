@@ -404,3 +404,32 @@ def test_full_size_microbench_shape_matches_the_oracle_over_a_layer_strided_pool
     assert parity["ok"] and parity["rows"] == 64, parity
     del key_pool, value_pool
     torch.cuda.empty_cache()
+
+
+def test_outgrown_scratch_stays_alive_for_graphs_that_captured_it(kernel):
+    # a caller's CUDA graph has the kernels baked in with the scratch buffer of its capture; when a later, larger call
+    # outgrows that buffer the old one must not go back to the allocator (someone else would get it while the graph
+    # goes on replaying over it): replay after growth + fresh allocations still gives the captured result
+    pool = make_pool([700, 300, 1200, 64], kv_heads=16, head_dim=128, block=16, dtype=torch.bfloat16, seed=41)
+    g = torch.Generator().manual_seed(42)
+    q = (torch.randn(4, 16, 128, generator=g) * 0.5).bfloat16().cuda()
+    key, value = pool["key_pool"].cuda()[:, 0], pool["value_pool"].cuda()[:, 0]
+    tables, lengths = pool["tables"].cuda(), pool["lengths"].cuda()
+    fresh = rlt.B200PagedAttention()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        want = fresh(q, key, value, tables, lengths).clone()          # eager warm-up on the capture stream: scratch allocated here
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            captured = fresh(q, key, value, tables, lengths)
+        before = fresh._workspaces[(torch.cuda.current_device(), stream.cuda_stream)]
+        many = (torch.randn(4096, 16, 128, generator=g) * 0.5).bfloat16().cuda()     # outgrows the scratch on the same stream
+        fresh(many, key, value, tables[:1].expand(4096, -1).contiguous(), lengths[:1].expand(4096).contiguous())
+        after = fresh._workspaces[(torch.cuda.current_device(), stream.cuda_stream)]
+        assert after.numel() > before.numel() and any(b is before for b in fresh._retired)
+        junk = [torch.full((before.numel() // 4,), float("nan"), device="cuda") for _ in range(8)]   # would land in freed scratch
+        captured.zero_()
+        graph.replay()
+    stream.synchronize()
+    assert torch.equal(captured, want) and len(junk) == 8

@@ -83,6 +83,7 @@ class B200PagedAttention:
     """Depth-aware paged-KV attention for verification and decode rows."""
 
     def __init__(self):
+        self._retired: list[torch.Tensor] = []      # outgrown scratch buffers (see _workspace)
         self._workspaces: dict[tuple[int, int], torch.Tensor] = {}
         self._planned: dict[tuple[int, int], tuple] = {}  # workspace key -> metadata the plan was built for
         self._sharing = 0
@@ -110,11 +111,16 @@ class B200PagedAttention:
 
     def _workspace(self, device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
         # One scratch buffer per (device, stream): calls on one stream are ordered, calls on
-        # different streams never share scratch.  Grown geometrically, never shrunk.
+        # different streams never share scratch.  Grown (doubling, by at most 256 MiB beyond the need),
+        # never shrunk — and an outgrown buffer is kept, not freed: a caller's captured CUDA graph may have
+        # this library's kernels baked in with that buffer as their scratch, and memory returned to the
+        # allocator would be handed to someone else while the graph goes on replaying over it.
         key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
         buffer = self._workspaces.get(key)
         if buffer is None or buffer.numel() < nbytes:
-            size = max(nbytes, 0 if buffer is None else 2 * buffer.numel())
+            if buffer is not None:
+                self._retired.append(buffer)
+            size = max(nbytes, 0 if buffer is None else min(2 * buffer.numel(), nbytes + (256 << 20)))
             buffer = torch.empty(size, dtype=torch.uint8, device=device)
             self._workspaces[key] = buffer
             self._planned.pop(key, None)
@@ -282,12 +288,18 @@ class B200PagedAttention:
             stream = _capi.stream_of(q)
             nbytes = lib.rlt_prefill_attention_workspace_bytes(rows, sequences, q.shape[1], kv_heads, head_dim,
                                                                block_size, max(width, 1))
-            workspace = self._workspace(device, stream.value or 0, nbytes)
-            status = lib.rlt_prefill_attention(
-                _capi.ptr(q), _capi.ptr(out), _capi.ptr(key_cache), _capi.ptr(value_cache), key_cache.stride(0),
-                key_cache.stride(1), blocks, block_size, q.shape[1], kv_heads, head_dim, _capi.DTYPE_CODES[q.dtype],
-                _capi.ptr(block_tables), sequences, width, _capi.ptr(context_lengths.contiguous()),
-                _capi.ptr(cu_seqlens_q.contiguous()), rows, _capi.ptr(workspace), workspace.numel(), stream)
+            lengths, cu = context_lengths.contiguous(), cu_seqlens_q.contiguous()
+            for attempt in range(2):
+                workspace = self._workspace(device, stream.value or 0, nbytes)
+                status = lib.rlt_prefill_attention(
+                    _capi.ptr(q), _capi.ptr(out), _capi.ptr(key_cache), _capi.ptr(value_cache), key_cache.stride(0),
+                    key_cache.stride(1), blocks, block_size, q.shape[1], kv_heads, head_dim, _capi.DTYPE_CODES[q.dtype],
+                    _capi.ptr(block_tables), sequences, width, _capi.ptr(lengths), _capi.ptr(cu), rows,
+                    _capi.ptr(workspace), workspace.numel(), stream)
+                if status != _capi.ERR_WORKSPACE or attempt == 1:
+                    break
+                # the rows fall back to the grouped kernel (32-bit dtype, or caches the tensor map cannot express)
+                nbytes = lib.rlt_verify_attention_workspace_bytes(rows, q.shape[1], kv_heads, head_dim, block_size, max(width, 1))
         _capi.check(status, "prefill_attention")
         return out
 

@@ -162,9 +162,10 @@ extern "C" RLT_API int rlt_verify_attention_noalloc(const void* q, void* out, co
 extern "C" RLT_API size_t rlt_prefill_attention_workspace_bytes(int rows, int sequences, int q_heads, int kv_heads,
                                                                 int head_dim, int block_size, int table_width) {
   if (rows <= 0 || sequences <= 0) return 256;
-  const size_t tiled = rlt::prefill_sm100_workspace_bytes(rows, sequences);
-  const size_t grouped = rlt_verify_attention_workspace_bytes(rows, q_heads, kv_heads, head_dim, block_size, table_width);
-  return tiled > grouped ? tiled : grouped;
+  // The prompt kernels' own scratch where they are the expected path; the grouped kernel's (which grows with
+  // rows x heads x context chunks: gigabytes for a batch of prompts) only for shapes they do not cover.
+  if (head_dim == 128 && block_size == 16) return rlt::prefill_sm100_workspace_bytes(rows, sequences);
+  return rlt_verify_attention_workspace_bytes(rows, q_heads, kv_heads, head_dim, block_size, table_width);
 }
 
 extern "C" RLT_API int rlt_prefill_attention(const void* q, void* out, const void* key_cache, const void* value_cache,
@@ -188,7 +189,8 @@ extern "C" RLT_API int rlt_prefill_attention(const void* q, void* out, const voi
     status = launch_prefill_sm100(a, workspace, workspace_bytes, s);
     if (status != RLT_ERR_UNSUPPORTED) return status;
   }
-  // shapes or cache placements outside the tiled prefill kernel: the grouped verify kernel, or the generic one
+  // shapes or cache placements outside the tiled prefill kernel: the grouped verify kernel (which reports
+  // RLT_ERR_WORKSPACE when the scratch was sized for the prompt kernels only), or the generic one
   if (attention_sm100_supported(a)) return launch_attention_sm100(a, workspace, workspace_bytes, s);
   return launch_attention_generic(a, s);
 }
