@@ -191,15 +191,22 @@ def test_graph_replay_equals_the_eager_loop_bit_for_bit():
     assert model.attention.last_status  # the wrapper stays usable after captures
 
 
+@pytest.mark.parametrize("graphs", [False, True])
 @pytest.mark.parametrize("name", ["tiny_k3", "config1"])
-def test_pipeline_mode_decoding_gives_the_reference_tokens(golden, name):
+def test_pipeline_mode_decoding_gives_the_reference_tokens(golden, name, graphs):
     # Pipeline self-speculation (every slot advances d loops per step at its own depth plane, the
-    # device state is updated by pipeline_shift) is lossless: the reference engine's greedy tokens.
+    # device state is updated by pipeline_shift) is lossless: the reference engine's greedy tokens —
+    # launched from the host, and with every step replayed from the CUDA graph of its batch-size bucket
+    # (requests that finish early leave padding rows behind: buckets of 4 and 3 cover 4, 3, 2 and 1 live requests).
     case = golden("decode.pt")[name]
-    decoder = rlt.SelfSpeculativeDecoder(build(case), block=case["block"])
+    decoder = rlt.SelfSpeculativeDecoder(build(case), block=case["block"], cuda_graphs=graphs,
+                                         capture_sizes=[3, 4] if graphs else None)
     tokens = decoder.generate_pipeline(case["prompts"], case["max_tokens"], num_speculative_tokens=case["k"],
                                        draft_loops=case["draft_loops"], target_loops=case["target_loops"])
     assert tokens == case["tokens"]
+    if graphs:
+        rounds = decoder.runner._rounds if getattr(decoder, "runner", None) is not None else {}
+        assert all(r.graph is not None for key, r in rounds.items() if key[0] == "pipeline")
     stats = decoder.stats
     assert stats.committed_tokens == sum(len(t) - 1 for t in tokens)
     assert 0 <= stats.accepted_tokens <= stats.committed_tokens and stats.drafted_tokens >= stats.accepted_tokens

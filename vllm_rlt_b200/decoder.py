@@ -377,7 +377,9 @@ class SelfSpeculativeDecoder:
         width = min(num_speculative_tokens + 1, target_loops // draft_loops)
         kv = self._allocate(prompts, [len(p) + max_tokens + width + 1 for p in prompts])
         requests = self._requests(prompts, self._prefill(kv, prompts), max_tokens, 0.0, -1, 1.0, 0)
-        runner = B200SpeculativeRunner(model, kv, config, max_num_seqs=len(prompts), cuda_graphs=False)
+        runner = B200SpeculativeRunner(model, kv, config, max_num_seqs=len(prompts), cuda_graphs=self.cuda_graphs,
+                                       capture_sizes=self.capture_sizes)
+        self.runner = runner
         self._drive(runner, requests, num_speculative_tokens, in_flight)
         return [r.generated_token_ids[:max_tokens] for r in requests]
 

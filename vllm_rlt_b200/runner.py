@@ -313,7 +313,7 @@ class B200SpeculativeRunner:
         self.width = config.num_speculative_tokens + 1 if config.mode == "block" else \
             min(config.num_speculative_tokens + 1, config.target_loops // config.draft_loops)
         self.max_num_seqs = max_num_seqs
-        self.cuda_graphs = bool(cuda_graphs) and config.mode == "block"
+        self.cuda_graphs = bool(cuda_graphs)
         if self.cuda_graphs and not model.fused:
             raise ValueError("graph capture needs the fused layer path")
         self.compute_stream = compute_stream
@@ -361,7 +361,7 @@ class B200SpeculativeRunner:
         largest = self.capture_sizes[-1] if self.bucketed else max_num_seqs
         self.buffers = [_HostBuffer(3 * largest, max(largest * self.width + 4 * largest, 6 * largest))
                         for _ in range(2)]
-        self._rounds: dict[tuple[int, bool], _Round] = {}
+        self._rounds: dict[tuple, object] = {}     # (bucket, sampled) -> _Round, ("pipeline", bucket) -> _PipelineRound
         self._pool = None
         self._bootstrap_keepalive: list = []
 
@@ -574,7 +574,10 @@ class B200SpeculativeRunner:
         if not self.cuda_graphs:
             return
         for nb in sorted(sizes or self.capture_sizes, reverse=True):    # largest first: scratch is sized once
-            self._prepare_round(self.bucket_of(nb), sampled)
+            if self.config.mode == "pipeline":
+                self._prepare_pipeline(self.bucket_of(nb))
+            else:
+                self._prepare_round(self.bucket_of(nb), sampled)
 
     def _lease(self) -> _HostBuffer:
         buffer = next((b for b in self.buffers if not b.leased), None)
@@ -641,19 +644,14 @@ class B200SpeculativeRunner:
         return SpeculativeRoundTicket(self, batch, buffer, states, nb, w, "block")
 
     # ---- pipeline mode ---------------------------------------------------------------------
-    def _submit_pipeline(self, batch, buffer, states):
-        """One pipeline step (async_speculative.py:502-584 of the reference): every active slot of
-        every request advances `draft_loops` loops at its own depth plane, the LM-head argmax of
-        every slot is taken, and `pipeline_shift` applies the outcome to the device state."""
-        model, cache, cfg, w = self.model, self.cache, self.config, self.width
-        device, n = self.device, len(batch.requests)
-        if any(span.request.sampling_params.temperature > 0 for span in batch.requests):
-            raise ValueError("pipeline speculation supports greedy requests only")
-        plan_host = torch.tensor([[s.slot for s in states],
-                                  [min(span.token_count, w) for span in batch.requests]]).pin_memory()
-        plan = plan_host.to(device, non_blocking=True)
-        self._bootstrap_keepalive.append((plan_host,))
-        slots, widths = plan[0], plan[1].int()
+    def _pipeline_body(self, r) -> None:
+        """The device part of one pipeline step on the static buffers of `r` (what a graph records): every active
+        slot of every request advances `draft_loops` loops at its own depth plane, the LM-head argmax of every slot
+        is taken, and `pipeline_shift` applies the outcome to the device state (async_speculative.py:502-584 of the
+        reference).  Padding requests carry the dummy slot and a width of 0: no active row, no write, no emission."""
+        model, cache, cfg, w, n = self.model, self.cache, self.config, self.width, r.nb
+        device = self.device
+        slots, widths = r.plan[0], r.plan[1].int()
         s = self.pipeline
         local = PipelineState(tokens=s.tokens[slots], depths=s.depths[slots], candidates=s.candidates[slots],
                               active=s.active[slots], hidden=s.hidden[slots], token=s.token[slots],
@@ -680,10 +678,61 @@ class B200SpeculativeRunner:
                               draft_loops=cfg.draft_loops, target_loops=cfg.target_loops)
         for name in ("tokens", "depths", "candidates", "active", "hidden", "token", "position"):
             getattr(s, name)[slots] = getattr(local, name)
-        buffer.wire[: 6 * n].copy_(wire.reshape(-1), non_blocking=True)
+        r.wire.copy_(wire.reshape(-1))
+
+    def _prepare_pipeline(self, nb: int):
+        r = self._rounds.get(("pipeline", nb))
+        if r is not None:
+            return r
+        r = _PipelineRound(self, nb)
+        r.plan[0].fill_(self.dummy_slot)                                # a step of padding only: changes nothing
+        if self.cuda_graphs:
+            stream = torch.cuda.current_stream(self.device)
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(stream)
+            with torch.cuda.stream(side):                               # library handles and workspaces exist before capture
+                self._pipeline_body(r)
+            stream.wait_stream(side)
+            if self._pool is None:
+                self._pool = torch.cuda.graph_pool_handle()
+            r.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(r.graph, pool=self._pool):
+                self._pipeline_body(r)
+        self._rounds[("pipeline", nb)] = r
+        return r
+
+    def _submit_pipeline(self, batch, buffer, states):
+        """One pipeline step: the plan (slots, widths) goes up, the step runs — replayed from the graph of its batch-size
+        bucket when graphs are on — and the six-word records come down."""
+        w, n = self.width, len(batch.requests)
+        if any(span.request.sampling_params.temperature > 0 for span in batch.requests):
+            raise ValueError("pipeline speculation supports greedy requests only")
+        nb = self.bucket_of(n)
+        plan = buffer.plan[: 2 * nb].view(2, nb)
+        plan[0, :n] = torch.tensor([s.slot for s in states])
+        plan[0, n:] = self.dummy_slot
+        plan[1, :n] = torch.tensor([min(span.token_count, w) for span in batch.requests])
+        plan[1, n:] = 0
+        r = self._prepare_pipeline(nb)
+        r.plan.copy_(plan, non_blocking=True)
+        if r.graph is not None:
+            r.graph.replay()
+        else:
+            self._pipeline_body(r)
+        buffer.wire[: 6 * nb].copy_(r.wire, non_blocking=True)
         for state in states:
             state.submitted += 1
         return SpeculativeRoundTicket(self, batch, buffer, states, n, w, "pipeline")
+
+
+class _PipelineRound:
+    """Static device buffers of one pipeline step shape, and its graph."""
+
+    def __init__(self, runner, nb: int):
+        self.nb = nb
+        self.plan = torch.zeros(2, nb, dtype=torch.int64, device=runner.device)
+        self.wire = torch.zeros(6 * nb, dtype=torch.int64, device=runner.device)
+        self.graph = None
 
 
 class _nullcontext:
