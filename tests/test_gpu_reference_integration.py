@@ -234,8 +234,9 @@ def test_reference_cache_manager_attends_through_the_b200_window_entry(reference
                               ours.attend(1, ["request"], [0], [11], query))
 
 
+@pytest.mark.parametrize("mode", ["block", "pipeline"])
 @pytest.mark.parametrize("graphs", [False, True])
-def test_reference_async_engine_drives_the_b200_runner_with_two_rounds_in_flight(reference, b200_backend, golden, graphs):
+def test_reference_async_engine_drives_the_b200_runner_with_two_rounds_in_flight(reference, b200_backend, golden, graphs, mode):
     # `ExecutionConfig(async_scheduling=True)`: the reference's engine submits a round ahead of the one it collects,
     # books placeholders at submission, checks every collected round against the device's frontier and counts
     # deliveries itself (engine/stage_engine.py:732-793, core/scheduler.py:1362-1375).  Its AsyncSpeculativeRunner is
@@ -245,11 +246,11 @@ def test_reference_async_engine_drives_the_b200_runner_with_two_rounds_in_flight
 
     case = golden("decode.pt")["config1"]
     model = reference_model(case)
-    loops = dict(draft_loops=case["draft_loops"], target_loops=case["target_loops"])
+    loops = dict(draft_loops=case["draft_loops"], target_loops=case["target_loops"], mode=mode)
     engine = StageEngine(model, cache_config=CacheConfig(256, case["block"]), attention_backend="b200",
                          execution_config=ExecutionConfig(async_scheduling=True),
                          speculative_config=SpeculativeConfig(case["k"], **loops))
-    assert engine.async_speculative
+    assert engine.async_speculative and engine.pipeline_speculative == (mode == "pipeline")
     ours = rlt.LoopedLM(rlt.LoopedLMConfig(**case["config"]), model.state_dict(), "cuda", torch.float32)
     view = rlt.KVCacheManagerView(engine.cache_manager, max_pages=-(-256 // case["block"]))
     runner = rlt.B200SpeculativeRunner(ours, view, rlt.SpeculativeConfig(case["k"], **loops),
@@ -268,6 +269,6 @@ def test_reference_async_engine_drives_the_b200_runner_with_two_rounds_in_flight
     params = SamplingParams(max_tokens=case["max_tokens"], ignore_eos=True)
     assert run_engine(engine, case["prompts"], params) == case["tokens"]
     assert max(in_flight) == 2 and not runner.states and not engine._pending_speculative
-    assert runner.stats.committed_tokens == case["stats"]["committed"]
+    assert runner.stats.committed_tokens == sum(len(t) - 1 for t in case["tokens"])
     assert all(not buffer.leased for buffer in runner.buffers)
     torch.cuda.synchronize()
