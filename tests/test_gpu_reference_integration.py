@@ -156,8 +156,9 @@ def test_reference_engine_decodes_the_golden_tokens_on_the_b200_backend(referenc
     torch.cuda.synchronize()
 
 
+@pytest.mark.parametrize("incremental", [False, True])
 @pytest.mark.parametrize("name", ["config1", "tiny_k3"])
-def test_reference_engine_drives_the_b200_round_controller_to_the_golden_tokens(reference, b200_backend, golden, name):
+def test_reference_engine_drives_the_b200_round_controller_to_the_golden_tokens(reference, b200_backend, golden, name, incremental):
     # the reference's scheduler, KV-cache manager, prompt path and token bookkeeping, unmodified, with the
     # B200 runner in the place of its SpeculativeRunner: same tokens, same round statistics
     from vllm_rlt import CacheConfig, SamplingParams, SpeculativeConfig
@@ -167,8 +168,10 @@ def test_reference_engine_drives_the_b200_round_controller_to_the_golden_tokens(
     model = reference_model(case)
     params = SamplingParams(max_tokens=case["max_tokens"], ignore_eos=True)
     loops = dict(draft_loops=case["draft_loops"], target_loops=case["target_loops"])
-    engine = StageEngine(model, cache_config=CacheConfig(256, case["block"]), attention_backend="b200",
-                         speculative_config=SpeculativeConfig(case["k"], **loops))
+    # incremental: the manager grows a request's block tables as it decodes (CacheConfig.incremental_allocation), so the
+    # runner's copy of them has to follow (`refresh_tables` before every round)
+    engine = StageEngine(model, cache_config=CacheConfig(256, case["block"], incremental_allocation=incremental),
+                         attention_backend="b200", speculative_config=SpeculativeConfig(case["k"], **loops))
     controller = RoundControllerOnTheReferenceCache(engine, case, torch.float32, case["k"], **loops)
     controller.install(engine)
     assert run_engine(engine, case["prompts"], params) == case["tokens"]
