@@ -10,7 +10,7 @@
 //                   Q and P are TMEM operands of the MMAs, separate warps copy, issue and do the
 //                   softmax (see the comment above prefill_pair_kernel).  Default for prompts.
 //   one-tile kernel tcgen05 / TMEM, one 128-row tile per CTA and two CTAs per SM (above
-//                   prefill_umma_kernel).  Default when the sequences average at most 128 new tokens.
+//                   prefill_umma_kernel).  The pair kernel's predecessor; selectable, no longer a default.
 //   mma.sync kernel 64-row tiles, four warps of 16 query rows each.  Thread 0 copies the next four
 //                   pages with TMA (one copy per page through the 5-D map over both caches, 128-byte
 //                   swizzle) into a two-stage ring guarded by full / empty mbarriers; every warp
@@ -1060,12 +1060,11 @@ int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspa
     set_last_error_text("prefill_attention: workspace missing, misaligned or too small");
     return RLT_ERR_WORKSPACE;
   }
-  // 'p'air, 'u'mma (one tile per CTA) or 'm'ma.sync; unset: the pair kernel when the sequences average
-  // more than one 128-row tile of new tokens (its second tile would idle otherwise), else one tile per CTA.
+  // 'p'air, 'u'mma (one tile per CTA) or 'm'ma.sync; unset: the pair kernel.  It is the fastest of the three also
+  // where its second tile stays empty (chunks of 128 new tokens per sequence: 48 against 66 and 80 us at 16 sequences
+  // on 1024-token contexts, 70 against 138 and 147 us at 4 sequences on 4096-token ones).
   const char* forced = getenv("RLT_PREFILL_KERNEL");
-  const char kernel_choice = forced != nullptr && forced[0] != 0
-                                 ? forced[0]
-                                 : (static_cast<int64_t>(a.rows) > static_cast<int64_t>(kUmmaRows) * a.table_rows ? 'p' : 'u');
+  const char kernel_choice = forced != nullptr && forced[0] != 0 ? forced[0] : 'p';
   const bool use_mma_sync = kernel_choice == 'm';
   PrefillHeader* header = static_cast<PrefillHeader*>(workspace);
   PrefillTile* tiles = reinterpret_cast<PrefillTile*>(static_cast<unsigned char*>(workspace) + 256);
