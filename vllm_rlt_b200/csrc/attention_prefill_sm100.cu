@@ -47,9 +47,11 @@ struct PrefillHeader {
 };
 struct PrefillTile {
   int seq;
-  int first;   // first query of the tile, counted from the sequence's first new token
-  int count;   // 1 .. 64
-  int pad;
+  int first;     // first query of the tile, counted from the sequence's first new token
+  int count;     // rows of the tile
+  int visible;   // keys the tile's first row sees: min(context, table capacity) - new tokens + 1 + first (may be <= 0)
+  int q_row;     // the first row's index in the packed query tensor
+  int pad[3];
 };
 
 struct __align__(1024) PrefillShared {
@@ -64,8 +66,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 
 // Tile list: sequence s contributes ceil(n_s / tile_rows) tiles, written last tile first.
 __global__ void __launch_bounds__(kPrefillPlanThreads)
-prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens_q, int seqs, int tile_rows, PrefillHeader* header,
-                    PrefillTile* tiles) {
+prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens_q, const int32_t* __restrict__ context_lengths, int table_width,
+                    int seqs, int tile_rows, PrefillHeader* header, PrefillTile* tiles) {
   __shared__ int warp_totals[32];
   __shared__ int carry;
   if (threadIdx.x == 0) carry = 0;
@@ -73,7 +75,9 @@ prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens_q, int seqs, int tile
   for (int base = 0; base < seqs; base += kPrefillPlanThreads) {
     __syncthreads();
     const int s = base + threadIdx.x;
-    const int n = s < seqs ? max(cu_seqlens_q[s + 1] - cu_seqlens_q[s], 0) : 0;
+    const int seq_first = s < seqs ? cu_seqlens_q[s] : 0;
+    const int n = s < seqs ? max(cu_seqlens_q[s + 1] - seq_first, 0) : 0;
+    const int base_len = s < seqs ? min(context_lengths[s], table_width * kPage) - n + 1 : 0;   // keys the first new token sees
     const int mine = (n + tile_rows - 1) / tile_rows;
     int inc = mine;
 #pragma unroll
@@ -88,7 +92,7 @@ prefill_plan_kernel(const int32_t* __restrict__ cu_seqlens_q, int seqs, int tile
     const int start = before + inc - mine;
     for (int t = 0; t < mine; ++t) {
       const int first = (mine - 1 - t) * tile_rows;
-      tiles[start + t] = PrefillTile{s, first, min(tile_rows, n - first), 0};
+      tiles[start + t] = PrefillTile{s, first, min(tile_rows, n - first), base_len + first, seq_first + first, {0, 0, 0}};
     }
     __syncthreads();
     if (threadIdx.x == kPrefillPlanThreads - 1) carry = before + inc;
@@ -773,11 +777,10 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   extern __shared__ unsigned char smem_raw[];
   PairShared& sm = *reinterpret_cast<PairShared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int lane = threadIdx.x & 31, warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);   // warp-uniform for the compiler too
-  const PrefillTile tile = tiles[blockIdx.x];
+  const PrefillTile tile = tiles[blockIdx.x];   // everything the CTA needs to know about its rows: one load
   const int q_head = blockIdx.y, kv_head = q_head / (a.q_heads / a.kv_heads);
-  const int seq_first = a.cu_seqlens_q[tile.seq];
-  const int n_new = a.cu_seqlens_q[tile.seq + 1] - seq_first;
-  const int base_len = min(a.context_lengths[tile.seq], a.table_width * kPage) - n_new + 1;
+  const int seq_first = tile.q_row - tile.first;
+  const int base_len = tile.visible - tile.first;
   // key stages of the two query tiles: tile 1 (the later rows) sees every stage tile 0 does
   const int count0 = min(tile.count, kUmmaRows), count1 = max(tile.count - kUmmaRows, 0);
   const int stages0 = (max(base_len + tile.first + count0 - 1, 0) + kUmmaKeys - 1) / kUmmaKeys;
@@ -1071,7 +1074,7 @@ int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspa
   const float scale_log2 = static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(kHeadDim)));
   CUtensorMap k_map, v_map;
   if (kernel_choice == 'p' && make_page_map(&k_map, a.key_cache, a) == RLT_OK && make_page_map(&v_map, a.value_cache, a) == RLT_OK) {
-    prefill_plan_kernel<<<1, kPrefillPlanThreads, 0, stream>>>(a.cu_seqlens_q, a.table_rows, kPairRows, header, tiles);
+    prefill_plan_kernel<<<1, kPrefillPlanThreads, 0, stream>>>(a.cu_seqlens_q, a.context_lengths, a.table_width, a.table_rows, kPairRows, header, tiles);
     int status = launch_status("prefill_plan_kernel");
     if (status != RLT_OK) return status;
     const size_t smem = sizeof(PairShared) + 1024;
@@ -1090,7 +1093,7 @@ int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspa
     return launch_status("prefill_pair_kernel");
   }
   if (!use_mma_sync && make_page_map(&k_map, a.key_cache, a) == RLT_OK && make_page_map(&v_map, a.value_cache, a) == RLT_OK) {
-    prefill_plan_kernel<<<1, kPrefillPlanThreads, 0, stream>>>(a.cu_seqlens_q, a.table_rows, kUmmaRows, header, tiles);
+    prefill_plan_kernel<<<1, kPrefillPlanThreads, 0, stream>>>(a.cu_seqlens_q, a.context_lengths, a.table_width, a.table_rows, kUmmaRows, header, tiles);
     int status = launch_status("prefill_plan_kernel");
     if (status != RLT_OK) return status;
     const size_t smem = sizeof(UmmaShared) + 1024;
@@ -1109,7 +1112,7 @@ int launch_prefill_sm100(const AttentionArgs& a, void* workspace, size_t workspa
   CUtensorMap kv_map;
   bool k_first = true;
   if (make_joint_map(&kv_map, a, &k_first) != RLT_OK) return RLT_ERR_UNSUPPORTED;
-  prefill_plan_kernel<<<1, kPrefillPlanThreads, 0, stream>>>(a.cu_seqlens_q, a.table_rows, kTileRows, header, tiles);
+  prefill_plan_kernel<<<1, kPrefillPlanThreads, 0, stream>>>(a.cu_seqlens_q, a.context_lengths, a.table_width, a.table_rows, kTileRows, header, tiles);
   int status = launch_status("prefill_plan_kernel");
   if (status != RLT_OK) return status;
   const size_t smem = sizeof(PrefillShared) + 1024;
