@@ -1203,7 +1203,7 @@ def main():
     parser.add_argument("--k", type=int, default=None, help="decode / sharded workloads: drafts per round")
     parser.add_argument("--in-flight", type=int, default=2, help="decode / sharded workloads: rounds in flight (1 or 2)")
     parser.add_argument("--total-requests", type=int, default=1024, help="sharded workload: requests over all ranks")
-    parser.add_argument("--kv-budget-gb", type=float, default=110.0, help="sharded workload: KV bytes a wave may reserve")
+    parser.add_argument("--kv-budget-gb", type=float, default=140.0, help="sharded workload: KV bytes a wave may reserve")
     parser.add_argument("--max-wave", type=int, default=128, help="sharded workload: most requests decoded together")
     parser.add_argument("--model-layers", type=int, default=LAYERS, help="sharded workload: decoder layers of the model (24; 48 for the 2.6B shape)")
     parser.add_argument("--output-tokens", type=int, default=None,
