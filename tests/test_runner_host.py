@@ -227,3 +227,38 @@ def test_the_reference_engine_can_drive_the_runner_in_place_of_its_own(golden, o
     assert (stats.rounds, stats.drafted_tokens, stats.accepted_tokens, stats.committed_tokens, stats.verified_rows) == \
         (want["rounds"], want["drafted"], want["accepted"], want["committed"], want["verified_rows"])
     assert not runner.states
+
+
+def test_manager_view_and_delivery_protocols(golden, on_cpu):
+    # KVCacheManagerView: pools as they are, a request's tables from its allocation, refusal of tables wider than the
+    # runner was sized for.  Delivery counting: a collected ticket counts its own delivery only in the synchronous
+    # protocol (report_frontiers=False); in the device-resident one the engine does, and the ticket leaves it alone.
+    from types import SimpleNamespace
+
+    allocation = SimpleNamespace(block_tables=[[3, 1], [0, 2, 5]])
+    manager = SimpleNamespace(key_cache=torch.zeros(8, 1, 4, 1, 8), value_cache=torch.zeros(8, 1, 4, 1, 8), block_size=4,
+                              _get_allocation=lambda rid: allocation)
+    view = rlt.KVCacheManagerView(manager, max_pages=3)
+    assert view.key is manager.key_cache and view.block == 4 and view.refcounts is None
+    assert view.device_tables("r").tolist() == [[3, 1, 0], [0, 2, 5]]
+    with pytest.raises(ValueError, match="wider than max_pages"):
+        rlt.KVCacheManagerView(manager, max_pages=2).device_tables("r")
+
+    case = golden("decode.pt")["tiny_k3"]
+    for frontiers in (True, False):
+        decoder = rlt.SelfSpeculativeDecoder(build(case), block=case["block"])
+        kv = decoder._allocate(case["prompts"], [len(p) + case["max_tokens"] + 8 for p in case["prompts"]])
+        requests = decoder._requests(case["prompts"], decoder._prefill(kv, case["prompts"]), case["max_tokens"], 0.0, -1, 1.0, 0)
+        runner = rlt.B200SpeculativeRunner(build(case), kv, rlt.SpeculativeConfig(case["k"], case["draft_loops"], case["target_loops"]),
+                                           max_num_seqs=4, cuda_graphs=False, report_frontiers=frontiers)
+        batch = decoder._schedule(requests, case["k"], False)
+        ticket = runner.submit(batch)
+        output = ticket.collect()
+        assert (output.frontiers is not None) == frontiers and ticket.retired
+        assert [s.delivered for s in ticket.states] == [0 if frontiers else 1] * len(ticket.states)
+        assert all(runner.request_ready(r) for r in requests)
+        with pytest.raises(RuntimeError, match="different speculative request generation"):
+            runner.release(SimpleNamespace(request_id=requests[0].request_id))
+        for request in requests:
+            runner.release(request)
+        assert not runner.states
